@@ -1,0 +1,413 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 decode hot path: the 497-GEMV per-step mix of the 27B hybrid decoder.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass over every linear layer of one decode step at batch 1: 497 NVFP4 GEMVs
+over 9 layer shapes (reference: experiments/_bench_gemv_real_shapes.py:28-38), 14.4 GB of packed
+weights and scales, each matrix with its own fp16 activation.  The metric is HBM GB/s computed from
+ALGORITHMIC bytes (per GEMV: M*K/2 + M*K/16 + 2K + 2M, the reference's own formula,
+experiments/_bench_gemv_real_shapes.py:67) divided by device time.
+
+  value    steps are replayed from a CUDA graph with all inputs resident in HBM.
+  e2e      the same step through the C ABI with HOST activations and HOST results: every step
+           copies the 497 activation vectors from pinned host memory to the device, launches the
+           GEMVs and copies the 497 result vectors back; copies are inside the timed region.
+  roofline the GEMV kernel against the measured HBM copy bandwidth (MEASURED_PEAKS.json).
+  cpu_baseline  the CPU oracle (vectorised codec decode + fp32 torch matvec) timed on this host.
+
+Every step streams 14.4 GB, far more than the 126 MB L2, so each weight byte is a cold HBM read.
+Synthetic data: random E2M1 bytes, scale bytes uniform in [118, 122] (the range N(0, 0.02^2)
+weights produce), activations ~N(0, 1) fp16.
+
+With --gpus N > 1 (launched by torchrun, one process per GPU) the step is tensor-parallel: q/k/v,
+gate/up, in_proj and lm_head are split by output rows, o_proj/out_proj/down_proj by K, and every
+K-split layer is followed by an NCCL all-reduce of its 5120-element fp16 output (128 per step).
+Total work is fixed, so scaling is "strong".
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, VOCAB = 5120, 17408, 248320
+N_LAYERS, FULL_ATTN_EVERY = 64, 4
+
+# (name, M, K, split) — split "col": output rows are sharded; "row": K is sharded + all-reduce;
+# "kv": 4 KV heads of 256 rows, replicated when there are more ranks than heads.
+ATTN_LAYER = [("q_proj", 12288, HIDDEN, "col"), ("k_proj", 1024, HIDDEN, "kv"),
+              ("v_proj", 1024, HIDDEN, "kv"), ("o_proj", HIDDEN, 6144, "row")]
+LINEAR_LAYER = [("in_proj_qkv", 10240, HIDDEN, "col"), ("in_proj_z", 6144, HIDDEN, "col"),
+                ("in_proj_b", 48, HIDDEN, "col"), ("in_proj_a", 48, HIDDEN, "col"),
+                ("out_proj", HIDDEN, 6144, "row")]
+MLP = [("gate_proj", INTER, HIDDEN, "col"), ("up_proj", INTER, HIDDEN, "col"),
+       ("down_proj", HIDDEN, INTER, "row")]
+
+
+def step_gemvs():
+    """The 497 GEMVs of one decode step, in execution order."""
+    out = []
+    for i in range(N_LAYERS):
+        mixer = ATTN_LAYER if (i + 1) % FULL_ATTN_EVERY == 0 else LINEAR_LAYER
+        out += [(f"L{i}.{n}", M, K, sp) for n, M, K, sp in mixer]
+        out += [(f"L{i}.{n}", M, K, sp) for n, M, K, sp in MLP]
+    out.append(("lm_head", VOCAB, HIDDEN, "col"))
+    return out
+
+
+def gemv_bytes(M, K):
+    return M * K // 2 + M * K // 16 + 2 * K + 2 * M
+
+
+def shard(M, K, split, world, rank):
+    """Shape of this rank's shard of an [M, K] layer."""
+    if world == 1:
+        return M, K
+    if split == "col":
+        per = -(-M // world)
+        return max(0, min(M, (rank + 1) * per) - rank * per), K
+    if split == "kv":
+        heads = M // 256
+        return (M // world, K) if world <= heads else (256, K)
+    if split == "row":
+        assert K % (world * 128) == 0
+        return M, K // world
+    raise ValueError(split)
+
+
+# ------------------------------------------------------------------------------------------------
+def sample_clocks(stop, out):
+    """nvidia-smi clock/throttle samples while the timed region runs."""
+    q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    idx = os.environ.get("LOCAL_RANK", "0")
+    try:
+        p = subprocess.Popen(["nvidia-smi", f"--query-gpu={q}", "--format=csv,noheader,nounits",
+                              "-i", idx, "-lms", "100"], stdout=subprocess.PIPE,
+                             stderr=subprocess.DEVNULL, text=True)
+    except OSError:
+        return
+    lines = []
+
+    def reader():
+        for line in p.stdout:
+            lines.append(line)
+
+    th = threading.Thread(target=reader, daemon=True)
+    th.start()
+    stop.wait()
+    p.terminate()
+    try:
+        p.wait(timeout=2)
+    except Exception:
+        p.kill()
+    th.join(timeout=2)
+    out.extend(lines)
+
+
+def summarise_clocks(lines):
+    sm, smax, reasons = [], [], set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    for ln in lines:
+        f = [x.strip() for x in ln.split(",")]
+        if len(f) < 9:
+            continue
+        try:
+            sm.append(float(f[1]))
+            smax.append(float(f[2]))
+        except ValueError:
+            continue
+        for name, val in zip(names, f[5:9]):
+            if val.lower().startswith("active"):
+                reasons.add(name)
+    if not sm:
+        return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+    return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+            "samples": len(sm)}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+def cpu_gemv_gbps(shapes, threads, repeats=1):
+    """The CPU oracle (vectorised codec decode + fp32 torch matvec) on a list of shapes.
+    Returns (GB/s of algorithmic bytes, seconds spent, description)."""
+    import torch
+
+    from oracle import nvfp4_codec_oracle as oc
+
+    torch.set_num_threads(threads)
+    rng = np.random.default_rng(0)
+    total_bytes, total_t = 0, 0.0
+    for M, K in shapes:
+        packed = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
+        scales = rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8)
+        act = rng.standard_normal(K).astype(np.float16)
+        for _ in range(repeats):
+            t0 = time.perf_counter()
+            w = oc.decode(packed, scales)                      # codec dequant -> fp16
+            y = torch.from_numpy(w.astype(np.float32)) @ torch.from_numpy(act.astype(np.float32))
+            _ = y.to(torch.float16)
+            total_t += time.perf_counter() - t0
+            total_bytes += gemv_bytes(M, K)
+    return total_bytes / total_t / 1e9, total_t
+
+
+CPU_SAMPLE = [(5120, 5120), (1024, 5120), (5120, 6144), (6144, 5120), (17408, 5120), (5120, 17408)]
+CPU_SAMPLE_DESC = ("one GEMV each of 5120x5120, 1024x5120, 5120x6144, 6144x5120, 17408x5120, "
+                   "5120x17408 (codec decode to fp16 + fp32 torch matvec)")
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU path for this metric (codec dequant + torch CPU
+    matmul), restated by the oracle, on all host threads.  Rank 0 only."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+
+    cores = os.cpu_count() or 1
+    for _ in range(args.warmup):
+        cpu_gemv_gbps(CPU_SAMPLE[:2], cores)
+    t0 = time.perf_counter()
+    vals = []
+    for _ in range(args.steps):
+        g, _t = cpu_gemv_gbps(CPU_SAMPLE, cores)
+        vals.append(g)
+    dt = time.perf_counter() - t0
+    v = sum(vals) / len(vals)
+    line = {
+        "impl": "reference", "metric": "nvfp4_gemv_hbm_gbps", "value": v, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "gemv_497_mix_27b", "sample": CPU_SAMPLE_DESC},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": CPU_SAMPLE_DESC},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from nvfp4_v100_b200 import _lib
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run "
+                             "(one process per GPU)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib = _lib.load()
+    vp = ctypes.c_void_p
+
+    gemvs = step_gemvs()
+    g = torch.Generator(device="cuda")
+    g.manual_seed(1234 + rank)
+    layers = []
+    total_alg = 0
+    for name, M, K, split in gemvs:
+        m, k = shard(M, K, split, world, rank)
+        if m == 0:
+            continue
+        packed = torch.randint(0, 256, (m * k // 2,), dtype=torch.uint8, device="cuda", generator=g)
+        scales = torch.randint(118, 123, (m * k // 16,), dtype=torch.uint8, device="cuda",
+                               generator=g)
+        act = torch.randn(k, dtype=torch.float32, device="cuda", generator=g).to(torch.float16)
+        out = torch.zeros(m, dtype=torch.float16, device="cuda")
+        layers.append((name, m, k, split, packed, scales, act, out))
+        total_alg += gemv_bytes(m, k)
+    n_launch = len(layers)
+    n_allreduce = sum(1 for l in layers if l[3] == "row") if world > 1 else 0
+
+    def enqueue_step():
+        st = vp(torch.cuda.current_stream().cuda_stream)
+        for name, m, k, split, packed, scales, act, out in layers:
+            rc = lib.launch_nvfp4_gemv_v8(vp(packed.data_ptr()), vp(scales.data_ptr()),
+                                          vp(act.data_ptr()), vp(out.data_ptr()), m, k, st)
+            if rc != 0:
+                raise RuntimeError(f"{name}: launch_nvfp4_gemv_v8 rc={rc}")
+            if world > 1 and split == "row":
+                dist.all_reduce(out)
+
+    # warm-up outside the graph (module load, NCCL channels), then capture one step
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        enqueue_step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        enqueue_step()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        graph.replay()
+    barrier()
+
+    stop = threading.Event()
+    clock_lines: list[str] = []
+    sampler = threading.Thread(target=sample_clocks, args=(stop, clock_lines), daemon=True)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        graph.replay()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+
+    # ---- end to end: host activations in, host results out, every step ----
+    h_act = [torch.empty(l[2], dtype=torch.float16).pin_memory() for l in layers]
+    h_out = [torch.empty(l[1], dtype=torch.float16).pin_memory() for l in layers]
+    for h, l in zip(h_act, layers):
+        h.copy_(l[6])
+    h2d = sum(h.numel() * 2 for h in h_act)
+    d2h = sum(h.numel() * 2 for h in h_out)
+
+    def e2e_step():
+        st = vp(torch.cuda.current_stream().cuda_stream)
+        for (name, m, k, split, packed, scales, act, out), ha, ho in zip(layers, h_act, h_out):
+            act.copy_(ha, non_blocking=True)
+            rc = lib.launch_nvfp4_gemv_v8(vp(packed.data_ptr()), vp(scales.data_ptr()),
+                                          vp(act.data_ptr()), vp(out.data_ptr()), m, k, st)
+            if rc != 0:
+                raise RuntimeError(f"{name}: rc={rc}")
+            if world > 1 and split == "row":
+                dist.all_reduce(out)
+            ho.copy_(out, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    if rank == 0:
+        time.sleep(0.2)
+        stop.set()
+        sampler.join(timeout=5)
+
+    # max over ranks
+    t = torch.tensor([ms, e2e_ms, float(total_alg)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = t.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        ms, e2e_ms, job_bytes = float(tmax[0]), float(tmax[1]), float(tsum[2])
+    else:
+        job_bytes = float(total_alg)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    value = job_bytes * args.steps / (ms * 1e-3) / 1e9
+    e2e_value = job_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
+    peak, peak_kind = measured_peak()
+    per_gpu = (float(total_alg) * args.steps / (ms * 1e-3) / 1e9)
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        threads = min(os.cpu_count() or 1, torch.get_num_threads())
+        v, secs = cpu_gemv_gbps(CPU_SAMPLE, threads)
+        cpu = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": CPU_SAMPLE_DESC, "seconds": round(secs, 2)}
+
+    line = {
+        "metric": "nvfp4_gemv_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "gemv_497_mix_27b", "gemvs_per_step": n_launch,
+                   "algorithmic_bytes_per_step": int(job_bytes),
+                   "l2": "each step streams 14.4 GB of weights (>> 126 MB L2): reads are cold",
+                   "parallelism": f"tp{world}", "allreduce_per_step": n_allreduce,
+                   "launch": "cuda_graph"},
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "ms_per_step": e2e_ms / e2e_steps},
+        "gpu_launches": n_launch * args.steps,
+        "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
+                     "frac": per_gpu / peak, "traffic": TRAFFIC_PER_LAUNCH, "peak_kind": peak_kind,
+                     "kernel": "gemv_mma_kernel",
+                     "frac_of_nominal_8000": per_gpu / 8000.0},
+        "cpu_baseline": cpu,
+        "clocks": summarise_clocks(clock_lines),
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) per average GEMV launch of the mix, from the ncu capture summarised
+# under profiles/; None until a capture exists.
+TRAFFIC_PER_LAUNCH = None
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,110 @@
+/* C ABI of libnvfp4_b200.so — the sm_100a replacement for the reference's six ctypes DLLs.
+ *
+ * Every function is `extern "C"`, takes plain pointers and sizes, and (unless stated otherwise)
+ * only enqueues work on the stream it is given: no allocation, no synchronisation, safe to call
+ * while that stream is being captured into a CUDA graph.  Device pointers are raw addresses
+ * (ctypes c_void_p built from tensor.data_ptr()); `stream` is a cudaStream_t passed as void*.
+ *
+ * Citations give the reference interface each entry point replaces (path within the reference
+ * project : line).
+ */
+#ifndef NVFP4_B200_H
+#define NVFP4_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------------------------------------
+ * Device memory helpers.  kernels/nvfp4_gemv.cu:820-835, kernels/nvfp4_cuda_v5.cu:424-457.
+ * gpu_malloc returns NULL on failure.  The copies are synchronous and return the cudaError_t as
+ * an int (0 = success).  The caller owns the memory and may do byte arithmetic on the address.
+ * ------------------------------------------------------------------------------------------- */
+void* gpu_malloc(size_t bytes);
+void gpu_free(void* p);
+int gpu_memcpy_h2d(void* dst, const void* src, size_t bytes);
+int gpu_memcpy_d2h(void* dst, const void* src, size_t bytes);
+int gpu_sync(void);                                              /* kernels/nvfp4_cuda_v5.cu:433 */
+int get_gpu_info(char* name_buf, int buf_size, int* cc_major, int* cc_minor); /* :447-457 */
+int nvfp4_b200_abi_version(void);                    /* no counterpart in the reference */
+
+/* ---------------------------------------------------------------------------------------------
+ * Batch-1 GEMV: output[M] (fp16) = W[M,K] . activation[K] (fp16), fp32 accumulation.
+ *   weight_packed [M, K/2] u8 (element 2i = low nibble of byte i), weight_scales [M, K/16] u8.
+ * Returns 0; -2 if K % 32 != 0, M <= 0, a pointer is NULL, weight_packed/activation are not
+ * 16-byte aligned or weight_scales is not 2-byte aligned; -1 if the launch failed.
+ * All generations of the reference kernel share one implementation here.
+ * kernels/nvfp4_gemv.cu:837-851 (v1), :929-943 (v8), :946-961 (v4), :854-877 (v5), :880-895 (v6),
+ * :898-926 (v7, additionally K % 64 == 0), :964-977 (nl).
+ * ------------------------------------------------------------------------------------------- */
+int launch_nvfp4_gemv(const void* weight_packed, const void* weight_scales, const void* activation,
+                      void* output, int M, int K, void* stream);
+int launch_nvfp4_gemv_v8(const void* weight_packed, const void* weight_scales,
+                         const void* activation, void* output, int M, int K, void* stream);
+int launch_nvfp4_gemv_v4(const void* weight_packed, const void* weight_scales,
+                         const void* activation, void* output, int M, int K, void* stream);
+int launch_nvfp4_gemv_v5(const void* weight_packed, const void* weight_scales,
+                         const void* activation, void* output, int M, int K, void* stream);
+int launch_nvfp4_gemv_v6(const void* weight_packed, const void* weight_scales,
+                         const void* activation, void* output, int M, int K, void* stream);
+int launch_nvfp4_gemv_v7(const void* weight_packed, const void* weight_scales,
+                         const void* activation, void* output, int M, int K, void* stream);
+int launch_nvfp4_gemvnl(const void* weight_packed, const void* weight_scales,
+                        const void* activation, void* output, int M, int K, void* stream);
+
+/* Two activations, one pass over the weights: output[2, M], output[m] = W[m,:].act0,
+ * output[M + m] = W[m,:].act1.  kernels/nvfp4_gemv.cu:979-994. */
+int launch_nvfp4_gemv2(const void* weight_packed, const void* weight_scales, const void* act0,
+                       const void* act1, void* output, int M, int K, void* stream);
+
+/* Tuning hook; no counterpart in the reference.  warps per CTA (0 = auto, 2, 4 or 8), resident
+ * CTAs per SM used to size the grid (0 = occupancy calculator), force_generic != 0 routes every
+ * GEMV to the non-tensor-core kernel.  Process-wide, not thread-safe.  Returns 0 or -2. */
+int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int force_generic);
+
+/* ---------------------------------------------------------------------------------------------
+ * Zero-centred RMSNorm: out[r, :] = f16( f32(x[r, :]) * rsqrt(mean(x^2) + eps) * w1 ).
+ * x fp16, row r starts at x + r*row_stride (elements); w1 fp32 [n] = 1 + weight; out fp16
+ * contiguous [rows, n].  Returns -1 for rows <= 0, n <= 0 or a NULL pointer, else the cudaError_t.
+ * kernels/nvfp4_rmsnorm.cu:65-76.
+ * ------------------------------------------------------------------------------------------- */
+int launch_rmsnorm(const void* x, long long row_stride, const void* w1, void* out, int rows, int n,
+                   float eps, void* stream);
+
+/* RoPE (full rotation over 256 dims) on q [hq, 256] and k [hkv, 256] fp16 with cos/sin fp16 [256]:
+ * out = f16(f16(v*cos) + f16(rotate_half(v)*sin)).  0; -1 bad arguments; -2 launch error.
+ * kernels/nvfp4_rope_silu.cu:70-81. */
+int launch_rope_qk(const void* q, const void* k, const void* cos, const void* sin, void* q_out,
+                   void* k_out, int hq, int hkv, void* stream);
+
+/* out[i] = f16( f32(f16(g/(1+exp(-g)))) * u ), g/u/out fp16 [n].  0; -1; -2 as above.
+ * kernels/nvfp4_rope_silu.cu:83-91. */
+int launch_silu_mul(const void* g, const void* u, void* out, int n, void* stream);
+
+/* GQA attention decode (24 query heads, 4 KV heads, head dim 256) over a static KV cache, with the
+ * sigmoid output gate.  q/gate/out fp16 [24*256]; keys/values fp16 [4, max_len, 256]; cum_len is a
+ * DEVICE int64 holding the number of valid keys including the current token (read at run time, so
+ * a captured graph follows the growing cache).  max_len is a run-time value here (the reference
+ * compiles one DLL per length); -2 if max_len <= 0, max_len > 57344 or a pointer is NULL; else the
+ * cudaError_t.  kernels/nvfp4_attn_decode.cu:121-132. */
+int launch_attn_decode(const void* q, const void* keys, const void* values, const void* cum_len,
+                       const void* gate, void* out, int max_len, float scale, void* stream);
+
+/* One Gated-DeltaNet decode step (16 key heads, 48 value heads, dim 128, conv kernel 4).
+ * mixed fp16 [10240] = [q 2048 | k 2048 | v 6144]; z fp16 [6144]; b, a fp16 [48];
+ * conv_w fp16 [10240*4]; conv_state fp16 [10240*4] in/out (layout c*4 + t);
+ * A_log, dt_bias fp16 [48]; norm_w fp16 [128]; state fp32 [48*128*128] in/out, transposed
+ * (value-dim major); scratch fp32 [10240] caller-provided workspace; out fp16 [6144].
+ * Returns 0, or -1 on a NULL pointer or launch error.  kernels/nvfp4_dn_fused.cu:156-176. */
+int launch_dn_fused(const void* mixed, const void* z, const void* b, const void* a,
+                    const void* conv_w, void* conv_state, const void* A_log, const void* dt_bias,
+                    const void* norm_w, void* state, void* scratch, void* out, float rms_eps,
+                    void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVFP4_B200_H */

@@ -1,0 +1,68 @@
+"""ctypes binding of ``libnvfp4_b200.so`` — the one C-ABI library behind every reference DLL name.
+
+There is no fallback: if the library is missing, or does not export a symbol the header declares,
+loading raises.  Signatures follow ``include/nvfp4_b200.h``.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libnvfp4_b200.so")
+KDIR = os.path.join(PKG_DIR, "kernels")
+
+_vp, _i, _f, _sz, _ll = (ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t,
+                         ctypes.c_longlong)
+
+_GEMV_SIG = ([_vp, _vp, _vp, _vp, _i, _i, _vp], _i)
+
+# symbol -> (argtypes, restype); mirrors include/nvfp4_b200.h
+SIGNATURES = {
+    "gpu_malloc": ([_sz], _vp),
+    "gpu_free": ([_vp], None),
+    "gpu_memcpy_h2d": ([_vp, _vp, _sz], _i),
+    "gpu_memcpy_d2h": ([_vp, _vp, _sz], _i),
+    "gpu_sync": ([], _i),
+    "get_gpu_info": ([ctypes.c_char_p, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)], _i),
+    "nvfp4_b200_abi_version": ([], _i),
+    "launch_nvfp4_gemv": _GEMV_SIG,
+    "launch_nvfp4_gemv_v8": _GEMV_SIG,
+    "launch_nvfp4_gemv_v4": _GEMV_SIG,
+    "launch_nvfp4_gemv_v5": _GEMV_SIG,
+    "launch_nvfp4_gemv_v6": _GEMV_SIG,
+    "launch_nvfp4_gemv_v7": _GEMV_SIG,
+    "launch_nvfp4_gemvnl": _GEMV_SIG,
+    "launch_nvfp4_gemv2": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _vp], _i),
+    "nvfp4_b200_gemv_config": ([_i, _i, _i], _i),
+    "launch_rmsnorm": ([_vp, _ll, _vp, _vp, _i, _i, _f, _vp], _i),
+    "launch_rope_qk": ([_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp], _i),
+    "launch_silu_mul": ([_vp, _vp, _vp, _i, _vp], _i),
+    "launch_attn_decode": ([_vp] * 6 + [_i, _f, _vp], _i),
+    "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
+}
+
+_LIB = None
+
+
+def load(path: str | None = None) -> ctypes.CDLL:
+    """Load the library once and attach argtypes/restype to every declared symbol."""
+    global _LIB
+    if _LIB is not None and path is None:
+        return _LIB
+    p = path or LIB_PATH
+    if not os.path.exists(p):
+        raise RuntimeError(
+            f"{p} is missing: build it with `python -m nvfp4_v100_b200.build` "
+            "(needs nvcc; there is no CPU fallback)")
+    lib = ctypes.CDLL(p)
+    for name, (argtypes, restype) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:
+            raise RuntimeError(f"{p} does not export `{name}`") from e
+        fn.argtypes = argtypes
+        fn.restype = restype
+    if path is None:
+        _LIB = lib
+    return lib

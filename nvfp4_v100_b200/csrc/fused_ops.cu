@@ -1,0 +1,429 @@
+// Decode-step elementwise / attention / DeltaNet kernels for sm_100a behind the reference's
+// launcher signatures:
+//   launch_rmsnorm      (reference: kernels/nvfp4_rmsnorm.cu:26-76)
+//   launch_rope_qk      (reference: kernels/nvfp4_rope_silu.cu:29-53,70-81)
+//   launch_silu_mul     (reference: kernels/nvfp4_rope_silu.cu:56-67,83-91)
+//   launch_attn_decode  (reference: kernels/nvfp4_attn_decode.cu:29-132)
+//   launch_dn_fused     (reference: kernels/nvfp4_dn_fused.cu:55-176)
+// Each kernel keeps the reference's fp16 rounding points (where a value passes through an fp16
+// tensor in the model it is rounded to fp16 here as well) and computes everything else in fp32.
+// Reductions are warp-shuffle trees, so fp32 sums may differ from the reference's thread order in
+// the last bit before the final fp16 rounding.
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace nvfp4 {
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm (zero-centred weight): out = f16( f32(x) * rsqrt(mean(x^2) + eps) * w1 ), w1 = 1 + w.
+// One CTA per row; rows may be strided (row_stride elements between row starts).
+// ---------------------------------------------------------------------------------------------
+template <int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_kernel(const __half* __restrict__ x, long long row_stride, const float* __restrict__ w1,
+               __half* __restrict__ out, int n, float eps) {
+    __shared__ float s_red[THREADS / 32];
+    __shared__ float s_inv;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const __half* xr = x + (size_t)blockIdx.x * (size_t)row_stride;
+    __half* orow = out + (size_t)blockIdx.x * (size_t)n;
+    // 8 elements per thread per pass when both rows are 16-byte aligned
+    const bool vec = ((n & 7) == 0) && ((((uintptr_t)xr) | ((uintptr_t)orow)) & 15) == 0 &&
+                     ((((uintptr_t)w1) & 15) == 0);
+    float ss = 0.0f;
+    if (vec) {
+        for (int i = t * 8; i < n; i += THREADS * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 f = __half22float2(h[j]);
+                ss = fmaf(f.x, f.x, ss);
+                ss = fmaf(f.y, f.y, ss);
+            }
+        }
+    } else {
+        for (int i = t; i < n; i += THREADS) {
+            const float v = __half2float(xr[i]);
+            ss = fmaf(v, v, ss);
+        }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) s_red[warp] = ss;
+    __syncthreads();
+    if (warp == 0) {
+        float v = (lane < THREADS / 32) ? s_red[lane] : 0.0f;
+        v = warp_sum(v);
+        if (lane == 0) s_inv = rsqrtf(v / (float)n + eps);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    if (vec) {
+        for (int i = t * 8; i < n; i += THREADS * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xr + i);
+            const float4 wa = *reinterpret_cast<const float4*>(w1 + i);
+            const float4 wb = *reinterpret_cast<const float4*>(w1 + i + 4);
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+            const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 f = __half22float2(h[j]);
+                oh[j] = __halves2half2(__float2half(f.x * inv * w[2 * j]),
+                                       __float2half(f.y * inv * w[2 * j + 1]));
+            }
+            *reinterpret_cast<uint4*>(orow + i) = o;
+        }
+    } else {
+        for (int i = t; i < n; i += THREADS)
+            orow[i] = __float2half(__half2float(xr[i]) * inv * w1[i]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// RoPE on q [hq][256] and k [hkv][256] (full rotation, rotate_half = (-x2, x1)):
+//   out = f16( f32(f16(v*c)) + f32(f16(rot(v)*s)) ).  One CTA per head, 128 threads, 2 dims each.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+rope_qk_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
+               const __half* __restrict__ cs, const __half* __restrict__ sn,
+               __half* __restrict__ q_out, __half* __restrict__ k_out, int hq) {
+    const int h = blockIdx.x, d = threadIdx.x;  // d in [0,128): handles d and d+128
+    const bool is_q = h < hq;
+    const size_t off = (size_t)(is_q ? h : h - hq) * 256;
+    const __half* src = is_q ? q + off : k + off;
+    __half* dst = is_q ? q_out + off : k_out + off;
+    const float x1 = __half2float(src[d]), x2 = __half2float(src[d + 128]);
+    const float c1 = __half2float(cs[d]), c2 = __half2float(cs[d + 128]);
+    const float s1 = __half2float(sn[d]), s2 = __half2float(sn[d + 128]);
+    const float lo = round_f16(x1 * c1) + round_f16(-x2 * s1);
+    const float hi = round_f16(x2 * c2) + round_f16(x1 * s2);
+    dst[d] = __float2half(lo);
+    dst[d + 128] = __float2half(hi);
+}
+
+// ---------------------------------------------------------------------------------------------
+// silu(g) * u with the model's rounding chain: s = f16(g / (1 + expf(-g))), out = f16(f32(s) * u).
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+
+__global__ void __launch_bounds__(256)
+silu_mul_kernel(const __half* __restrict__ g, const __half* __restrict__ u,
+                __half* __restrict__ out, int n) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    const float gf = __half2float(g[i]), uf = __half2float(u[i]);
+    out[i] = __float2half(round_f16(silu_f(gf)) * uf);
+}
+
+// ---------------------------------------------------------------------------------------------
+// GQA attention decode (T = 1) over a static KV cache + sigmoid output gate.
+//   q [HQ][256], keys/values [HKV][max_len][256] fp16, L = *cum_len (current token included),
+//   gate [HQ][256]; out[h][d] = f16( f32(f16(o)) * f32(f16(sigmoid(gate))) ).
+// One CTA per query head.  Pass 1: one warp per key, 16 bytes per lane (a 512-byte key row is one
+// coalesced warp read), fp32 dot product + shuffle reduction, scores to shared memory.  Softmax in
+// fp32 with expf.  Pass 2: each thread owns one head dim and walks the keys (coalesced rows).
+// max_len is a runtime argument; the score buffer is dynamic shared memory (4 bytes per key).
+// ---------------------------------------------------------------------------------------------
+#define ATT_D 256
+#define ATT_THREADS 256
+
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys,
+                   const __half* __restrict__ values, const long long* __restrict__ cum_len,
+                   const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
+                   int gqa, float scale) {
+    extern __shared__ float s_sc[];  // [max_len]
+    __shared__ float s_red[ATT_THREADS / 32];
+    __shared__ float s_bcast;
+    const int h = blockIdx.x, kv = h / gqa;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    long long L64 = *cum_len;
+    if (L64 > max_len) L64 = max_len;  // never index past the cache
+    const int L = (int)L64;
+
+    // this lane's 8 query dims, kept in registers as fp32
+    float qf[8];
+    {
+        const uint4 qv = *reinterpret_cast<const uint4*>(q + (size_t)h * ATT_D + lane * 8);
+        const __half2* qh = reinterpret_cast<const __half2*>(&qv);
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(qh[j]);
+            qf[2 * j] = f.x;
+            qf[2 * j + 1] = f.y;
+        }
+    }
+    const __half* kbase = keys + (size_t)kv * (size_t)max_len * ATT_D;
+    float m = -3.4e38f;
+    for (int i = warp; i < L; i += ATT_THREADS / 32) {
+        const uint4 kvv = *reinterpret_cast<const uint4*>(kbase + (size_t)i * ATT_D + lane * 8);
+        const __half2* kh = reinterpret_cast<const __half2*>(&kvv);
+        float acc = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const float2 f = __half22float2(kh[j]);
+            acc = fmaf(qf[2 * j], f.x, acc);
+            acc = fmaf(qf[2 * j + 1], f.y, acc);
+        }
+        acc = warp_sum(acc) * scale;
+        if (lane == 0) s_sc[i] = acc;
+        m = fmaxf(m, acc);
+    }
+    // block max (every lane of a warp already holds the warp's max)
+    if (lane == 0) s_red[warp] = m;
+    __syncthreads();
+    if (warp == 0) {
+        float v = (lane < ATT_THREADS / 32) ? s_red[lane] : -3.4e38f;
+        v = warp_max(v);
+        if (lane == 0) s_bcast = v;
+    }
+    __syncthreads();
+    m = s_bcast;
+    float l = 0.0f;
+    for (int i = t; i < L; i += ATT_THREADS) {
+        const float e = expf(s_sc[i] - m);
+        s_sc[i] = e;
+        l += e;
+    }
+    l = warp_sum(l);
+    __syncthreads();  // s_red / s_bcast reuse
+    if (lane == 0) s_red[warp] = l;
+    __syncthreads();
+    if (warp == 0) {
+        float v = (lane < ATT_THREADS / 32) ? s_red[lane] : 0.0f;
+        v = warp_sum(v);
+        if (lane == 0) s_bcast = 1.0f / v;
+    }
+    __syncthreads();
+    const float inv_l = s_bcast;
+
+    const __half* vbase = values + (size_t)kv * (size_t)max_len * ATT_D + t;
+    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+    int i = 0;
+    for (; i + 4 <= L; i += 4) {
+        const float v0 = __half2float(vbase[(size_t)(i + 0) * ATT_D]);
+        const float v1 = __half2float(vbase[(size_t)(i + 1) * ATT_D]);
+        const float v2 = __half2float(vbase[(size_t)(i + 2) * ATT_D]);
+        const float v3 = __half2float(vbase[(size_t)(i + 3) * ATT_D]);
+        acc0 = fmaf(s_sc[i + 0] * inv_l, v0, acc0);
+        acc1 = fmaf(s_sc[i + 1] * inv_l, v1, acc1);
+        acc2 = fmaf(s_sc[i + 2] * inv_l, v2, acc2);
+        acc3 = fmaf(s_sc[i + 3] * inv_l, v3, acc3);
+    }
+    for (; i < L; i++)
+        acc0 = fmaf(s_sc[i] * inv_l, __half2float(vbase[(size_t)i * ATT_D]), acc0);
+    const float o = (acc0 + acc1) + (acc2 + acc3);
+
+    const float a = round_f16(o);
+    const float gt = __half2float(gate[(size_t)h * ATT_D + t]);
+    const float sg = round_f16(1.0f / (1.0f + expf(-gt)));
+    out[(size_t)h * ATT_D + t] = __float2half(a * sg);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Gated DeltaNet decode step (16 key heads, 48 value heads, head dim 128, conv kernel 4).
+// Kernel 1: causal conv1d update + silu per channel -> scratch (fp32 holding fp16-rounded values).
+// Kernel 2: one CTA per value head, 16 warps; a warp owns 8 state rows (one row = 128 fp32 =
+//           one float4 per lane, so every state access is a coalesced 512-byte row).
+// ---------------------------------------------------------------------------------------------
+#define DN_DK 128
+#define DN_NVH 48
+#define DN_KEY_DIM 2048
+#define DN_CONV_DIM 10240
+#define DN_REC_THREADS 512
+
+__device__ __forceinline__ float softplus_f(float x) { return (x > 20.0f) ? x : log1pf(expf(x)); }
+
+__global__ void __launch_bounds__(256)
+dn_conv_kernel(const __half* __restrict__ mixed, const __half* __restrict__ conv_w,
+               __half* __restrict__ conv_state, float* __restrict__ scratch) {
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= DN_CONV_DIM) return;
+    // state and weights of a channel are 4 consecutive halves: one 8-byte load each
+    const uint2 sv = *reinterpret_cast<const uint2*>(conv_state + (size_t)c * 4);
+    const uint2 wv = *reinterpret_cast<const uint2*>(conv_w + (size_t)c * 4);
+    const __half2 s01 = *reinterpret_cast<const __half2*>(&sv.x);
+    const __half2 s23 = *reinterpret_cast<const __half2*>(&sv.y);
+    const __half2 w01 = *reinterpret_cast<const __half2*>(&wv.x);
+    const __half2 w23 = *reinterpret_cast<const __half2*>(&wv.y);
+    const __half x = mixed[c];
+    const float s1 = __high2float(s01), s2 = __low2float(s23), s3 = __high2float(s23);
+    // window [s1, s2, s3, x]; the sum is evaluated left to right with fused multiply-adds
+    float acc = __low2float(w01) * s1;
+    acc = fmaf(__high2float(w01), s2, acc);
+    acc = fmaf(__low2float(w23), s3, acc);
+    acc = fmaf(__high2float(w23), __half2float(x), acc);
+    scratch[c] = round_f16(silu_f(acc));
+    uint2 ns;
+    const __half2 n01 = __halves2half2(__high2half(s01), __low2half(s23));
+    const __half2 n23 = __halves2half2(__high2half(s23), x);
+    ns.x = *reinterpret_cast<const uint32_t*>(&n01);
+    ns.y = *reinterpret_cast<const uint32_t*>(&n23);
+    *reinterpret_cast<uint2*>(conv_state + (size_t)c * 4) = ns;
+}
+
+__global__ void __launch_bounds__(DN_REC_THREADS)
+dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
+              const __half* __restrict__ a_in, const __half* __restrict__ A_log,
+              const __half* __restrict__ dt_bias, const __half* __restrict__ norm_w,
+              const float* __restrict__ scratch, float* __restrict__ state,
+              __half* __restrict__ out, float rms_eps) {
+    __shared__ float s_o[DN_DK];
+    __shared__ float s_red[8];
+    const int h = blockIdx.x, kh = h / 3;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+
+    const float beta = round_f16(1.0f / (1.0f + expf(-__half2float(b_in[h]))));
+    const float gdec = -expf(__half2float(A_log[h])) *
+                       softplus_f(__half2float(a_in[h]) + __half2float(dt_bias[h]));
+    const float eg = expf(gdec);
+
+    // every warp normalises q and k itself: lane owns dims 4*lane .. 4*lane+3
+    float4 qv = *reinterpret_cast<const float4*>(scratch + kh * DN_DK + lane * 4);
+    float4 kv = *reinterpret_cast<const float4*>(scratch + DN_KEY_DIM + kh * DN_DK + lane * 4);
+    const float qss = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
+    const float kss = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
+    const float inv_q = rsqrtf(qss + 1e-6f) * 0.08838834764831845f;
+    const float inv_k = rsqrtf(kss + 1e-6f);
+    qv.x *= inv_q; qv.y *= inv_q; qv.z *= inv_q; qv.w *= inv_q;
+    kv.x *= inv_k; kv.y *= inv_k; kv.z *= inv_k; kv.w *= inv_k;
+
+    // rows j = warp*8 .. warp*8+7 of S_t[h][j][:]
+    float* Sbase = state + ((size_t)h * DN_DK + (size_t)warp * 8) * DN_DK + lane * 4;
+    float4 S[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) S[r] = *reinterpret_cast<const float4*>(Sbase + (size_t)r * DN_DK);
+#pragma unroll
+    for (int r = 0; r < 8; r++) {
+        const int j = warp * 8 + r;
+        S[r].x *= eg; S[r].y *= eg; S[r].z *= eg; S[r].w *= eg;
+        float kvp = S[r].x * kv.x;
+        kvp = fmaf(S[r].y, kv.y, kvp);
+        kvp = fmaf(S[r].z, kv.z, kvp);
+        kvp = fmaf(S[r].w, kv.w, kvp);
+        kvp = warp_sum(kvp);
+        const float v_j = scratch[DN_KEY_DIM * 2 + h * DN_DK + j];
+        const float delta = (v_j - kvp) * beta;
+        S[r].x = fmaf(kv.x, delta, S[r].x);
+        S[r].y = fmaf(kv.y, delta, S[r].y);
+        S[r].z = fmaf(kv.z, delta, S[r].z);
+        S[r].w = fmaf(kv.w, delta, S[r].w);
+        *reinterpret_cast<float4*>(Sbase + (size_t)r * DN_DK) = S[r];
+        float o = S[r].x * qv.x;
+        o = fmaf(S[r].y, qv.y, o);
+        o = fmaf(S[r].z, qv.z, o);
+        o = fmaf(S[r].w, qv.w, o);
+        o = warp_sum(o);
+        if (lane == 0) s_o[j] = round_f16(o);
+    }
+    __syncthreads();
+    // RMSNormGated over the head's 128 outputs, then * silu(z)
+    if (warp < 4) {
+        const int j = t;  // 0..127
+        const float o = s_o[j];
+        float ss = warp_sum(o * o);
+        if (lane == 0) s_red[warp] = ss;
+    }
+    __syncthreads();
+    if (t < DN_DK) {
+        const float var_mean = ((s_red[0] + s_red[1]) + (s_red[2] + s_red[3])) / (float)DN_DK;
+        const float o = s_o[t];
+        const float xn = o * rsqrtf(var_mean + rms_eps);
+        const __half hw = __hmul(__float2half(xn), norm_w[t]);
+        const float res = __half2float(hw) * silu_f(__half2float(z_in[(size_t)h * DN_DK + t]));
+        out[(size_t)h * DN_DK + t] = __float2half(res);
+    }
+}
+
+}  // namespace nvfp4
+
+extern "C" {
+
+int launch_rmsnorm(const void* x, long long row_stride, const void* w1, void* out, int rows, int n,
+                   float eps, void* stream) {
+    if (rows <= 0 || n <= 0) return -1;
+    if (!x || !w1 || !out) return -1;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n >= 2048)
+        nvfp4::rmsnorm_kernel<512><<<rows, 512, 0, st>>>((const __half*)x, row_stride,
+                                                         (const float*)w1, (__half*)out, n, eps);
+    else
+        nvfp4::rmsnorm_kernel<64><<<rows, 64, 0, st>>>((const __half*)x, row_stride,
+                                                       (const float*)w1, (__half*)out, n, eps);
+    const cudaError_t e = cudaGetLastError();
+    return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+int launch_rope_qk(const void* q, const void* k, const void* cs, const void* sn, void* q_out,
+                   void* k_out, int hq, int hkv, void* stream) {
+    if (hq < 0 || hkv < 0 || hq + hkv <= 0) return -1;
+    if (!cs || !sn || (hq > 0 && (!q || !q_out)) || (hkv > 0 && (!k || !k_out))) return -1;
+    nvfp4::rope_qk_kernel<<<hq + hkv, 128, 0, (cudaStream_t)stream>>>(
+        (const __half*)q, (const __half*)k, (const __half*)cs, (const __half*)sn, (__half*)q_out,
+        (__half*)k_out, hq);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int launch_silu_mul(const void* g, const void* u, void* out, int n, void* stream) {
+    if (n <= 0 || !g || !u || !out) return -1;
+    nvfp4::silu_mul_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
+        (const __half*)g, (const __half*)u, (__half*)out, n);
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// Heads are the 27B model's: 24 query heads, 4 KV heads, head dim 256.  max_len is the cache's
+// allocated length and may be any value whose fp32 score buffer fits in shared memory
+// (max_len <= 57344); larger values return -2, as the reference does for an unsupported length.
+int launch_attn_decode(const void* q, const void* keys, const void* values, const void* cum_len,
+                       const void* gate, void* out, int max_len, float scale, void* stream) {
+    static bool smem_opt_in = false;
+    if (max_len <= 0 || max_len > 57344) return -2;
+    if (!q || !keys || !values || !cum_len || !gate || !out) return -2;
+    const size_t smem = (size_t)max_len * sizeof(float);
+    if (!smem_opt_in) {
+        // one-time opt-in to the large dynamic shared memory carve-out (a host-side attribute,
+        // not a stream operation)
+        if (cudaFuncSetAttribute(nvfp4::attn_decode_kernel,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(57344 * sizeof(float))) != cudaSuccess)
+            return -2;
+        smem_opt_in = true;
+    }
+    nvfp4::attn_decode_kernel<<<24, ATT_THREADS, smem, (cudaStream_t)stream>>>(
+        (const __half*)q, (const __half*)keys, (const __half*)values, (const long long*)cum_len,
+        (const __half*)gate, (__half*)out, max_len, 6, scale);
+    const cudaError_t e = cudaGetLastError();
+    return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+int launch_dn_fused(const void* mixed, const void* z_in, const void* b_in, const void* a_in,
+                    const void* conv_w, void* conv_state, const void* A_log, const void* dt_bias,
+                    const void* norm_w, void* state, void* scratch, void* out, float rms_eps,
+                    void* stream) {
+    if (!mixed || !z_in || !b_in || !a_in || !conv_w || !conv_state || !A_log || !dt_bias ||
+        !norm_w || !state || !scratch || !out)
+        return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    nvfp4::dn_conv_kernel<<<(DN_CONV_DIM + 255) / 256, 256, 0, s>>>(
+        (const __half*)mixed, (const __half*)conv_w, (__half*)conv_state, (float*)scratch);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "dn_conv launch: %s\n", cudaGetErrorString(e));
+        return -1;
+    }
+    nvfp4::dn_rec_kernel<<<DN_NVH, DN_REC_THREADS, 0, s>>>(
+        (const __half*)z_in, (const __half*)b_in, (const __half*)a_in, (const __half*)A_log,
+        (const __half*)dt_bias, (const __half*)norm_w, (const float*)scratch, (float*)state,
+        (__half*)out, rms_eps);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "dn_rec launch: %s\n", cudaGetErrorString(e));
+        return -1;
+    }
+    return 0;
+}
+
+}  // extern "C"
