@@ -180,6 +180,12 @@ CPU_SAMPLE_DESC = ("one GEMV each of 5120x5120, 1024x5120, 5120x6144, 6144x5120,
                    "5120x17408 (codec decode to fp16 + fp32 torch matvec)")
 
 
+# one step of the reference arm: a bounded sample (~4 s of CPU work)
+REF_STEP_SAMPLE = CPU_SAMPLE[:3]
+REF_STEP_DESC = ("one GEMV each of 5120x5120, 1024x5120, 5120x6144 "
+                 "(codec decode to fp16 + fp32 torch matvec)")
+
+
 def run_reference(args):
     """--impl reference: the reference's CPU path for this metric (codec dequant + torch CPU
     matmul), restated by the oracle, on all host threads.  Rank 0 only."""
@@ -193,7 +199,7 @@ def run_reference(args):
     t0 = time.perf_counter()
     vals = []
     for _ in range(args.steps):
-        g, _t = cpu_gemv_gbps(CPU_SAMPLE, cores)
+        g, _t = cpu_gemv_gbps(REF_STEP_SAMPLE, cores)
         vals.append(g)
     dt = time.perf_counter() - t0
     v = sum(vals) / len(vals)
@@ -202,9 +208,9 @@ def run_reference(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "gemv_497_mix_27b", "sample": CPU_SAMPLE_DESC},
+        "config": {"workload": "gemv_497_mix_27b", "sample": REF_STEP_DESC},
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": CPU_SAMPLE_DESC},
+                         "kind": "port", "sample": REF_STEP_DESC},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -388,6 +394,79 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+SHAPES_27B = [("lm_head", VOCAB, HIDDEN, 1), ("down_proj", HIDDEN, INTER, 64),
+              ("gate/up_proj", INTER, HIDDEN, 128), ("q_proj+gate", 12288, HIDDEN, 16),
+              ("in_proj_qkv", 10240, HIDDEN, 48), ("in_proj_z", 6144, HIDDEN, 48),
+              ("o/out_proj", HIDDEN, 6144, 64), ("k/v_proj", 1024, HIDDEN, 32),
+              ("in_proj_b/a", 48, HIDDEN, 96),
+              # shapes BASELINE.json lists beside the reference's own table
+              ("q_proj 6144", 6144, HIDDEN, 0), ("o_proj 5120", HIDDEN, HIDDEN, 0),
+              ("lm_head 151936", 151936, HIDDEN, 0)]
+
+
+def run_per_shape(args):
+    """Each layer shape timed alone, cold L2: launches rotate over enough weight copies that the
+    working set is several times the L2 (method of experiments/_bench_gemv_real_shapes.py:68-94)."""
+    import torch
+
+    from nvfp4_v100_b200 import _lib
+
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    vp = ctypes.c_void_p
+    only = None
+    if args.only:
+        m, k = args.only.lower().split("x")
+        only = (int(m), int(k))
+    peak, peak_kind = measured_peak()
+    rows = []
+    for name, M, K, count in SHAPES_27B:
+        if only and (M, K) != only:
+            continue
+        nbytes = gemv_bytes(M, K)
+        ncopy = max(2, min(64, -(-(1 << 30) // nbytes)))
+        packed = torch.randint(0, 256, (ncopy, M * K // 2), dtype=torch.uint8, device="cuda")
+        scales = torch.randint(118, 123, (ncopy, M * K // 16), dtype=torch.uint8, device="cuda")
+        act = torch.randn(ncopy, K, device="cuda").to(torch.float16)
+        out = torch.zeros(ncopy, M, dtype=torch.float16, device="cuda")
+        st = vp(torch.cuda.current_stream().cuda_stream)
+
+        def launch(i):
+            c = i % ncopy
+            rc = lib.launch_nvfp4_gemv_v8(vp(packed[c].data_ptr()), vp(scales[c].data_ptr()),
+                                          vp(act[c].data_ptr()), vp(out[c].data_ptr()), M, K, st)
+            assert rc == 0, rc
+
+        reps = args.reps
+        for i in range(max(3, ncopy)):
+            launch(i)
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(reps):
+                launch(i)
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            best = us if best is None else min(best, us)
+        gbps = nbytes / (best * 1e-6) / 1e9
+        rows.append({"shape": f"{M}x{K}", "name": name, "count_per_step": count, "us": best,
+                     "gbps": gbps, "frac_of_" + peak_kind: gbps / peak, "copies": ncopy})
+        print(f"{name:16s} {M:7d}x{K:<6d} {best:9.2f} us {gbps:8.1f} GB/s "
+              f"{100 * gbps / peak:5.1f}% of {peak_kind} {peak:.0f}", file=sys.stderr, flush=True)
+        del packed, scales, act, out
+    mix_us = sum(r["us"] * r["count_per_step"] for r in rows)
+    mix_bytes = sum(gemv_bytes(*map(int, r["shape"].split("x"))) * r["count_per_step"] for r in rows)
+    line = {"metric": "nvfp4_gemv_hbm_gbps_per_shape", "unit": "GB/s", "n_gpus": 1,
+            "timing": "cuda events over back-to-back launches, best of 3, cold L2 by rotation",
+            "per_shape": rows,
+            "mix_497": {"ms_per_step": mix_us / 1e3,
+                        "gbps": (mix_bytes / (mix_us * 1e-6) / 1e9) if mix_us else None}}
+    print(json.dumps(line), flush=True)
+
+
 # DRAM bytes (read + write) per average GEMV launch of the mix, from the ncu capture summarised
 # under profiles/; None until a capture exists.
 TRAFFIC_PER_LAUNCH = None
@@ -400,10 +479,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--per-shape", action="store_true",
+                    help="time every 27B layer shape alone (cold L2) instead of the step mix")
+    ap.add_argument("--only", default="", help="with --per-shape: a single MxK shape")
+    ap.add_argument("--reps", type=int, default=200, help="with --per-shape: launches per timing")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.per_shape:
+        run_per_shape(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
