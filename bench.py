@@ -441,12 +441,33 @@ def run_per_shape(args):
         for i in range(max(3, ncopy)):
             launch(i)
         torch.cuda.synchronize()
+        # replay the launches from a CUDA graph so that host launch cost (about 9 us per ctypes
+        # call) does not hide the kernel time of the small shapes
+        graph = None
+        if not args.eager:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                st = vp(side.cuda_stream)
+                launch(0)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                st = vp(torch.cuda.current_stream().cuda_stream)
+                for i in range(reps):
+                    launch(i)
+            graph.replay()
+            torch.cuda.synchronize()
         best = None
         for _ in range(3):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for i in range(reps):
-                launch(i)
+            if graph is not None:
+                graph.replay()
+            else:
+                for i in range(reps):
+                    launch(i)
             e1.record()
             torch.cuda.synchronize()
             us = e0.elapsed_time(e1) * 1e3 / reps
@@ -460,7 +481,7 @@ def run_per_shape(args):
     mix_us = sum(r["us"] * r["count_per_step"] for r in rows)
     mix_bytes = sum(gemv_bytes(*map(int, r["shape"].split("x"))) * r["count_per_step"] for r in rows)
     line = {"metric": "nvfp4_gemv_hbm_gbps_per_shape", "unit": "GB/s", "n_gpus": 1,
-            "timing": "cuda events over back-to-back launches, best of 3, cold L2 by rotation",
+            "timing": "cuda events over back-to-back launches (CUDA graph replay unless --eager), best of 3, cold L2 by rotation over weight copies",
             "per_shape": rows,
             "mix_497": {"ms_per_step": mix_us / 1e3,
                         "gbps": (mix_bytes / (mix_us * 1e-6) / 1e9) if mix_us else None}}
@@ -483,6 +504,8 @@ def main():
                     help="time every 27B layer shape alone (cold L2) instead of the step mix")
     ap.add_argument("--only", default="", help="with --per-shape: a single MxK shape")
     ap.add_argument("--reps", type=int, default=200, help="with --per-shape: launches per timing")
+    ap.add_argument("--eager", action="store_true",
+                    help="with --per-shape: launch from the host instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

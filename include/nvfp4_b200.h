@@ -61,9 +61,10 @@ int launch_nvfp4_gemv2(const void* weight_packed, const void* weight_scales, con
                        const void* act1, void* output, int M, int K, void* stream);
 
 /* Tuning hook; no counterpart in the reference.  warps per CTA (0 = auto, 2, 4 or 8), resident
- * CTAs per SM used to size the grid (0 = occupancy calculator), force_generic != 0 routes every
- * GEMV to the non-tensor-core kernel.  Process-wide, not thread-safe.  Returns 0 or -2. */
-int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int force_generic);
+ * CTAs per SM used to size the grid (0 = occupancy calculator), flags: bit 0 routes every GEMV to
+ * the non-tensor-core kernel, bit 1 turns programmatic dependent launch off.  Process-wide, not
+ * thread-safe.  Returns 0 or -2. */
+int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int flags);
 
 /* ---------------------------------------------------------------------------------------------
  * Zero-centred RMSNorm: out[r, :] = f16( f32(x[r, :]) * rsqrt(mean(x^2) + eps) * w1 ).

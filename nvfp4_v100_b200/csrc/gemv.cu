@@ -42,9 +42,39 @@ __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// byte q (0..3) of w as an E8M0 scale in fp32
+// byte q (0..3) of w as an E8M0 scale in fp32: isolate the byte where it sits, then move it to
+// the exponent field.  For q < 3 the move is an integer multiply (issued on the FMA pipe, which
+// this kernel leaves almost idle) instead of a shift on the busier ALU pipe.
 __device__ __forceinline__ float scale_byte(uint32_t w, int q) {
-    return __uint_as_float(((w >> (8 * q)) & 0xFFu) << 23);
+    if (q == 3) return __uint_as_float((w >> 1) & 0x7F800000u);
+    return __uint_as_float((w & (0xFFu << (8 * q))) * (1u << (23 - 8 * q)));
+}
+
+// 16-byte activation load executed only where pred != 0; other lanes keep what the registers
+// held (zero, set once), so no per-step zero fill is needed.
+__device__ __forceinline__ void ld_x_pred(const void* p, uint32_t pred, uint32_t& r0, uint32_t& r1,
+                                          uint32_t& r2, uint32_t& r3) {
+    asm("{\n"
+        ".reg .pred p;\n"
+        "setp.ne.u32 p, %4, 0;\n"
+        "@p ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%5];\n"
+        "}\n"
+        : "+r"(r0), "+r"(r1), "+r"(r2), "+r"(r3)
+        : "r"(pred), "l"(p));
+}
+
+// Programmatic dependent launch: let the next kernel in the stream begin its weight prefetch
+// while this one drains, and wait for the previous kernel before touching anything it may have
+// written.  Both are no-ops when the kernel was launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+// Ask the L2 to fetch [p, p + bytes): both 16-byte multiples.  A prefetch has no register result,
+// so it is safe on memory another kernel may still be writing: L2 is the coherence point.
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p), "r"(bytes) : "memory");
 }
 
 struct WeightRegs {
@@ -69,6 +99,31 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
     // Lane (g,t) supplies column g of B with the activation of K chunk t when (g & 3) == t.
     const bool supplies = ((g & 3) == t) && (g < 4 || NACT == 2);
     const __half* xsrc = (g < 4 || NACT == 1) ? act0 : act1;
+
+    // ---- prologue that does not depend on the previous kernel: L2 prefetch of the first tile ----
+    pdl_launch_dependents();
+    if (blockIdx.x < ntiles) {
+        const int r0 = blockIdx.x * 16;
+        const int nrows = min(16, M - r0);
+        // the tile's rows are adjacent in memory: one packed slab and one scale slab
+        const uint8_t* pslab = packed + (size_t)r0 * prow;
+        const size_t pbytes = (size_t)nrows * prow;             // multiple of 64
+        const uint32_t PF_CHUNK = 8192;
+        for (size_t off = (size_t)threadIdx.x * PF_CHUNK; off < pbytes;
+             off += (size_t)blockDim.x * PF_CHUNK) {
+            const size_t n = pbytes - off;
+            prefetch_l2_bulk(pslab + off, (uint32_t)(n < PF_CHUNK ? n : PF_CHUNK));
+        }
+        if (threadIdx.x == blockDim.x - 1) {
+            const size_t sbytes = ((size_t)nrows * srow) & ~(size_t)15;
+            if (sbytes) prefetch_l2_bulk(scales + (size_t)r0 * srow, (uint32_t)sbytes);
+        }
+    }
+    pdl_wait();
+
+    uint32_t xr[2][8];  // two passes of activation registers (zero where this lane supplies none)
+#pragma unroll
+    for (int i = 0; i < 8; i++) { xr[0][i] = 0u; xr[1][i] = 0u; }
 
     for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
         const int ra = min(tile * 16 + g, M - 1);
@@ -104,33 +159,27 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
             const int sn = s + WARPS;
             if (sn < nsteps) load_w(sn, nxt);
 
-            // activation of this lane's chunk (suppliers only), 64 halves = 32 half2
-            uint32_t xr[32];
+            // activation of this lane's chunk, 16 halves per pass (suppliers only)
             const int kc = s * 256 + t * 64;
-            if (supplies && kc < K) {
-                const uint4* xp = reinterpret_cast<const uint4*>(xsrc + kc);
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                    const uint4 v = __ldg(xp + i);
-                    xr[4 * i + 0] = v.x; xr[4 * i + 1] = v.y;
-                    xr[4 * i + 2] = v.z; xr[4 * i + 3] = v.w;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < 32; i++) xr[i] = 0u;
-            }
-
+            const uint32_t xp = (supplies && kc < K) ? 1u : 0u;
+            const __half* xptr = xsrc + min(kc, K - 64);
+            auto load_x = [&](int q, uint32_t (&x)[8]) {
+                ld_x_pred(xptr + 16 * q, xp, x[0], x[1], x[2], x[3]);
+                ld_x_pred(xptr + 16 * q + 8, xp, x[4], x[5], x[6], x[7]);
+            };
+            load_x(0, xr[0]);
 #pragma unroll
             for (int q = 0; q < 4; q++) {  // scale block q of every chunk
+                if (q < 3) load_x(q + 1, xr[(q + 1) & 1]);
+                const uint32_t(&x)[8] = xr[q & 1];
                 float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int h = 0; h < 2; h++) {
                     uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
                     e2m1x8_to_half2x4(cur.wa[2 * q + h], a0, a1, a2, a3);
                     e2m1x8_to_half2x4(cur.wb[2 * q + h], b0, b1, b2, b3);
-                    const int xi = 8 * q + 4 * h;
-                    mma_f16_16816(c, a0, b0, a1, b1, xr[xi + 0], xr[xi + 1]);
-                    mma_f16_16816(c, a2, b2, a3, b3, xr[xi + 2], xr[xi + 3]);
+                    mma_f16_16816(c, a0, b0, a1, b1, x[4 * h + 0], x[4 * h + 1]);
+                    mma_f16_16816(c, a2, b2, a3, b3, x[4 * h + 2], x[4 * h + 3]);
                 }
                 acc_a = fmaf(c[0], scale_byte(cur.sa.x, q), acc_a);
                 acc_a = fmaf(c[1], scale_byte(cur.sa.y, q), acc_a);
@@ -158,6 +207,187 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         }
         __syncthreads();
     }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Same arithmetic, but the weight and scale bytes travel global -> shared with asynchronous
+// copies (cp.async) into a per-thread ring of STAGES slots, so the number of bytes in flight per
+// SM is set by shared memory (tens of KB per CTA) instead of by registers, and the prefetch runs
+// across tile boundaries.  Every thread copies and later reads only its own slots, so the only
+// synchronisation is cp.async.wait_group; slot addresses are (slot * THREADS + tid) * 16 and are
+// therefore bank-conflict free.  A copy whose source lies past the end of a row is issued with a
+// source size of 0, which zero-fills the slot.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc, uint32_t src_bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gsrc, uint32_t src_bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(gsrc),
+                 "r"(src_bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+template <int WARPS, int NACT, int STAGES>
+__global__ void __launch_bounds__(WARPS * 32)
+gemv_mma_async_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                      const __half* __restrict__ act0, const __half* __restrict__ act1,
+                      __half* __restrict__ out, int M, int K) {
+    constexpr int T = WARPS * 32;
+    extern __shared__ __align__(16) uint8_t ring[];
+    uint4* wbuf = reinterpret_cast<uint4*>(ring);                          // [STAGES][4][T]
+    uint2* sbuf = reinterpret_cast<uint2*>(ring + (size_t)STAGES * 4 * T * 16);  // [STAGES][2][T]
+    __shared__ float red[WARPS][16][2];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int nsteps = (K + 255) >> 8;
+    const int ntiles = (M + 15) >> 4;
+    const size_t prow = (size_t)(K >> 1), srow = (size_t)(K >> 4);
+    const bool supplies = ((g & 3) == t) && (g < 4 || NACT == 2);
+    const __half* xsrc = (g < 4 || NACT == 1) ? act0 : act1;
+
+    pdl_launch_dependents();
+    if (blockIdx.x < ntiles) {
+        const int r0 = blockIdx.x * 16;
+        const int nrows = min(16, M - r0);
+        const uint8_t* pslab = packed + (size_t)r0 * prow;
+        const size_t pbytes = (size_t)nrows * prow;
+        const uint32_t PF_CHUNK = 8192;
+        for (size_t off = (size_t)tid * PF_CHUNK; off < pbytes; off += (size_t)T * PF_CHUNK) {
+            const size_t n = pbytes - off;
+            prefetch_l2_bulk(pslab + off, (uint32_t)(n < PF_CHUNK ? n : PF_CHUNK));
+        }
+        if (tid == T - 1) {
+            const size_t sbytes = ((size_t)nrows * srow) & ~(size_t)15;
+            if (sbytes) prefetch_l2_bulk(scales + (size_t)r0 * srow, (uint32_t)sbytes);
+        }
+    }
+    pdl_wait();
+
+    // per-warp work sequence: for each of this CTA's tiles, nsw steps (step = warp + k * WARPS;
+    // steps past the end of the row are issued as zero fills so every warp runs the same count)
+    const int nsw = (nsteps + WARPS - 1) / WARPS;
+    const int my_tiles = (blockIdx.x < ntiles) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+    const int total = my_tiles * nsw;
+
+    // issue the copies of sequence element (tile index j, step index k) into ring slot `slot`
+    auto issue = [&](int j, int k, int slot) {
+        const int tile = blockIdx.x + j * gridDim.x;
+        const int s = warp + k * WARPS;
+        const int ra = min(tile * 16 + g, M - 1);
+        const int rb = min(tile * 16 + g + 8, M - 1);
+        const int kc = s * 256 + t * 64;            // first weight of this lane's chunk
+        const bool wv = kc < K;
+        const size_t poff = (size_t)(wv ? kc : 0) >> 1;
+        const uint8_t* pa = packed + (size_t)ra * prow + poff;
+        const uint8_t* pb = packed + (size_t)rb * prow + poff;
+        const uint32_t wn = wv ? 16u : 0u;
+        cp_async_16(&wbuf[(slot * 4 + 0) * T + tid], pa, wn);
+        cp_async_16(&wbuf[(slot * 4 + 1) * T + tid], pa + 16, wn);
+        cp_async_16(&wbuf[(slot * 4 + 2) * T + tid], pb, wn);
+        cp_async_16(&wbuf[(slot * 4 + 3) * T + tid], pb + 16, wn);
+        const int kg = s * 256 + (t & 1) * 128;     // first weight of this lane's scale group
+        const bool sv = kg < K;
+        const size_t soff = (size_t)(sv ? kg : 0) >> 4;
+        cp_async_8(&sbuf[(slot * 2 + 0) * T + tid], scales + (size_t)ra * srow + soff, sv ? 8u : 0u);
+        cp_async_8(&sbuf[(slot * 2 + 1) * T + tid], scales + (size_t)rb * srow + soff, sv ? 8u : 0u);
+    };
+
+    // prologue: STAGES - 1 elements in flight
+    int ij = 0, ik = 0;  // (tile index, step index) of the next element to issue
+#pragma unroll
+    for (int p = 0; p < STAGES - 1; p++) {
+        if (ij < my_tiles) issue(ij, ik, p);
+        cp_async_commit();
+        if (++ik == nsw) { ik = 0; ++ij; }
+    }
+
+    uint32_t xr[2][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { xr[0][i] = 0u; xr[1][i] = 0u; }
+
+    float acc_a = 0.0f, acc_b = 0.0f;
+    int cj = 0, ck = 0;  // element being consumed
+    for (int e = 0; e < total; e++) {
+        const int slot = e % STAGES;
+        // keep the ring full: the slot freed by element e-1 receives element e + STAGES - 1
+        if (ij < my_tiles) issue(ij, ik, (e + STAGES - 1) % STAGES);
+        cp_async_commit();
+        if (++ik == nsw) { ik = 0; ++ij; }
+        cp_async_wait<STAGES - 1>();  // element e has landed (this thread's own copies)
+
+        uint32_t wa[8], wb[8];
+        {
+            const uint4 v0 = wbuf[(slot * 4 + 0) * T + tid], v1 = wbuf[(slot * 4 + 1) * T + tid];
+            const uint4 v2 = wbuf[(slot * 4 + 2) * T + tid], v3 = wbuf[(slot * 4 + 3) * T + tid];
+            wa[0] = v0.x; wa[1] = v0.y; wa[2] = v0.z; wa[3] = v0.w;
+            wa[4] = v1.x; wa[5] = v1.y; wa[6] = v1.z; wa[7] = v1.w;
+            wb[0] = v2.x; wb[1] = v2.y; wb[2] = v2.z; wb[3] = v2.w;
+            wb[4] = v3.x; wb[5] = v3.y; wb[6] = v3.z; wb[7] = v3.w;
+        }
+        const uint2 sca = sbuf[(slot * 2 + 0) * T + tid], scb = sbuf[(slot * 2 + 1) * T + tid];
+
+        const int s = warp + ck * WARPS;
+        const int kc = s * 256 + t * 64;
+        const uint32_t xp = (supplies && kc < K) ? 1u : 0u;
+        const __half* xptr = xsrc + min(kc, K - 64);
+        auto load_x = [&](int q, uint32_t (&x)[8]) {
+            ld_x_pred(xptr + 16 * q, xp, x[0], x[1], x[2], x[3]);
+            ld_x_pred(xptr + 16 * q + 8, xp, x[4], x[5], x[6], x[7]);
+        };
+        load_x(0, xr[0]);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            if (q < 3) load_x(q + 1, xr[(q + 1) & 1]);
+            const uint32_t(&x)[8] = xr[q & 1];
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                e2m1x8_to_half2x4(wa[2 * q + h], a0, a1, a2, a3);
+                e2m1x8_to_half2x4(wb[2 * q + h], b0, b1, b2, b3);
+                mma_f16_16816(c, a0, b0, a1, b1, x[4 * h + 0], x[4 * h + 1]);
+                mma_f16_16816(c, a2, b2, a3, b3, x[4 * h + 2], x[4 * h + 3]);
+            }
+            acc_a = fmaf(c[0], scale_byte(sca.x, q), acc_a);
+            acc_a = fmaf(c[1], scale_byte(sca.y, q), acc_a);
+            acc_b = fmaf(c[2], scale_byte(scb.x, q), acc_b);
+            acc_b = fmaf(c[3], scale_byte(scb.y, q), acc_b);
+        }
+
+        if (++ck == nsw) {  // tile finished: combine the warps' partial sums
+            const int tile = blockIdx.x + cj * gridDim.x;
+            acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
+            acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
+            if ((t & 1) == 0) {
+                red[warp][g][t >> 1] = acc_a;
+                red[warp][g + 8][t >> 1] = acc_b;
+            }
+            __syncthreads();
+            if (tid < 16 * NACT) {
+                const int r = tid & 15, a = tid >> 4;
+                float v = 0.0f;
+#pragma unroll
+                for (int w = 0; w < WARPS; w++) v += red[w][r][a];
+                const int row = tile * 16 + r;
+                if (row < M) out[(size_t)a * M + row] = __float2half(v);
+            }
+            __syncthreads();
+            acc_a = 0.0f;
+            acc_b = 0.0f;
+            ck = 0;
+            ++cj;
+        }
+    }
+    cp_async_wait<0>();
 }
 
 // Generic path for shapes or pointers the tensor-core kernel does not take (K % 128 != 0, or
@@ -214,6 +444,8 @@ struct GemvConfig {
     int warps = 0;         // 0 = choose from the shape
     int ctas_per_sm = 0;   // 0 = choose from the occupancy calculator
     int force_generic = 0;
+    int no_pdl = 0;        // 1 = plain stream-ordered launches (no programmatic dependent launch)
+    int async_ring = 0;    // 0 = register-prefetch kernel; 3, 4 or 6 = cp.async ring with that many slots
 };
 static GemvConfig g_cfg;
 static int g_num_sms = 0;
@@ -244,10 +476,54 @@ static cudaError_t launch_mma(const void* packed, const void* scales, const void
     const int ntiles = (M + 15) / 16;
     int grid = num_sms() * per_sm;
     if (grid > ntiles) grid = ntiles;
-    gemv_mma_kernel<WARPS, NACT><<<grid, WARPS * 32, 0, st>>>(
-        (const uint8_t*)packed, (const uint8_t*)scales, (const __half*)a0, (const __half*)a1,
-        (__half*)out, M, K);
-    return cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_cfg.no_pdl ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<WARPS, NACT>, (const uint8_t*)packed,
+                              (const uint8_t*)scales, (const __half*)a0, (const __half*)a1,
+                              (__half*)out, M, K);
+}
+
+template <int WARPS, int NACT, int STAGES>
+static cudaError_t launch_mma_async(const void* packed, const void* scales, const void* a0,
+                                    const void* a1, void* out, int M, int K, cudaStream_t st) {
+    constexpr int T = WARPS * 32;
+    constexpr int SMEM = STAGES * T * (64 + 16);
+    static int occ = 0;
+    if (occ == 0) {
+        if (cudaFuncSetAttribute(gemv_mma_async_kernel<WARPS, NACT, STAGES>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
+            return cudaErrorInvalidValue;
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &n, gemv_mma_async_kernel<WARPS, NACT, STAGES>, T, SMEM) != cudaSuccess || n <= 0)
+            n = 2;
+        occ = n;
+    }
+    const int per_sm = g_cfg.ctas_per_sm > 0 ? g_cfg.ctas_per_sm : occ;
+    const int ntiles = (M + 15) / 16;
+    int grid = num_sms() * per_sm;
+    if (grid > ntiles) grid = ntiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(T);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_cfg.no_pdl ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, gemv_mma_async_kernel<WARPS, NACT, STAGES>,
+                              (const uint8_t*)packed, (const uint8_t*)scales, (const __half*)a0,
+                              (const __half*)a1, (__half*)out, M, K);
 }
 
 static inline bool aligned(const void* p, uintptr_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
@@ -267,8 +543,25 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
                       aligned(scales, 8);
     if (fast) {
         int warps = g_cfg.warps;
-        if (warps == 0) warps = (K >= 8192) ? 8 : 4;
-        if (nact == 1) {
+        // few row tiles or a long K: spread each tile's K range over 8 warps; many tiles: 4 warps
+        // per CTA and more resident CTAs (measured on B200 over the 27B layer shapes)
+        if (warps == 0) warps = (K >= 8192 || (M + 15) / 16 <= 3 * num_sms()) ? 8 : 4;
+        if (g_cfg.async_ring) {
+            const int st_n = g_cfg.async_ring;
+            if (nact == 1) {
+                if (warps == 8)
+                    e = (st_n == 3) ? launch_mma_async<8, 1, 3>(packed, scales, a0, a1, out, M, K, st)
+                      : (st_n == 6) ? launch_mma_async<8, 1, 6>(packed, scales, a0, a1, out, M, K, st)
+                                    : launch_mma_async<8, 1, 4>(packed, scales, a0, a1, out, M, K, st);
+                else
+                    e = (st_n == 3) ? launch_mma_async<4, 1, 3>(packed, scales, a0, a1, out, M, K, st)
+                      : (st_n == 6) ? launch_mma_async<4, 1, 6>(packed, scales, a0, a1, out, M, K, st)
+                                    : launch_mma_async<4, 1, 4>(packed, scales, a0, a1, out, M, K, st);
+            } else {
+                e = (warps == 8) ? launch_mma_async<8, 2, 4>(packed, scales, a0, a1, out, M, K, st)
+                                 : launch_mma_async<4, 2, 4>(packed, scales, a0, a1, out, M, K, st);
+            }
+        } else if (nact == 1) {
             e = (warps == 8) ? launch_mma<8, 1>(packed, scales, a0, a1, out, M, K, st)
               : (warps == 2) ? launch_mma<2, 1>(packed, scales, a0, a1, out, M, K, st)
                              : launch_mma<4, 1>(packed, scales, a0, a1, out, M, K, st);
@@ -328,14 +621,21 @@ int launch_nvfp4_gemv2(const void* weight_packed, const void* weight_scales, con
 }
 
 // Tuning hook (no counterpart in the reference): warps per CTA (0 = auto, 2/4/8), resident CTAs
-// per SM used to size the grid (0 = occupancy calculator), force_generic != 0 routes every call
-// to the non-tensor-core kernel.  Returns 0, or -2 for an unsupported value.
-int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int force_generic) {
+// per SM used to size the grid (0 = occupancy calculator); flags bit 0 routes every call to the
+// non-tensor-core kernel, bit 1 turns programmatic dependent launch off.  Returns 0, or -2 for
+// an unsupported value.
+int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int flags) {
     if (!(warps == 0 || warps == 2 || warps == 4 || warps == 8) || ctas_per_sm < 0)
         return NVFP4_ERR_SHAPE;
     nvfp4::g_cfg.warps = warps;
     nvfp4::g_cfg.ctas_per_sm = ctas_per_sm;
-    nvfp4::g_cfg.force_generic = force_generic;
+    nvfp4::g_cfg.force_generic = flags & 1;
+    nvfp4::g_cfg.no_pdl = (flags >> 1) & 1;
+    {
+        const int ring = (flags >> 4) & 0xF;  // bits 4..7: cp.async ring slots (0, 3, 4 or 6)
+        if (!(ring == 0 || ring == 3 || ring == 4 || ring == 6)) return NVFP4_ERR_SHAPE;
+        nvfp4::g_cfg.async_ring = ring;
+    }
     return NVFP4_OK;
 }
 

@@ -80,7 +80,8 @@ def test_both_kernels_agree_and_config_hook(lib):
     a = oc.synthetic_act(1024, seed=22)
     outs = []
     try:
-        for cfg in ((0, 0, 0), (2, 0, 0), (4, 1, 0), (8, 0, 0), (0, 0, 1)):
+        for cfg in ((0, 0, 0), (2, 0, 0), (4, 1, 0), (8, 0, 0), (0, 0, 1), (0, 0, 2),
+                    (4, 0, 0x40), (8, 0, 0x30), (4, 2, 0x60), (8, 1, 0x42)):
             assert lib.nvfp4_b200_gemv_config(*cfg) == 0
             rc, y = gemv(lib, p, s, a)
             assert rc == 0
@@ -93,6 +94,28 @@ def test_both_kernels_agree_and_config_hook(lib):
         assert oc.rel_error_floored(y, outs[0].astype(np.float64)).max() <= 1e-3
 
 
+@pytest.mark.parametrize("flags", [0x40, 0x30, 0x60])
+@pytest.mark.parametrize("M,K", [(1, 128), (100, 768), (257, 6144), (33, 17408), (1024, 5120)])
+def test_async_ring_kernel(lib, M, K, flags):
+    # the cp.async ring variant of the tensor-core kernel, incl. ragged rows and K % 256 != 0
+    w = oc.synthetic_weight(M, K, seed=M * 7 + K)
+    p, s = oc.encode(w)
+    a = oc.synthetic_act(K, seed=K + 1)
+    try:
+        for warps in (4, 8):
+            assert lib.nvfp4_b200_gemv_config(warps, 0, flags) == 0
+            rc, y = gemv(lib, p, s, a)
+            assert rc == 0
+            check(y, p, s, a)
+            a2 = oc.synthetic_act(K, seed=K + 2)
+            rc, y2 = gemv2(lib, p, s, a, a2)
+            assert rc == 0
+            check(y2[0], p, s, a)
+            check(y2[1], p, s, a2)
+    finally:
+        lib.nvfp4_b200_gemv_config(0, 0, 0)
+
+
 def test_mixed_magnitude_scales(lib):
     # blocks whose scale bytes span a wide range, including all-zero blocks (byte 127)
     rng = np.random.default_rng(5)
@@ -100,7 +123,7 @@ def test_mixed_magnitude_scales(lib):
     w[3, 32:48] = 0
     w[5] = 0
     p, s = oc.encode(w)
-    assert s.min() < 110 and s.max() > 130
+    assert s.min() < 116 and s.max() > 130
     a = oc.synthetic_act(512, seed=9)
     rc, y = gemv(lib, p, s, a)
     assert rc == 0
