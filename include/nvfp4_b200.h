@@ -105,6 +105,16 @@ int launch_dn_fused(const void* mixed, const void* z, const void* b, const void*
                     const void* norm_w, void* state, void* scratch, void* out, float rms_eps,
                     void* stream);
 
+/* The same step on a tensor-parallel shard holding n_kheads key heads and n_vheads value heads
+ * (n_vheads a multiple of n_kheads; the full model is 16 / 48): mixed is
+ * [q n_k*128 | k n_k*128 | v n_v*128], scratch holds (2 n_k + n_v)*128 floats, the other buffers
+ * shrink the same way.  -1 also for invalid head counts.  No counterpart in the reference (it
+ * has no multi-GPU path); the arithmetic is launch_dn_fused's. */
+int launch_dn_fused_heads(const void* mixed, const void* z, const void* b, const void* a,
+                          const void* conv_w, void* conv_state, const void* A_log,
+                          const void* dt_bias, const void* norm_w, void* state, void* scratch,
+                          void* out, int n_kheads, int n_vheads, float rms_eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -224,7 +224,8 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys
 }
 
 // ---------------------------------------------------------------------------------------------
-// Gated DeltaNet decode step (16 key heads, 48 value heads, head dim 128, conv kernel 4).
+// Gated DeltaNet decode step (head dim 128, conv kernel 4; 16 key / 48 value heads in the full
+// model, fewer on a tensor-parallel shard).
 // Kernel 1: causal conv1d update + silu per channel -> scratch (fp32 holding fp16-rounded values).
 // Kernel 2: one CTA per value head, 16 warps; a warp owns 8 state rows (one row = 128 fp32 =
 //           one float4 per lane, so every state access is a coalesced 512-byte row).
@@ -239,9 +240,9 @@ __device__ __forceinline__ float softplus_f(float x) { return (x > 20.0f) ? x : 
 
 __global__ void __launch_bounds__(256)
 dn_conv_kernel(const __half* __restrict__ mixed, const __half* __restrict__ conv_w,
-               __half* __restrict__ conv_state, float* __restrict__ scratch) {
+               __half* __restrict__ conv_state, float* __restrict__ scratch, int conv_dim) {
     const int c = blockIdx.x * 256 + threadIdx.x;
-    if (c >= DN_CONV_DIM) return;
+    if (c >= conv_dim) return;
     // state and weights of a channel are 4 consecutive halves: one 8-byte load each
     const uint2 sv = *reinterpret_cast<const uint2*>(conv_state + (size_t)c * 4);
     const uint2 wv = *reinterpret_cast<const uint2*>(conv_w + (size_t)c * 4);
@@ -270,10 +271,10 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
               const __half* __restrict__ a_in, const __half* __restrict__ A_log,
               const __half* __restrict__ dt_bias, const __half* __restrict__ norm_w,
               const float* __restrict__ scratch, float* __restrict__ state,
-              __half* __restrict__ out, float rms_eps) {
+              __half* __restrict__ out, float rms_eps, int key_dim, int rep) {
     __shared__ float s_o[DN_DK];
     __shared__ float s_red[8];
-    const int h = blockIdx.x, kh = h / 3;
+    const int h = blockIdx.x, kh = h / rep;  // value head h reads key head h / rep
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
 
     const float beta = round_f16(1.0f / (1.0f + expf(-__half2float(b_in[h]))));
@@ -283,7 +284,7 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
 
     // every warp normalises q and k itself: lane owns dims 4*lane .. 4*lane+3
     float4 qv = *reinterpret_cast<const float4*>(scratch + kh * DN_DK + lane * 4);
-    float4 kv = *reinterpret_cast<const float4*>(scratch + DN_KEY_DIM + kh * DN_DK + lane * 4);
+    float4 kv = *reinterpret_cast<const float4*>(scratch + key_dim + kh * DN_DK + lane * 4);
     const float qss = warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
     const float kss = warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
     const float inv_q = rsqrtf(qss + 1e-6f) * 0.08838834764831845f;
@@ -305,7 +306,7 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
         kvp = fmaf(S[r].z, kv.z, kvp);
         kvp = fmaf(S[r].w, kv.w, kvp);
         kvp = warp_sum(kvp);
-        const float v_j = scratch[DN_KEY_DIM * 2 + h * DN_DK + j];
+        const float v_j = scratch[key_dim * 2 + h * DN_DK + j];
         const float delta = (v_j - kvp) * beta;
         S[r].x = fmaf(kv.x, delta, S[r].x);
         S[r].y = fmaf(kv.y, delta, S[r].y);
@@ -399,31 +400,54 @@ int launch_attn_decode(const void* q, const void* keys, const void* values, cons
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 
-int launch_dn_fused(const void* mixed, const void* z_in, const void* b_in, const void* a_in,
-                    const void* conv_w, void* conv_state, const void* A_log, const void* dt_bias,
-                    const void* norm_w, void* state, void* scratch, void* out, float rms_eps,
-                    void* stream) {
+static int dn_fused_launch(const void* mixed, const void* z_in, const void* b_in, const void* a_in,
+                           const void* conv_w, void* conv_state, const void* A_log,
+                           const void* dt_bias, const void* norm_w, void* state, void* scratch,
+                           void* out, int n_kheads, int n_vheads, float rms_eps, void* stream) {
     if (!mixed || !z_in || !b_in || !a_in || !conv_w || !conv_state || !A_log || !dt_bias ||
         !norm_w || !state || !scratch || !out)
         return -1;
+    if (n_kheads <= 0 || n_vheads <= 0 || n_vheads % n_kheads != 0) return -1;
+    const int key_dim = n_kheads * DN_DK;
+    const int conv_dim = 2 * key_dim + n_vheads * DN_DK;
     cudaStream_t s = (cudaStream_t)stream;
-    nvfp4::dn_conv_kernel<<<(DN_CONV_DIM + 255) / 256, 256, 0, s>>>(
-        (const __half*)mixed, (const __half*)conv_w, (__half*)conv_state, (float*)scratch);
+    nvfp4::dn_conv_kernel<<<(conv_dim + 255) / 256, 256, 0, s>>>(
+        (const __half*)mixed, (const __half*)conv_w, (__half*)conv_state, (float*)scratch,
+        conv_dim);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) {
         fprintf(stderr, "dn_conv launch: %s\n", cudaGetErrorString(e));
         return -1;
     }
-    nvfp4::dn_rec_kernel<<<DN_NVH, DN_REC_THREADS, 0, s>>>(
+    nvfp4::dn_rec_kernel<<<n_vheads, DN_REC_THREADS, 0, s>>>(
         (const __half*)z_in, (const __half*)b_in, (const __half*)a_in, (const __half*)A_log,
         (const __half*)dt_bias, (const __half*)norm_w, (const float*)scratch, (float*)state,
-        (__half*)out, rms_eps);
+        (__half*)out, rms_eps, key_dim, n_vheads / n_kheads);
     e = cudaGetLastError();
     if (e != cudaSuccess) {
         fprintf(stderr, "dn_rec launch: %s\n", cudaGetErrorString(e));
         return -1;
     }
     return 0;
+}
+
+int launch_dn_fused(const void* mixed, const void* z_in, const void* b_in, const void* a_in,
+                    const void* conv_w, void* conv_state, const void* A_log, const void* dt_bias,
+                    const void* norm_w, void* state, void* scratch, void* out, float rms_eps,
+                    void* stream) {
+    return dn_fused_launch(mixed, z_in, b_in, a_in, conv_w, conv_state, A_log, dt_bias, norm_w,
+                           state, scratch, out, DN_KEY_DIM / DN_DK, DN_NVH, rms_eps, stream);
+}
+
+// Same step for a tensor-parallel shard that holds n_kheads key heads and n_vheads value heads
+// (n_vheads a multiple of n_kheads): mixed is [q n_k*128 | k n_k*128 | v n_v*128], every other
+// buffer shrinks accordingly, scratch holds (2 n_k + n_v) * 128 floats.
+int launch_dn_fused_heads(const void* mixed, const void* z_in, const void* b_in, const void* a_in,
+                          const void* conv_w, void* conv_state, const void* A_log,
+                          const void* dt_bias, const void* norm_w, void* state, void* scratch,
+                          void* out, int n_kheads, int n_vheads, float rms_eps, void* stream) {
+    return dn_fused_launch(mixed, z_in, b_in, a_in, conv_w, conv_state, A_log, dt_bias, norm_w,
+                           state, scratch, out, n_kheads, n_vheads, rms_eps, stream);
 }
 
 }  // extern "C"

@@ -172,3 +172,41 @@ def test_dn_fused_two_steps(lib, seed):
         assert_close_f16(out.cpu().numpy(), want_out, min_exact=0.97, max_steps=2)
         # carry the GPU's own state forward so one-step differences do not accumulate in the test
         state = got_state
+
+
+@pytest.mark.parametrize("nk,nv", [(16, 48), (8, 24), (2, 6), (1, 3), (4, 4)])
+def test_dn_fused_heads_shard(lib, nk, nv):
+    # a tensor-parallel shard: fewer heads, same arithmetic
+    rng = np.random.default_rng(nk * 100 + nv)
+    f16 = np.float16
+    C = (2 * nk + nv) * 128
+    x = dict(
+        mixed=rng.standard_normal(C).astype(f16), z=rng.standard_normal(nv * 128).astype(f16),
+        b=rng.standard_normal(nv).astype(f16), a=rng.standard_normal(nv).astype(f16),
+        conv_w=(rng.standard_normal((C, 4)) * 0.5).astype(f16),
+        conv_state=rng.standard_normal((C, 4)).astype(f16),
+        A_log=np.log(rng.uniform(0.1, 16, nv)).astype(f16), dt_bias=np.ones(nv, dtype=f16),
+        norm_w=(1 + 0.1 * rng.standard_normal(128)).astype(f16),
+        state=(rng.standard_normal((nv, 128, 128)) * 0.1).astype(np.float32))
+    scr_want, conv_want = fo.dn_conv(x["mixed"], x["conv_w"], x["conv_state"])
+    out_want, state_want = fo.dn_rec(scr_want, x["z"], x["b"], x["a"], x["A_log"], x["dt_bias"],
+                                     x["norm_w"], x["state"], 1e-6, n_vheads=nv, n_kheads=nk)
+    d = {k: dev(v) for k, v in x.items()}
+    scratch = torch.zeros(C, dtype=torch.float32, device="cuda")
+    out = torch.zeros(nv * 128, dtype=torch.float16, device="cuda")
+    rc = lib.launch_dn_fused_heads(ptr(d["mixed"]), ptr(d["z"]), ptr(d["b"]), ptr(d["a"]),
+                                   ptr(d["conv_w"]), ptr(d["conv_state"]), ptr(d["A_log"]),
+                                   ptr(d["dt_bias"]), ptr(d["norm_w"]), ptr(d["state"]),
+                                   ptr(scratch), ptr(out), nk, nv, 1e-6, stream())
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.array_equal(d["conv_state"].cpu().numpy().view(np.uint16), conv_want.view(np.uint16))
+    assert np.abs(d["state"].cpu().numpy() - state_want).max() <= 1e-5 * np.abs(state_want).max()
+    assert_close_f16(out.cpu().numpy(), out_want, min_exact=0.97, max_steps=2)
+
+
+def test_dn_fused_heads_rejects_bad_counts(lib):
+    one = ctypes.c_void_p(0x1000)
+    args = [one] * 12
+    assert lib.launch_dn_fused_heads(*args, 0, 3, 1e-6, None) == -1
+    assert lib.launch_dn_fused_heads(*args, 4, 6, 1e-6, None) == -1
