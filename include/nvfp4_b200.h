@@ -115,6 +115,22 @@ int launch_dn_fused_heads(const void* mixed, const void* z, const void* b, const
                           const void* dt_bias, const void* norm_w, void* state, void* scratch,
                           void* out, int n_kheads, int n_vheads, float rms_eps, void* stream);
 
+/* The DeltaNet step without a caller-provided workspace.  It has no counterpart in the reference,
+ * whose caller always allocates the scratch tensor itself.  It exists for callers that cannot
+ * allocate device memory at the point of the call: code that runs after all device memory has
+ * been given to another allocator, a plug-in that only receives its input and output buffers, or
+ * code entered during stream capture, where cudaMalloc is not allowed.  The workspace is a 40 KB
+ * array inside the library (every GPU that loads the library holds it until exit), so the shard
+ * may have at most 10240 conv channels, (2 n_kheads + n_vheads) * 128 <= 10240 — the full model
+ * exactly; beyond that the call prints a message and returns -2.  The array's device address is
+ * looked up on the first call on each device: make that first call outside stream capture.
+ * Calls on one device share the workspace and must not overlap on the GPU.  Arguments and results
+ * otherwise as launch_dn_fused_heads, minus `scratch`. */
+int launch_dn_fused_noalloc(const void* mixed, const void* z, const void* b, const void* a,
+                            const void* conv_w, void* conv_state, const void* A_log,
+                            const void* dt_bias, const void* norm_w, void* state, void* out,
+                            int n_kheads, int n_vheads, float rms_eps, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

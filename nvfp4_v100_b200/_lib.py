@@ -41,6 +41,7 @@ SIGNATURES = {
     "launch_attn_decode": ([_vp] * 6 + [_i, _f, _vp], _i),
     "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
     "launch_dn_fused_heads": ([_vp] * 12 + [_i, _i, _f, _vp], _i),
+    "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),
 }
 
 _LIB = None

@@ -450,4 +450,66 @@ int launch_dn_fused_heads(const void* mixed, const void* z_in, const void* b_in,
                            state, scratch, out, n_kheads, n_vheads, rms_eps, stream);
 }
 
+// ---------------------------------------------------------------------------------------------
+// DeltaNet step for callers that cannot allocate device memory.
+//
+// The step needs a small workspace between its two kernels (the conv+silu result, one float per
+// conv channel).  launch_dn_fused makes the caller provide it.  Some callers cannot: a host loop
+// that has already handed every byte of device memory to another allocator, a plug-in that is
+// only given its input and output buffers, or code that is entered while the stream is being
+// captured (cudaMalloc synchronises the device and is not permitted there).  For them the
+// workspace lives in the library itself: a file-scope device array of
+// NVFP4_DN_NOALLOC_MAX_CHANNELS floats (40 KB), which every GPU that loads the library keeps
+// until the process exits.
+//
+// Host code may not hand the array's name to a kernel: in host code the name is only a handle
+// for the runtime, not a device address.  The address is obtained with cudaGetSymbolAddress,
+// once per device, with that device current, and cached.  That look-up happens on the first
+// call on each device, so make the first call on a device outside any stream capture.
+//
+// All calls on one device share the workspace.  Nothing in it has to start at zero (the first
+// kernel writes every element the second one reads), so it is never cleared; but two calls that
+// run on the GPU at the same time (different streams, or graph branches) would overwrite each
+// other's intermediate values: keep calls on one device ordered.
+// The function calls no cudaMalloc, cudaFree or any other allocating routine.
+// ---------------------------------------------------------------------------------------------
+#define NVFP4_DN_NOALLOC_MAX_CHANNELS 10240
+#define NVFP4_MAX_DEVICES 64
+
+static __device__ __align__(256) float g_dn_noalloc_scratch[NVFP4_DN_NOALLOC_MAX_CHANNELS];
+static float* g_dn_noalloc_addr[NVFP4_MAX_DEVICES] = {};
+
+int launch_dn_fused_noalloc(const void* mixed, const void* z_in, const void* b_in,
+                            const void* a_in, const void* conv_w, void* conv_state,
+                            const void* A_log, const void* dt_bias, const void* norm_w,
+                            void* state, void* out, int n_kheads, int n_vheads, float rms_eps,
+                            void* stream) {
+    if (n_kheads <= 0 || n_vheads <= 0 || n_vheads % n_kheads != 0) return -1;
+    const long long channels = (2LL * n_kheads + n_vheads) * DN_DK;
+    if (channels > NVFP4_DN_NOALLOC_MAX_CHANNELS) {
+        fprintf(stderr,
+                "launch_dn_fused_noalloc: %lld conv channels (%d key + %d value heads) exceed the "
+                "built-in workspace of %d; use launch_dn_fused_heads with your own scratch\n",
+                channels, n_kheads, n_vheads, NVFP4_DN_NOALLOC_MAX_CHANNELS);
+        return -2;
+    }
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NVFP4_MAX_DEVICES) {
+        fprintf(stderr, "launch_dn_fused_noalloc: no usable current device\n");
+        return -1;
+    }
+    float* scratch = g_dn_noalloc_addr[dev];
+    if (scratch == nullptr) {
+        const cudaError_t e = cudaGetSymbolAddress((void**)&scratch, g_dn_noalloc_scratch);
+        if (e != cudaSuccess || scratch == nullptr) {
+            fprintf(stderr, "launch_dn_fused_noalloc: cudaGetSymbolAddress: %s\n",
+                    cudaGetErrorString(e));
+            return -1;
+        }
+        g_dn_noalloc_addr[dev] = scratch;
+    }
+    return dn_fused_launch(mixed, z_in, b_in, a_in, conv_w, conv_state, A_log, dt_bias, norm_w,
+                           state, scratch, out, n_kheads, n_vheads, rms_eps, stream);
+}
+
 }  // extern "C"
