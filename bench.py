@@ -488,6 +488,81 @@ def run_per_shape(args):
     print(json.dumps(line), flush=True)
 
 
+def decode_step_bytes(cfg, context):
+    """Algorithmic HBM bytes of one decode step: every weight byte once, DeltaNet state read and
+    written, the KV prefix read, embedding row and logits."""
+    w = 0
+    for i in range(cfg.n_layers):
+        for M, K in cfg.layer_shapes(i).values():
+            w += gemv_bytes(M, K)
+    w += gemv_bytes(cfg.vocab, cfg.hidden)
+    n_dn = sum(0 if cfg.is_attn(i) else 1 for i in range(cfg.n_layers))
+    state = 2 * cfg.dn_vheads * 128 * 128 * 4 * n_dn
+    kv = (cfg.n_layers - n_dn) * cfg.hkv * context * 256 * 2 * 2
+    return w + state + kv
+
+
+def run_decode(args, quiet=False):
+    """27B-shape decode: 512-token prompt fed through the step graph, then 63 greedy tokens
+    (BASELINE config 3).  Random-init NVFP4 weights, random token ids."""
+    import torch
+
+    from nvfp4_v100_b200.engine import DecodeEngine, ModelConfig
+
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    cfg = ModelConfig(max_len=1024, vocab=args.vocab)
+    eng = DecodeEngine(cfg)
+    eng.load_random(seed=0)
+    prompt = np.random.default_rng(0).integers(0, cfg.vocab, args.prompt_len)
+    eng.reset(int(prompt[0]))
+    n_launch = eng.capture(n_warmup=1)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for t in range(1, len(prompt)):
+        eng.step()
+        eng.tok.fill_(int(prompt[t]))
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    n_gen = args.gen
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_gen):
+        eng.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    # end to end: read every token back on the host as the reference loop does (.item() per step)
+    snap_pos = int(eng.pos.item())
+    t0 = time.perf_counter()
+    toks = []
+    for _ in range(min(n_gen, cfg.max_len - snap_pos - 1)):
+        eng.step()
+        toks.append(int(eng.tok.item()))
+    e2e_s = time.perf_counter() - t0
+    peak, peak_kind = measured_peak()
+    step_bytes = decode_step_bytes(cfg, args.prompt_len + n_gen // 2)
+    res = {
+        "metric": "decode_tok_s", "value": n_gen / (ms * 1e-3), "unit": "tok/s",
+        "ms_per_step": ms / n_gen, "n_gpus": 1, "prompt_len": int(args.prompt_len), "gen": n_gen,
+        "kernel_launches_per_step": n_launch,
+        "prefill_by_decode_tok_s": (len(prompt) - 1) / prefill_s,
+        "e2e": {"value": len(toks) / e2e_s, "unit": "tok/s", "d2h_bytes_per_step": 8,
+                "h2d_bytes_per_step": 0},
+        "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
+                     "achieved": step_bytes / (ms / n_gen * 1e-3) / 1e9, "peak": peak,
+                     "unit": "GB/s", "frac": step_bytes / (ms / n_gen * 1e-3) / 1e9 / peak,
+                     "peak_kind": peak_kind},
+        "config": {"workload": "decode_27b_shape", "layers": cfg.n_layers, "hidden": cfg.hidden,
+                   "vocab": cfg.vocab, "launch": "cuda_graph", "weights": "random NVFP4 bytes"},
+        "finite_logits": bool(torch.isfinite(eng.logits.float()).all().item()),
+    }
+    if not quiet:
+        print(json.dumps(res), flush=True)
+    del eng
+    torch.cuda.empty_cache()
+    return res
+
+
 # DRAM bytes (read + write) per average GEMV launch of the mix, from the ncu capture summarised
 # under profiles/; None until a capture exists.
 TRAFFIC_PER_LAUNCH = None
@@ -504,12 +579,19 @@ def main():
                     help="time every 27B layer shape alone (cold L2) instead of the step mix")
     ap.add_argument("--only", default="", help="with --per-shape: a single MxK shape")
     ap.add_argument("--reps", type=int, default=200, help="with --per-shape: launches per timing")
+    ap.add_argument("--decode", action="store_true",
+                    help="27B-shape decode tok/s (512-token prompt, 63 tokens) instead of the mix")
+    ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--gen", type=int, default=63)
+    ap.add_argument("--vocab", type=int, default=VOCAB)
     ap.add_argument("--eager", action="store_true",
                     help="with --per-shape: launch from the host instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.per_shape:
+    if args.decode:
+        run_decode(args)
+    elif args.per_shape:
         run_per_shape(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -94,6 +94,13 @@ int launch_silu_mul(const void* g, const void* u, void* out, int n, void* stream
 int launch_attn_decode(const void* q, const void* keys, const void* values, const void* cum_len,
                        const void* gate, void* out, int max_len, float scale, void* stream);
 
+/* launch_attn_decode for hq query heads and hkv KV heads (hq a multiple of hkv, head dim 256): a
+ * tensor-parallel shard or a smaller model.  No counterpart in the reference (single GPU, fixed
+ * 24/4 heads); the kernel is launch_attn_decode's.  -2 also for invalid head counts. */
+int launch_attn_decode_heads(const void* q, const void* keys, const void* values,
+                             const void* cum_len, const void* gate, void* out, int max_len, int hq,
+                             int hkv, float scale, void* stream);
+
 /* One Gated-DeltaNet decode step (16 key heads, 48 value heads, dim 128, conv kernel 4).
  * mixed fp16 [10240] = [q 2048 | k 2048 | v 6144]; z fp16 [6144]; b, a fp16 [48];
  * conv_w fp16 [10240*4]; conv_state fp16 [10240*4] in/out (layout c*4 + t);
@@ -114,6 +121,43 @@ int launch_dn_fused_heads(const void* mixed, const void* z, const void* b, const
                           const void* conv_w, void* conv_state, const void* A_log,
                           const void* dt_bias, const void* norm_w, void* state, void* scratch,
                           void* out, int n_kheads, int n_vheads, float rms_eps, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Decode-engine entry points.  None has a C counterpart in the reference: there the same work is
+ * done by PyTorch operators inside the captured model forward (pipeline/_qwen38_infer.py:679-685)
+ * and by the monkey-patched module forwards (:456-479, :612-644, experiments/_qwen38_p9_fuse.py).
+ * They exist so that a whole decode step is a fixed list of launches with no host work between.
+ * ------------------------------------------------------------------------------------------- */
+
+/* GEMV with fused neighbours.  prologue 1: the activation is first RMS-normalised with norm_w1
+ * (fp32 [K], 1 + weight) and eps, arithmetic of launch_rmsnorm.  epilogue 1: output =
+ * f16(residual + f16(y)), residual fp16 [M].  epilogue 2: weight rows are gate and up rows
+ * interleaved in groups of 8 (rows 16j..16j+7 = gate rows 8j..8j+7, rows 16j+8..16j+15 = up rows
+ * 8j..8j+7, M = 2 * outputs, M % 16 == 0) and output[8j+r] = silu(gate)*up with the arithmetic of
+ * launch_silu_mul.  Requires K % 128 == 0, weights 32-byte, scales 8-byte, activation 16-byte
+ * aligned.  0; -2 bad arguments; -1 launch error. */
+int launch_nvfp4_gemv_fused(const void* weight_packed, const void* weight_scales,
+                            const void* activation, void* output, int M, int K, int prologue,
+                            const void* norm_w1, float eps, int epilogue, const void* residual,
+                            void* stream);
+
+/* out[hidden] = table[*tok] — table fp16 [vocab, hidden], tok a device int64.  0 / -1. */
+int launch_embed_gather(const void* table, const void* tok, void* out, int hidden, long long vocab,
+                        void* stream);
+
+/* Between the q/k/v projection and launch_attn_decode: per-head RMSNorm of q and k (q_w1, k_w1
+ * fp32 [256]), RoPE at position *pos from cos/sin tables fp16 [max_len, 256], k and v written into
+ * the cache at *pos, the per-head gate halves of the q projection gathered into gate_out.
+ * qkv fp16 [hq*512 + 2*hkv*256] = [per head q256|gate256][k][v]; pos a device int64.  0 / -1. */
+int launch_attn_prep(const void* qkv, const void* q_w1, const void* k_w1, const void* cos_tab,
+                     const void* sin_tab, const void* pos, void* q_out, void* gate_out, void* keys,
+                     void* values, int hq, int hkv, int max_len, float eps, void* stream);
+
+/* *tok = argmax(logits fp16 [vocab]) (lowest index among equal maxima); appends it to history
+ * (device int64 [hist_cap], counter hist_count) and increments *pos and *len (device int64; any
+ * of pos, len, history, hist_count may be NULL).  0 / -1. */
+int launch_argmax_advance(const void* logits, int vocab, void* tok, void* pos, void* len,
+                          void* history, void* hist_count, int hist_cap, void* stream);
 
 /* The DeltaNet step without a caller-provided workspace.  It has no counterpart in the reference,
  * whose caller always allocates the scratch tensor itself.  It exists for callers that cannot

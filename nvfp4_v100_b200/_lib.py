@@ -39,6 +39,11 @@ SIGNATURES = {
     "launch_rope_qk": ([_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "launch_silu_mul": ([_vp, _vp, _vp, _i, _vp], _i),
     "launch_attn_decode": ([_vp] * 6 + [_i, _f, _vp], _i),
+    "launch_attn_decode_heads": ([_vp] * 6 + [_i, _i, _i, _f, _vp], _i),
+    "launch_nvfp4_gemv_fused": ([_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _f, _i, _vp, _vp], _i),
+    "launch_embed_gather": ([_vp, _vp, _vp, _i, _ll, _vp], _i),
+    "launch_attn_prep": ([_vp] * 10 + [_i, _i, _i, _f, _vp], _i),
+    "launch_argmax_advance": ([_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),
     "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
     "launch_dn_fused_heads": ([_vp] * 12 + [_i, _i, _f, _vp], _i),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),

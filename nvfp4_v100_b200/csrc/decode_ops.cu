@@ -1,0 +1,173 @@
+// Small kernels that glue one decode step together on the device, so that a whole step — from
+// the previous token id to the next one — is a fixed sequence of launches that a CUDA graph can
+// replay without host work in between.
+//
+// In the reference these pieces are PyTorch operators inside the captured model forward
+// (pipeline/_qwen38_infer.py:679-685: the forward, logits[:, -1].argmax, static_pos.add_(1)) and
+// a host-side embedding gather before each replay (:714-716).  Position-dependent work reads the
+// position from device memory, as the reference's attention kernel does with cum_len
+// (kernels/nvfp4_attn_decode.cu:33,43).
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace nvfp4 {
+
+// out[0..hidden) = table[tok][0..hidden), tok read from device memory.
+__global__ void __launch_bounds__(256)
+embed_gather_kernel(const __half* __restrict__ table, const long long* __restrict__ tok,
+                    __half* __restrict__ out, int hidden, long long vocab) {
+    long long id = *tok;
+    if (id < 0) id = 0;
+    if (id >= vocab) id = vocab - 1;
+    const int i = (blockIdx.x * 256 + threadIdx.x) * 8;
+    if (i + 8 <= hidden) {
+        *reinterpret_cast<uint4*>(out + i) =
+            *reinterpret_cast<const uint4*>(table + (size_t)id * hidden + i);
+    } else {
+        for (int j = i; j < hidden; j++) out[j] = table[(size_t)id * hidden + j];
+    }
+}
+
+// Everything between the q/k/v projection and the attention kernel, one CTA per head:
+//   query head h : q = rmsnorm(qkv[h*512 .. +256]) with q_w1, RoPE at *pos -> q_out[h];
+//                  gate_out[h] = qkv[h*512+256 .. +256]   (the projection emits [q | gate] per head)
+//   key head j   : k = rmsnorm(k_j) with k_w1, RoPE at *pos -> keys[j][*pos]
+//   value head j : values[j][*pos] = v_j
+// RMSNorm and RoPE use exactly the arithmetic of rmsnorm_kernel and rope_qk_kernel, including the
+// fp16 rounding between them.
+__global__ void __launch_bounds__(256)
+attn_prep_kernel(const __half* __restrict__ qkv, const float* __restrict__ q_w1,
+                 const float* __restrict__ k_w1, const __half* __restrict__ cos_tab,
+                 const __half* __restrict__ sin_tab, const long long* __restrict__ pos_ptr,
+                 __half* __restrict__ q_out, __half* __restrict__ gate_out,
+                 __half* __restrict__ keys, __half* __restrict__ values, int hq, int hkv,
+                 int max_len, float eps) {
+    __shared__ float s_red[8];
+    __shared__ float s_n[256];
+    const int b = blockIdx.x, d = threadIdx.x, lane = d & 31, warp = d >> 5;
+    long long pos = *pos_ptr;
+    if (pos < 0) pos = 0;
+    if (pos >= max_len) pos = max_len - 1;  // never index past the cache or the tables
+    const __half* kbase = qkv + (size_t)hq * 512;
+    const __half* vbase = kbase + (size_t)hkv * 256;
+    if (b >= hq + hkv) {  // value head: plain copy into the cache
+        const int j = b - hq - hkv;
+        values[((size_t)j * max_len + pos) * 256 + d] = vbase[(size_t)j * 256 + d];
+        return;
+    }
+    const bool is_q = b < hq;
+    const __half* src = is_q ? qkv + (size_t)b * 512 : kbase + (size_t)(b - hq) * 256;
+    const float* w1 = is_q ? q_w1 : k_w1;
+    const float x = __half2float(src[d]);
+    float ss = warp_sum(x * x);
+    if (lane == 0) s_red[warp] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) tot += s_red[w];
+    const float inv = rsqrtf(tot / 256.0f + eps);
+    const float xn = round_f16(x * inv * w1[d]);
+    s_n[d] = xn;
+    __syncthreads();
+    const float c = __half2float(cos_tab[(size_t)pos * 256 + d]);
+    const float s = __half2float(sin_tab[(size_t)pos * 256 + d]);
+    const float partner = (d < 128) ? -s_n[d + 128] : s_n[d - 128];
+    const __half r = __float2half(round_f16(xn * c) + round_f16(partner * s));
+    if (is_q) {
+        q_out[(size_t)b * 256 + d] = r;
+        gate_out[(size_t)b * 256 + d] = src[256 + d];
+    } else {
+        keys[((size_t)(b - hq) * max_len + pos) * 256 + d] = r;
+    }
+}
+
+// next = argmax(logits) (lowest index among equal maxima); also records the token and advances
+// the position counters, so the next replay of the step graph needs no host input.
+__global__ void __launch_bounds__(1024)
+argmax_advance_kernel(const __half* __restrict__ logits, int vocab, long long* __restrict__ tok,
+                      long long* __restrict__ pos, long long* __restrict__ len,
+                      long long* __restrict__ history, long long* __restrict__ hist_count,
+                      int hist_cap) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = t; i < vocab; i += 1024) {
+        const float v = __half2float(logits[i]);
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = s_v[lane];
+        bi = s_i[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            if (bi == 0x7fffffff) bi = 0;  // all-NaN logits
+            *tok = bi;
+            if (history && hist_count) {
+                const long long n = *hist_count;
+                if (n < hist_cap) history[n] = bi;
+                *hist_count = n + 1;
+            }
+            if (pos) *pos += 1;
+            if (len) *len += 1;
+        }
+    }
+}
+
+}  // namespace nvfp4
+
+extern "C" {
+
+// table fp16 [vocab, hidden]; tok: device int64; out fp16 [hidden].  0, or -1 bad args / launch.
+int launch_embed_gather(const void* table, const void* tok, void* out, int hidden, long long vocab,
+                        void* stream) {
+    if (!table || !tok || !out || hidden <= 0 || vocab <= 0) return -1;
+    const int per = 256 * 8;
+    nvfp4::embed_gather_kernel<<<(hidden + per - 1) / per, 256, 0, (cudaStream_t)stream>>>(
+        (const __half*)table, (const long long*)tok, (__half*)out, hidden, vocab);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// qkv fp16 [hq*512 + 2*hkv*256]; q_w1, k_w1 fp32 [256] (1 + weight); cos/sin tables fp16
+// [max_len, 256]; pos: device int64 index of the current token; q_out, gate_out fp16 [hq*256];
+// keys, values fp16 [hkv, max_len, 256].  0, or -1 bad args / launch error.
+int launch_attn_prep(const void* qkv, const void* q_w1, const void* k_w1, const void* cos_tab,
+                     const void* sin_tab, const void* pos, void* q_out, void* gate_out, void* keys,
+                     void* values, int hq, int hkv, int max_len, float eps, void* stream) {
+    if (!qkv || !q_w1 || !k_w1 || !cos_tab || !sin_tab || !pos || !q_out || !gate_out || !keys ||
+        !values || hq <= 0 || hkv <= 0 || max_len <= 0)
+        return -1;
+    nvfp4::attn_prep_kernel<<<hq + 2 * hkv, 256, 0, (cudaStream_t)stream>>>(
+        (const __half*)qkv, (const float*)q_w1, (const float*)k_w1, (const __half*)cos_tab,
+        (const __half*)sin_tab, (const long long*)pos, (__half*)q_out, (__half*)gate_out,
+        (__half*)keys, (__half*)values, hq, hkv, max_len, eps);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// logits fp16 [vocab]; tok/pos/len/hist_count: device int64 scalars (pos, len, history and
+// hist_count may be NULL); history: device int64 [hist_cap].  0, or -1.
+int launch_argmax_advance(const void* logits, int vocab, void* tok, void* pos, void* len,
+                          void* history, void* hist_count, int hist_cap, void* stream) {
+    if (!logits || !tok || vocab <= 0) return -1;
+    nvfp4::argmax_advance_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(
+        (const __half*)logits, vocab, (long long*)tok, (long long*)pos, (long long*)len,
+        (long long*)history, (long long*)hist_count, hist_cap);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+}  // extern "C"

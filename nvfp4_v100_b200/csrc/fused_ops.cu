@@ -378,11 +378,13 @@ int launch_silu_mul(const void* g, const void* u, void* out, int n, void* stream
 // Heads are the 27B model's: 24 query heads, 4 KV heads, head dim 256.  max_len is the cache's
 // allocated length and may be any value whose fp32 score buffer fits in shared memory
 // (max_len <= 57344); larger values return -2, as the reference does for an unsupported length.
-int launch_attn_decode(const void* q, const void* keys, const void* values, const void* cum_len,
-                       const void* gate, void* out, int max_len, float scale, void* stream) {
+static int attn_decode_launch(const void* q, const void* keys, const void* values,
+                              const void* cum_len, const void* gate, void* out, int max_len,
+                              int hq, int hkv, float scale, void* stream) {
     static bool smem_opt_in = false;
     if (max_len <= 0 || max_len > 57344) return -2;
     if (!q || !keys || !values || !cum_len || !gate || !out) return -2;
+    if (hq <= 0 || hkv <= 0 || hq % hkv != 0) return -2;
     const size_t smem = (size_t)max_len * sizeof(float);
     if (!smem_opt_in) {
         // one-time opt-in to the large dynamic shared memory carve-out (a host-side attribute,
@@ -393,11 +395,24 @@ int launch_attn_decode(const void* q, const void* keys, const void* values, cons
             return -2;
         smem_opt_in = true;
     }
-    nvfp4::attn_decode_kernel<<<24, ATT_THREADS, smem, (cudaStream_t)stream>>>(
+    nvfp4::attn_decode_kernel<<<hq, ATT_THREADS, smem, (cudaStream_t)stream>>>(
         (const __half*)q, (const __half*)keys, (const __half*)values, (const long long*)cum_len,
-        (const __half*)gate, (__half*)out, max_len, 6, scale);
+        (const __half*)gate, (__half*)out, max_len, hq / hkv, scale);
     const cudaError_t e = cudaGetLastError();
     return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+int launch_attn_decode(const void* q, const void* keys, const void* values, const void* cum_len,
+                       const void* gate, void* out, int max_len, float scale, void* stream) {
+    return attn_decode_launch(q, keys, values, cum_len, gate, out, max_len, 24, 4, scale, stream);
+}
+
+// The same kernel for a tensor-parallel shard or a smaller model: hq query heads, hkv KV heads
+// (hq a multiple of hkv), head dim 256.
+int launch_attn_decode_heads(const void* q, const void* keys, const void* values,
+                             const void* cum_len, const void* gate, void* out, int max_len, int hq,
+                             int hkv, float scale, void* stream) {
+    return attn_decode_launch(q, keys, values, cum_len, gate, out, max_len, hq, hkv, scale, stream);
 }
 
 static int dn_fused_launch(const void* mixed, const void* z_in, const void* b_in, const void* a_in,

@@ -83,14 +83,43 @@ struct WeightRegs {
     uint2 sa, sb;    // 8 scale bytes of row g / g+8: .x = blocks 0..3 of the even chunk, .y = odd
 };
 
+// Optional work fused around the dot products (used by the decode engine; the reference-named
+// entry points run with PRO_NONE / EPI_STORE).
+enum { PRO_NONE = 0, PRO_RMSNORM = 1 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2 };
+struct GemvExtra {
+    const float* norm_w1;     // PRO_RMSNORM: fp32 (1 + weight) [K]
+    float eps;                // PRO_RMSNORM
+    const __half* residual;   // EPI_RESIDUAL: fp16 [M], out = f16(residual + f16(y))
+};
+
+__device__ __forceinline__ void lds_x_pred(uint32_t saddr, uint32_t pred, uint32_t& r0,
+                                           uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm("{\n"
+        ".reg .pred p;\n"
+        "setp.ne.u32 p, %4, 0;\n"
+        "@p ld.shared.v4.u32 {%0,%1,%2,%3}, [%5];\n"
+        "}\n"
+        : "+r"(r0), "+r"(r1), "+r"(r2), "+r"(r3)
+        : "r"(pred), "r"(saddr));
+}
+
 // Tensor-core GEMV.  Requirements checked by the launcher: K % 128 == 0, packed 32-byte aligned,
 // scales 8-byte aligned, activations 16-byte aligned.
-template <int WARPS, int NACT>
+//   PRO_RMSNORM : the activation is RMS-normalised first, x' = f16(f32(x) * rsqrt(mean(x^2)+eps)
+//                 * w1) — the arithmetic of rmsnorm_kernel — once per CTA into shared memory
+//                 (dynamic, 2K bytes), and the dot products read x' from there.
+//   EPI_RESIDUAL: out[m] = f16(f32(residual[m]) + f32(f16(y[m]))).
+//   EPI_SILU_MUL: W holds gate and up rows interleaved in groups of 8 (tile rows 0..7 = gate rows
+//                 8j..8j+7, rows 8..15 = up rows 8j..8j+7; M = 2 * outputs);
+//                 out[8j+r] = f16( f32(f16(silu(f16(g)))) * f32(f16(u)) ), the silu_mul_kernel chain.
+template <int WARPS, int NACT, int PRO, int EPI>
 __global__ void __launch_bounds__(WARPS * 32)
 gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                 const __half* __restrict__ act0, const __half* __restrict__ act1,
-                __half* __restrict__ out, int M, int K) {
+                __half* __restrict__ out, int M, int K, GemvExtra ex) {
     __shared__ float red[WARPS][16][2];
+    extern __shared__ __align__(16) __half xs[];  // PRO_RMSNORM: normalised activation [K]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int nsteps = (K + 255) >> 8;
@@ -120,6 +149,51 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         }
     }
     pdl_wait();
+
+    if (PRO == PRO_RMSNORM) {
+        __shared__ float s_part[WARPS];
+        __shared__ float s_inv;
+        float ss = 0.0f;
+        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(act0 + i);
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 f = __half22float2(h[j]);
+                ss = fmaf(f.x, f.x, ss);
+                ss = fmaf(f.y, f.y, ss);
+            }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) s_part[warp] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < WARPS; w++) v += s_part[w];
+            s_inv = rsqrtf(v / (float)K + ex.eps);
+        }
+        __syncthreads();
+        const float inv = s_inv;
+        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(act0 + i);
+            const float4 wa = *reinterpret_cast<const float4*>(ex.norm_w1 + i);
+            const float4 wb = *reinterpret_cast<const float4*>(ex.norm_w1 + i + 4);
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+            const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            uint4 o;
+            __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float2 f = __half22float2(h[j]);
+                oh[j] = __halves2half2(__float2half(f.x * inv * w[2 * j]),
+                                       __float2half(f.y * inv * w[2 * j + 1]));
+            }
+            *reinterpret_cast<uint4*>(xs + i) = o;
+        }
+        __syncthreads();
+    }
+    const uint32_t xs_base = (uint32_t)__cvta_generic_to_shared(xs);
 
     uint32_t xr[2][8];  // two passes of activation registers (zero where this lane supplies none)
 #pragma unroll
@@ -162,10 +236,17 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
             // activation of this lane's chunk, 16 halves per pass (suppliers only)
             const int kc = s * 256 + t * 64;
             const uint32_t xp = (supplies && kc < K) ? 1u : 0u;
-            const __half* xptr = xsrc + min(kc, K - 64);
+            const int kx = min(kc, K - 64);
+            const __half* xptr = xsrc + kx;
             auto load_x = [&](int q, uint32_t (&x)[8]) {
-                ld_x_pred(xptr + 16 * q, xp, x[0], x[1], x[2], x[3]);
-                ld_x_pred(xptr + 16 * q + 8, xp, x[4], x[5], x[6], x[7]);
+                if (PRO == PRO_RMSNORM) {
+                    const uint32_t a = xs_base + (uint32_t)(kx + 16 * q) * 2u;
+                    lds_x_pred(a, xp, x[0], x[1], x[2], x[3]);
+                    lds_x_pred(a + 16u, xp, x[4], x[5], x[6], x[7]);
+                } else {
+                    ld_x_pred(xptr + 16 * q, xp, x[0], x[1], x[2], x[3]);
+                    ld_x_pred(xptr + 16 * q + 8, xp, x[4], x[5], x[6], x[7]);
+                }
             };
             load_x(0, xr[0]);
 #pragma unroll
@@ -197,197 +278,34 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
             red[warp][g + 8][t >> 1] = acc_b;
         }
         __syncthreads();
-        if (threadIdx.x < 16 * NACT) {
+        if (EPI == EPI_SILU_MUL) {
+            if (threadIdx.x < 8) {
+                const int r = threadIdx.x;
+                float gsum = 0.0f, usum = 0.0f;
+#pragma unroll
+                for (int w = 0; w < WARPS; w++) { gsum += red[w][r][0]; usum += red[w][r + 8][0]; }
+                const int orow = tile * 8 + r;
+                if (tile * 16 + r + 8 < M) {
+                    const float gf = round_f16(gsum), uf = round_f16(usum);
+                    const float sl = round_f16(gf / (1.0f + expf(-gf)));
+                    out[orow] = __float2half(sl * uf);
+                }
+            }
+        } else if (threadIdx.x < 16 * NACT) {
             const int r = threadIdx.x & 15, a = threadIdx.x >> 4;
             float v = 0.0f;
 #pragma unroll
             for (int w = 0; w < WARPS; w++) v += red[w][r][a];
             const int row = tile * 16 + r;
-            if (row < M) out[(size_t)a * M + row] = __float2half(v);
+            if (row < M) {
+                if (EPI == EPI_RESIDUAL)
+                    out[row] = __float2half(__half2float(ex.residual[row]) + round_f16(v));
+                else
+                    out[(size_t)a * M + row] = __float2half(v);
+            }
         }
         __syncthreads();
     }
-}
-
-// ---------------------------------------------------------------------------------------------
-// Same arithmetic, but the weight and scale bytes travel global -> shared with asynchronous
-// copies (cp.async) into a per-thread ring of STAGES slots, so the number of bytes in flight per
-// SM is set by shared memory (tens of KB per CTA) instead of by registers, and the prefetch runs
-// across tile boundaries.  Every thread copies and later reads only its own slots, so the only
-// synchronisation is cp.async.wait_group; slot addresses are (slot * THREADS + tid) * 16 and are
-// therefore bank-conflict free.  A copy whose source lies past the end of a row is issued with a
-// source size of 0, which zero-fills the slot.
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc, uint32_t src_bytes) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(gsrc),
-                 "r"(src_bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_8(void* smem_dst, const void* gsrc, uint32_t src_bytes) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8, %2;\n" ::"r"(d), "l"(gsrc),
-                 "r"(src_bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
-}
-
-template <int WARPS, int NACT, int STAGES>
-__global__ void __launch_bounds__(WARPS * 32)
-gemv_mma_async_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
-                      const __half* __restrict__ act0, const __half* __restrict__ act1,
-                      __half* __restrict__ out, int M, int K) {
-    constexpr int T = WARPS * 32;
-    extern __shared__ __align__(16) uint8_t ring[];
-    uint4* wbuf = reinterpret_cast<uint4*>(ring);                          // [STAGES][4][T]
-    uint2* sbuf = reinterpret_cast<uint2*>(ring + (size_t)STAGES * 4 * T * 16);  // [STAGES][2][T]
-    __shared__ float red[WARPS][16][2];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    const int nsteps = (K + 255) >> 8;
-    const int ntiles = (M + 15) >> 4;
-    const size_t prow = (size_t)(K >> 1), srow = (size_t)(K >> 4);
-    const bool supplies = ((g & 3) == t) && (g < 4 || NACT == 2);
-    const __half* xsrc = (g < 4 || NACT == 1) ? act0 : act1;
-
-    pdl_launch_dependents();
-    if (blockIdx.x < ntiles) {
-        const int r0 = blockIdx.x * 16;
-        const int nrows = min(16, M - r0);
-        const uint8_t* pslab = packed + (size_t)r0 * prow;
-        const size_t pbytes = (size_t)nrows * prow;
-        const uint32_t PF_CHUNK = 8192;
-        for (size_t off = (size_t)tid * PF_CHUNK; off < pbytes; off += (size_t)T * PF_CHUNK) {
-            const size_t n = pbytes - off;
-            prefetch_l2_bulk(pslab + off, (uint32_t)(n < PF_CHUNK ? n : PF_CHUNK));
-        }
-        if (tid == T - 1) {
-            const size_t sbytes = ((size_t)nrows * srow) & ~(size_t)15;
-            if (sbytes) prefetch_l2_bulk(scales + (size_t)r0 * srow, (uint32_t)sbytes);
-        }
-    }
-    pdl_wait();
-
-    // per-warp work sequence: for each of this CTA's tiles, nsw steps (step = warp + k * WARPS;
-    // steps past the end of the row are issued as zero fills so every warp runs the same count)
-    const int nsw = (nsteps + WARPS - 1) / WARPS;
-    const int my_tiles = (blockIdx.x < ntiles) ? (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-    const int total = my_tiles * nsw;
-
-    // issue the copies of sequence element (tile index j, step index k) into ring slot `slot`
-    auto issue = [&](int j, int k, int slot) {
-        const int tile = blockIdx.x + j * gridDim.x;
-        const int s = warp + k * WARPS;
-        const int ra = min(tile * 16 + g, M - 1);
-        const int rb = min(tile * 16 + g + 8, M - 1);
-        const int kc = s * 256 + t * 64;            // first weight of this lane's chunk
-        const bool wv = kc < K;
-        const size_t poff = (size_t)(wv ? kc : 0) >> 1;
-        const uint8_t* pa = packed + (size_t)ra * prow + poff;
-        const uint8_t* pb = packed + (size_t)rb * prow + poff;
-        const uint32_t wn = wv ? 16u : 0u;
-        cp_async_16(&wbuf[(slot * 4 + 0) * T + tid], pa, wn);
-        cp_async_16(&wbuf[(slot * 4 + 1) * T + tid], pa + 16, wn);
-        cp_async_16(&wbuf[(slot * 4 + 2) * T + tid], pb, wn);
-        cp_async_16(&wbuf[(slot * 4 + 3) * T + tid], pb + 16, wn);
-        const int kg = s * 256 + (t & 1) * 128;     // first weight of this lane's scale group
-        const bool sv = kg < K;
-        const size_t soff = (size_t)(sv ? kg : 0) >> 4;
-        cp_async_8(&sbuf[(slot * 2 + 0) * T + tid], scales + (size_t)ra * srow + soff, sv ? 8u : 0u);
-        cp_async_8(&sbuf[(slot * 2 + 1) * T + tid], scales + (size_t)rb * srow + soff, sv ? 8u : 0u);
-    };
-
-    // prologue: STAGES - 1 elements in flight
-    int ij = 0, ik = 0;  // (tile index, step index) of the next element to issue
-#pragma unroll
-    for (int p = 0; p < STAGES - 1; p++) {
-        if (ij < my_tiles) issue(ij, ik, p);
-        cp_async_commit();
-        if (++ik == nsw) { ik = 0; ++ij; }
-    }
-
-    uint32_t xr[2][8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) { xr[0][i] = 0u; xr[1][i] = 0u; }
-
-    float acc_a = 0.0f, acc_b = 0.0f;
-    int cj = 0, ck = 0;  // element being consumed
-    for (int e = 0; e < total; e++) {
-        const int slot = e % STAGES;
-        // keep the ring full: the slot freed by element e-1 receives element e + STAGES - 1
-        if (ij < my_tiles) issue(ij, ik, (e + STAGES - 1) % STAGES);
-        cp_async_commit();
-        if (++ik == nsw) { ik = 0; ++ij; }
-        cp_async_wait<STAGES - 1>();  // element e has landed (this thread's own copies)
-
-        uint32_t wa[8], wb[8];
-        {
-            const uint4 v0 = wbuf[(slot * 4 + 0) * T + tid], v1 = wbuf[(slot * 4 + 1) * T + tid];
-            const uint4 v2 = wbuf[(slot * 4 + 2) * T + tid], v3 = wbuf[(slot * 4 + 3) * T + tid];
-            wa[0] = v0.x; wa[1] = v0.y; wa[2] = v0.z; wa[3] = v0.w;
-            wa[4] = v1.x; wa[5] = v1.y; wa[6] = v1.z; wa[7] = v1.w;
-            wb[0] = v2.x; wb[1] = v2.y; wb[2] = v2.z; wb[3] = v2.w;
-            wb[4] = v3.x; wb[5] = v3.y; wb[6] = v3.z; wb[7] = v3.w;
-        }
-        const uint2 sca = sbuf[(slot * 2 + 0) * T + tid], scb = sbuf[(slot * 2 + 1) * T + tid];
-
-        const int s = warp + ck * WARPS;
-        const int kc = s * 256 + t * 64;
-        const uint32_t xp = (supplies && kc < K) ? 1u : 0u;
-        const __half* xptr = xsrc + min(kc, K - 64);
-        auto load_x = [&](int q, uint32_t (&x)[8]) {
-            ld_x_pred(xptr + 16 * q, xp, x[0], x[1], x[2], x[3]);
-            ld_x_pred(xptr + 16 * q + 8, xp, x[4], x[5], x[6], x[7]);
-        };
-        load_x(0, xr[0]);
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            if (q < 3) load_x(q + 1, xr[(q + 1) & 1]);
-            const uint32_t(&x)[8] = xr[q & 1];
-            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-                e2m1x8_to_half2x4(wa[2 * q + h], a0, a1, a2, a3);
-                e2m1x8_to_half2x4(wb[2 * q + h], b0, b1, b2, b3);
-                mma_f16_16816(c, a0, b0, a1, b1, x[4 * h + 0], x[4 * h + 1]);
-                mma_f16_16816(c, a2, b2, a3, b3, x[4 * h + 2], x[4 * h + 3]);
-            }
-            acc_a = fmaf(c[0], scale_byte(sca.x, q), acc_a);
-            acc_a = fmaf(c[1], scale_byte(sca.y, q), acc_a);
-            acc_b = fmaf(c[2], scale_byte(scb.x, q), acc_b);
-            acc_b = fmaf(c[3], scale_byte(scb.y, q), acc_b);
-        }
-
-        if (++ck == nsw) {  // tile finished: combine the warps' partial sums
-            const int tile = blockIdx.x + cj * gridDim.x;
-            acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
-            acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
-            if ((t & 1) == 0) {
-                red[warp][g][t >> 1] = acc_a;
-                red[warp][g + 8][t >> 1] = acc_b;
-            }
-            __syncthreads();
-            if (tid < 16 * NACT) {
-                const int r = tid & 15, a = tid >> 4;
-                float v = 0.0f;
-#pragma unroll
-                for (int w = 0; w < WARPS; w++) v += red[w][r][a];
-                const int row = tile * 16 + r;
-                if (row < M) out[(size_t)a * M + row] = __float2half(v);
-            }
-            __syncthreads();
-            acc_a = 0.0f;
-            acc_b = 0.0f;
-            ck = 0;
-            ++cj;
-        }
-    }
-    cp_async_wait<0>();
 }
 
 // Generic path for shapes or pointers the tensor-core kernel does not take (K % 128 != 0, or
@@ -445,7 +363,6 @@ struct GemvConfig {
     int ctas_per_sm = 0;   // 0 = choose from the occupancy calculator
     int force_generic = 0;
     int no_pdl = 0;        // 1 = plain stream-ordered launches (no programmatic dependent launch)
-    int async_ring = 0;    // 0 = register-prefetch kernel; 3, 4 or 6 = cp.async ring with that many slots
 };
 static GemvConfig g_cfg;
 static int g_num_sms = 0;
@@ -461,17 +378,25 @@ static int num_sms() {
     return g_num_sms;
 }
 
-template <int WARPS, int NACT>
+template <int WARPS, int NACT, int PRO, int EPI>
 static cudaError_t launch_mma(const void* packed, const void* scales, const void* a0, const void* a1,
-                              void* out, int M, int K, cudaStream_t st) {
-    static int occ = 0;  // resident CTAs per SM for this instantiation
-    if (occ == 0) {
+                              void* out, int M, int K, cudaStream_t st, const GemvExtra& ex) {
+    const int smem = (PRO == PRO_RMSNORM) ? K * 2 : 0;
+    static int occ_cache[2] = {0, 0};  // [0]: no dynamic shared memory, [1]: last K used
+    static int occ_k = -1;
+    int occ;
+    if (smem == 0 ? occ_cache[0] == 0 : occ_k != K) {
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(gemv_mma_kernel<WARPS, NACT, PRO, EPI>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return cudaErrorInvalidValue;
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_mma_kernel<WARPS, NACT>,
-                                                          WARPS * 32, 0) != cudaSuccess || n <= 0)
-            n = 4;
-        occ = n;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                &n, gemv_mma_kernel<WARPS, NACT, PRO, EPI>, WARPS * 32, smem) != cudaSuccess || n <= 0)
+            n = 2;
+        if (smem == 0) occ_cache[0] = n; else { occ_cache[1] = n; occ_k = K; }
     }
+    occ = smem == 0 ? occ_cache[0] : occ_cache[1];
     const int per_sm = g_cfg.ctas_per_sm > 0 ? g_cfg.ctas_per_sm : occ;
     const int ntiles = (M + 15) / 16;
     int grid = num_sms() * per_sm;
@@ -479,51 +404,16 @@ static cudaError_t launch_mma(const void* packed, const void* scales, const void
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(WARPS * 32);
-    cfg.dynamicSmemBytes = 0;
+    cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_cfg.no_pdl ? 0 : 1;
-    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<WARPS, NACT>, (const uint8_t*)packed,
+    return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<WARPS, NACT, PRO, EPI>, (const uint8_t*)packed,
                               (const uint8_t*)scales, (const __half*)a0, (const __half*)a1,
-                              (__half*)out, M, K);
-}
-
-template <int WARPS, int NACT, int STAGES>
-static cudaError_t launch_mma_async(const void* packed, const void* scales, const void* a0,
-                                    const void* a1, void* out, int M, int K, cudaStream_t st) {
-    constexpr int T = WARPS * 32;
-    constexpr int SMEM = STAGES * T * (64 + 16);
-    static int occ = 0;
-    if (occ == 0) {
-        if (cudaFuncSetAttribute(gemv_mma_async_kernel<WARPS, NACT, STAGES>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess)
-            return cudaErrorInvalidValue;
-        int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-                &n, gemv_mma_async_kernel<WARPS, NACT, STAGES>, T, SMEM) != cudaSuccess || n <= 0)
-            n = 2;
-        occ = n;
-    }
-    const int per_sm = g_cfg.ctas_per_sm > 0 ? g_cfg.ctas_per_sm : occ;
-    const int ntiles = (M + 15) / 16;
-    int grid = num_sms() * per_sm;
-    if (grid > ntiles) grid = ntiles;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(T);
-    cfg.dynamicSmemBytes = SMEM;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = g_cfg.no_pdl ? 0 : 1;
-    return cudaLaunchKernelEx(&cfg, gemv_mma_async_kernel<WARPS, NACT, STAGES>,
-                              (const uint8_t*)packed, (const uint8_t*)scales, (const __half*)a0,
-                              (const __half*)a1, (__half*)out, M, K);
+                              (__half*)out, M, K, ex);
 }
 
 static inline bool aligned(const void* p, uintptr_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
@@ -546,28 +436,14 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
         // few row tiles or a long K: spread each tile's K range over 8 warps; many tiles: 4 warps
         // per CTA and more resident CTAs (measured on B200 over the 27B layer shapes)
         if (warps == 0) warps = (K >= 8192 || (M + 15) / 16 <= 3 * num_sms()) ? 8 : 4;
-        if (g_cfg.async_ring) {
-            const int st_n = g_cfg.async_ring;
-            if (nact == 1) {
-                if (warps == 8)
-                    e = (st_n == 3) ? launch_mma_async<8, 1, 3>(packed, scales, a0, a1, out, M, K, st)
-                      : (st_n == 6) ? launch_mma_async<8, 1, 6>(packed, scales, a0, a1, out, M, K, st)
-                                    : launch_mma_async<8, 1, 4>(packed, scales, a0, a1, out, M, K, st);
-                else
-                    e = (st_n == 3) ? launch_mma_async<4, 1, 3>(packed, scales, a0, a1, out, M, K, st)
-                      : (st_n == 6) ? launch_mma_async<4, 1, 6>(packed, scales, a0, a1, out, M, K, st)
-                                    : launch_mma_async<4, 1, 4>(packed, scales, a0, a1, out, M, K, st);
-            } else {
-                e = (warps == 8) ? launch_mma_async<8, 2, 4>(packed, scales, a0, a1, out, M, K, st)
-                                 : launch_mma_async<4, 2, 4>(packed, scales, a0, a1, out, M, K, st);
-            }
-        } else if (nact == 1) {
-            e = (warps == 8) ? launch_mma<8, 1>(packed, scales, a0, a1, out, M, K, st)
-              : (warps == 2) ? launch_mma<2, 1>(packed, scales, a0, a1, out, M, K, st)
-                             : launch_mma<4, 1>(packed, scales, a0, a1, out, M, K, st);
+        const GemvExtra none = {nullptr, 0.0f, nullptr};
+        if (nact == 1) {
+            e = (warps == 8) ? launch_mma<8, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none)
+              : (warps == 2) ? launch_mma<2, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none)
+                             : launch_mma<4, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none);
         } else {
-            e = (warps == 8) ? launch_mma<8, 2>(packed, scales, a0, a1, out, M, K, st)
-                             : launch_mma<4, 2>(packed, scales, a0, a1, out, M, K, st);
+            e = (warps == 8) ? launch_mma<8, 2, 0, 0>(packed, scales, a0, a1, out, M, K, st, none)
+                             : launch_mma<4, 2, 0, 0>(packed, scales, a0, a1, out, M, K, st, none);
         }
     } else {
         const unsigned grid = (unsigned)((M + 7) / 8);
@@ -586,9 +462,60 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
     return NVFP4_OK;
 }
 
+// Fused GEMV of the decode engine.  Only the tensor-core kernel implements the fusions, so the
+// shape and alignment rules of that kernel are requirements here.
+int gemv_ex_dispatch(const void* packed, const void* scales, const void* act, void* out, int M,
+                     int K, int prologue, const void* norm_w1, float eps, int epilogue,
+                     const void* residual, void* stream) {
+    if (K <= 0 || K % 128 != 0 || M <= 0) return NVFP4_ERR_SHAPE;
+    if (!packed || !scales || !act || !out) return NVFP4_ERR_SHAPE;
+    if (!aligned(packed, 32) || !aligned(scales, 8) || !aligned(act, 16) || !aligned(out, 2))
+        return NVFP4_ERR_SHAPE;
+    if (prologue != PRO_NONE && prologue != PRO_RMSNORM) return NVFP4_ERR_SHAPE;
+    if (prologue == PRO_RMSNORM && (!norm_w1 || !aligned(norm_w1, 16) || K * 2 > 200 * 1024))
+        return NVFP4_ERR_SHAPE;
+    if (epilogue < EPI_STORE || epilogue > EPI_SILU_MUL) return NVFP4_ERR_SHAPE;
+    if (epilogue == EPI_RESIDUAL && !residual) return NVFP4_ERR_SHAPE;
+    if (epilogue == EPI_SILU_MUL && M % 16 != 0) return NVFP4_ERR_SHAPE;
+    const GemvExtra ex = {(const float*)norm_w1, eps, (const __half*)residual};
+    cudaStream_t st = (cudaStream_t)stream;
+    int warps = g_cfg.warps;
+    if (warps != 4 && warps != 8) warps = (K >= 8192 || (M + 15) / 16 <= 3 * num_sms()) ? 8 : 4;
+    cudaError_t e;
+#define NVFP4_EX_CASE(P, E)                                                                     \
+    e = (warps == 8) ? launch_mma<8, 1, P, E>(packed, scales, act, nullptr, out, M, K, st, ex)  \
+                     : launch_mma<4, 1, P, E>(packed, scales, act, nullptr, out, M, K, st, ex)
+    if (prologue == PRO_NONE) {
+        if (epilogue == EPI_STORE) { NVFP4_EX_CASE(0, 0); }
+        else if (epilogue == EPI_RESIDUAL) { NVFP4_EX_CASE(0, 1); }
+        else { NVFP4_EX_CASE(0, 2); }
+    } else {
+        if (epilogue == EPI_STORE) { NVFP4_EX_CASE(1, 0); }
+        else if (epilogue == EPI_RESIDUAL) { NVFP4_EX_CASE(1, 1); }
+        else { NVFP4_EX_CASE(1, 2); }
+    }
+#undef NVFP4_EX_CASE
+    if (e != cudaSuccess) {
+        fprintf(stderr, "launch_nvfp4_gemv_fused: %s\n", cudaGetErrorString(e));
+        return NVFP4_ERR_LAUNCH;
+    }
+    return NVFP4_OK;
+}
+
 }  // namespace nvfp4
 
 extern "C" {
+
+// GEMV with optional fused RMSNorm of the activation (prologue = 1) and fused residual add
+// (epilogue = 1) or silu(gate)*up over interleaved gate/up rows (epilogue = 2).  No counterpart in
+// the reference, which launches those operators as separate kernels.
+int launch_nvfp4_gemv_fused(const void* weight_packed, const void* weight_scales,
+                            const void* activation, void* output, int M, int K, int prologue,
+                            const void* norm_w1, float eps, int epilogue, const void* residual,
+                            void* stream) {
+    return nvfp4::gemv_ex_dispatch(weight_packed, weight_scales, activation, output, M, K,
+                                   prologue, norm_w1, eps, epilogue, residual, stream);
+}
 
 // Every single-activation GEMV generation of the reference library resolves to the same kernel;
 // the names are kept so code written against any of them loads unchanged.
@@ -631,11 +558,6 @@ int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int flags) {
     nvfp4::g_cfg.ctas_per_sm = ctas_per_sm;
     nvfp4::g_cfg.force_generic = flags & 1;
     nvfp4::g_cfg.no_pdl = (flags >> 1) & 1;
-    {
-        const int ring = (flags >> 4) & 0xF;  // bits 4..7: cp.async ring slots (0, 3, 4 or 6)
-        if (!(ring == 0 || ring == 3 || ring == 4 || ring == 6)) return NVFP4_ERR_SHAPE;
-        nvfp4::g_cfg.async_ring = ring;
-    }
     return NVFP4_OK;
 }
 

@@ -1,0 +1,403 @@
+"""Native decode engine: one decode step of the hybrid (Gated-DeltaNet + gated-attention) decoder
+as a fixed list of C-ABI launches, captured once in a CUDA graph and replayed per token.
+
+It plays the role of the reference's decode engine bridge — ``QLinear`` dispatch, the
+``patch_fused_deltanet`` / ``patch_attn_decode`` / ``patch_rmsnorm`` forwards and ``GraphDecoder``
+(reference: pipeline/_qwen38_infer.py:144-184, 425-510, 587-650, 653-729, 856-903;
+experiments/_qwen38_p7_pair.py pair fusion; experiments/_qwen38_p9_fuse.py RoPE / silu fusion) —
+without the third-party model code in the loop: every operator of the step is one of this
+library's kernels, the token id, position and KV length live in device memory, and a replay needs
+no host work.  PyTorch is used for device buffers, streams and graph capture only.
+
+Weight layout: the engine consumes matrices in the reference container's raw layout
+(packed [M, K/2] + scales [M, K/16]) and, like the reference's pair fusion, concatenates
+projections that share an input by rows at load time: [q|k|v], [in_proj_qkv|z|b|a]; gate and up
+rows are interleaved in groups of 8 so the GEMV epilogue can apply silu(gate)*up.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from . import _lib
+
+vp = ctypes.c_void_p
+HEAD_DIM = 256      # attention head dim (fixed by the kernels)
+DN_DIM = 128        # DeltaNet head dim (fixed by the kernels)
+CONV_K = 4
+
+
+@dataclass
+class ModelConfig:
+    """Shapes of the decoder.  Defaults are the reference's 27B model (SURVEY: hidden 5120,
+    intermediate 17408, 24 q / 4 kv heads x 256, DeltaNet 16 key / 48 value heads x 128,
+    q projection with per-head output gate, every 4th layer full attention)."""
+    hidden: int = 5120
+    inter: int = 17408
+    vocab: int = 248320
+    n_layers: int = 64
+    full_attn_interval: int = 4
+    hq: int = 24
+    hkv: int = 4
+    dn_kheads: int = 16
+    dn_vheads: int = 48
+    rms_eps: float = 1e-6
+    rope_theta: float = 1e7
+    max_len: int = 1024
+
+    def is_attn(self, i: int) -> bool:
+        return (i + 1) % self.full_attn_interval == 0
+
+    @property
+    def conv_dim(self) -> int:
+        return (2 * self.dn_kheads + self.dn_vheads) * DN_DIM
+
+    def layer_shapes(self, i: int) -> dict:
+        """name -> (M, K) of the layer's linear weights, reference naming."""
+        H = self.hidden
+        if self.is_attn(i):
+            mix = {"q_proj": (self.hq * 2 * HEAD_DIM, H), "k_proj": (self.hkv * HEAD_DIM, H),
+                   "v_proj": (self.hkv * HEAD_DIM, H), "o_proj": (H, self.hq * HEAD_DIM)}
+        else:
+            mix = {"in_proj_qkv": (self.conv_dim, H), "in_proj_z": (self.dn_vheads * DN_DIM, H),
+                   "in_proj_b": (self.dn_vheads, H), "in_proj_a": (self.dn_vheads, H),
+                   "out_proj": (H, self.dn_vheads * DN_DIM)}
+        mix.update({"gate_proj": (self.inter, H), "up_proj": (self.inter, H),
+                    "down_proj": (H, self.inter)})
+        return mix
+
+
+def rope_tables(cfg: ModelConfig):
+    """cos/sin fp16 [max_len, 256]: angle = pos * theta^(-2i/256), i = 0..127, duplicated over the
+    two halves (the model's rotary embedding; computed in fp32, stored as fp16)."""
+    inv = (1.0 / (np.float32(cfg.rope_theta) ** (np.arange(0, HEAD_DIM, 2, dtype=np.float32)
+                                                 / np.float32(HEAD_DIM)))).astype(np.float32)
+    ang = np.arange(cfg.max_len, dtype=np.float32)[:, None] * inv[None, :]
+    emb = np.concatenate([ang, ang], axis=1)
+    return np.cos(emb).astype(np.float16), np.sin(emb).astype(np.float16)
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[inter, X] gate and up byte matrices -> [2*inter, X] with rows in groups of 8:
+    gate rows 8j..8j+7 then up rows 8j..8j+7."""
+    n, x = gate.shape
+    assert n % 8 == 0 and up.shape == gate.shape
+    return torch.stack([gate.view(n // 8, 8, x), up.view(n // 8, 8, x)], dim=1).reshape(2 * n, x)
+
+
+@dataclass
+class _Mat:
+    packed: torch.Tensor
+    scales: torch.Tensor
+    M: int
+    K: int
+
+
+@dataclass
+class _Layer:
+    attn: bool
+    in_w1: torch.Tensor            # fp32 (1 + input_layernorm.weight)
+    post_w1: torch.Tensor
+    w_in: _Mat = None              # [q|k|v] or [in_proj_qkv|z|b|a]
+    w_out: _Mat = None             # o_proj / out_proj
+    w_gu: _Mat = None
+    w_down: _Mat = None
+    extra: dict = field(default_factory=dict)
+
+
+class DecodeEngine:
+    """Holds the prepared weights and all state of one sequence and replays the step graph."""
+
+    def __init__(self, cfg: ModelConfig, device: str = "cuda"):
+        if not torch.cuda.is_available():
+            raise RuntimeError("DecodeEngine needs a CUDA device; there is no CPU fallback")
+        self.cfg = cfg
+        self.dev = torch.device(device)
+        self.lib = _lib.load()
+        self.layers: list[_Layer] = []
+        self.graph = None
+        self.n_launch = 0
+        c = cfg
+        f16, f32, i64 = torch.float16, torch.float32, torch.int64
+        z = lambda *s, dt=f16: torch.zeros(*s, dtype=dt, device=self.dev)
+        self.h = z(c.hidden)
+        self.qkv = z(c.hq * 2 * HEAD_DIM + 2 * c.hkv * HEAD_DIM)
+        self.q_out = z(c.hq * HEAD_DIM)
+        self.gate_out = z(c.hq * HEAD_DIM)
+        self.attn_out = z(c.hq * HEAD_DIM)
+        self.dn_in = z(c.conv_dim + c.dn_vheads * DN_DIM + 2 * c.dn_vheads)
+        self.dn_out = z(c.dn_vheads * DN_DIM)
+        self.dn_scratch = z(c.conv_dim, dt=f32)
+        self.act = z(c.inter)
+        self.logits = z(c.vocab)
+        self.tok = z(1, dt=i64)
+        self.pos = z(1, dt=i64)            # index of the token being processed
+        self.len = z(1, dt=i64)            # keys in the cache including that token
+        self.hist_cap = 4096
+        self.history = z(self.hist_cap, dt=i64)
+        self.hist_count = z(1, dt=i64)
+        cos, sin = rope_tables(c)
+        self.cos = torch.from_numpy(cos).to(self.dev)
+        self.sin = torch.from_numpy(sin).to(self.dev)
+        self.embed = None
+        self.final_w1 = None
+        self.lm_head = None
+
+    # ------------------------------------------------------------------ weights
+    def _mat(self, packed: torch.Tensor, scales: torch.Tensor, M: int, K: int) -> _Mat:
+        packed = packed.contiguous().view(-1)
+        scales = scales.contiguous().view(-1)
+        assert packed.numel() == M * K // 2 and scales.numel() == M * K // 16
+        assert packed.data_ptr() % 32 == 0 and scales.data_ptr() % 8 == 0
+        return _Mat(packed, scales, M, K)
+
+    def load_random(self, seed: int = 0):
+        """Random E2M1 bytes and scale bytes in [118, 122] (what N(0, 0.02^2) weights produce),
+        fp16 embedding ~N(0, 0.02^2), unit norm weights: the throughput workload."""
+        c = self.cfg
+        g = torch.Generator(device=self.dev)
+        g.manual_seed(seed)
+
+        def rnd(M, K):
+            p = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device=self.dev, generator=g)
+            s = torch.randint(118, 123, (M * K // 16,), dtype=torch.uint8, device=self.dev,
+                              generator=g)
+            return self._mat(p, s, M, K)
+
+        ones = lambda n: torch.ones(n, dtype=torch.float32, device=self.dev)
+        self.layers = []
+        for i in range(c.n_layers):
+            L = _Layer(c.is_attn(i), ones(c.hidden), ones(c.hidden))
+            if L.attn:
+                L.w_in = rnd(c.hq * 2 * HEAD_DIM + 2 * c.hkv * HEAD_DIM, c.hidden)
+                L.w_out = rnd(c.hidden, c.hq * HEAD_DIM)
+                L.extra = dict(
+                    q_w1=ones(HEAD_DIM), k_w1=ones(HEAD_DIM),
+                    keys=torch.zeros(c.hkv, c.max_len, HEAD_DIM, dtype=torch.float16, device=self.dev),
+                    values=torch.zeros(c.hkv, c.max_len, HEAD_DIM, dtype=torch.float16, device=self.dev))
+            else:
+                L.w_in = rnd(c.conv_dim + c.dn_vheads * DN_DIM + 2 * c.dn_vheads, c.hidden)
+                L.w_out = rnd(c.hidden, c.dn_vheads * DN_DIM)
+                L.extra = dict(
+                    conv_w=(torch.randn(c.conv_dim, CONV_K, device=self.dev, generator=g) * 0.02).half(),
+                    conv_state=torch.zeros(c.conv_dim, CONV_K, dtype=torch.float16, device=self.dev),
+                    A_log=torch.log(torch.rand(c.dn_vheads, device=self.dev, generator=g) * 16 + 1e-3).half(),
+                    dt_bias=torch.ones(c.dn_vheads, dtype=torch.float16, device=self.dev),
+                    norm_w=torch.ones(DN_DIM, dtype=torch.float16, device=self.dev),
+                    state=torch.zeros(c.dn_vheads, DN_DIM, DN_DIM, dtype=torch.float32, device=self.dev))
+            L.w_gu = rnd(2 * c.inter, c.hidden)
+            L.w_down = rnd(c.hidden, c.inter)
+            self.layers.append(L)
+        self.embed = (torch.randn(c.vocab, c.hidden, device=self.dev, generator=g) * 0.02).half()
+        self.final_w1 = ones(c.hidden)
+        self.lm_head = rnd(c.vocab, c.hidden)
+
+    def load_weights(self, weights: dict):
+        """``weights``: reference-named numpy arrays, e.g. ``layers.3.self_attn.q_proj`` ->
+        (packed u8 [M, K/2], scales u8 [M, K/16]) and ``layers.3.input_layernorm.weight`` ->
+        fp16 array, ``embed_tokens`` fp16 [V, H], ``norm.weight``, ``lm_head`` (packed, scales).
+        Matrices are uploaded raw and fused by rows on the device."""
+        c = self.cfg
+        dev = self.dev
+
+        def up(name):
+            p, s = weights[name]
+            return torch.from_numpy(np.ascontiguousarray(p)).to(dev), \
+                torch.from_numpy(np.ascontiguousarray(s)).to(dev)
+
+        def w1(name):
+            return (1.0 + torch.from_numpy(np.asarray(weights[name], dtype=np.float16)).float()).to(dev)
+
+        def f16(name):
+            return torch.from_numpy(np.ascontiguousarray(weights[name], dtype=np.float16)).to(dev)
+
+        def cat(names, K):
+            ps, ss = zip(*(up(n) for n in names))
+            p, s = torch.cat(ps, 0), torch.cat(ss, 0)
+            return self._mat(p, s, p.shape[0], K)
+
+        self.layers = []
+        for i in range(c.n_layers):
+            pre = f"layers.{i}."
+            L = _Layer(c.is_attn(i), w1(pre + "input_layernorm.weight"),
+                       w1(pre + "post_attention_layernorm.weight"))
+            if L.attn:
+                a = pre + "self_attn."
+                L.w_in = cat([a + "q_proj", a + "k_proj", a + "v_proj"], c.hidden)
+                L.w_out = cat([a + "o_proj"], c.hq * HEAD_DIM)
+                L.extra = dict(
+                    q_w1=w1(a + "q_norm.weight"), k_w1=w1(a + "k_norm.weight"),
+                    keys=torch.zeros(c.hkv, c.max_len, HEAD_DIM, dtype=torch.float16, device=dev),
+                    values=torch.zeros(c.hkv, c.max_len, HEAD_DIM, dtype=torch.float16, device=dev))
+            else:
+                a = pre + "linear_attn."
+                L.w_in = cat([a + "in_proj_qkv", a + "in_proj_z", a + "in_proj_b", a + "in_proj_a"],
+                             c.hidden)
+                L.w_out = cat([a + "out_proj"], c.dn_vheads * DN_DIM)
+                L.extra = dict(
+                    conv_w=f16(a + "conv1d.weight").reshape(c.conv_dim, CONV_K).contiguous(),
+                    conv_state=torch.zeros(c.conv_dim, CONV_K, dtype=torch.float16, device=dev),
+                    A_log=f16(a + "A_log"), dt_bias=f16(a + "dt_bias"),
+                    norm_w=f16(a + "norm.weight"),
+                    state=torch.zeros(c.dn_vheads, DN_DIM, DN_DIM, dtype=torch.float32, device=dev))
+            m = pre + "mlp."
+            gp, gs = up(m + "gate_proj")
+            upp, ups = up(m + "up_proj")
+            L.w_gu = self._mat(interleave_gate_up(gp, upp), interleave_gate_up(gs, ups),
+                               2 * c.inter, c.hidden)
+            L.w_down = cat([m + "down_proj"], c.inter)
+            self.layers.append(L)
+        self.embed = f16("embed_tokens")
+        self.final_w1 = w1("norm.weight")
+        self.lm_head = cat(["lm_head"], c.hidden)
+
+    # ------------------------------------------------------------------ one step
+    def _gemv(self, st, m: _Mat, x, out, pro_w1=None, epi=0, residual=None):
+        rc = self.lib.launch_nvfp4_gemv_fused(
+            vp(m.packed.data_ptr()), vp(m.scales.data_ptr()), vp(x.data_ptr()), vp(out.data_ptr()),
+            m.M, m.K, 0 if pro_w1 is None else 1,
+            vp(0 if pro_w1 is None else pro_w1.data_ptr()), float(self.cfg.rms_eps), epi,
+            vp(0 if residual is None else residual.data_ptr()), st)
+        if rc != 0:
+            raise RuntimeError(f"launch_nvfp4_gemv_fused rc={rc} (M={m.M}, K={m.K})")
+        self.n_launch += 1
+
+    def enqueue_step(self):
+        """Enqueue one decode step on torch's current stream (capturable)."""
+        c, lib = self.cfg, self.lib
+        st = vp(torch.cuda.current_stream().cuda_stream)
+        self.n_launch = 0
+        rc = lib.launch_embed_gather(vp(self.embed.data_ptr()), vp(self.tok.data_ptr()),
+                                     vp(self.h.data_ptr()), c.hidden, c.vocab, st)
+        assert rc == 0, rc
+        self.n_launch += 1
+        nq = c.conv_dim
+        for L in self.layers:
+            e = L.extra
+            if L.attn:
+                self._gemv(st, L.w_in, self.h, self.qkv, pro_w1=L.in_w1)
+                rc = lib.launch_attn_prep(
+                    vp(self.qkv.data_ptr()), vp(e["q_w1"].data_ptr()), vp(e["k_w1"].data_ptr()),
+                    vp(self.cos.data_ptr()), vp(self.sin.data_ptr()), vp(self.pos.data_ptr()),
+                    vp(self.q_out.data_ptr()), vp(self.gate_out.data_ptr()),
+                    vp(e["keys"].data_ptr()), vp(e["values"].data_ptr()), c.hq, c.hkv, c.max_len,
+                    float(c.rms_eps), st)
+                assert rc == 0, rc
+                rc = lib.launch_attn_decode_heads(
+                    vp(self.q_out.data_ptr()), vp(e["keys"].data_ptr()), vp(e["values"].data_ptr()),
+                    vp(self.len.data_ptr()), vp(self.gate_out.data_ptr()),
+                    vp(self.attn_out.data_ptr()), c.max_len, c.hq, c.hkv, float(HEAD_DIM) ** -0.5, st)
+                assert rc == 0, rc
+                self.n_launch += 2
+                self._gemv(st, L.w_out, self.attn_out, self.h, epi=1, residual=self.h)
+            else:
+                self._gemv(st, L.w_in, self.h, self.dn_in, pro_w1=L.in_w1)
+                base = self.dn_in.data_ptr()
+                zoff = nq * 2
+                boff = zoff + c.dn_vheads * DN_DIM * 2
+                aoff = boff + c.dn_vheads * 2
+                rc = lib.launch_dn_fused_heads(
+                    vp(base), vp(base + zoff), vp(base + boff), vp(base + aoff),
+                    vp(e["conv_w"].data_ptr()), vp(e["conv_state"].data_ptr()),
+                    vp(e["A_log"].data_ptr()), vp(e["dt_bias"].data_ptr()),
+                    vp(e["norm_w"].data_ptr()), vp(e["state"].data_ptr()),
+                    vp(self.dn_scratch.data_ptr()), vp(self.dn_out.data_ptr()),
+                    c.dn_kheads, c.dn_vheads, float(c.rms_eps), st)
+                assert rc == 0, rc
+                self.n_launch += 2
+                self._gemv(st, L.w_out, self.dn_out, self.h, epi=1, residual=self.h)
+            self._gemv(st, L.w_gu, self.h, self.act, pro_w1=L.post_w1, epi=2)
+            self._gemv(st, L.w_down, self.act, self.h, epi=1, residual=self.h)
+        self._gemv(st, self.lm_head, self.h, self.logits, pro_w1=self.final_w1)
+        rc = lib.launch_argmax_advance(
+            vp(self.logits.data_ptr()), c.vocab, vp(self.tok.data_ptr()), vp(self.pos.data_ptr()),
+            vp(self.len.data_ptr()), vp(self.history.data_ptr()), vp(self.hist_count.data_ptr()),
+            self.hist_cap, st)
+        assert rc == 0, rc
+        self.n_launch += 1
+
+    # ------------------------------------------------------------------ state
+    def reset(self, first_token: int = 0):
+        """Empty caches and recurrent state, position 0, next token to process = first_token."""
+        for L in self.layers:
+            e = L.extra
+            if L.attn:
+                e["keys"].zero_()
+                e["values"].zero_()
+            else:
+                e["conv_state"].zero_()
+                e["state"].zero_()
+        self.tok.fill_(int(first_token))
+        self.pos.zero_()
+        self.len.fill_(1)
+        self.hist_count.zero_()
+
+    def snapshot(self):
+        """Copy of every piece of mutable state (reference: snap_decode_state plus the fused
+        DeltaNet buffers, pipeline/_qwen38_infer.py:530-552, 817-818)."""
+        snap = {"tok": self.tok.clone(), "pos": self.pos.clone(), "len": self.len.clone(),
+                "hist_count": self.hist_count.clone(), "history": self.history.clone(), "layers": []}
+        n = int(self.len.item())
+        for L in self.layers:
+            e = L.extra
+            if L.attn:
+                snap["layers"].append((e["keys"][:, :n].clone(), e["values"][:, :n].clone()))
+            else:
+                snap["layers"].append((e["conv_state"].clone(), e["state"].clone()))
+        return snap
+
+    def restore(self, snap):
+        for L, s in zip(self.layers, snap["layers"]):
+            e = L.extra
+            if L.attn:
+                n = s[0].shape[1]
+                e["keys"][:, :n].copy_(s[0])
+                e["values"][:, :n].copy_(s[1])
+            else:
+                e["conv_state"].copy_(s[0])
+                e["state"].copy_(s[1])
+        for k in ("tok", "pos", "len", "hist_count", "history"):
+            getattr(self, k).copy_(snap[k])
+
+    # ------------------------------------------------------------------ graph
+    def capture(self, n_warmup: int = 1):
+        """Warm up on a side stream (the warm-up steps mutate state: the caller's state is saved
+        and restored around them, the hygiene rule of the reference's capture protocol,
+        pipeline/_qwen38_infer.py:687-701, 825-829), then capture one step."""
+        snap = self.snapshot()
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(n_warmup):
+                self.enqueue_step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self.restore(snap)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.enqueue_step()
+        self.restore(snap)
+        torch.cuda.synchronize()
+        return self.n_launch
+
+    def step(self) -> None:
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self.enqueue_step()
+
+    def run(self, prompt, n_gen: int):
+        """Feed the prompt token by token through the step (teacher forced), then generate n_gen
+        tokens greedily.  Returns the generated token ids (host list)."""
+        self.reset(int(prompt[0]))
+        for t in range(1, len(prompt)):
+            self.step()
+            self.tok.fill_(int(prompt[t]))      # overwrite the model's own prediction
+        base = int(self.hist_count.item())
+        for _ in range(n_gen):
+            self.step()
+        torch.cuda.synchronize()
+        return self.history[base:base + n_gen].cpu().tolist()

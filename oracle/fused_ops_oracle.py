@@ -167,3 +167,12 @@ def dn_fused(mixed, z, b, a, conv_w, conv_state, A_log, dt_bias, norm_w, state, 
     scratch, new_conv = dn_conv(mixed, conv_w, conv_state)
     out, new_state = dn_rec(scratch, z, b, a, A_log, dt_bias, norm_w, state, rms_eps)
     return out, new_conv, new_state, scratch
+
+
+def dn_fused_heads(mixed, z, b, a, conv_w, conv_state, A_log, dt_bias, norm_w, state, rms_eps,
+                   n_kheads, n_vheads):
+    """dn_fused for a shard / model with n_kheads key heads and n_vheads value heads."""
+    scratch, new_conv = dn_conv(mixed, conv_w, conv_state)
+    out, new_state = dn_rec(scratch, z, b, a, A_log, dt_bias, norm_w, state, rms_eps,
+                            n_vheads=n_vheads, n_kheads=n_kheads)
+    return out, new_conv, new_state, scratch
