@@ -515,6 +515,9 @@ def run_decode(args, quiet=False):
     eng.load_random(seed=0)
     prompt = np.random.default_rng(0).integers(0, cfg.vocab, args.prompt_len)
     eng.reset(int(prompt[0]))
+    if args.fake_context > 0:       # profiling aid: pretend the cache already holds this many keys
+        eng.pos.fill_(args.fake_context - 1)
+        eng.len.fill_(args.fake_context)
     n_launch = eng.capture(n_warmup=1)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -584,6 +587,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--gen", type=int, default=63)
     ap.add_argument("--vocab", type=int, default=VOCAB)
+    ap.add_argument("--fake-context", type=int, default=0,
+                    help="with --decode: start at this cache length (zero-filled cache)")
     ap.add_argument("--eager", action="store_true",
                     help="with --per-shape: launch from the host instead of replaying a CUDA graph")
     args = ap.parse_args()

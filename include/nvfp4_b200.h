@@ -62,8 +62,9 @@ int launch_nvfp4_gemv2(const void* weight_packed, const void* weight_scales, con
 
 /* Tuning hook; no counterpart in the reference.  warps per CTA (0 = auto, 2, 4 or 8), resident
  * CTAs per SM used to size the grid (0 = occupancy calculator), flags: bit 0 routes every GEMV to
- * the non-tensor-core kernel, bit 1 turns programmatic dependent launch off.  Process-wide, not
- * thread-safe.  Returns 0 or -2. */
+ * the non-tensor-core kernel, bit 1 turns programmatic dependent launch off, bits 4..6 cap and
+ * bits 8..10 force the cluster K split (1, 2 or 4 CTAs per row tile; 0 = planner decides).
+ * Process-wide, not thread-safe.  Returns 0 or -2. */
 int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int flags);
 
 /* ---------------------------------------------------------------------------------------------
@@ -89,7 +90,7 @@ int launch_silu_mul(const void* g, const void* u, void* out, int n, void* stream
  * sigmoid output gate.  q/gate/out fp16 [24*256]; keys/values fp16 [4, max_len, 256]; cum_len is a
  * DEVICE int64 holding the number of valid keys including the current token (read at run time, so
  * a captured graph follows the growing cache).  max_len is a run-time value here (the reference
- * compiles one DLL per length); -2 if max_len <= 0, max_len > 57344 or a pointer is NULL; else the
+ * compiles one DLL per length); -2 if max_len <= 0, max_len > 47104 or a pointer is NULL; else the
  * cudaError_t.  kernels/nvfp4_attn_decode.cu:121-132. */
 int launch_attn_decode(const void* q, const void* keys, const void* values, const void* cum_len,
                        const void* gate, void* out, int max_len, float scale, void* stream);
@@ -135,7 +136,7 @@ int launch_dn_fused_heads(const void* mixed, const void* z, const void* b, const
  * interleaved in groups of 8 (rows 16j..16j+7 = gate rows 8j..8j+7, rows 16j+8..16j+15 = up rows
  * 8j..8j+7, M = 2 * outputs, M % 16 == 0) and output[8j+r] = silu(gate)*up with the arithmetic of
  * launch_silu_mul.  Requires K % 128 == 0, weights 32-byte, scales 8-byte, activation 16-byte
- * aligned.  0; -2 bad arguments; -1 launch error. */
+ * aligned; with prologue 1 also K <= 10240.  0; -2 bad arguments; -1 launch error. */
 int launch_nvfp4_gemv_fused(const void* weight_packed, const void* weight_scales,
                             const void* activation, void* output, int M, int K, int prologue,
                             const void* norm_w1, float eps, int epilogue, const void* residual,

@@ -94,7 +94,34 @@ argmax_advance_kernel(const __half* __restrict__ logits, int vocab, long long* _
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = t; i < vocab; i += 1024) {
+    // 8 logits per 16-byte load, 4 loads in flight per thread (logits is 16-byte aligned when it
+    // is a whole allocation; otherwise the scalar loop below handles everything)
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+        const int nvec = vocab >> 3;
+        for (int v0 = t; v0 < nvec; v0 += 1024 * 4) {
+            uint4 r[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int vi = v0 + u * 1024;
+                r[u] = (vi < nvec) ? *reinterpret_cast<const uint4*>(logits + (size_t)vi * 8)
+                                   : make_uint4(0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u, 0xFC00FC00u);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int vi = v0 + u * 1024;
+                const __half* h = reinterpret_cast<const __half*>(&r[u]);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const float v = __half2float(h[e]);
+                    const int i = vi * 8 + e;
+                    if (vi < nvec && (v > best || (v == best && i < bi))) { best = v; bi = i; }
+                }
+            }
+        }
+        done = nvec << 3;
+    }
+    for (int i = done + t; i < vocab; i += 1024) {
         const float v = __half2float(logits[i]);
         if (v > best || (v == best && i < bi)) { best = v; bi = i; }
     }

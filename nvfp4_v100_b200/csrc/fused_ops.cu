@@ -122,13 +122,27 @@ silu_mul_kernel(const __half* __restrict__ g, const __half* __restrict__ u,
 // GQA attention decode (T = 1) over a static KV cache + sigmoid output gate.
 //   q [HQ][256], keys/values [HKV][max_len][256] fp16, L = *cum_len (current token included),
 //   gate [HQ][256]; out[h][d] = f16( f32(f16(o)) * f32(f16(sigmoid(gate))) ).
-// One CTA per query head.  Pass 1: one warp per key, 16 bytes per lane (a 512-byte key row is one
-// coalesced warp read), fp32 dot product + shuffle reduction, scores to shared memory.  Softmax in
-// fp32 with expf.  Pass 2: each thread owns one head dim and walks the keys (coalesced rows).
-// max_len is a runtime argument; the score buffer is dynamic shared memory (4 bytes per key).
+// One CTA per query head, 32 warps.  Keys are dealt to warps round-robin; a 512-byte key or value
+// row is one coalesced warp read (16 bytes per lane), and each warp keeps 4 rows in flight.
+// Pass 1: fp32 dot product + shuffle reduction, scores to shared memory.  Softmax in fp32 with
+// expf (p_i = expf(s_i - max) * (1 / sum), as the reference computes it).  Pass 2: each lane owns
+// 8 head dims and accumulates p_i * v_i over its warp's keys; the warps' partial sums are
+// added in shared memory.  max_len is a run-time argument; the score buffer is dynamic shared
+// memory (4 bytes per key).
 // ---------------------------------------------------------------------------------------------
 #define ATT_D 256
-#define ATT_THREADS 256
+#define ATT_THREADS 1024
+#define ATT_WARPS (ATT_THREADS / 32)
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float2 x = __half22float2(h[j]);
+        f[2 * j] = x.x;
+        f[2 * j + 1] = x.y;
+    }
+}
 
 __global__ void __launch_bounds__(ATT_THREADS)
 attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys,
@@ -136,47 +150,47 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys
                    const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
                    int gqa, float scale) {
     extern __shared__ float s_sc[];  // [max_len]
-    __shared__ float s_red[ATT_THREADS / 32];
+    __shared__ float s_red[ATT_WARPS];
     __shared__ float s_bcast;
+    __shared__ float s_o[ATT_WARPS][ATT_D];
     const int h = blockIdx.x, kv = h / gqa;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     long long L64 = *cum_len;
     if (L64 > max_len) L64 = max_len;  // never index past the cache
+    if (L64 < 0) L64 = 0;
     const int L = (int)L64;
 
-    // this lane's 8 query dims, kept in registers as fp32
     float qf[8];
-    {
-        const uint4 qv = *reinterpret_cast<const uint4*>(q + (size_t)h * ATT_D + lane * 8);
-        const __half2* qh = reinterpret_cast<const __half2*>(&qv);
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float2 f = __half22float2(qh[j]);
-            qf[2 * j] = f.x;
-            qf[2 * j + 1] = f.y;
-        }
-    }
-    const __half* kbase = keys + (size_t)kv * (size_t)max_len * ATT_D;
+    unpack8(*reinterpret_cast<const uint4*>(q + (size_t)h * ATT_D + lane * 8), qf);
+    const __half* kbase = keys + (size_t)kv * (size_t)max_len * ATT_D + lane * 8;
     float m = -3.4e38f;
-    for (int i = warp; i < L; i += ATT_THREADS / 32) {
-        const uint4 kvv = *reinterpret_cast<const uint4*>(kbase + (size_t)i * ATT_D + lane * 8);
-        const __half2* kh = reinterpret_cast<const __half2*>(&kvv);
-        float acc = 0.0f;
+    for (int i0 = warp; i0 < L; i0 += ATT_WARPS * 4) {
+        uint4 kr[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float2 f = __half22float2(kh[j]);
-            acc = fmaf(qf[2 * j], f.x, acc);
-            acc = fmaf(qf[2 * j + 1], f.y, acc);
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * ATT_WARPS;
+            kr[u] = (i < L) ? *reinterpret_cast<const uint4*>(kbase + (size_t)i * ATT_D)
+                            : make_uint4(0u, 0u, 0u, 0u);
         }
-        acc = warp_sum(acc) * scale;
-        if (lane == 0) s_sc[i] = acc;
-        m = fmaxf(m, acc);
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * ATT_WARPS;
+            float kf[8];
+            unpack8(kr[u], kf);
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc = fmaf(qf[j], kf[j], acc);
+            acc = warp_sum(acc) * scale;
+            if (i < L) {
+                if (lane == 0) s_sc[i] = acc;
+                m = fmaxf(m, acc);
+            }
+        }
     }
-    // block max (every lane of a warp already holds the warp's max)
     if (lane == 0) s_red[warp] = m;
     __syncthreads();
     if (warp == 0) {
-        float v = (lane < ATT_THREADS / 32) ? s_red[lane] : -3.4e38f;
+        float v = (lane < ATT_WARPS) ? s_red[lane] : -3.4e38f;
         v = warp_max(v);
         if (lane == 0) s_bcast = v;
     }
@@ -193,31 +207,43 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys
     if (lane == 0) s_red[warp] = l;
     __syncthreads();
     if (warp == 0) {
-        float v = (lane < ATT_THREADS / 32) ? s_red[lane] : 0.0f;
+        float v = (lane < ATT_WARPS) ? s_red[lane] : 0.0f;
         v = warp_sum(v);
         if (lane == 0) s_bcast = 1.0f / v;
     }
     __syncthreads();
     const float inv_l = s_bcast;
 
-    const __half* vbase = values + (size_t)kv * (size_t)max_len * ATT_D + t;
-    float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
-    int i = 0;
-    for (; i + 4 <= L; i += 4) {
-        const float v0 = __half2float(vbase[(size_t)(i + 0) * ATT_D]);
-        const float v1 = __half2float(vbase[(size_t)(i + 1) * ATT_D]);
-        const float v2 = __half2float(vbase[(size_t)(i + 2) * ATT_D]);
-        const float v3 = __half2float(vbase[(size_t)(i + 3) * ATT_D]);
-        acc0 = fmaf(s_sc[i + 0] * inv_l, v0, acc0);
-        acc1 = fmaf(s_sc[i + 1] * inv_l, v1, acc1);
-        acc2 = fmaf(s_sc[i + 2] * inv_l, v2, acc2);
-        acc3 = fmaf(s_sc[i + 3] * inv_l, v3, acc3);
+    const __half* vbase = values + (size_t)kv * (size_t)max_len * ATT_D + lane * 8;
+    float o[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    for (int i0 = warp; i0 < L; i0 += ATT_WARPS * 4) {
+        uint4 vr[4];
+        float p[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const int i = i0 + u * ATT_WARPS;
+            const bool ok = i < L;
+            vr[u] = ok ? *reinterpret_cast<const uint4*>(vbase + (size_t)i * ATT_D)
+                       : make_uint4(0u, 0u, 0u, 0u);
+            p[u] = ok ? s_sc[i] * inv_l : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            float vf[8];
+            unpack8(vr[u], vf);
+#pragma unroll
+            for (int j = 0; j < 8; j++) o[j] = fmaf(p[u], vf[j], o[j]);
+        }
     }
-    for (; i < L; i++)
-        acc0 = fmaf(s_sc[i] * inv_l, __half2float(vbase[(size_t)i * ATT_D]), acc0);
-    const float o = (acc0 + acc1) + (acc2 + acc3);
+#pragma unroll
+    for (int j = 0; j < 8; j++) s_o[warp][lane * 8 + j] = o[j];
+    __syncthreads();
+    if (t >= ATT_D) return;
+    float acc = 0.0f;
+#pragma unroll
+    for (int w = 0; w < ATT_WARPS; w++) acc += s_o[w][t];
 
-    const float a = round_f16(o);
+    const float a = round_f16(acc);
     const float gt = __half2float(gate[(size_t)h * ATT_D + t]);
     const float sg = round_f16(1.0f / (1.0f + expf(-gt)));
     out[(size_t)h * ATT_D + t] = __float2half(a * sg);
@@ -382,7 +408,7 @@ static int attn_decode_launch(const void* q, const void* keys, const void* value
                               const void* cum_len, const void* gate, void* out, int max_len,
                               int hq, int hkv, float scale, void* stream) {
     static bool smem_opt_in = false;
-    if (max_len <= 0 || max_len > 57344) return -2;
+    if (max_len <= 0 || max_len > 47104) return -2;
     if (!q || !keys || !values || !cum_len || !gate || !out) return -2;
     if (hq <= 0 || hkv <= 0 || hq % hkv != 0) return -2;
     const size_t smem = (size_t)max_len * sizeof(float);
@@ -391,7 +417,7 @@ static int attn_decode_launch(const void* q, const void* keys, const void* value
         // not a stream operation)
         if (cudaFuncSetAttribute(nvfp4::attn_decode_kernel,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)(57344 * sizeof(float))) != cudaSuccess)
+                                 (int)(47104 * sizeof(float))) != cudaSuccess)
             return -2;
         smem_opt_in = true;
     }

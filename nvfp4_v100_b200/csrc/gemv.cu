@@ -77,6 +77,32 @@ __device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) 
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p), "r"(bytes) : "memory");
 }
 
+// Thread-block cluster helpers: the CTAs of a cluster split one row tile's K range and combine
+// their partial sums through distributed shared memory.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_nctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;\n" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// read a float at the same shared-memory offset as `local` in CTA `rank` of this cluster
+__device__ __forceinline__ float ld_cluster_f32(const float* local, uint32_t rank) {
+    const uint32_t la = (uint32_t)__cvta_generic_to_shared(local);
+    uint32_t ra;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(ra) : "r"(la), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(ra) : "memory");
+    return v;
+}
+
 struct WeightRegs {
     uint32_t wa[8];  // 32 packed bytes of row g
     uint32_t wb[8];  // 32 packed bytes of row g+8
@@ -86,6 +112,7 @@ struct WeightRegs {
 // Optional work fused around the dot products (used by the decode engine; the reference-named
 // entry points run with PRO_NONE / EPI_STORE).
 enum { PRO_NONE = 0, PRO_RMSNORM = 1 };
+#define PRO_NV 5  // 16-byte activation vectors a thread holds in the RMSNorm prologue
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2 };
 struct GemvExtra {
     const float* norm_w1;     // PRO_RMSNORM: fp32 (1 + weight) [K]
@@ -114,13 +141,19 @@ __device__ __forceinline__ void lds_x_pred(uint32_t saddr, uint32_t pred, uint32
 //                 8j..8j+7, rows 8..15 = up rows 8j..8j+7; M = 2 * outputs);
 //                 out[8j+r] = f16( f32(f16(silu(f16(g)))) * f32(f16(u)) ), the silu_mul_kernel chain.
 template <int WARPS, int NACT, int PRO, int EPI>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 768 / (WARPS * 32))  // 24 warps per SM resident
 gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                 const __half* __restrict__ act0, const __half* __restrict__ act1,
                 __half* __restrict__ out, int M, int K, GemvExtra ex) {
     __shared__ float red[WARPS][16][2];
+    __shared__ float part[2][16][2];  // this CTA's partial row sums, double-buffered by tile parity
     extern __shared__ __align__(16) __half xs[];  // PRO_RMSNORM: normalised activation [K]
+    // A cluster of S CTAs shares each row tile: CTA `crank` takes the K steps
+    // crank*WARPS + warp (mod S*WARPS).  S = 1 when launched without a cluster.
+    const int S = (int)cluster_nctarank(), crank = (int)cluster_ctarank();
+    const int cid = (int)blockIdx.x / S, ncl = (int)gridDim.x / S;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gwarp = crank * WARPS + warp, gstride = S * WARPS;
     const int g = lane >> 2, t = lane & 3;
     const int nsteps = (K + 255) >> 8;
     const int ntiles = (M + 15) >> 4;
@@ -131,35 +164,99 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
 
     // ---- prologue that does not depend on the previous kernel: L2 prefetch of the first tile ----
     pdl_launch_dependents();
-    if (blockIdx.x < ntiles) {
-        const int r0 = blockIdx.x * 16;
+    if (cid < ntiles) {
+        const int r0 = cid * 16;
         const int nrows = min(16, M - r0);
-        // the tile's rows are adjacent in memory: one packed slab and one scale slab
+        // the tile's rows are adjacent in memory: one packed slab and one scale slab; the CTAs of
+        // the cluster prefetch interleaved chunks of it
         const uint8_t* pslab = packed + (size_t)r0 * prow;
         const size_t pbytes = (size_t)nrows * prow;             // multiple of 64
         const uint32_t PF_CHUNK = 8192;
-        for (size_t off = (size_t)threadIdx.x * PF_CHUNK; off < pbytes;
-             off += (size_t)blockDim.x * PF_CHUNK) {
+        for (size_t off = ((size_t)threadIdx.x * S + crank) * PF_CHUNK; off < pbytes;
+             off += (size_t)blockDim.x * S * PF_CHUNK) {
             const size_t n = pbytes - off;
             prefetch_l2_bulk(pslab + off, (uint32_t)(n < PF_CHUNK ? n : PF_CHUNK));
         }
-        if (threadIdx.x == blockDim.x - 1) {
+        if (threadIdx.x == blockDim.x - 1 && crank == 0) {
             const size_t sbytes = ((size_t)nrows * srow) & ~(size_t)15;
             if (sbytes) prefetch_l2_bulk(scales + (size_t)r0 * srow, (uint32_t)sbytes);
         }
     }
     pdl_wait();
 
+
+    // Per-warp work sequence: for each of this CTA's row tiles, nsw K steps (step = warp + k *
+    // WARPS; a step past the end of the row loads nothing and contributes zero, so every warp
+    // runs the same count and meets the others at each tile's reduction).  The register prefetch
+    // of the next element runs across tile boundaries, so the memory pipeline drains only once
+    // per CTA, not once per tile.
+    const int nsw = (nsteps + gstride - 1) / gstride;
+    const int my_tiles = (cid < ntiles) ? (ntiles - cid + ncl - 1) / ncl : 0;
+
+    // row pointers of the tile the load stream is in (it runs one element ahead of the compute)
+    const uint8_t *lpa, *lpb, *lsa, *lsb;
+    auto set_load_tile = [&](int j) {
+        const int tile = cid + j * ncl;
+        const int ra = min(tile * 16 + g, M - 1);
+        const int rb = min(tile * 16 + g + 8, M - 1);
+        lpa = packed + (size_t)ra * prow + t * 32;
+        lpb = packed + (size_t)rb * prow + t * 32;
+        lsa = scales + (size_t)ra * srow + (t & 1) * 8;
+        lsb = scales + (size_t)rb * srow + (t & 1) * 8;
+    };
+    auto load_w = [&](int k, WeightRegs& w) {
+        const int s = gwarp + k * gstride;
+        if (s * 256 + t * 64 < K) {
+            ld_stream_256(lpa + (size_t)s * 128, w.wa);
+            ld_stream_256(lpb + (size_t)s * 128, w.wb);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) { w.wa[i] = 0u; w.wb[i] = 0u; }
+        }
+        if (s * 256 + (t & 1) * 128 < K) {
+            w.sa = __ldg(reinterpret_cast<const uint2*>(lsa + (size_t)s * 16));
+            w.sb = __ldg(reinterpret_cast<const uint2*>(lsb + (size_t)s * 16));
+        } else {
+            w.sa = make_uint2(0u, 0u);
+            w.sb = make_uint2(0u, 0u);
+        }
+    };
+
+    WeightRegs cur;
+    if (my_tiles > 0) {
+        set_load_tile(0);
+        load_w(0, cur);  // in flight while the activation is prepared
+    }
+
     if (PRO == PRO_RMSNORM) {
+        // Every thread keeps its share of x in registers between the two phases and issues all
+        // of its loads up front: the prologue sits on the kernel's critical path, so it must
+        // cost one memory round trip, not one per loop iteration.  K <= PRO_NV * 8 * threads.
         __shared__ float s_part[WARPS];
         __shared__ float s_inv;
-        float ss = 0.0f;
-        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) {
-            const uint4 v = *reinterpret_cast<const uint4*>(act0 + i);
-            const __half2* h = reinterpret_cast<const __half2*>(&v);
+        constexpr int T = WARPS * 32;
+        uint4 xv[PRO_NV];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 f = __half22float2(h[j]);
+        for (int j = 0; j < PRO_NV; j++) {
+            const int i = (threadIdx.x + j * T) * 8;
+            xv[j] = (i < K) ? *reinterpret_cast<const uint4*>(act0 + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        float4 wv[PRO_NV][2];
+#pragma unroll
+        for (int j = 0; j < PRO_NV; j++) {
+            const int i = (threadIdx.x + j * T) * 8;
+            if (i < K) {
+                wv[j][0] = __ldg(reinterpret_cast<const float4*>(ex.norm_w1 + i));
+                wv[j][1] = __ldg(reinterpret_cast<const float4*>(ex.norm_w1 + i + 4));
+            }
+        }
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < PRO_NV; j++) {
+            const __half2* h = reinterpret_cast<const __half2*>(&xv[j]);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float2 f = __half22float2(h[e]);
                 ss = fmaf(f.x, f.x, ss);
                 ss = fmaf(f.y, f.y, ss);
             }
@@ -175,21 +272,23 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         }
         __syncthreads();
         const float inv = s_inv;
-        for (int i = threadIdx.x * 8; i < K; i += WARPS * 32 * 8) {
-            const uint4 v = *reinterpret_cast<const uint4*>(act0 + i);
-            const float4 wa = *reinterpret_cast<const float4*>(ex.norm_w1 + i);
-            const float4 wb = *reinterpret_cast<const float4*>(ex.norm_w1 + i + 4);
-            const __half2* h = reinterpret_cast<const __half2*>(&v);
-            const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-            uint4 o;
-            __half2* oh = reinterpret_cast<__half2*>(&o);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 f = __half22float2(h[j]);
-                oh[j] = __halves2half2(__float2half(f.x * inv * w[2 * j]),
-                                       __float2half(f.y * inv * w[2 * j + 1]));
+        for (int j = 0; j < PRO_NV; j++) {
+            const int i = (threadIdx.x + j * T) * 8;
+            if (i < K) {
+                const __half2* h = reinterpret_cast<const __half2*>(&xv[j]);
+                const float w[8] = {wv[j][0].x, wv[j][0].y, wv[j][0].z, wv[j][0].w,
+                                    wv[j][1].x, wv[j][1].y, wv[j][1].z, wv[j][1].w};
+                uint4 o;
+                __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(h[e]);
+                    oh[e] = __halves2half2(__float2half(f.x * inv * w[2 * e]),
+                                           __float2half(f.y * inv * w[2 * e + 1]));
+                }
+                *reinterpret_cast<uint4*>(xs + i) = o;
             }
-            *reinterpret_cast<uint4*>(xs + i) = o;
         }
         __syncthreads();
     }
@@ -199,77 +298,62 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
 #pragma unroll
     for (int i = 0; i < 8; i++) { xr[0][i] = 0u; xr[1][i] = 0u; }
 
-    for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-        const int ra = min(tile * 16 + g, M - 1);
-        const int rb = min(tile * 16 + g + 8, M - 1);
-        const uint8_t* pa = packed + (size_t)ra * prow + t * 32;
-        const uint8_t* pb = packed + (size_t)rb * prow + t * 32;
-        const uint8_t* sa = scales + (size_t)ra * srow + (t & 1) * 8;
-        const uint8_t* sb = scales + (size_t)rb * srow + (t & 1) * 8;
-        float acc_a = 0.0f, acc_b = 0.0f;
+    float acc_a = 0.0f, acc_b = 0.0f;
+    int lj = 0, lk = 0;  // (tile index, step index) of the newest element requested from memory
+    int cj = 0, ck = 0;  // (tile index, step index) of the element being computed
 
-        auto load_w = [&](int s, WeightRegs& w) {
-            if (s * 256 + t * 64 < K) {
-                ld_stream_256(pa + (size_t)s * 128, w.wa);
-                ld_stream_256(pb + (size_t)s * 128, w.wb);
+    // One element: request the next element into `nxt`, compute the one held in `cur`, and at a
+    // tile's last step combine the warps' partial sums and write the tile's outputs.  The main
+    // loop calls it with the two register buffers swapped on alternate elements, so no buffer is
+    // ever copied.
+    auto do_elem = [&](WeightRegs& cur, WeightRegs& nxt) {
+        if (++lk == nsw) {
+            lk = 0;
+            if (++lj < my_tiles) set_load_tile(lj);
+        }
+        if (lj < my_tiles) load_w(lk, nxt);
+
+        // activation of this lane's chunk, 16 halves per pass (suppliers only)
+        const int s = gwarp + ck * gstride;
+        const int kc = s * 256 + t * 64;
+        const uint32_t xp = (supplies && kc < K) ? 1u : 0u;
+        const int kx = max(0, min(kc, K - 64));
+        const __half* xptr = xsrc + kx;
+        auto load_x = [&](int q, uint32_t (&x)[8]) {
+            if (PRO == PRO_RMSNORM) {
+                const uint32_t a = xs_base + (uint32_t)(kx + 16 * q) * 2u;
+                lds_x_pred(a, xp, x[0], x[1], x[2], x[3]);
+                lds_x_pred(a + 16u, xp, x[4], x[5], x[6], x[7]);
             } else {
-#pragma unroll
-                for (int i = 0; i < 8; i++) { w.wa[i] = 0u; w.wb[i] = 0u; }
-            }
-            if (s * 256 + (t & 1) * 128 < K) {
-                w.sa = __ldg(reinterpret_cast<const uint2*>(sa + (size_t)s * 16));
-                w.sb = __ldg(reinterpret_cast<const uint2*>(sb + (size_t)s * 16));
-            } else {
-                w.sa = make_uint2(0u, 0u);
-                w.sb = make_uint2(0u, 0u);
+                ld_x_pred(xptr + 16 * q, xp, x[0], x[1], x[2], x[3]);
+                ld_x_pred(xptr + 16 * q + 8, xp, x[4], x[5], x[6], x[7]);
             }
         };
-
-        WeightRegs cur;
-        int s = warp;
-        if (s < nsteps) load_w(s, cur);
-        for (; s < nsteps; s += WARPS) {
-            WeightRegs nxt;
-            const int sn = s + WARPS;
-            if (sn < nsteps) load_w(sn, nxt);
-
-            // activation of this lane's chunk, 16 halves per pass (suppliers only)
-            const int kc = s * 256 + t * 64;
-            const uint32_t xp = (supplies && kc < K) ? 1u : 0u;
-            const int kx = min(kc, K - 64);
-            const __half* xptr = xsrc + kx;
-            auto load_x = [&](int q, uint32_t (&x)[8]) {
-                if (PRO == PRO_RMSNORM) {
-                    const uint32_t a = xs_base + (uint32_t)(kx + 16 * q) * 2u;
-                    lds_x_pred(a, xp, x[0], x[1], x[2], x[3]);
-                    lds_x_pred(a + 16u, xp, x[4], x[5], x[6], x[7]);
-                } else {
-                    ld_x_pred(xptr + 16 * q, xp, x[0], x[1], x[2], x[3]);
-                    ld_x_pred(xptr + 16 * q + 8, xp, x[4], x[5], x[6], x[7]);
-                }
-            };
-            load_x(0, xr[0]);
+        load_x(0, xr[0]);
 #pragma unroll
-            for (int q = 0; q < 4; q++) {  // scale block q of every chunk
-                if (q < 3) load_x(q + 1, xr[(q + 1) & 1]);
-                const uint32_t(&x)[8] = xr[q & 1];
-                float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int q = 0; q < 4; q++) {  // scale block q of every chunk
+            if (q < 3) load_x(q + 1, xr[(q + 1) & 1]);
+            const uint32_t(&x)[8] = xr[q & 1];
+            float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
-                    e2m1x8_to_half2x4(cur.wa[2 * q + h], a0, a1, a2, a3);
-                    e2m1x8_to_half2x4(cur.wb[2 * q + h], b0, b1, b2, b3);
-                    mma_f16_16816(c, a0, b0, a1, b1, x[4 * h + 0], x[4 * h + 1]);
-                    mma_f16_16816(c, a2, b2, a3, b3, x[4 * h + 2], x[4 * h + 3]);
-                }
-                acc_a = fmaf(c[0], scale_byte(cur.sa.x, q), acc_a);
-                acc_a = fmaf(c[1], scale_byte(cur.sa.y, q), acc_a);
-                acc_b = fmaf(c[2], scale_byte(cur.sb.x, q), acc_b);
-                acc_b = fmaf(c[3], scale_byte(cur.sb.y, q), acc_b);
+            for (int h = 0; h < 2; h++) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                e2m1x8_to_half2x4(cur.wa[2 * q + h], a0, a1, a2, a3);
+                e2m1x8_to_half2x4(cur.wb[2 * q + h], b0, b1, b2, b3);
+                mma_f16_16816(c, a0, b0, a1, b1, x[4 * h + 0], x[4 * h + 1]);
+                mma_f16_16816(c, a2, b2, a3, b3, x[4 * h + 2], x[4 * h + 3]);
             }
-            if (sn < nsteps) cur = nxt;
+            acc_a = fmaf(c[0], scale_byte(cur.sa.x, q), acc_a);
+            acc_a = fmaf(c[1], scale_byte(cur.sa.y, q), acc_a);
+            acc_b = fmaf(c[2], scale_byte(cur.sb.x, q), acc_b);
+            acc_b = fmaf(c[3], scale_byte(cur.sb.y, q), acc_b);
         }
+        if (++ck < nsw) return;
 
+        // ---- end of a row tile ----
+        ck = 0;
+        const int j = cj++;
+        const int tile = cid + j * ncl;
         // lanes t=0,1 hold activation 0 (columns 0..3), lanes t=2,3 activation 1 (columns 4..7)
         acc_a += __shfl_xor_sync(0xffffffffu, acc_a, 1);
         acc_b += __shfl_xor_sync(0xffffffffu, acc_b, 1);
@@ -277,35 +361,59 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
             red[warp][g][t >> 1] = acc_a;
             red[warp][g + 8][t >> 1] = acc_b;
         }
+        acc_a = 0.0f;
+        acc_b = 0.0f;
         __syncthreads();
-        if (EPI == EPI_SILU_MUL) {
-            if (threadIdx.x < 8) {
-                const int r = threadIdx.x;
-                float gsum = 0.0f, usum = 0.0f;
-#pragma unroll
-                for (int w = 0; w < WARPS; w++) { gsum += red[w][r][0]; usum += red[w][r + 8][0]; }
-                const int orow = tile * 8 + r;
-                if (tile * 16 + r + 8 < M) {
-                    const float gf = round_f16(gsum), uf = round_f16(usum);
-                    const float sl = round_f16(gf / (1.0f + expf(-gf)));
-                    out[orow] = __float2half(sl * uf);
-                }
-            }
-        } else if (threadIdx.x < 16 * NACT) {
+        float (*pt)[2] = part[j & 1];
+        if (threadIdx.x < 32) {   // row r = tid & 15, activation a = tid >> 4
             const int r = threadIdx.x & 15, a = threadIdx.x >> 4;
             float v = 0.0f;
 #pragma unroll
             for (int w = 0; w < WARPS; w++) v += red[w][r][a];
-            const int row = tile * 16 + r;
-            if (row < M) {
-                if (EPI == EPI_RESIDUAL)
-                    out[row] = __float2half(__half2float(ex.residual[row]) + round_f16(v));
-                else
-                    out[(size_t)a * M + row] = __float2half(v);
+            pt[r][a] = v;
+        }
+        if (S > 1) cluster_sync_all();   // every CTA's partial sums are visible cluster-wide
+        else __syncthreads();
+        if (crank == 0) {
+            if (EPI == EPI_SILU_MUL) {
+                if (threadIdx.x < 8) {
+                    const int r = threadIdx.x;
+                    float gsum = pt[r][0], usum = pt[r + 8][0];
+                    for (int c = 1; c < S; c++) {
+                        gsum += ld_cluster_f32(&pt[r][0], c);
+                        usum += ld_cluster_f32(&pt[r + 8][0], c);
+                    }
+                    if (tile * 16 + r + 8 < M) {
+                        const float gf = round_f16(gsum), uf = round_f16(usum);
+                        const float sl = round_f16(gf / (1.0f + expf(-gf)));
+                        out[tile * 8 + r] = __float2half(sl * uf);
+                    }
+                }
+            } else if (threadIdx.x < 16 * NACT) {
+                const int r = threadIdx.x & 15, a = threadIdx.x >> 4;
+                float v = pt[r][a];
+                for (int c = 1; c < S; c++) v += ld_cluster_f32(&pt[r][a], c);
+                const int row = tile * 16 + r;
+                if (row < M) {
+                    if (EPI == EPI_RESIDUAL)
+                        out[row] = __float2half(__half2float(ex.residual[row]) + round_f16(v));
+                    else
+                        out[(size_t)a * M + row] = __float2half(v);
+                }
             }
         }
-        __syncthreads();
+        // `red` is rewritten only after the next tile's K loop and `part` alternates, so no
+        // second barrier is needed here: a CTA can be at most one tile ahead of the leader's
+        // reads, because the next tile's cluster barrier needs the leader too.
+    };
+
+    WeightRegs other;
+    const int total = my_tiles * nsw;
+    for (int e = 0; e < total; e += 2) {
+        do_elem(cur, other);
+        if (e + 1 < total) do_elem(other, cur);
     }
+    if (S > 1) cluster_sync_all();   // no CTA may exit while a peer can still read its shared memory
 }
 
 // Generic path for shapes or pointers the tensor-core kernel does not take (K % 128 != 0, or
@@ -363,6 +471,8 @@ struct GemvConfig {
     int ctas_per_sm = 0;   // 0 = choose from the occupancy calculator
     int force_generic = 0;
     int no_pdl = 0;        // 1 = plain stream-ordered launches (no programmatic dependent launch)
+    int max_split = 0;     // largest cluster K split the planner may pick (0 or 1 = none; 2; 4)
+    int force_split = 0;   // 0 = planner decides; 1, 2 or 4 = use exactly this K split
 };
 static GemvConfig g_cfg;
 static int g_num_sms = 0;
@@ -378,39 +488,86 @@ static int num_sms() {
     return g_num_sms;
 }
 
+// Work partition of one GEMV: CTAs of `warps` warps, clusters of `split` CTAs that share a row
+// tile's K range, `grid` CTAs in total.  Chosen so that every cluster gets the same number of
+// tiles and as many of the machine's warp slots as possible are busy over whole rounds: a grid
+// that simply filled every slot leaves most CTAs idle in its last round (1088 tiles on 888 slots:
+// two rounds, the second 22 % full), and with few row tiles (M = 5120: 320) only the K split
+// provides enough CTAs.
+struct GemvPlan { int warps, split, grid; };
+
+static GemvPlan plan_gemv(int M, int K) {
+    const int ntiles = (M + 15) / 16, nsteps = (K + 255) / 256;
+    GemvPlan best = {4, 1, ntiles};
+    double best_score = -1.0;
+    for (int w = 4; w <= 8; w += 4) {
+        if (g_cfg.warps && g_cfg.warps != w && (g_cfg.warps == 4 || g_cfg.warps == 8)) continue;
+        const int slots = num_sms() * (24 / w);
+        for (int sp = 1; sp <= 4; sp *= 2) {
+            if (sp > (g_cfg.max_split ? g_cfg.max_split : 1) && !g_cfg.force_split) continue;
+            if (g_cfg.force_split && sp != g_cfg.force_split) continue;
+            if (sp * w > nsteps && sp > 1 && !g_cfg.force_split) continue;  // nothing left to split
+            const long long units = (long long)ntiles * sp;
+            const int r = (int)((units + slots - 1) / slots);      // tiles per cluster
+            const int clusters = (ntiles + r - 1) / r;
+            const int grid = clusters * sp;
+            const int nsw = (nsteps + sp * w - 1) / (sp * w);
+            const double fill = (double)ntiles / ((double)r * clusters);
+            double occ = (double)grid * w / (num_sms() * 24.0);
+            if (occ > 1.0) occ = 1.0;
+            const double kfill = (double)nsteps / ((double)nsw * sp * w);
+            const double cost = (sp == 1) ? 1.0 : (sp == 2 ? 0.97 : 0.94);  // cluster barrier per tile
+            const double score = fill * occ * kfill * cost;
+            if (score > best_score + 1e-9) {
+                best_score = score;
+                best = {w, sp, grid};
+            }
+        }
+    }
+    return best;
+}
+
 template <int WARPS, int NACT, int PRO, int EPI>
 static cudaError_t launch_mma(const void* packed, const void* scales, const void* a0, const void* a1,
-                              void* out, int M, int K, cudaStream_t st, const GemvExtra& ex) {
+                              void* out, int M, int K, cudaStream_t st, const GemvExtra& ex,
+                              const GemvPlan& plan) {
     const int smem = (PRO == PRO_RMSNORM) ? K * 2 : 0;
-    static int occ_cache[2] = {0, 0};  // [0]: no dynamic shared memory, [1]: last K used
-    static int occ_k = -1;
-    int occ;
-    if (smem == 0 ? occ_cache[0] == 0 : occ_k != K) {
-        if (smem > 48 * 1024 &&
-            cudaFuncSetAttribute(gemv_mma_kernel<WARPS, NACT, PRO, EPI>,
+    static int max_smem_set = 0;
+    if (smem > 48 * 1024 && smem > max_smem_set) {
+        if (cudaFuncSetAttribute(gemv_mma_kernel<WARPS, NACT, PRO, EPI>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return cudaErrorInvalidValue;
-        int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(
-                &n, gemv_mma_kernel<WARPS, NACT, PRO, EPI>, WARPS * 32, smem) != cudaSuccess || n <= 0)
-            n = 2;
-        if (smem == 0) occ_cache[0] = n; else { occ_cache[1] = n; occ_k = K; }
+        max_smem_set = smem;
     }
-    occ = smem == 0 ? occ_cache[0] : occ_cache[1];
-    const int per_sm = g_cfg.ctas_per_sm > 0 ? g_cfg.ctas_per_sm : occ;
     const int ntiles = (M + 15) / 16;
-    int grid = num_sms() * per_sm;
-    if (grid > ntiles) grid = ntiles;
+    int grid = plan.grid;
+    if (g_cfg.ctas_per_sm > 0) {
+        grid = num_sms() * g_cfg.ctas_per_sm;
+        if (grid > ntiles * plan.split) grid = ntiles * plan.split;
+        grid -= grid % plan.split;
+        if (grid < plan.split) grid = plan.split;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(WARPS * 32);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (!g_cfg.no_pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    if (plan.split > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = (unsigned)plan.split;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        na++;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = g_cfg.no_pdl ? 0 : 1;
+    cfg.numAttrs = na;
     return cudaLaunchKernelEx(&cfg, gemv_mma_kernel<WARPS, NACT, PRO, EPI>, (const uint8_t*)packed,
                               (const uint8_t*)scales, (const __half*)a0, (const __half*)a1,
                               (__half*)out, M, K, ex);
@@ -432,18 +589,19 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
     const bool fast = !g_cfg.force_generic && (K % 128 == 0) && aligned(packed, 32) &&
                       aligned(scales, 8);
     if (fast) {
-        int warps = g_cfg.warps;
-        // few row tiles or a long K: spread each tile's K range over 8 warps; many tiles: 4 warps
-        // per CTA and more resident CTAs (measured on B200 over the 27B layer shapes)
-        if (warps == 0) warps = (K >= 8192 || (M + 15) / 16 <= 3 * num_sms()) ? 8 : 4;
+        GemvPlan plan = plan_gemv(M, K);
+        if (g_cfg.warps == 2) plan = {2, 1, (M + 15) / 16 < num_sms() * 12 ? (M + 15) / 16 : num_sms() * 12};
+        const int warps = plan.warps;
         const GemvExtra none = {nullptr, 0.0f, nullptr};
         if (nact == 1) {
-            e = (warps == 8) ? launch_mma<8, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none)
-              : (warps == 2) ? launch_mma<2, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none)
-                             : launch_mma<4, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none);
+            e = (warps == 8) ? launch_mma<8, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none, plan)
+              : (warps == 2) ? launch_mma<2, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none, plan)
+                             : launch_mma<4, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none, plan);
         } else {
-            e = (warps == 8) ? launch_mma<8, 2, 0, 0>(packed, scales, a0, a1, out, M, K, st, none)
-                             : launch_mma<4, 2, 0, 0>(packed, scales, a0, a1, out, M, K, st, none);
+            if (plan.warps == 2) plan.warps = 4;
+            e = (plan.warps == 8)
+                    ? launch_mma<8, 2, 0, 0>(packed, scales, a0, a1, out, M, K, st, none, plan)
+                    : launch_mma<4, 2, 0, 0>(packed, scales, a0, a1, out, M, K, st, none, plan);
         }
     } else {
         const unsigned grid = (unsigned)((M + 7) / 8);
@@ -479,12 +637,23 @@ int gemv_ex_dispatch(const void* packed, const void* scales, const void* act, vo
     if (epilogue == EPI_SILU_MUL && M % 16 != 0) return NVFP4_ERR_SHAPE;
     const GemvExtra ex = {(const float*)norm_w1, eps, (const __half*)residual};
     cudaStream_t st = (cudaStream_t)stream;
-    int warps = g_cfg.warps;
-    if (warps != 4 && warps != 8) warps = (K >= 8192 || (M + 15) / 16 <= 3 * num_sms()) ? 8 : 4;
+    GemvPlan plan = plan_gemv(M, K);
+    if (prologue == PRO_RMSNORM) {
+        // the prologue keeps PRO_NV vectors of 8 activations per thread
+        if (K > PRO_NV * 8 * 256) return NVFP4_ERR_SHAPE;
+        if (K > PRO_NV * 8 * 128 && plan.warps != 8) {
+            const int save = g_cfg.warps;
+            g_cfg.warps = 8;
+            plan = plan_gemv(M, K);
+            g_cfg.warps = save;
+        }
+    }
+    const int warps = plan.warps;
     cudaError_t e;
 #define NVFP4_EX_CASE(P, E)                                                                     \
-    e = (warps == 8) ? launch_mma<8, 1, P, E>(packed, scales, act, nullptr, out, M, K, st, ex)  \
-                     : launch_mma<4, 1, P, E>(packed, scales, act, nullptr, out, M, K, st, ex)
+    e = (warps == 8)                                                                            \
+            ? launch_mma<8, 1, P, E>(packed, scales, act, nullptr, out, M, K, st, ex, plan)     \
+            : launch_mma<4, 1, P, E>(packed, scales, act, nullptr, out, M, K, st, ex, plan)
     if (prologue == PRO_NONE) {
         if (epilogue == EPI_STORE) { NVFP4_EX_CASE(0, 0); }
         else if (epilogue == EPI_RESIDUAL) { NVFP4_EX_CASE(0, 1); }
@@ -558,6 +727,14 @@ int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int flags) {
     nvfp4::g_cfg.ctas_per_sm = ctas_per_sm;
     nvfp4::g_cfg.force_generic = flags & 1;
     nvfp4::g_cfg.no_pdl = (flags >> 1) & 1;
+    {
+        const int ms = (flags >> 4) & 7;   // bits 4..6: largest cluster K split (0 = planner decides)
+        if (!(ms == 0 || ms == 1 || ms == 2 || ms == 4)) return NVFP4_ERR_SHAPE;
+        nvfp4::g_cfg.max_split = ms;
+        const int fs = (flags >> 8) & 7;   // bits 8..10: force this cluster K split
+        if (!(fs == 0 || fs == 1 || fs == 2 || fs == 4)) return NVFP4_ERR_SHAPE;
+        nvfp4::g_cfg.force_split = fs;
+    }
     return NVFP4_OK;
 }
 

@@ -40,7 +40,7 @@ def fused(lib, p, s, x, M, K, pro_w1=None, epi=0, residual=None, out_rows=None):
     return rc, o[:n]
 
 
-@pytest.mark.parametrize("M,K", [(772, 256), (5120, 5120), (100, 17408), (1000, 512)])
+@pytest.mark.parametrize("M,K", [(772, 256), (5120, 5120), (100, 10240), (1000, 512), (40, 6144)])
 def test_fused_rmsnorm_prologue_and_residual(lib, M, K):
     w = oc.synthetic_weight(M, K, seed=M + K)
     p, s = oc.encode(w)
@@ -76,8 +76,12 @@ def test_fused_silu_mul_epilogue(lib, inter, K):
     s = interleave_gate_up(torch.from_numpy(gs), torch.from_numpy(us)).numpy()
     rc, got = fused(lib, p, s, x, 2 * inter, K, epi=2, out_rows=inter)
     assert rc == 0
+    # g and u are each within one fp16 step of the oracle's; through silu, its fp16 rounding and
+    # the product that is a few fp16 steps in rare cases, so the bound is relative
     d = ulp_diff_f16(got, want)
-    assert (d <= 2).all() and (d == 0).mean() > 0.97, (d.max(), (d == 0).mean())
+    assert (d == 0).mean() > 0.99, (d == 0).mean()
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert (err <= 4e-3 * np.abs(want.astype(np.float64)) + 1e-6).all(), d.max()
 
 
 def test_fused_rejects_bad_arguments(lib):
@@ -89,6 +93,7 @@ def test_fused_rejects_bad_arguments(lib):
     assert f(one, one, one, one, 16, 128, 0, z, 1e-6, 1, z, None) == -2      # residual missing
     assert f(one, one, one, one, 24, 128, 0, z, 1e-6, 2, z, None) == -2      # M % 16 for gate/up
     assert f(one, one, one, one, 16, 128, 0, z, 1e-6, 3, z, None) == -2
+    assert f(one, one, one, one, 16, 17408, 1, one, 1e-6, 0, z, None) == -2   # prologue: K <= 10240
 
 
 def test_embed_attn_prep_argmax(lib):

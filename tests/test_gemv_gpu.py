@@ -81,7 +81,7 @@ def test_both_kernels_agree_and_config_hook(lib):
     outs = []
     try:
         for cfg in ((0, 0, 0), (2, 0, 0), (4, 1, 0), (8, 0, 0), (0, 0, 1), (0, 0, 2),
-                    (4, 0, 0x40), (8, 0, 0x30), (4, 2, 0x60), (8, 1, 0x42)):
+                    (4, 0, 0x200), (8, 0, 0x400), (4, 2, 0x200), (8, 1, 0x402), (4, 0, 0x100), (0, 0, 0x10)):
             assert lib.nvfp4_b200_gemv_config(*cfg) == 0
             rc, y = gemv(lib, p, s, a)
             assert rc == 0
@@ -94,10 +94,11 @@ def test_both_kernels_agree_and_config_hook(lib):
         assert oc.rel_error_floored(y, outs[0].astype(np.float64)).max() <= 1e-3
 
 
-@pytest.mark.parametrize("flags", [0x40, 0x30, 0x60])
+@pytest.mark.parametrize("flags", [0x200, 0x400])
 @pytest.mark.parametrize("M,K", [(1, 128), (100, 768), (257, 6144), (33, 17408), (1024, 5120)])
-def test_async_ring_kernel(lib, M, K, flags):
-    # the cp.async ring variant of the tensor-core kernel, incl. ragged rows and K % 256 != 0
+def test_cluster_split_k(lib, M, K, flags):
+    # row tiles shared by a cluster of 2 or 4 CTAs (partial sums combined through distributed
+    # shared memory), incl. ragged rows, K % 256 != 0 and more CTAs than K steps
     w = oc.synthetic_weight(M, K, seed=M * 7 + K)
     p, s = oc.encode(w)
     a = oc.synthetic_act(K, seed=K + 1)
