@@ -351,9 +351,18 @@ def run_ours(args):
     else:
         job_bytes = float(total_alg)
 
-    if rank != 0:
+    def finish():
+        """Leave without tearing the communicator down: destroying an NCCL process group while a
+        captured graph still references its kernels has been seen to block forever at exit."""
+        sys.stdout.flush()
+        sys.stderr.flush()
         if world > 1:
-            dist.destroy_process_group()
+            dist.barrier()
+            torch.cuda.synchronize()
+            os._exit(0)
+
+    if rank != 0:
+        finish()
         return
 
     value = job_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -390,8 +399,7 @@ def run_ours(args):
         "clocks": summarise_clocks(clock_lines),
     }
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    finish()
 
 
 SHAPES_27B = [("lm_head", VOCAB, HIDDEN, 1), ("down_proj", HIDDEN, INTER, 64),
@@ -504,14 +512,21 @@ def decode_step_bytes(cfg, context):
 
 def run_decode(args, quiet=False):
     """27B-shape decode: 512-token prompt fed through the step graph, then 63 greedy tokens
-    (BASELINE config 3).  Random-init NVFP4 weights, random token ids."""
+    (BASELINE configs 3 and 4).  Random-init NVFP4 weights, random token ids.  Under torchrun the
+    model is tensor-parallel over the ranks (one process per GPU, NCCL all-reduce in the graph)."""
     import torch
+    import torch.distributed as dist
 
     from nvfp4_v100_b200.engine import DecodeEngine, ModelConfig
 
-    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = ModelConfig(max_len=1024, vocab=args.vocab)
-    eng = DecodeEngine(cfg)
+    eng = DecodeEngine(cfg, device=f"cuda:{local}", tp_rank=rank, tp_world=world)
     eng.load_random(seed=0)
     prompt = np.random.default_rng(0).integers(0, cfg.vocab, args.prompt_len)
     eng.reset(int(prompt[0]))
@@ -519,20 +534,28 @@ def run_decode(args, quiet=False):
         eng.pos.fill_(args.fake_context - 1)
         eng.len.fill_(args.fake_context)
     n_launch = eng.capture(n_warmup=1)
-    torch.cuda.synchronize()
+    n_coll = eng.n_collective
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    barrier()
     t0 = time.perf_counter()
     for t in range(1, len(prompt)):
         eng.step()
         eng.tok.fill_(int(prompt[t]))
-    torch.cuda.synchronize()
+    barrier()
     prefill_s = time.perf_counter() - t0
     n_gen = args.gen
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
     e0.record()
     for _ in range(n_gen):
         eng.step()
     e1.record()
-    torch.cuda.synchronize()
+    barrier()
     ms = e0.elapsed_time(e1)
     # end to end: read every token back on the host as the reference loop does (.item() per step)
     snap_pos = int(eng.pos.item())
@@ -541,26 +564,39 @@ def run_decode(args, quiet=False):
     for _ in range(min(n_gen, cfg.max_len - snap_pos - 1)):
         eng.step()
         toks.append(int(eng.tok.item()))
+    barrier()
     e2e_s = time.perf_counter() - t0
-    peak, peak_kind = measured_peak()
-    step_bytes = decode_step_bytes(cfg, args.prompt_len + n_gen // 2)
-    res = {
-        "metric": "decode_tok_s", "value": n_gen / (ms * 1e-3), "unit": "tok/s",
-        "ms_per_step": ms / n_gen, "n_gpus": 1, "prompt_len": int(args.prompt_len), "gen": n_gen,
-        "kernel_launches_per_step": n_launch,
-        "prefill_by_decode_tok_s": (len(prompt) - 1) / prefill_s,
-        "e2e": {"value": len(toks) / e2e_s, "unit": "tok/s", "d2h_bytes_per_step": 8,
-                "h2d_bytes_per_step": 0},
-        "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
-                     "achieved": step_bytes / (ms / n_gen * 1e-3) / 1e9, "peak": peak,
-                     "unit": "GB/s", "frac": step_bytes / (ms / n_gen * 1e-3) / 1e9 / peak,
-                     "peak_kind": peak_kind},
-        "config": {"workload": "decode_27b_shape", "layers": cfg.n_layers, "hidden": cfg.hidden,
-                   "vocab": cfg.vocab, "launch": "cuda_graph", "weights": "random NVFP4 bytes"},
-        "finite_logits": bool(torch.isfinite(eng.logits.float()).all().item()),
-    }
-    if not quiet:
-        print(json.dumps(res), flush=True)
+    if world > 1:
+        tm = torch.tensor([ms, e2e_s, prefill_s], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ms, e2e_s, prefill_s = (float(x) for x in tm)
+    res = None
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        step_bytes = decode_step_bytes(cfg, args.prompt_len + n_gen // 2)
+        per_gpu = step_bytes / world / (ms / n_gen * 1e-3) / 1e9
+        res = {
+            "metric": "decode_tok_s", "value": n_gen / (ms * 1e-3), "unit": "tok/s",
+            "ms_per_step": ms / n_gen, "n_gpus": world, "prompt_len": int(args.prompt_len),
+            "gen": n_gen, "kernel_launches_per_step": n_launch, "collectives_per_step": n_coll,
+            "scaling": "strong", "prefill_by_decode_tok_s": (len(prompt) - 1) / prefill_s,
+            "e2e": {"value": len(toks) / e2e_s, "unit": "tok/s", "d2h_bytes_per_step": 8,
+                    "h2d_bytes_per_step": 0},
+            "roofline": {"bound": "hbm", "algorithmic_bytes_per_step": step_bytes,
+                         "achieved": per_gpu, "peak": peak, "unit": "GB/s (per GPU)",
+                         "frac": per_gpu / peak, "peak_kind": peak_kind},
+            "config": {"workload": "decode_27b_shape", "layers": cfg.n_layers,
+                       "hidden": cfg.hidden, "vocab": cfg.vocab, "launch": "cuda_graph",
+                       "weights": "random NVFP4 bytes", "parallelism": f"tp{world}"},
+            "finite_logits": bool(torch.isfinite(eng.logits.float()).all().item()),
+        }
+        if not quiet:
+            print(json.dumps(res), flush=True)
+    if world > 1:
+        sys.stdout.flush()
+        dist.barrier()
+        torch.cuda.synchronize()
+        os._exit(0)
     del eng
     torch.cuda.empty_cache()
     return res

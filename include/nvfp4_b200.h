@@ -160,6 +160,15 @@ int launch_attn_prep(const void* qkv, const void* q_w1, const void* k_w1, const 
 int launch_argmax_advance(const void* logits, int vocab, void* tok, void* pos, void* len,
                           void* history, void* hist_count, int hist_cap, void* stream);
 
+/* Tensor-parallel glue (the reference has no multi-GPU path): h += y after the all-reduce of a
+ * K-split layer (fp16 [n], fp32 add, one rounding); per-rank argmax of a vocabulary slice into an
+ * fp32 pair (value, offset + index; offset + vocab <= 2^24); and the pick of the global maximum from
+ * all ranks' pairs (fp32 [world, 2]) with the counter updates of launch_argmax_advance.  0 / -1. */
+int launch_residual_add(void* h, const void* y, int n, void* stream);
+int launch_argmax_slice(const void* logits, int vocab, long long offset, void* cand, void* stream);
+int launch_pick_global_argmax(const void* cand_all, int world, void* tok, void* pos, void* len,
+                              void* history, void* hist_count, int hist_cap, void* stream);
+
 /* The DeltaNet step without a caller-provided workspace.  It has no counterpart in the reference,
  * whose caller always allocates the scratch tensor itself.  It exists for callers that cannot
  * allocate device memory at the point of the call: code that runs after all device memory has

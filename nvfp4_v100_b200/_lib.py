@@ -44,6 +44,9 @@ SIGNATURES = {
     "launch_embed_gather": ([_vp, _vp, _vp, _i, _ll, _vp], _i),
     "launch_attn_prep": ([_vp] * 10 + [_i, _i, _i, _f, _vp], _i),
     "launch_argmax_advance": ([_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),
+    "launch_residual_add": ([_vp, _vp, _i, _vp], _i),
+    "launch_argmax_slice": ([_vp, _i, _ll, _vp, _vp], _i),
+    "launch_pick_global_argmax": ([_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),
     "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
     "launch_dn_fused_heads": ([_vp] * 12 + [_i, _i, _f, _vp], _i),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),

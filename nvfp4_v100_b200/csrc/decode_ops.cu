@@ -156,9 +156,114 @@ argmax_advance_kernel(const __half* __restrict__ logits, int vocab, long long* _
     }
 }
 
+// h[i] = f16(f32(h[i]) + f32(y[i])): the residual add that follows the all-reduce of a K-split
+// layer's partial outputs in tensor-parallel decode.
+__global__ void __launch_bounds__(256)
+residual_add_kernel(__half* __restrict__ h, const __half* __restrict__ y, int n) {
+    const int i = (blockIdx.x * 256 + threadIdx.x) * 2;
+    if (i + 1 < n) {
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(h + i));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(y + i));
+        *reinterpret_cast<__half2*>(h + i) = __floats2half2_rn(a.x + b.x, a.y + b.y);
+    } else if (i < n) {
+        h[i] = __float2half(__half2float(h[i]) + __half2float(y[i]));
+    }
+}
+
+// Tensor-parallel greedy pick: every rank has the (value, global index) of its vocabulary slice's
+// maximum; cand holds all ranks' pairs [world][2] as fp32 (index stored exactly: vocab < 2^24).
+__global__ void pick_global_argmax_kernel(const float* __restrict__ cand, int world,
+                                          long long* __restrict__ tok, long long* __restrict__ pos,
+                                          long long* __restrict__ len,
+                                          long long* __restrict__ history,
+                                          long long* __restrict__ hist_count, int hist_cap) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    float best = -INFINITY;
+    long long bi = 0;
+    for (int r = 0; r < world; r++) {
+        const float v = cand[2 * r];
+        const long long i = (long long)cand[2 * r + 1];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+    *tok = bi;
+    if (history && hist_count) {
+        const long long n = *hist_count;
+        if (n < hist_cap) history[n] = bi;
+        *hist_count = n + 1;
+    }
+    if (pos) *pos += 1;
+    if (len) *len += 1;
+}
+
+// local argmax of a vocabulary slice -> cand[0] = value, cand[1] = offset + index
+__global__ void __launch_bounds__(1024)
+argmax_slice_kernel(const __half* __restrict__ logits, int vocab, long long offset,
+                    float* __restrict__ cand) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = t; i < vocab; i += 1024) {
+        const float v = __half2float(logits[i]);
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = s_v[lane];
+        bi = s_i[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            if (bi == 0x7fffffff) bi = 0;
+            cand[0] = best;
+            cand[1] = (float)(offset + bi);
+        }
+    }
+}
+
 }  // namespace nvfp4
 
 extern "C" {
+
+// h, y fp16 [n]: h += y (fp32 add, one rounding).  0 / -1.
+int launch_residual_add(void* h, const void* y, int n, void* stream) {
+    if (!h || !y || n <= 0) return -1;
+    nvfp4::residual_add_kernel<<<(n + 511) / 512, 256, 0, (cudaStream_t)stream>>>(
+        (__half*)h, (const __half*)y, n);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Tensor-parallel argmax, step 1: cand (fp32 [2]) = (max of logits[0..vocab), offset + argmax).
+int launch_argmax_slice(const void* logits, int vocab, long long offset, void* cand, void* stream) {
+    if (!logits || !cand || vocab <= 0 || offset < 0 || offset + vocab > (1 << 24)) return -1;
+    nvfp4::argmax_slice_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>((const __half*)logits, vocab,
+                                                                     offset, (float*)cand);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
+
+// Step 2, after an all-gather of every rank's cand pair into cand_all (fp32 [world, 2]): pick the
+// global maximum (lowest index among equals) and advance the step counters as
+// launch_argmax_advance does.
+int launch_pick_global_argmax(const void* cand_all, int world, void* tok, void* pos, void* len,
+                              void* history, void* hist_count, int hist_cap, void* stream) {
+    if (!cand_all || !tok || world <= 0) return -1;
+    nvfp4::pick_global_argmax_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(
+        (const float*)cand_all, world, (long long*)tok, (long long*)pos, (long long*)len,
+        (long long*)history, (long long*)hist_count, hist_cap);
+    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+}
 
 // table fp16 [vocab, hidden]; tok: device int64; out fp16 [hidden].  0, or -1 bad args / launch.
 int launch_embed_gather(const void* table, const void* tok, void* out, int hidden, long long vocab,

@@ -22,7 +22,7 @@ from dataclasses import dataclass, field
 import numpy as np
 import torch
 
-from . import _lib
+from . import _lib, tp
 
 vp = ctypes.c_void_p
 HEAD_DIM = 256      # attention head dim (fixed by the kernels)
@@ -111,28 +111,48 @@ class _Layer:
 class DecodeEngine:
     """Holds the prepared weights and all state of one sequence and replays the step graph."""
 
-    def __init__(self, cfg: ModelConfig, device: str = "cuda"):
+    def __init__(self, cfg: ModelConfig, device: str = "cuda", tp_rank: int = 0, tp_world: int = 1):
+        """tp_world > 1: this process holds shard tp_rank of a tensor-parallel group (one process
+        per GPU, torch.distributed initialised with the NCCL backend by the caller)."""
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; there is no CPU fallback")
         self.cfg = cfg
         self.dev = torch.device(device)
         self.lib = _lib.load()
+        self.rank, self.world = tp_rank, tp_world
+        c = cfg
+        W = tp_world
+        if c.hq % W or c.dn_kheads % W or c.dn_vheads % W or c.inter % (W * 128):
+            raise ValueError(f"model shapes do not split over {W} ranks")
+        if W > c.hkv and W % c.hkv:
+            raise ValueError("ranks must be a multiple of the KV heads when there are more ranks")
+        # local (per-rank) sizes
+        self.hq_l = c.hq // W
+        self.hkv_l = max(1, c.hkv // W)
+        self.nk_l, self.nv_l = c.dn_kheads // W, c.dn_vheads // W
+        self.inter_l = c.inter // W
+        self.conv_l = (2 * self.nk_l + self.nv_l) * DN_DIM
+        self.v_lo, self.v_hi = tp.split_range(c.vocab, W, tp_rank, 16) if c.vocab % 16 == 0 \
+            else tp.split_range(c.vocab, W, tp_rank, 1)
         self.layers: list[_Layer] = []
         self.graph = None
         self.n_launch = 0
-        c = cfg
+        self.n_collective = 0
         f16, f32, i64 = torch.float16, torch.float32, torch.int64
         z = lambda *s, dt=f16: torch.zeros(*s, dtype=dt, device=self.dev)
         self.h = z(c.hidden)
-        self.qkv = z(c.hq * 2 * HEAD_DIM + 2 * c.hkv * HEAD_DIM)
-        self.q_out = z(c.hq * HEAD_DIM)
-        self.gate_out = z(c.hq * HEAD_DIM)
-        self.attn_out = z(c.hq * HEAD_DIM)
-        self.dn_in = z(c.conv_dim + c.dn_vheads * DN_DIM + 2 * c.dn_vheads)
-        self.dn_out = z(c.dn_vheads * DN_DIM)
-        self.dn_scratch = z(c.conv_dim, dt=f32)
-        self.act = z(c.inter)
-        self.logits = z(c.vocab)
+        self.partial = z(c.hidden)          # K-split layer output before the all-reduce
+        self.qkv = z(self.hq_l * 2 * HEAD_DIM + 2 * self.hkv_l * HEAD_DIM)
+        self.q_out = z(self.hq_l * HEAD_DIM)
+        self.gate_out = z(self.hq_l * HEAD_DIM)
+        self.attn_out = z(self.hq_l * HEAD_DIM)
+        self.dn_in = z(self.conv_l + self.nv_l * DN_DIM + 2 * self.nv_l)
+        self.dn_out = z(self.nv_l * DN_DIM)
+        self.dn_scratch = z(self.conv_l, dt=f32)
+        self.act = z(self.inter_l)
+        self.logits = z(self.v_hi - self.v_lo)
+        self.cand = z(2, dt=f32)
+        self.cand_all = z(2 * W, dt=f32)
         self.tok = z(1, dt=i64)
         self.pos = z(1, dt=i64)            # index of the token being processed
         self.len = z(1, dt=i64)            # keys in the cache including that token
@@ -159,7 +179,7 @@ class DecodeEngine:
         fp16 embedding ~N(0, 0.02^2), unit norm weights: the throughput workload."""
         c = self.cfg
         g = torch.Generator(device=self.dev)
-        g.manual_seed(seed)
+        g.manual_seed(seed * 64 + self.rank)
 
         def rnd(M, K):
             p = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device=self.dev, generator=g)
@@ -172,52 +192,69 @@ class DecodeEngine:
         for i in range(c.n_layers):
             L = _Layer(c.is_attn(i), ones(c.hidden), ones(c.hidden))
             if L.attn:
-                L.w_in = rnd(c.hq * 2 * HEAD_DIM + 2 * c.hkv * HEAD_DIM, c.hidden)
-                L.w_out = rnd(c.hidden, c.hq * HEAD_DIM)
+                L.w_in = rnd(self.hq_l * 2 * HEAD_DIM + 2 * self.hkv_l * HEAD_DIM, c.hidden)
+                L.w_out = rnd(c.hidden, self.hq_l * HEAD_DIM)
                 L.extra = dict(
                     q_w1=ones(HEAD_DIM), k_w1=ones(HEAD_DIM),
-                    keys=torch.zeros(c.hkv, c.max_len, HEAD_DIM, dtype=torch.float16, device=self.dev),
-                    values=torch.zeros(c.hkv, c.max_len, HEAD_DIM, dtype=torch.float16, device=self.dev))
+                    keys=torch.zeros(self.hkv_l, c.max_len, HEAD_DIM, dtype=torch.float16, device=self.dev),
+                    values=torch.zeros(self.hkv_l, c.max_len, HEAD_DIM, dtype=torch.float16, device=self.dev))
             else:
-                L.w_in = rnd(c.conv_dim + c.dn_vheads * DN_DIM + 2 * c.dn_vheads, c.hidden)
-                L.w_out = rnd(c.hidden, c.dn_vheads * DN_DIM)
+                L.w_in = rnd(self.conv_l + self.nv_l * DN_DIM + 2 * self.nv_l, c.hidden)
+                L.w_out = rnd(c.hidden, self.nv_l * DN_DIM)
                 L.extra = dict(
-                    conv_w=(torch.randn(c.conv_dim, CONV_K, device=self.dev, generator=g) * 0.02).half(),
-                    conv_state=torch.zeros(c.conv_dim, CONV_K, dtype=torch.float16, device=self.dev),
-                    A_log=torch.log(torch.rand(c.dn_vheads, device=self.dev, generator=g) * 16 + 1e-3).half(),
-                    dt_bias=torch.ones(c.dn_vheads, dtype=torch.float16, device=self.dev),
+                    conv_w=(torch.randn(self.conv_l, CONV_K, device=self.dev, generator=g) * 0.02).half(),
+                    conv_state=torch.zeros(self.conv_l, CONV_K, dtype=torch.float16, device=self.dev),
+                    A_log=torch.log(torch.rand(self.nv_l, device=self.dev, generator=g) * 16 + 1e-3).half(),
+                    dt_bias=torch.ones(self.nv_l, dtype=torch.float16, device=self.dev),
                     norm_w=torch.ones(DN_DIM, dtype=torch.float16, device=self.dev),
-                    state=torch.zeros(c.dn_vheads, DN_DIM, DN_DIM, dtype=torch.float32, device=self.dev))
-            L.w_gu = rnd(2 * c.inter, c.hidden)
-            L.w_down = rnd(c.hidden, c.inter)
+                    state=torch.zeros(self.nv_l, DN_DIM, DN_DIM, dtype=torch.float32, device=self.dev))
+            L.w_gu = rnd(2 * self.inter_l, c.hidden)
+            L.w_down = rnd(c.hidden, self.inter_l)
             self.layers.append(L)
-        self.embed = (torch.randn(c.vocab, c.hidden, device=self.dev, generator=g) * 0.02).half()
+        ge = torch.Generator(device=self.dev)
+        ge.manual_seed(seed + 7919)          # the embedding is replicated: same on every rank
+        self.embed = (torch.randn(c.vocab, c.hidden, device=self.dev, generator=ge) * 0.02).half()
         self.final_w1 = ones(c.hidden)
-        self.lm_head = rnd(c.vocab, c.hidden)
+        self.lm_head = rnd(self.v_hi - self.v_lo, c.hidden)
 
     def load_weights(self, weights: dict):
-        """``weights``: reference-named numpy arrays, e.g. ``layers.3.self_attn.q_proj`` ->
-        (packed u8 [M, K/2], scales u8 [M, K/16]) and ``layers.3.input_layernorm.weight`` ->
-        fp16 array, ``embed_tokens`` fp16 [V, H], ``norm.weight``, ``lm_head`` (packed, scales).
-        Matrices are uploaded raw and fused by rows on the device."""
+        """``weights``: reference-named numpy arrays of the FULL model, e.g.
+        ``layers.3.self_attn.q_proj`` -> (packed u8 [M, K/2], scales u8 [M, K/16]),
+        ``layers.3.input_layernorm.weight`` -> fp16 array, ``embed_tokens`` fp16 [V, H],
+        ``norm.weight``, ``lm_head`` (packed, scales).  Each rank cuts its shard out of the raw
+        bytes (rows for q/k/v, in_proj, gate/up, lm_head; a K range for o_proj, out_proj,
+        down_proj), uploads it and fuses projections that share an input by rows on the device."""
         c = self.cfg
         dev = self.dev
+        R, W = self.rank, self.world
 
-        def up(name):
-            p, s = weights[name]
-            return torch.from_numpy(np.ascontiguousarray(p)).to(dev), \
-                torch.from_numpy(np.ascontiguousarray(s)).to(dev)
+        def dv(a):
+            return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
 
         def w1(name):
             return (1.0 + torch.from_numpy(np.asarray(weights[name], dtype=np.float16)).float()).to(dev)
 
-        def f16(name):
-            return torch.from_numpy(np.ascontiguousarray(weights[name], dtype=np.float16)).to(dev)
+        def f16(a):
+            return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float16)).to(dev)
 
-        def cat(names, K):
-            ps, ss = zip(*(up(n) for n in names))
-            p, s = torch.cat(ps, 0), torch.cat(ss, 0)
+        def mat(parts, K):
+            p = torch.cat([dv(x[0]) for x in parts], 0)
+            s = torch.cat([dv(x[1]) for x in parts], 0)
             return self._mat(p, s, p.shape[0], K)
+
+        def rows(name, unit):
+            p, s = weights[name]
+            lo, hi = tp.split_range(p.shape[0], W, R, unit)
+            return tp.shard_rows(p, s, lo, hi)
+
+        def kslice(name, K):
+            p, s = weights[name]
+            pk, sk, k0, k1 = tp.shard_k(p, s, K, W, R)
+            return (pk, sk), k1 - k0
+
+        def vec_rows(a, unit):
+            lo, hi = tp.split_range(a.shape[0], W, R, unit)
+            return a[lo:hi]
 
         self.layers = []
         for i in range(c.n_layers):
@@ -226,33 +263,47 @@ class DecodeEngine:
                        w1(pre + "post_attention_layernorm.weight"))
             if L.attn:
                 a = pre + "self_attn."
-                L.w_in = cat([a + "q_proj", a + "k_proj", a + "v_proj"], c.hidden)
-                L.w_out = cat([a + "o_proj"], c.hq * HEAD_DIM)
+                kp, ks = weights[a + "k_proj"]
+                vpk, vs = weights[a + "v_proj"]
+                L.w_in = mat([rows(a + "q_proj", 2 * HEAD_DIM),
+                              tp.shard_kv_heads(kp, ks, c.hkv, W, R)[:2],
+                              tp.shard_kv_heads(vpk, vs, c.hkv, W, R)[:2]], c.hidden)
+                wo, ko = kslice(a + "o_proj", c.hq * HEAD_DIM)
+                L.w_out = mat([wo], ko)
                 L.extra = dict(
                     q_w1=w1(a + "q_norm.weight"), k_w1=w1(a + "k_norm.weight"),
-                    keys=torch.zeros(c.hkv, c.max_len, HEAD_DIM, dtype=torch.float16, device=dev),
-                    values=torch.zeros(c.hkv, c.max_len, HEAD_DIM, dtype=torch.float16, device=dev))
+                    keys=torch.zeros(self.hkv_l, c.max_len, HEAD_DIM, dtype=torch.float16, device=dev),
+                    values=torch.zeros(self.hkv_l, c.max_len, HEAD_DIM, dtype=torch.float16, device=dev))
             else:
                 a = pre + "linear_attn."
-                L.w_in = cat([a + "in_proj_qkv", a + "in_proj_z", a + "in_proj_b", a + "in_proj_a"],
-                             c.hidden)
-                L.w_out = cat([a + "out_proj"], c.dn_vheads * DN_DIM)
+                groups = (c.dn_kheads * DN_DIM, c.dn_kheads * DN_DIM, c.dn_vheads * DN_DIM)
+                qp, qs = weights[a + "in_proj_qkv"]
+                L.w_in = mat([tp.shard_grouped_rows(qp, qs, groups, DN_DIM, W, R, np.concatenate),
+                              rows(a + "in_proj_z", DN_DIM), rows(a + "in_proj_b", 1),
+                              rows(a + "in_proj_a", 1)], c.hidden)
+                wo, ko = kslice(a + "out_proj", c.dn_vheads * DN_DIM)
+                L.w_out = mat([wo], ko)
+                cw = np.asarray(weights[a + "conv1d.weight"], dtype=np.float16).reshape(c.conv_dim, CONV_K)
+                cw_l, _ = tp.shard_grouped_rows(cw, cw, groups, DN_DIM, W, R, np.concatenate)
                 L.extra = dict(
-                    conv_w=f16(a + "conv1d.weight").reshape(c.conv_dim, CONV_K).contiguous(),
-                    conv_state=torch.zeros(c.conv_dim, CONV_K, dtype=torch.float16, device=dev),
-                    A_log=f16(a + "A_log"), dt_bias=f16(a + "dt_bias"),
-                    norm_w=f16(a + "norm.weight"),
-                    state=torch.zeros(c.dn_vheads, DN_DIM, DN_DIM, dtype=torch.float32, device=dev))
+                    conv_w=f16(cw_l),
+                    conv_state=torch.zeros(self.conv_l, CONV_K, dtype=torch.float16, device=dev),
+                    A_log=f16(vec_rows(np.asarray(weights[a + "A_log"]), 1)),
+                    dt_bias=f16(vec_rows(np.asarray(weights[a + "dt_bias"]), 1)),
+                    norm_w=f16(weights[a + "norm.weight"]),
+                    state=torch.zeros(self.nv_l, DN_DIM, DN_DIM, dtype=torch.float32, device=dev))
             m = pre + "mlp."
-            gp, gs = up(m + "gate_proj")
-            upp, ups = up(m + "up_proj")
-            L.w_gu = self._mat(interleave_gate_up(gp, upp), interleave_gate_up(gs, ups),
-                               2 * c.inter, c.hidden)
-            L.w_down = cat([m + "down_proj"], c.inter)
+            gp, gs = rows(m + "gate_proj", 128)
+            upp, ups = rows(m + "up_proj", 128)
+            L.w_gu = self._mat(interleave_gate_up(dv(gp), dv(upp)), interleave_gate_up(dv(gs), dv(ups)),
+                               2 * self.inter_l, c.hidden)
+            wd, kd = kslice(m + "down_proj", c.inter)
+            L.w_down = mat([wd], kd)
             self.layers.append(L)
-        self.embed = f16("embed_tokens")
+        self.embed = f16(weights["embed_tokens"])
         self.final_w1 = w1("norm.weight")
-        self.lm_head = cat(["lm_head"], c.hidden)
+        lp, ls = weights["lm_head"]
+        self.lm_head = mat([tp.shard_rows(lp, ls, self.v_lo, self.v_hi)], c.hidden)
 
     # ------------------------------------------------------------------ one step
     def _gemv(self, st, m: _Mat, x, out, pro_w1=None, epi=0, residual=None):
@@ -265,16 +316,34 @@ class DecodeEngine:
             raise RuntimeError(f"launch_nvfp4_gemv_fused rc={rc} (M={m.M}, K={m.K})")
         self.n_launch += 1
 
+    def _row_parallel(self, st, m: _Mat, x):
+        """o_proj / out_proj / down_proj: h += W x.  One GPU: the residual add is the GEMV's
+        epilogue.  Tensor parallel: each rank's K slice gives a partial vector; all-reduce (NCCL,
+        captured in the graph), then the residual add."""
+        if self.world == 1:
+            self._gemv(st, m, x, self.h, epi=1, residual=self.h)
+            return
+        import torch.distributed as dist
+
+        self._gemv(st, m, x, self.partial)
+        dist.all_reduce(self.partial)
+        self.n_collective += 1
+        rc = self.lib.launch_residual_add(vp(self.h.data_ptr()), vp(self.partial.data_ptr()),
+                                          self.cfg.hidden, st)
+        assert rc == 0, rc
+        self.n_launch += 1
+
     def enqueue_step(self):
         """Enqueue one decode step on torch's current stream (capturable)."""
         c, lib = self.cfg, self.lib
         st = vp(torch.cuda.current_stream().cuda_stream)
         self.n_launch = 0
+        self.n_collective = 0
         rc = lib.launch_embed_gather(vp(self.embed.data_ptr()), vp(self.tok.data_ptr()),
                                      vp(self.h.data_ptr()), c.hidden, c.vocab, st)
         assert rc == 0, rc
         self.n_launch += 1
-        nq = c.conv_dim
+        nq = self.conv_l
         for L in self.layers:
             e = L.extra
             if L.attn:
@@ -283,41 +352,57 @@ class DecodeEngine:
                     vp(self.qkv.data_ptr()), vp(e["q_w1"].data_ptr()), vp(e["k_w1"].data_ptr()),
                     vp(self.cos.data_ptr()), vp(self.sin.data_ptr()), vp(self.pos.data_ptr()),
                     vp(self.q_out.data_ptr()), vp(self.gate_out.data_ptr()),
-                    vp(e["keys"].data_ptr()), vp(e["values"].data_ptr()), c.hq, c.hkv, c.max_len,
-                    float(c.rms_eps), st)
+                    vp(e["keys"].data_ptr()), vp(e["values"].data_ptr()), self.hq_l, self.hkv_l,
+                    c.max_len, float(c.rms_eps), st)
                 assert rc == 0, rc
                 rc = lib.launch_attn_decode_heads(
                     vp(self.q_out.data_ptr()), vp(e["keys"].data_ptr()), vp(e["values"].data_ptr()),
                     vp(self.len.data_ptr()), vp(self.gate_out.data_ptr()),
-                    vp(self.attn_out.data_ptr()), c.max_len, c.hq, c.hkv, float(HEAD_DIM) ** -0.5, st)
+                    vp(self.attn_out.data_ptr()), c.max_len, self.hq_l, self.hkv_l,
+                    float(HEAD_DIM) ** -0.5, st)
                 assert rc == 0, rc
                 self.n_launch += 2
-                self._gemv(st, L.w_out, self.attn_out, self.h, epi=1, residual=self.h)
+                self._row_parallel(st, L.w_out, self.attn_out)
             else:
                 self._gemv(st, L.w_in, self.h, self.dn_in, pro_w1=L.in_w1)
                 base = self.dn_in.data_ptr()
                 zoff = nq * 2
-                boff = zoff + c.dn_vheads * DN_DIM * 2
-                aoff = boff + c.dn_vheads * 2
+                boff = zoff + self.nv_l * DN_DIM * 2
+                aoff = boff + self.nv_l * 2
                 rc = lib.launch_dn_fused_heads(
                     vp(base), vp(base + zoff), vp(base + boff), vp(base + aoff),
                     vp(e["conv_w"].data_ptr()), vp(e["conv_state"].data_ptr()),
                     vp(e["A_log"].data_ptr()), vp(e["dt_bias"].data_ptr()),
                     vp(e["norm_w"].data_ptr()), vp(e["state"].data_ptr()),
                     vp(self.dn_scratch.data_ptr()), vp(self.dn_out.data_ptr()),
-                    c.dn_kheads, c.dn_vheads, float(c.rms_eps), st)
+                    self.nk_l, self.nv_l, float(c.rms_eps), st)
                 assert rc == 0, rc
                 self.n_launch += 2
-                self._gemv(st, L.w_out, self.dn_out, self.h, epi=1, residual=self.h)
+                self._row_parallel(st, L.w_out, self.dn_out)
             self._gemv(st, L.w_gu, self.h, self.act, pro_w1=L.post_w1, epi=2)
-            self._gemv(st, L.w_down, self.act, self.h, epi=1, residual=self.h)
+            self._row_parallel(st, L.w_down, self.act)
         self._gemv(st, self.lm_head, self.h, self.logits, pro_w1=self.final_w1)
-        rc = lib.launch_argmax_advance(
-            vp(self.logits.data_ptr()), c.vocab, vp(self.tok.data_ptr()), vp(self.pos.data_ptr()),
-            vp(self.len.data_ptr()), vp(self.history.data_ptr()), vp(self.hist_count.data_ptr()),
-            self.hist_cap, st)
-        assert rc == 0, rc
-        self.n_launch += 1
+        if self.world == 1:
+            rc = lib.launch_argmax_advance(
+                vp(self.logits.data_ptr()), c.vocab, vp(self.tok.data_ptr()), vp(self.pos.data_ptr()),
+                vp(self.len.data_ptr()), vp(self.history.data_ptr()), vp(self.hist_count.data_ptr()),
+                self.hist_cap, st)
+            assert rc == 0, rc
+            self.n_launch += 1
+        else:
+            import torch.distributed as dist
+
+            rc = lib.launch_argmax_slice(vp(self.logits.data_ptr()), self.v_hi - self.v_lo,
+                                         self.v_lo, vp(self.cand.data_ptr()), st)
+            assert rc == 0, rc
+            dist.all_gather_into_tensor(self.cand_all, self.cand)
+            self.n_collective += 1
+            rc = lib.launch_pick_global_argmax(
+                vp(self.cand_all.data_ptr()), self.world, vp(self.tok.data_ptr()),
+                vp(self.pos.data_ptr()), vp(self.len.data_ptr()), vp(self.history.data_ptr()),
+                vp(self.hist_count.data_ptr()), self.hist_cap, st)
+            assert rc == 0, rc
+            self.n_launch += 2
 
     # ------------------------------------------------------------------ state
     def reset(self, first_token: int = 0):
