@@ -526,7 +526,8 @@ def run_decode(args, quiet=False):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = ModelConfig(max_len=1024, vocab=args.vocab)
-    eng = DecodeEngine(cfg, device=f"cuda:{local}", tp_rank=rank, tp_world=world)
+    eng = DecodeEngine(cfg, device=f"cuda:{local}", tp_rank=rank, tp_world=world,
+                       allreduce=args.allreduce)
     eng.load_random(seed=0)
     prompt = np.random.default_rng(0).integers(0, cfg.vocab, args.prompt_len)
     eng.reset(int(prompt[0]))
@@ -587,7 +588,8 @@ def run_decode(args, quiet=False):
                          "frac": per_gpu / peak, "peak_kind": peak_kind},
             "config": {"workload": "decode_27b_shape", "layers": cfg.n_layers,
                        "hidden": cfg.hidden, "vocab": cfg.vocab, "launch": "cuda_graph",
-                       "weights": "random NVFP4 bytes", "parallelism": f"tp{world}"},
+                       "weights": "random NVFP4 bytes", "parallelism": f"tp{world}",
+                       "allreduce": eng.allreduce, "comm_status": eng.comm_status()},
             "finite_logits": bool(torch.isfinite(eng.logits.float()).all().item()),
         }
         if not quiet:
@@ -623,6 +625,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--gen", type=int, default=63)
     ap.add_argument("--vocab", type=int, default=VOCAB)
+    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
+                    help="with --decode under torchrun: one-shot peer-memory all-reduce or NCCL")
     ap.add_argument("--fake-context", type=int, default=0,
                     help="with --decode: start at this cache length (zero-filled cache)")
     ap.add_argument("--eager", action="store_true",

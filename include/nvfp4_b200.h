@@ -169,6 +169,26 @@ int launch_argmax_slice(const void* logits, int vocab, long long offset, void* c
 int launch_pick_global_argmax(const void* cand_all, int world, void* tok, void* pos, void* len,
                               void* history, void* hist_count, int hist_cap, void* stream);
 
+/* One-shot all-reduce + residual add over NVLink peer memory (no counterpart in the reference).
+ * Each rank owns a communication buffer (gpu_malloc of nvfp4_comm_buffer_bytes(n), zeroed by
+ * nvfp4_comm_init) that the other ranks map through CUDA IPC (nvfp4_ipc_get_handle gives the
+ * 64-byte handle, nvfp4_ipc_open_handle maps a peer's).  The K-split GEMV writes its partial
+ * vector into its own buffer at nvfp4_comm_data_offset(n, parity); launch_allreduce_residual then
+ * signals the peers, waits for them with a bounded spin, pulls their vectors with peer loads and
+ * does h += f16(sum over ranks, fp32, rank order).  parity alternates 0, 1, 0, ... over the calls;
+ * every rank makes the same sequence of calls.  bufs is a HOST array of `world` device pointers
+ * (rank r's buffer as mapped in this process).  world <= 8, n % 8 == 0.  nvfp4_comm_status returns
+ * 0, or 1 + r if peer r failed to arrive within the spin limit at some call. */
+long long nvfp4_comm_buffer_bytes(int n);
+long long nvfp4_comm_data_offset(int n, int parity);
+int nvfp4_comm_init(void* buf, int n);
+int nvfp4_ipc_get_handle(void* dev_ptr, void* handle_out);
+void* nvfp4_ipc_open_handle(const void* handle);
+int nvfp4_ipc_close_handle(void* p);
+int nvfp4_comm_status(const void* my_buf);
+int launch_allreduce_residual(void* h, const void* const* bufs, int rank, int world, int n,
+                              int parity, void* stream);
+
 /* The DeltaNet step without a caller-provided workspace.  It has no counterpart in the reference,
  * whose caller always allocates the scratch tensor itself.  It exists for callers that cannot
  * allocate device memory at the point of the call: code that runs after all device memory has

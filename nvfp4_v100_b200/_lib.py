@@ -47,6 +47,14 @@ SIGNATURES = {
     "launch_residual_add": ([_vp, _vp, _i, _vp], _i),
     "launch_argmax_slice": ([_vp, _i, _ll, _vp, _vp], _i),
     "launch_pick_global_argmax": ([_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),
+    "nvfp4_comm_buffer_bytes": ([_i], _ll),
+    "nvfp4_comm_data_offset": ([_i, _i], _ll),
+    "nvfp4_comm_init": ([_vp, _i], _i),
+    "nvfp4_ipc_get_handle": ([_vp, _vp], _i),
+    "nvfp4_ipc_open_handle": ([_vp], _vp),
+    "nvfp4_ipc_close_handle": ([_vp], _i),
+    "nvfp4_comm_status": ([_vp], _i),
+    "launch_allreduce_residual": ([_vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _vp], _i),
     "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
     "launch_dn_fused_heads": ([_vp] * 12 + [_i, _i, _f, _vp], _i),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),

@@ -111,9 +111,12 @@ class _Layer:
 class DecodeEngine:
     """Holds the prepared weights and all state of one sequence and replays the step graph."""
 
-    def __init__(self, cfg: ModelConfig, device: str = "cuda", tp_rank: int = 0, tp_world: int = 1):
+    def __init__(self, cfg: ModelConfig, device: str = "cuda", tp_rank: int = 0, tp_world: int = 1,
+                 allreduce: str = "peer"):
         """tp_world > 1: this process holds shard tp_rank of a tensor-parallel group (one process
-        per GPU, torch.distributed initialised with the NCCL backend by the caller)."""
+        per GPU, torch.distributed initialised with the NCCL backend by the caller).
+        allreduce: "peer" = this library's one-shot all-reduce + residual kernel over NVLink peer
+        memory; "nccl" = NCCL all-reduce followed by a residual-add kernel."""
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; there is no CPU fallback")
         self.cfg = cfg
@@ -165,6 +168,44 @@ class DecodeEngine:
         self.embed = None
         self.final_w1 = None
         self.lm_head = None
+        self.allreduce = allreduce if W > 1 else "none"
+        self.ar_calls = 0
+        if self.allreduce == "peer":
+            self._setup_peer_comm()
+
+    def _setup_peer_comm(self):
+        """Allocate this rank's communication buffer, exchange CUDA IPC handles, map the peers'."""
+        import torch.distributed as dist
+
+        lib, n = self.lib, self.cfg.hidden
+        nbytes = lib.nvfp4_comm_buffer_bytes(n)
+        self.comm_own = lib.gpu_malloc(nbytes)
+        if not self.comm_own or lib.nvfp4_comm_init(vp(self.comm_own), n) != 0:
+            raise RuntimeError("communication buffer allocation failed")
+        hdl = ctypes.create_string_buffer(64)
+        if lib.nvfp4_ipc_get_handle(vp(self.comm_own), hdl) != 0:
+            raise RuntimeError("cudaIpcGetMemHandle failed")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, hdl.raw)
+        ptrs = []
+        for r, raw in enumerate(handles):
+            if r == self.rank:
+                ptrs.append(self.comm_own)
+            else:
+                p = lib.nvfp4_ipc_open_handle(ctypes.create_string_buffer(raw, 64))
+                if not p:
+                    raise RuntimeError(f"cannot map rank {r}'s communication buffer")
+                ptrs.append(p)
+        self.comm_ptrs = (vp * self.world)(*ptrs)
+        self.comm_slot = [self.comm_own + lib.nvfp4_comm_data_offset(n, p) for p in (0, 1)]
+        dist.barrier()
+
+    def comm_status(self) -> int:
+        """0 if every peer wait of the one-shot all-reduce was answered in time."""
+        if self.allreduce != "peer":
+            return 0
+        torch.cuda.synchronize()
+        return self.lib.nvfp4_comm_status(vp(self.comm_own))
 
     # ------------------------------------------------------------------ weights
     def _mat(self, packed: torch.Tensor, scales: torch.Tensor, M: int, K: int) -> _Mat:
@@ -307,8 +348,9 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------ one step
     def _gemv(self, st, m: _Mat, x, out, pro_w1=None, epi=0, residual=None):
+        out_ptr = out if isinstance(out, int) else out.data_ptr()
         rc = self.lib.launch_nvfp4_gemv_fused(
-            vp(m.packed.data_ptr()), vp(m.scales.data_ptr()), vp(x.data_ptr()), vp(out.data_ptr()),
+            vp(m.packed.data_ptr()), vp(m.scales.data_ptr()), vp(x.data_ptr()), vp(out_ptr),
             m.M, m.K, 0 if pro_w1 is None else 1,
             vp(0 if pro_w1 is None else pro_w1.data_ptr()), float(self.cfg.rms_eps), epi,
             vp(0 if residual is None else residual.data_ptr()), st)
@@ -322,6 +364,16 @@ class DecodeEngine:
         captured in the graph), then the residual add."""
         if self.world == 1:
             self._gemv(st, m, x, self.h, epi=1, residual=self.h)
+            return
+        if self.allreduce == "peer":
+            parity = self.ar_calls & 1
+            self.ar_calls += 1
+            self._gemv(st, m, x, self.comm_slot[parity])
+            rc = self.lib.launch_allreduce_residual(vp(self.h.data_ptr()), self.comm_ptrs, self.rank,
+                                                    self.world, self.cfg.hidden, parity, st)
+            assert rc == 0, rc
+            self.n_launch += 1
+            self.n_collective += 1
             return
         import torch.distributed as dist
 
@@ -339,6 +391,9 @@ class DecodeEngine:
         st = vp(torch.cuda.current_stream().cuda_stream)
         self.n_launch = 0
         self.n_collective = 0
+        # an even number of K-split layers per step keeps the slot parity of every call site the
+        # same in every step, which a captured graph needs
+        assert self.ar_calls % 2 == 0
         rc = lib.launch_embed_gather(vp(self.embed.data_ptr()), vp(self.tok.data_ptr()),
                                      vp(self.h.data_ptr()), c.hidden, c.vocab, st)
         assert rc == 0, rc

@@ -224,3 +224,30 @@ def test_engine_snapshot_restore_poison(lib):
     torch.cuda.synchronize()
     b = eng.history[:int(eng.hist_count)].cpu().tolist()
     assert a == b
+
+
+def test_allreduce_residual_single_rank(lib):
+    # world = 1: no peers to wait for; h += f16(own partial vector), alternating data slots
+    n = 5120
+    nbytes = lib.nvfp4_comm_buffer_bytes(n)
+    assert nbytes == 256 + 4 * n
+    buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    assert lib.nvfp4_comm_init(ptr(buf), n) == 0
+    rng = np.random.default_rng(0)
+    h = rng.standard_normal(n).astype(np.float16)
+    d_h = dev(h)
+    bufs = (ctypes.c_void_p * 1)(buf.data_ptr())
+    want = h.astype(np.float64)
+    for call in range(4):
+        part = rng.standard_normal(n).astype(np.float16)
+        off = lib.nvfp4_comm_data_offset(n, call & 1)
+        buf[off:off + 2 * n].copy_(torch.from_numpy(part.view(np.uint8)))
+        rc = lib.launch_allreduce_residual(ptr(d_h), bufs, 0, 1, n, call & 1, stream())
+        assert rc == 0
+        want = (want + part.astype(np.float64)).astype(np.float16).astype(np.float64)
+    torch.cuda.synchronize()
+    assert np.array_equal(d_h.cpu().numpy().astype(np.float64), want)
+    assert lib.nvfp4_comm_status(ptr(buf)) == 0
+    assert int(buf[:4].view(torch.int32)) == 4           # the call counter
+    assert lib.launch_allreduce_residual(ptr(d_h), bufs, 0, 9, n, 0, stream()) == -1
+    assert lib.launch_allreduce_residual(ptr(d_h), bufs, 0, 1, n + 4, 0, stream()) == -1
