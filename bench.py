@@ -604,9 +604,11 @@ def run_decode(args, quiet=False):
     return res
 
 
-# DRAM bytes (read + write) per average GEMV launch of the mix, from the ncu capture summarised
-# under profiles/; None until a capture exists.
-TRAFFIC_PER_LAUNCH = None
+# DRAM bytes (read + write) per average GEMV launch of the mix.  The full-set ncu capture was taken
+# on the 151936x5120 shape (profiles/gemv_mma_kernel_lm_head_151936x5120.md): 441.69 MB of DRAM
+# traffic for 437.89 MB of algorithmic bytes, ratio 1.0087; every weight byte is read once at any
+# shape, so the traffic of the mix's average launch (14 427 447 296 B / 497) is scaled by that ratio.
+TRAFFIC_PER_LAUNCH = int(14_427_447_296 / 497 * (441.69 / 437.89))
 
 
 def main():
