@@ -60,6 +60,20 @@ int launch_nvfp4_gemvnl(const void* weight_packed, const void* weight_scales,
 int launch_nvfp4_gemv2(const void* weight_packed, const void* weight_scales, const void* act0,
                        const void* act1, void* output, int M, int K, void* stream);
 
+/* Dense GEMM for more than two tokens: output[M, N] (fp16) = dequant(W)[M, K] . activation[K, N]
+ * (fp16, N = tokens, token-minor as the reference's caller prepares it).  Weight x block scale in
+ * fp16, fp16 x fp16 products, fp32 accumulation, as the reference's wmma kernel.  Runs on tcgen05
+ * tensor cores when K % 64 == 0, N % 8 == 0 and the pointers are 16-byte aligned (scales 4-byte),
+ * otherwise on a CUDA-core kernel.  Returns 0 or the cudaError_t of the launch; -2 for K % 16 != 0,
+ * non-positive sizes or NULL pointers.  kernels/nvfp4_cuda_v5.cu:406-422. */
+int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
+                           const void* d_activation, void* d_output, int M, int N, int K,
+                           void* stream);
+int get_kernel_shared_mem_bytes(void);                          /* kernels/nvfp4_cuda_v5.cu:460-464 */
+/* 0 if no bounded wait inside the tensor-core GEMM ever ran out; 1 + wait id otherwise.  reset != 0
+ * clears it.  Synchronous.  No counterpart in the reference. */
+int nvfp4_gemm_status(int reset);
+
 /* Tuning hook; no counterpart in the reference.  warps per CTA (0 = auto, 2, 4 or 8), resident
  * CTAs per SM used to size the grid (0 = occupancy calculator), flags: bit 0 routes every GEMV to
  * the non-tensor-core kernel, bit 1 turns programmatic dependent launch off, bits 4..6 cap and

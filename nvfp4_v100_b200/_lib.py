@@ -35,6 +35,9 @@ SIGNATURES = {
     "launch_nvfp4_gemvnl": _GEMV_SIG,
     "launch_nvfp4_gemv2": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "nvfp4_b200_gemv_config": ([_i, _i, _i], _i),
+    "launch_nvfp4_gemmtc_v5": ([_vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
+    "get_kernel_shared_mem_bytes": ([], _i),
+    "nvfp4_gemm_status": ([_i], _i),
     "launch_rmsnorm": ([_vp, _ll, _vp, _vp, _i, _i, _f, _vp], _i),
     "launch_rope_qk": ([_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "launch_silu_mul": ([_vp, _vp, _vp, _i, _vp], _i),

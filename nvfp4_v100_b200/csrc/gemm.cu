@@ -1,0 +1,449 @@
+// Dense NVFP4 GEMM for more than two tokens (prefill, batched decode) on the 5th-generation
+// tensor cores:  out[M, N] = dequant(W)[M, K] . act[K, N]   (N = tokens, act token-minor).
+//
+// Replaces the reference's wmma kernel behind the same entry point (kernels/nvfp4_cuda_v5.cu:188-399
+// kernel, :406-422 launcher, caller pipeline/_qwen38_infer.py:174-181).  Arithmetic follows the
+// reference (W4A16): a weight is decoded to fp16 and multiplied by its block scale IN fp16
+// (kernels/nvfp4_cuda_v5.cu:163-175), products are fp16 x fp16, accumulation is fp32.
+//
+// Structure of one CTA (192 threads), tile = 128 weight rows x BN tokens, K in steps of 64:
+//   warp 0        : TMA producer.  One elected thread issues cp.async.bulk.tensor.2d loads of the
+//                   activation tile ([64 k] x [64 tokens] boxes, 128-byte swizzle) into a 4-stage
+//                   shared-memory ring, completion on an mbarrier (transaction bytes).
+//   warp 1        : MMA issuer.  One elected thread issues tcgen05.mma.kind::f16 (M = 128, N = BN,
+//                   K = 16, four per stage) with shared-memory descriptors; the fp32 accumulator
+//                   lives in tensor memory (BN columns).  tcgen05.commit releases each stage.
+//   warps 2..5    : weight producers, one thread per weight row: 32 packed bytes + 4 scale bytes
+//                   per K step from global memory, nibbles -> fp16 (cvt.rn.f16x2.e2m1x2) x scale,
+//                   written as a K-major, 128-byte-swizzled A tile; then the epilogue: tcgen05.ld
+//                   of the accumulator (each warp its own 32-lane quarter), fp16 store.
+// A operand: K-major SWIZZLE_128B (row = 128 bytes = 64 fp16).  B operand: MN-major SWIZZLE_128B
+// (one k row = 64 tokens = 128 bytes), exactly what the token-minor activation gives a TMA box.
+//
+// Every wait on an mbarrier is bounded: when the limit is reached the waiter records it in a
+// device status word, stops waiting, and the CTA still runs to its end and frees its tensor
+// memory, so a logic error can produce wrong numbers but never a hung GPU.
+//
+// Shapes the tensor-core kernel does not take (K % 64 != 0, N % 8 != 0, unaligned pointers) run
+// on a plain CUDA-core kernel with the same arithmetic.
+#include <cuda.h>
+
+#include <cstdio>
+
+#include "common.cuh"
+
+namespace nvfp4 {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_STAGES = 4;
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t GEMM_SPIN_LIMIT = 1u << 24;
+
+__device__ int g_gemm_status = 0;  // 0 ok; otherwise 1 + id of the wait that ran out
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false (after recording `id`) if the barrier never completed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int id) {
+    for (uint32_t i = 0; i < GEMM_SPIN_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(&g_gemm_status, 1 + id);
+    return false;
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1,
+                                            uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+            "r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_alloc(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(dst_smem),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tcgen05_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before() {
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after() {
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t taddr, uint64_t adesc, uint64_t bdesc,
+                                                uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(taddr),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+          "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_ld() {
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+}
+
+// Shared-memory matrix descriptor (tcgen05): start address, leading / stride byte offsets (16-byte
+// units), descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr, uint32_t lbo_bytes,
+                                                    uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;   // version
+    d |= (uint64_t)2 << 61;   // SWIZZLE_128B
+    return d;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The kernel.  BN = tokens per CTA tile (64 or 128).
+// Shared memory (dynamic, 1024-byte aligned): per stage A tile 128 x 128 B = 16 KB, then per stage
+// B tile (BN/64) boxes of 64 k-rows x 128 B = 8 KB each.
+// ---------------------------------------------------------------------------------------------
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS)
+gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
+                          const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                          __half* __restrict__ out, int M, int N, int K) {
+    constexpr int A_BYTES = GEMM_BM * 128;          // 16 KB
+    constexpr int B_BOX = GEMM_BK * 128;            // 8 KB: 64 k rows of 64 tokens
+    constexpr int B_BYTES = (BN / 64) * B_BOX;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // the runtime aligns dynamic shared memory to 16 bytes only: round up to the swizzle atom
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + GEMM_STAGES * A_BYTES;
+    __shared__ __align__(8) uint64_t bar_full_b[GEMM_STAGES];   // TMA bytes landed
+    __shared__ __align__(8) uint64_t bar_full_a[GEMM_STAGES];   // 128 weight rows written
+    __shared__ __align__(8) uint64_t bar_empty[GEMM_STAGES];    // MMAs that read the stage retired
+    __shared__ __align__(8) uint64_t bar_accum;                 // whole accumulation retired
+    __shared__ uint32_t s_tmem;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * GEMM_BM, n0 = blockIdx.y * BN;
+    const int ksteps = K / GEMM_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < GEMM_STAGES; s++) {
+            mbar_init(smem_u32(&bar_full_b[s]), 1);
+            mbar_init(smem_u32(&bar_full_a[s]), 128);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_accum), 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) {  // one warp allocates the accumulator's tensor-memory columns
+        tcgen05_alloc(smem_u32(&s_tmem), BN);
+        tcgen05_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = s_tmem;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: activation tiles ----------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < ksteps && ok; it++) {
+                const int s = it % GEMM_STAGES;
+                const uint32_t ph = (uint32_t)(it / GEMM_STAGES) & 1u;
+                ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 0);
+                if (!ok) break;
+                const uint32_t bar = smem_u32(&bar_full_b[s]);
+                mbar_arrive_expect_tx(bar, B_BYTES);
+#pragma unroll
+                for (int b = 0; b < BN / 64; b++)
+                    tma_load_2d(smem_u32(smem_b + s * B_BYTES + b * B_BOX), &act_map, n0 + b * 64,
+                                it * GEMM_BK, bar);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // instruction descriptor: D fp32, A fp16 K-major, B fp16 MN-major, N = BN, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) |
+                                   ((uint32_t)(GEMM_BM >> 4) << 24);
+            bool ok = true;
+            for (int it = 0; it < ksteps && ok; it++) {
+                const int s = it % GEMM_STAGES;
+                const uint32_t ph = (uint32_t)(it / GEMM_STAGES) & 1u;
+                ok = mbar_wait(smem_u32(&bar_full_a[s]), ph, 1) &&
+                     mbar_wait(smem_u32(&bar_full_b[s]), ph, 2);
+                if (!ok) break;
+                tcgen05_fence_after();
+                const uint32_t a_base = smem_u32(smem_a + s * A_BYTES);
+                const uint32_t b_base = smem_u32(smem_b + s * B_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < GEMM_BK / 16; kk++) {
+                    // A, K-major: 16 k = 32 bytes further along the 128-byte row; 8-row groups
+                    // are 1024 bytes apart.  B, MN-major: 16 k = two groups of 8 k rows (1024
+                    // bytes each); 64-token atoms are one box (8 KB) apart.
+                    const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
+                    const uint64_t bdesc = make_desc_sw128(b_base + kk * 2048, B_BOX, 1024);
+                    tcgen05_mma_f16(tmem, adesc, bdesc, idesc, (it | kk) != 0 ? 1u : 0u);
+                }
+                tcgen05_commit(smem_u32(&bar_empty[s]));   // stage reusable when these MMAs retire
+            }
+            tcgen05_commit(smem_u32(&bar_accum));
+        }
+    } else {
+        // ---------------- weight producers (one thread per weight row), then epilogue ----------------
+        const int r = threadIdx.x - 64;                  // 0..127: row of the tile
+        const int row = min(m0 + r, M - 1);
+        const bool row_ok = (m0 + r) < M;
+        const uint8_t* prow = packed + (size_t)row * (size_t)(K >> 1);
+        const uint8_t* srow = scales + (size_t)row * (size_t)(K >> 4);
+        bool ok = true;
+        for (int it = 0; it < ksteps; it++) {
+            const int s = it % GEMM_STAGES;
+            const uint32_t ph = (uint32_t)(it / GEMM_STAGES) & 1u;
+            // 32 packed bytes (64 weights) and 4 scale bytes of this K step
+            const uint4 p0 = ld_stream_u4(prow + (size_t)it * 32);
+            const uint4 p1 = ld_stream_u4(prow + (size_t)it * 32 + 16);
+            const uint32_t sc4 = __ldg(reinterpret_cast<const uint32_t*>(srow + (size_t)it * 4));
+            if (ok) ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 3);
+            const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+            uint8_t* arow = smem_a + s * A_BYTES + r * 128;
+#pragma unroll
+            for (int c = 0; c < 8; c++) {               // 16-byte chunk c = weights 8c .. 8c+7
+                uint32_t h0, h1, h2, h3;
+                e2m1x8_to_half2x4(w[c], h0, h1, h2, h3);
+                // block scale 2^(sb-127) as fp16, applied in fp16 as the reference does
+                const __half sc = __float2half(e8m0_to_f32((sc4 >> (8 * (c >> 1))) & 0xFFu));
+                const __half2 s2 = __half2half2(sc);
+                uint4 v;
+                __half2 t;
+                t = __hmul2(*reinterpret_cast<__half2*>(&h0), s2); v.x = *reinterpret_cast<uint32_t*>(&t);
+                t = __hmul2(*reinterpret_cast<__half2*>(&h1), s2); v.y = *reinterpret_cast<uint32_t*>(&t);
+                t = __hmul2(*reinterpret_cast<__half2*>(&h2), s2); v.z = *reinterpret_cast<uint32_t*>(&t);
+                t = __hmul2(*reinterpret_cast<__half2*>(&h3), s2); v.w = *reinterpret_cast<uint32_t*>(&t);
+                if (!row_ok) v = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = v;   // 128-byte swizzle
+            }
+            fence_proxy_async_smem();     // make the generic-proxy writes visible to the tensor core
+            mbar_arrive(smem_u32(&bar_full_a[s]));
+        }
+
+        // ---------------- epilogue: TMEM -> registers -> fp16 out[m][n] ----------------
+        mbar_wait(smem_u32(&bar_accum), 0, 4);
+        tcgen05_fence_after();
+        const int q = warp & 3;                          // this warp's 32-lane quarter of TMEM
+        const int m = m0 + q * 32 + lane;
+#pragma unroll
+        for (int cb = 0; cb < BN / 32; cb++) {
+            uint32_t v[32];
+            tcgen05_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), v);
+            tcgen05_wait_ld();
+            const int nb = n0 + cb * 32;
+            if (m < M && nb < N) {
+                __half* orow = out + (size_t)m * (size_t)N + nb;
+                if (nb + 32 <= N) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 o;
+                        __half2 t;
+                        t = __floats2half2_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                        o.x = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        o.y = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                        o.z = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                        o.w = *reinterpret_cast<uint32_t*>(&t);
+                        *reinterpret_cast<uint4*>(orow + j) = o;
+                    }
+                } else {
+                    for (int j = 0; j < 32 && nb + j < N; j++)
+                        orow[j] = __float2half(__uint_as_float(v[j]));
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tcgen05_dealloc(tmem, BN);
+}
+
+// ---------------------------------------------------------------------------------------------
+// CUDA-core fallback: any K % 16 == 0, any N, any alignment.  One thread per output, same
+// arithmetic (weight x scale in fp16, fp32 accumulation).
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+gemm_w4a16_fallback_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
+                           const __half* __restrict__ act, __half* __restrict__ out, int M, int N,
+                           int K) {
+    const int n = blockIdx.x * 64 + (threadIdx.x & 63);
+    const int m = blockIdx.y * 4 + (threadIdx.x >> 6);
+    if (m >= M || n >= N) return;
+    const uint8_t* prow = packed + (size_t)m * (size_t)(K >> 1);
+    const uint8_t* srow = scales + (size_t)m * (size_t)(K >> 4);
+    float acc = 0.0f;
+    for (int b = 0; b < (K >> 4); b++) {
+        const __half sc = __float2half(e8m0_to_f32(srow[b]));
+        for (int i = 0; i < 8; i++) {
+            const uint32_t h = e2m1x2_to_half2(prow[b * 8 + i]);
+            const __half2 w = __hmul2(*reinterpret_cast<const __half2*>(&h), __half2half2(sc));
+            const int k = b * 16 + 2 * i;
+            acc = fmaf(__low2float(w), __half2float(act[(size_t)k * N + n]), acc);
+            acc = fmaf(__high2float(w), __half2float(act[(size_t)(k + 1) * N + n]), acc);
+        }
+    }
+    out[(size_t)m * N + n] = __float2half(acc);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+                cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+template <int BN>
+static cudaError_t launch_tc(const CUtensorMap& map, const uint8_t* packed, const uint8_t* scales,
+                             __half* out, int M, int N, int K, cudaStream_t st) {
+    constexpr int SMEM = GEMM_STAGES * (GEMM_BM * 128 + (BN / 64) * GEMM_BK * 128) + 1024;
+    static bool attr = false;
+    if (!attr) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<BN>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return e;
+        attr = true;
+    }
+    dim3 grid((unsigned)((M + GEMM_BM - 1) / GEMM_BM), (unsigned)((N + BN - 1) / BN));
+    gemm_w4a16_tcgen05_kernel<BN><<<grid, GEMM_THREADS, SMEM, st>>>(map, packed, scales, out, M, N, K);
+    return cudaGetLastError();
+}
+
+}  // namespace nvfp4
+
+extern "C" {
+
+// out[M, N] (fp16) = dequant(W)[M, K] . act[K, N] (fp16, token-minor).  Returns 0 or the
+// cudaError_t of the launch, as the reference does; -2 for a shape no kernel takes (K % 16 != 0,
+// non-positive sizes, NULL pointers).
+int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
+                           const __half* d_activation, __half* d_output, int M, int N, int K,
+                           void* stream) {
+    using namespace nvfp4;
+    if (M <= 0 || N <= 0 || K <= 0 || K % 16 != 0) return NVFP4_ERR_SHAPE;
+    if (!d_weight_packed || !d_weight_scales || !d_activation || !d_output) return NVFP4_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool tc_ok = (K % 64 == 0) && (N % 8 == 0) &&
+                       (((uintptr_t)d_weight_packed & 15) == 0) &&
+                       (((uintptr_t)d_weight_scales & 3) == 0) &&
+                       (((uintptr_t)d_activation & 15) == 0) && (((uintptr_t)d_output & 15) == 0);
+    EncodeTiledFn enc = tc_ok ? encode_tiled_fn() : nullptr;
+    if (enc) {
+        CUtensorMap map;
+        const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K};        // inner = tokens
+        const cuuint64_t strides[1] = {(cuuint64_t)N * sizeof(__half)};   // bytes between k rows
+        const cuuint32_t box[2] = {64, (cuuint32_t)GEMM_BK};
+        const cuuint32_t estr[2] = {1, 1};
+        const CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void*)d_activation, dims,
+                               strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS) {
+            const cudaError_t e =
+                (N > 64) ? launch_tc<128>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
+                         : launch_tc<64>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st);
+            return (e == cudaSuccess) ? 0 : (int)e;
+        }
+    }
+    dim3 grid((unsigned)((N + 63) / 64), (unsigned)((M + 3) / 4));
+    gemm_w4a16_fallback_kernel<<<grid, 256, 0, st>>>(d_weight_packed, d_weight_scales, d_activation,
+                                                     d_output, M, N, K);
+    const cudaError_t e = cudaGetLastError();
+    return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+// 0 if no bounded wait inside the tensor-core GEMM has run out since the library was loaded (or
+// since the last call with reset != 0); otherwise 1 + the id of the wait.  Synchronises the device.
+int nvfp4_gemm_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, nvfp4::g_gemm_status, sizeof(int)) != cudaSuccess) return -1;
+    if (reset) {
+        const int z = 0;
+        cudaMemcpyToSymbol(nvfp4::g_gemm_status, &z, sizeof(int));
+    }
+    return v;
+}
+
+// Shared memory of the tensor-core GEMM's widest tile, for callers that size their launches the
+// way the reference's get_kernel_shared_mem_bytes does (kernels/nvfp4_cuda_v5.cu:460-464).
+int get_kernel_shared_mem_bytes() {
+    return nvfp4::GEMM_STAGES * (nvfp4::GEMM_BM * 128 + 2 * nvfp4::GEMM_BK * 128) + 1024;
+}
+
+}  // extern "C"

@@ -1,0 +1,90 @@
+"""Dense NVFP4 GEMM (launch_nvfp4_gemmtc_v5) on the GPU against the CPU oracle.
+
+Oracle: the reference's truth recipe — decode the weights to fp16 with the codec, multiply with
+the fp16 activations (simulation/nvfp4_cuda_v5_test.py:90-91), here in float64.  Tolerances: the
+reference's own acceptance rule (mean_rel < 0.01 and max_abs < max(0.1, 1 % of max|ref|),
+simulation/nvfp4_cuda_v5_test.py:92-95,186) and, tighter, max |y - ref| / max(|ref|, 1e-3 max|ref|)
+<= 2e-3 (fp32 accumulation; fp16 output rounding alone is 4.9e-4)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_codec_oracle as oc
+from tests.gpu_util import dev, ptr, stream
+
+pytestmark = pytest.mark.gpu
+
+
+def run_gemm(lib, packed, scales, act_kn):
+    M, K = packed.shape[0], packed.shape[1] * 2
+    N = act_kn.shape[1]
+    d_p, d_s, d_a = dev(packed), dev(scales), dev(act_kn.astype(np.float16))
+    out = torch.full((M * N + 16,), float("nan"), dtype=torch.float16, device="cuda")
+    rc = lib.launch_nvfp4_gemmtc_v5(ptr(d_p), ptr(d_s), ptr(d_a), ptr(out), M, N, K, stream())
+    torch.cuda.synchronize()
+    o = out.cpu().numpy()
+    assert np.isnan(o[M * N:]).all(), "wrote past the output"
+    return rc, o[:M * N].reshape(M, N)
+
+
+def check(y, packed, scales, act_kn):
+    w = oc.decode(packed, scales).astype(np.float64)
+    ref = w @ act_kn.astype(np.float16).astype(np.float64)
+    assert np.isfinite(y.astype(np.float64)).all()
+    ok, mean_rel, max_abs = oc.reference_gemm_check(y, ref)
+    assert ok, (mean_rel, max_abs)
+    rel = oc.rel_error_floored(y, ref)
+    assert rel.max() <= 2e-3, rel.max()
+
+
+@pytest.mark.parametrize("M,N,K", [
+    (128, 64, 64), (128, 128, 256), (256, 8, 128), (300, 200, 512), (100, 24, 320),
+    (1024, 512, 5120), (512, 256, 16384), (17408, 32, 5120), (5120, 136, 6144),
+])
+def test_tensor_core_path(lib, M, N, K):
+    lib.nvfp4_gemm_status(1)
+    w = oc.synthetic_weight(M, K, seed=M + N + K)
+    p, s = oc.encode(w)
+    a = np.random.default_rng(N).standard_normal((K, N)).astype(np.float16)
+    rc, y = run_gemm(lib, p, s, a)
+    assert rc == 0
+    assert lib.nvfp4_gemm_status(0) == 0, "a bounded wait inside the kernel ran out"
+    check(y, p, s, a)
+
+
+@pytest.mark.parametrize("M,N,K", [(100, 100, 112), (7, 3, 16), (64, 33, 64), (33, 8, 48)])
+def test_fallback_path(lib, M, N, K):
+    # the reference's boundary shape 100 x 100 x 112 and other shapes the tensor-core kernel
+    # does not take (K % 64 != 0 or N % 8 != 0)
+    w = oc.synthetic_weight(M, K, seed=M * K)
+    p, s = oc.encode(w)
+    a = np.random.default_rng(K).standard_normal((K, N)).astype(np.float16)
+    rc, y = run_gemm(lib, p, s, a)
+    assert rc == 0
+    check(y, p, s, a)
+
+
+def test_matches_gemv_column_by_column(lib):
+    # a GEMM over N tokens equals N GEMVs up to the fp16-scaled-weight rounding of the W4A16 path
+    from tests.gpu_util import gemv
+
+    M, N, K = 256, 16, 1024
+    w = oc.synthetic_weight(M, K, seed=5)
+    p, s = oc.encode(w)
+    a = np.random.default_rng(6).standard_normal((K, N)).astype(np.float16)
+    rc, y = run_gemm(lib, p, s, a)
+    assert rc == 0
+    for n in (0, 7, 15):
+        rc, yv = gemv(lib, p, s, np.ascontiguousarray(a[:, n]))
+        assert rc == 0
+        assert oc.rel_error_floored(y[:, n], yv.astype(np.float64)).max() <= 2e-3
+
+
+def test_argument_validation(lib):
+    import ctypes
+
+    one = ctypes.c_void_p(0x1000)
+    assert lib.launch_nvfp4_gemmtc_v5(one, one, one, one, 16, 8, 24, None) == -2   # K % 16
+    assert lib.launch_nvfp4_gemmtc_v5(one, one, one, one, 0, 8, 64, None) == -2
+    assert lib.launch_nvfp4_gemmtc_v5(None, one, one, one, 16, 8, 64, None) == -2
+    assert lib.get_kernel_shared_mem_bytes() > 64 * 1024
