@@ -496,6 +496,64 @@ def run_per_shape(args):
     print(json.dumps(line), flush=True)
 
 
+def run_gemm(args):
+    """Dense GEMM through launch_nvfp4_gemmtc_v5 at the 27B layer shapes (BASELINE config 5):
+    tokens = 32 (batched decode, weight-bandwidth bound) and 8192 (prefill, tensor bound)."""
+    import torch
+
+    from nvfp4_v100_b200 import _lib
+
+    torch.cuda.set_device(0)
+    lib = _lib.load()
+    vp = ctypes.c_void_p
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        tf_peak, tf_kind = float(peaks["bf16_tflops"]), "measured bf16 burst"
+    except Exception:
+        tf_peak, tf_kind = 1590.0, "fallback"
+    hbm_peak, hbm_kind = measured_peak()
+    rows = []
+    for tokens in (32, 8192):
+        for M, K in ((6144, HIDDEN), (INTER, HIDDEN), (HIDDEN, HIDDEN), (HIDDEN, INTER)):
+            p = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device="cuda")
+            s = torch.randint(118, 123, (M * K // 16,), dtype=torch.uint8, device="cuda")
+            a = torch.randn(K, tokens, device="cuda").to(torch.float16)
+            o = torch.zeros(M, tokens, dtype=torch.float16, device="cuda")
+            st = vp(torch.cuda.current_stream().cuda_stream)
+
+            def launch():
+                rc = lib.launch_nvfp4_gemmtc_v5(vp(p.data_ptr()), vp(s.data_ptr()), vp(a.data_ptr()),
+                                                vp(o.data_ptr()), M, tokens, K, st)
+                assert rc == 0, rc
+
+            for _ in range(3):
+                launch()
+            torch.cuda.synchronize()
+            reps = 20 if tokens == 32 else 5
+            best = None
+            for _ in range(3):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    launch()
+                e1.record()
+                torch.cuda.synchronize()
+                us = e0.elapsed_time(e1) * 1e3 / reps
+                best = us if best is None else min(best, us)
+            flops = 2.0 * M * tokens * K
+            nbytes = M * K * 0.5625 + 2.0 * K * tokens + 2.0 * M * tokens
+            rows.append({"tokens": tokens, "M": M, "K": K, "us": best,
+                         "tflops": flops / best / 1e6, "frac_tensor_" + tf_kind.split()[0]:
+                         flops / best / 1e6 / tf_peak, "gbps": nbytes / best / 1e3,
+                         "frac_hbm_" + hbm_kind: nbytes / best / 1e3 / hbm_peak})
+            print(f"tokens {tokens:5d}  {M:6d}x{K:<6d} {best:9.1f} us {flops / best / 1e6:8.1f} TFLOP/s "
+                  f"({100 * flops / best / 1e6 / tf_peak:4.1f}% of {tf_kind} {tf_peak:.0f}) "
+                  f"{nbytes / best / 1e3:7.0f} GB/s", file=sys.stderr, flush=True)
+    print(json.dumps({"metric": "nvfp4_gemm_tflops", "unit": "TFLOP/s", "n_gpus": 1, "dtype": "f16",
+                      "kernel": "gemm_w4a16_tcgen05_kernel (W4A16: fp16 activations, fp32 accumulation in TMEM)",
+                      "status": lib.nvfp4_gemm_status(0), "shapes": rows}), flush=True)
+
+
 def decode_step_bytes(cfg, context):
     """Algorithmic HBM bytes of one decode step: every weight byte once, DeltaNet state read and
     written, the KV prefix read, embedding row and logits."""
@@ -622,6 +680,8 @@ def main():
                     help="time every 27B layer shape alone (cold L2) instead of the step mix")
     ap.add_argument("--only", default="", help="with --per-shape: a single MxK shape")
     ap.add_argument("--reps", type=int, default=200, help="with --per-shape: launches per timing")
+    ap.add_argument("--gemm", action="store_true",
+                    help="dense GEMM (tokens = 32 and 8192) at the 27B layer shapes")
     ap.add_argument("--decode", action="store_true",
                     help="27B-shape decode tok/s (512-token prompt, 63 tokens) instead of the mix")
     ap.add_argument("--prompt-len", type=int, default=512)
@@ -636,7 +696,9 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.decode:
+    if args.gemm:
+        run_gemm(args)
+    elif args.decode:
         run_decode(args)
     elif args.per_shape:
         run_per_shape(args)

@@ -6,17 +6,18 @@
 // reference (W4A16): a weight is decoded to fp16 and multiplied by its block scale IN fp16
 // (kernels/nvfp4_cuda_v5.cu:163-175), products are fp16 x fp16, accumulation is fp32.
 //
-// Structure of one CTA (192 threads), tile = 128 weight rows x BN tokens, K in steps of 64:
+// Structure of one CTA (320 threads), tile = 128 weight rows x BN tokens, K in steps of 64:
 //   warp 0        : TMA producer.  One elected thread issues cp.async.bulk.tensor.2d loads of the
 //                   activation tile ([64 k] x [64 tokens] boxes, 128-byte swizzle) into a 4-stage
 //                   shared-memory ring, completion on an mbarrier (transaction bytes).
 //   warp 1        : MMA issuer.  One elected thread issues tcgen05.mma.kind::f16 (M = 128, N = BN,
 //                   K = 16, four per stage) with shared-memory descriptors; the fp32 accumulator
 //                   lives in tensor memory (BN columns).  tcgen05.commit releases each stage.
-//   warps 2..5    : weight producers, one thread per weight row: 32 packed bytes + 4 scale bytes
-//                   per K step from global memory, nibbles -> fp16 (cvt.rn.f16x2.e2m1x2) x scale,
-//                   written as a K-major, 128-byte-swizzled A tile; then the epilogue: tcgen05.ld
-//                   of the accumulator (each warp its own 32-lane quarter), fp16 store.
+//   warps 2..9    : weight producers, two threads per weight row: 16 packed bytes + 2 scale bytes
+//                   each per K step from global memory, nibbles -> fp16 (cvt.rn.f16x2.e2m1x2) x
+//                   scale, written as a K-major, 128-byte-swizzled A tile; then the epilogue:
+//                   tcgen05.ld of the accumulator (each warp its own 32-lane quarter and half of
+//                   the token columns), fp16 store.
 // A operand: K-major SWIZZLE_128B (row = 128 bytes = 64 fp16).  B operand: MN-major SWIZZLE_128B
 // (one k row = 64 tokens = 128 bytes), exactly what the token-minor activation gives a TMA box.
 //
@@ -37,7 +38,8 @@ namespace nvfp4 {
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;
 constexpr int GEMM_STAGES = 4;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_PRODUCER_WARPS = 8;   // weight-dequant warps (two threads per weight row)
+constexpr int GEMM_THREADS = 64 + 32 * GEMM_PRODUCER_WARPS;
 constexpr uint32_t GEMM_SPIN_LIMIT = 1u << 24;
 
 __device__ int g_gemm_status = 0;  // 0 ok; otherwise 1 + id of the wait that ran out
@@ -152,7 +154,7 @@ __device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr, uint32_t lbo
 }
 
 // ---------------------------------------------------------------------------------------------
-// The kernel.  BN = tokens per CTA tile (64 or 128).
+// The kernel.  BN = tokens per CTA tile (64, 128 or 256).
 // Shared memory (dynamic, 1024-byte aligned): per stage A tile 128 x 128 B = 16 KB, then per stage
 // B tile (BN/64) boxes of 64 k-rows x 128 B = 8 KB each.
 // ---------------------------------------------------------------------------------------------
@@ -183,7 +185,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
     if (threadIdx.x == 0) {
         for (int s = 0; s < GEMM_STAGES; s++) {
             mbar_init(smem_u32(&bar_full_b[s]), 1);
-            mbar_init(smem_u32(&bar_full_a[s]), 128);
+            mbar_init(smem_u32(&bar_full_a[s]), 32 * GEMM_PRODUCER_WARPS);
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
         mbar_init(smem_u32(&bar_accum), 1);
@@ -245,29 +247,30 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
             tcgen05_commit(smem_u32(&bar_accum));
         }
     } else {
-        // ---------------- weight producers (one thread per weight row), then epilogue ----------------
-        const int r = threadIdx.x - 64;                  // 0..127: row of the tile
+        // ---------------- weight producers (two threads per weight row), then epilogue ----------------
+        const int pt = threadIdx.x - 64;                 // 0..255
+        const int r = pt >> 1, half = pt & 1;            // row of the tile, which 32 of its 64 weights
         const int row = min(m0 + r, M - 1);
         const bool row_ok = (m0 + r) < M;
-        const uint8_t* prow = packed + (size_t)row * (size_t)(K >> 1);
-        const uint8_t* srow = scales + (size_t)row * (size_t)(K >> 4);
+        const uint8_t* prow = packed + (size_t)row * (size_t)(K >> 1) + half * 16;
+        const uint8_t* srow = scales + (size_t)row * (size_t)(K >> 4) + half * 2;
         bool ok = true;
         for (int it = 0; it < ksteps; it++) {
             const int s = it % GEMM_STAGES;
             const uint32_t ph = (uint32_t)(it / GEMM_STAGES) & 1u;
-            // 32 packed bytes (64 weights) and 4 scale bytes of this K step
+            // 16 packed bytes (32 weights = 2 scale blocks) of this K step
             const uint4 p0 = ld_stream_u4(prow + (size_t)it * 32);
-            const uint4 p1 = ld_stream_u4(prow + (size_t)it * 32 + 16);
-            const uint32_t sc4 = __ldg(reinterpret_cast<const uint32_t*>(srow + (size_t)it * 4));
+            const uint32_t sc2 = __ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)it * 4));
             if (ok) ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 3);
-            const uint32_t w[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+            const uint32_t w[4] = {p0.x, p0.y, p0.z, p0.w};
             uint8_t* arow = smem_a + s * A_BYTES + r * 128;
 #pragma unroll
-            for (int c = 0; c < 8; c++) {               // 16-byte chunk c = weights 8c .. 8c+7
+            for (int j = 0; j < 4; j++) {               // 16-byte chunk c = weights 8c .. 8c+7
+                const int c = half * 4 + j;
                 uint32_t h0, h1, h2, h3;
-                e2m1x8_to_half2x4(w[c], h0, h1, h2, h3);
+                e2m1x8_to_half2x4(w[j], h0, h1, h2, h3);
                 // block scale 2^(sb-127) as fp16, applied in fp16 as the reference does
-                const __half sc = __float2half(e8m0_to_f32((sc4 >> (8 * (c >> 1))) & 0xFFu));
+                const __half sc = __float2half(e8m0_to_f32((sc2 >> (8 * (j >> 1))) & 0xFFu));
                 const __half2 s2 = __half2half2(sc);
                 uint4 v;
                 __half2 t;
@@ -286,9 +289,13 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
         mbar_wait(smem_u32(&bar_accum), 0, 4);
         tcgen05_fence_after();
         const int q = warp & 3;                          // this warp's 32-lane quarter of TMEM
+        const int chalf = (warp - 2) >> 2;               // which half of the token columns
         const int m = m0 + q * 32 + lane;
+        constexpr int CB = BN / 32;                      // 32-column blocks in the tile
 #pragma unroll
-        for (int cb = 0; cb < BN / 32; cb++) {
+        for (int cbi = 0; cbi < (CB + 1) / 2; cbi++) {
+            const int cb = chalf * ((CB + 1) / 2) + cbi;
+            if (cb >= CB) break;
             uint32_t v[32];
             tcgen05_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), v);
             tcgen05_wait_ld();
@@ -311,8 +318,9 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                         *reinterpret_cast<uint4*>(orow + j) = o;
                     }
                 } else {
-                    for (int j = 0; j < 32 && nb + j < N; j++)
-                        orow[j] = __float2half(__uint_as_float(v[j]));
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (nb + j < N) orow[j] = __float2half(__uint_as_float(v[j]));
                 }
             }
         }
@@ -415,9 +423,11 @@ int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weig
                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r == CUDA_SUCCESS) {
+            // wider token tiles amortise the weight dequantisation over more tensor-core work
             const cudaError_t e =
-                (N > 64) ? launch_tc<128>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
-                         : launch_tc<64>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st);
+                (N > 128) ? launch_tc<256>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
+              : (N > 64)  ? launch_tc<128>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
+                          : launch_tc<64>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st);
             return (e == cudaSuccess) ? 0 : (int)e;
         }
     }
@@ -443,7 +453,7 @@ int nvfp4_gemm_status(int reset) {
 // Shared memory of the tensor-core GEMM's widest tile, for callers that size their launches the
 // way the reference's get_kernel_shared_mem_bytes does (kernels/nvfp4_cuda_v5.cu:460-464).
 int get_kernel_shared_mem_bytes() {
-    return nvfp4::GEMM_STAGES * (nvfp4::GEMM_BM * 128 + 2 * nvfp4::GEMM_BK * 128) + 1024;
+    return nvfp4::GEMM_STAGES * (nvfp4::GEMM_BM * 128 + 4 * nvfp4::GEMM_BK * 128) + 1024;
 }
 
 }  // extern "C"

@@ -4,7 +4,8 @@ Oracle: the reference's truth recipe — decode the weights to fp16 with the cod
 the fp16 activations (simulation/nvfp4_cuda_v5_test.py:90-91), here in float64.  Tolerances: the
 reference's own acceptance rule (mean_rel < 0.01 and max_abs < max(0.1, 1 % of max|ref|),
 simulation/nvfp4_cuda_v5_test.py:92-95,186) and, tighter, max |y - ref| / max(|ref|, 1e-3 max|ref|)
-<= 2e-3 (fp32 accumulation; fp16 output rounding alone is 4.9e-4)."""
+<= 2e-3 * max(1, sqrt(K / 4096)) (fp32 accumulation in tensor memory; fp16 output rounding alone
+is 4.9e-4)."""
 import numpy as np
 import pytest
 import torch
@@ -34,7 +35,9 @@ def check(y, packed, scales, act_kn):
     ok, mean_rel, max_abs = oc.reference_gemm_check(y, ref)
     assert ok, (mean_rel, max_abs)
     rel = oc.rel_error_floored(y, ref)
-    assert rel.max() <= 2e-3, rel.max()
+    K = act_kn.shape[0]
+    # the tensor core's fp32 accumulation error grows with the number of terms
+    assert rel.max() <= 2e-3 * max(1.0, (K / 4096) ** 0.5), rel.max()
 
 
 @pytest.mark.parametrize("M,N,K", [
