@@ -1,0 +1,155 @@
+"""The reference-style stack on the GPU: third-party model code + QLinear + patch_* + GraphDecoder
+(nvfp4_v100_b200/pipeline/_qwen38_infer.py), checked the way the reference's acceptance scripts do
+(pipeline/_qwen38_r1.py:269-296, experiments/_qwen38_p9_acc.py:90-119): greedy tokens of the fully
+patched, graph-replayed stack against the unpatched eager stack from the same prefill state, in
+one process.  A token may differ only where the eager stack's own top-1/top-2 margin is a few fp16
+steps; the comparison stops there."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+tf = pytest.importorskip("transformers")
+SMALL = dict(hidden=256, inter=512, vocab=1000, n_layers=4, hq=2, hkv=1, dn_kheads=1,
+             dn_vheads=2, max_len=64, rope_theta=1e7)
+MARGIN = 6e-3
+
+
+def write_container(tmp, cfg, W):
+    from nvfp4_v100_b200.pipeline import _qwen38_nvfp4_pack as pk
+
+    pre = "model.language_model."
+    tensors, quant = {}, {}
+    for name, val in W.items():
+        if name == "embed_tokens":
+            tensors[pre + "embed_tokens.weight"] = np.asarray(val, np.float16)
+        elif name == "lm_head":
+            quant["lm_head.weight"] = val
+        elif isinstance(val, tuple):
+            quant[pre + name + ".weight"] = val
+        elif name == "norm.weight":
+            tensors[pre + "norm.weight"] = np.asarray(val, np.float32)
+        elif name.endswith("conv1d.weight"):
+            tensors[pre + name] = np.asarray(val, np.float32).reshape(-1, 1, 4)
+        else:
+            tensors[pre + name] = np.asarray(val, np.float32)
+    index = pk.pack_tensors(tensors, tmp, prequantised=quant)
+    hf_cfg = dict(
+        vocab_size=cfg.vocab, hidden_size=cfg.hidden, intermediate_size=cfg.inter,
+        num_hidden_layers=cfg.n_layers, num_attention_heads=cfg.hq, num_key_value_heads=cfg.hkv,
+        head_dim=256, linear_num_key_heads=cfg.dn_kheads, linear_num_value_heads=cfg.dn_vheads,
+        linear_key_head_dim=128, linear_value_head_dim=128, linear_conv_kernel_dim=4,
+        rms_norm_eps=cfg.rms_eps, max_position_embeddings=cfg.max_len, tie_word_embeddings=False,
+        rope_parameters={"rope_type": "default", "rope_theta": cfg.rope_theta,
+                         "partial_rotary_factor": 1.0})
+    json.dump(hf_cfg, open(os.path.join(tmp, "config.json"), "w"))
+    return index
+
+
+def snap_all(model, cache, L, Q):
+    kv = Q.snap_decode_state(model, cache, L)
+    lin = []
+    for i, lay in enumerate(cache.layers):
+        if hasattr(lay, "conv_states"):
+            lin.append((i, lay.conv_states.clone(), lay.recurrent_states.clone()))
+    return kv, lin
+
+
+def restore_all(model, cache, snap, L, Q):
+    kv, lin = snap
+    Q.restore_decode_state(model, cache, kv, L)
+    for i, c, r in lin:
+        cache.layers[i].conv_states.copy_(c)
+        cache.layers[i].recurrent_states.copy_(r)
+
+
+def test_patched_graph_stack_matches_eager_stack(lib, tmp_path):
+    from transformers import StaticCache
+
+    from nvfp4_v100_b200.engine import ModelConfig
+    from nvfp4_v100_b200.pipeline import _qwen38_infer as Q
+    from oracle import decode_oracle as do
+
+    cfg = ModelConfig(**SMALL)
+    W = do.make_weights(cfg, 1)
+    index = write_container(str(tmp_path), cfg, W)
+    assert index["lm_head.weight"]["fmt"] == "nvfp4_v2_embedded_sign"
+    hf_cfg, model = Q.build_model(str(tmp_path))
+    assert isinstance(model.lm_head, Q.QLinear) and model.lm_head.M == cfg.vocab
+
+    prompt = np.random.default_rng(1).integers(0, cfg.vocab, 8)
+    ids = torch.from_numpy(prompt).cuda().view(1, -1)
+    L, n_gen = ids.shape[1], 12
+    cache = StaticCache(config=model.config, max_cache_len=cfg.max_len)
+    first = Q.prefill(model, cache, ids)              # T = 8: every QLinear takes the GEMM path
+    snap = snap_all(model, cache, L, Q)
+    emb_w = model.model.embed_tokens.weight_cpu
+
+    # ---- stack A: eager, unpatched (third-party operators + QLinear GEMV) ----
+    toks_a, margins = [first], []
+    cur = first
+    with torch.no_grad():
+        for t in range(n_gen):
+            o = model(torch.tensor([[cur]], device="cuda"), past_key_values=cache, use_cache=True,
+                      cache_position=torch.tensor([L + t], device="cuda"))
+            lg = o.logits[0, -1].float()
+            top2 = torch.topk(lg, 2).values
+            margins.append(float(top2[0] - top2[1]))
+            cur = int(lg.argmax())
+            toks_a.append(cur)
+
+    # ---- stack B: every fused kernel + the whole step in a CUDA graph ----
+    restore_all(model, cache, snap, L, Q)
+    mods = Q.patch_fused_deltanet(model, cache)
+    Q.patch_attn_decode(model, cache, max_len=cfg.max_len)
+    Q.patch_rmsnorm(model)
+    Q.patch_rope()
+    Q.patch_mlp_silu_mul(model)
+    vf_snap = [(m._vf_conv.clone(), m._vf_S.clone()) for m in mods]
+    dec = Q.GraphDecoder(model, cache, L, cfg.hidden)
+    restore_all(model, cache, snap, L, Q)             # warm-up and capture advanced the state
+    for m, (c, s) in zip(mods, vf_snap):
+        m._vf_conv.copy_(c)
+        m._vf_S.copy_(s)
+    dec.reset_pos()
+    torch.cuda.synchronize()
+    toks_b = [first]
+    cur = first
+    with torch.no_grad():
+        for _ in range(n_gen):
+            cur = dec.step(cur, emb_w)
+            toks_b.append(cur)
+
+    matched = 0
+    for i in range(1, n_gen + 1):
+        if toks_a[i] == toks_b[i]:
+            matched += 1
+            continue
+        assert margins[i - 1] < MARGIN, (i, toks_a[i], toks_b[i], margins[i - 1])
+        break
+    print(f"\npatched+graph vs eager: {matched}/{n_gen} tokens identical; min margin {min(margins):.4f}")
+    assert matched >= 1
+    # restore the module-level patch for other tests in this process
+    from transformers.models.qwen3_5 import modeling_qwen3_5 as hf
+    hf.apply_rotary_pos_emb = hf._vf_rope_orig
+
+
+def test_qlinear_dispatch_by_token_count(lib):
+    from nvfp4_v100_b200.pipeline import _qwen38_infer as Q
+    from oracle import nvfp4_codec_oracle as oc
+
+    M, K = 320, 512
+    w = oc.synthetic_weight(M, K, seed=2)
+    p, s = oc.encode(w)
+    d_p, d_s = torch.from_numpy(p).cuda(), torch.from_numpy(s).cuda()
+    lin = Q.QLinear(d_p.data_ptr(), d_s.data_ptr(), M, K)
+    wd = oc.decode_f64(p, s)
+    for T in (1, 2, 3, 8, 40):
+        x = torch.randn(1, T, K, device="cuda").half()
+        y = lin(x)
+        assert y.shape == (1, T, M)
+        ref = x[0].double().cpu().numpy() @ wd.T
+        assert oc.rel_error_floored(y[0].cpu().numpy(), ref).max() <= 2e-3, T
