@@ -22,7 +22,8 @@ weights produce), activations ~N(0, 1) fp16.
 
 With --gpus N > 1 (launched by torchrun, one process per GPU) the step is tensor-parallel: q/k/v,
 gate/up, in_proj and lm_head are split by output rows, o_proj/out_proj/down_proj by K, and every
-K-split layer is followed by an NCCL all-reduce of its 5120-element fp16 output (128 per step).
+K-split layer is followed by an all-reduce of its 5120-element fp16 output (128 per step), done by
+the library's one-shot peer-memory kernel over NVLink (NCCL only carries the rendezvous).
 Total work is fixed, so scaling is "strong".
 """
 from __future__ import annotations
@@ -257,16 +258,32 @@ def run_ours(args):
         total_alg += gemv_bytes(m, k)
     n_launch = len(layers)
     n_allreduce = sum(1 for l in layers if l[3] == "row") if world > 1 else 0
+    comm = None
+    if world > 1:
+        # K-split layers write their partial vector into this rank's peer-visible buffer; the
+        # library's one-shot all-reduce kernel sums the ranks' vectors into `resid`
+        from nvfp4_v100_b200.comm import PeerComm
+
+        comm = PeerComm(HIDDEN, rank, world)
+        resid = torch.zeros(HIDDEN, dtype=torch.float16, device="cuda")
+        assert n_allreduce % 2 == 0
+
+    def gemv(name, m, k, split, packed, scales, act, out, st):
+        dst = out.data_ptr()
+        parity = 0
+        if comm is not None and split == "row":
+            dst, parity = comm.next_slot()
+        rc = lib.launch_nvfp4_gemv_v8(vp(packed.data_ptr()), vp(scales.data_ptr()),
+                                      vp(act.data_ptr()), vp(dst), m, k, st)
+        if rc != 0:
+            raise RuntimeError(f"{name}: launch_nvfp4_gemv_v8 rc={rc}")
+        if comm is not None and split == "row":
+            comm.allreduce_residual(resid, parity, st)
 
     def enqueue_step():
         st = vp(torch.cuda.current_stream().cuda_stream)
         for name, m, k, split, packed, scales, act, out in layers:
-            rc = lib.launch_nvfp4_gemv_v8(vp(packed.data_ptr()), vp(scales.data_ptr()),
-                                          vp(act.data_ptr()), vp(out.data_ptr()), m, k, st)
-            if rc != 0:
-                raise RuntimeError(f"{name}: launch_nvfp4_gemv_v8 rc={rc}")
-            if world > 1 and split == "row":
-                dist.all_reduce(out)
+            gemv(name, m, k, split, packed, scales, act, out, st)
 
     # warm-up outside the graph (module load, NCCL channels), then capture one step
     side = torch.cuda.Stream()
@@ -316,13 +333,8 @@ def run_ours(args):
         st = vp(torch.cuda.current_stream().cuda_stream)
         for (name, m, k, split, packed, scales, act, out), ha, ho in zip(layers, h_act, h_out):
             act.copy_(ha, non_blocking=True)
-            rc = lib.launch_nvfp4_gemv_v8(vp(packed.data_ptr()), vp(scales.data_ptr()),
-                                          vp(act.data_ptr()), vp(out.data_ptr()), m, k, st)
-            if rc != 0:
-                raise RuntimeError(f"{name}: rc={rc}")
-            if world > 1 and split == "row":
-                dist.all_reduce(out)
-            ho.copy_(out, non_blocking=True)
+            gemv(name, m, k, split, packed, scales, act, out, st)
+            ho.copy_(resid if (comm is not None and split == "row") else out, non_blocking=True)
 
     e2e_steps = max(1, min(args.steps, 5))
     e2e_step()
@@ -386,6 +398,8 @@ def run_ours(args):
                    "algorithmic_bytes_per_step": int(job_bytes),
                    "l2": "each step streams 14.4 GB of weights (>> 126 MB L2): reads are cold",
                    "parallelism": f"tp{world}", "allreduce_per_step": n_allreduce,
+                   "allreduce": "one-shot peer-memory kernel" if comm is not None else "none",
+                   "comm_status": comm.status() if comm is not None else 0,
                    "launch": "cuda_graph"},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps,
@@ -687,8 +701,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--gen", type=int, default=63)
     ap.add_argument("--vocab", type=int, default=VOCAB)
-    ap.add_argument("--allreduce", default="peer", choices=["peer", "nccl"],
-                    help="with --decode under torchrun: one-shot peer-memory all-reduce or NCCL")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "peer", "nccl"],
+                    help="with --decode under torchrun: GEMV+all-reduce in one kernel, a separate "
+                         "one-shot peer-memory all-reduce kernel, or NCCL")
     ap.add_argument("--fake-context", type=int, default=0,
                     help="with --decode: start at this cache length (zero-filled cache)")
     ap.add_argument("--eager", action="store_true",

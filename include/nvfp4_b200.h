@@ -192,7 +192,16 @@ int launch_pick_global_argmax(const void* cand_all, int world, void* tok, void* 
  * does h += f16(sum over ranks, fp32, rank order).  parity alternates 0, 1, 0, ... over the calls;
  * every rank makes the same sequence of calls.  bufs is a HOST array of `world` device pointers
  * (rank r's buffer as mapped in this process).  world <= 8, n % 8 == 0.  nvfp4_comm_status returns
- * 0, or 1 + r if peer r failed to arrive within the spin limit at some call. */
+ * 0, or 1 + r if peer r failed to arrive within the spin limit at some call.
+ * launch_nvfp4_gemv_allreduce fuses the K-split GEMV itself with that all-reduce: h[M] +=
+ * f16(sum over ranks of W_r . act_r) in ONE kernel — each CTA stores its tile's partial outputs
+ * into every rank's buffer (peer stores, overlapping the remaining tiles), the last CTA to finish
+ * exchanges flags with the peers (bounded wait; status 101 + r on timeout) and applies the sum to
+ * h.  M % 16 == 0, M <= n, K % 128 == 0, GEMV alignment rules; -2 bad arguments, -1 launch error. */
+int launch_nvfp4_gemv_allreduce(const void* weight_packed, const void* weight_scales,
+                                const void* activation, void* h, int M, int K,
+                                const void* const* bufs, int rank, int world, int n, int parity,
+                                void* stream);
 long long nvfp4_comm_buffer_bytes(int n);
 long long nvfp4_comm_data_offset(int n, int parity);
 int nvfp4_comm_init(void* buf, int n);

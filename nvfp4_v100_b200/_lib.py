@@ -57,6 +57,8 @@ SIGNATURES = {
     "nvfp4_ipc_open_handle": ([_vp], _vp),
     "nvfp4_ipc_close_handle": ([_vp], _i),
     "nvfp4_comm_status": ([_vp], _i),
+    "launch_nvfp4_gemv_allreduce": ([_vp, _vp, _vp, _vp, _i, _i, ctypes.POINTER(_vp), _i, _i, _i, _i,
+                                     _vp], _i),
     "launch_allreduce_residual": ([_vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _vp], _i),
     "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
     "launch_dn_fused_heads": ([_vp] * 12 + [_i, _i, _f, _vp], _i),

@@ -13,7 +13,8 @@
 // nothing is copied on the sending side.
 //
 // Communication buffer (one per rank, cudaMalloc'ed by that rank, opened by the others through
-// CUDA IPC):  u32 counter | u32 error | pad | u32 flags[8] at byte 64 | data[2][n] fp16 at byte 256.
+// CUDA IPC):  u32 counter | u32 error | pad | u32 flags[8] at byte 64 | data[2][n] fp16 at byte 256,
+// followed by the push area used by the fused GEMV + all-reduce kernel (gemv.cu).
 // Vectors alternate between the two data slots (`parity`): a rank can overwrite slot p for call
 // s+2 only after it has finished call s+1, which needed every peer's flag for s+1, which a peer
 // sends only after it has finished reading call s.
@@ -118,7 +119,8 @@ extern "C" {
 // Bytes a communication buffer for vectors of n fp16 elements needs.
 long long nvfp4_comm_buffer_bytes(int n) {
     if (n <= 0 || n % 8 != 0) return -1;
-    return NVFP4_COMM_DATA_OFF + 2LL * n * 2;
+    // header + pull area data[2][n] + push area data[2][8][n] (launch_nvfp4_gemv_allreduce)
+    return NVFP4_COMM_DATA_OFF + 2LL * n * 2 + 2LL * 8 * n * 2;
 }
 
 // Byte offset of data slot `parity` (0 or 1): where the producing GEMV writes its partial vector.

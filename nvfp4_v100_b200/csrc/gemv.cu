@@ -113,12 +113,27 @@ struct WeightRegs {
 // entry points run with PRO_NONE / EPI_STORE).
 enum { PRO_NONE = 0, PRO_RMSNORM = 1 };
 #define PRO_NV 5  // 16-byte activation vectors a thread holds in the RMSNorm prologue
-enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2 };
+enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_ALLREDUCE = 3 };
 struct GemvExtra {
     const float* norm_w1;     // PRO_RMSNORM: fp32 (1 + weight) [K]
     float eps;                // PRO_RMSNORM
     const __half* residual;   // EPI_RESIDUAL: fp16 [M], out = f16(residual + f16(y))
+    // EPI_ALLREDUCE: every rank's communication buffer as mapped in this process, this rank,
+    // the number of ranks, the data slot, and the buffers' vector capacity
+    unsigned char* comm[8];
+    int rank, world, parity, comm_n;
 };
+
+// Layout of the push area of a communication buffer (shared with comm.cu, which owns the
+// buffer): u32 push sequence at byte 16, u32 finished-CTA counter at byte 20, u32 flags[2][8] at
+// byte 128, and after the pull area (256 + 4 n bytes) fp16 data[2][8][n].
+#define NVFP4_PUSH_SEQ_OFF 16
+#define NVFP4_PUSH_DONE_OFF 20
+#define NVFP4_PUSH_FLAGS_OFF 128
+#define NVFP4_PUSH_SPIN_LIMIT (1u << 22)
+__device__ __forceinline__ size_t push_data_off(int n, int parity, int src) {
+    return 256 + (size_t)4 * n + ((size_t)(parity * 8 + src) * n) * sizeof(__half);
+}
 
 __device__ __forceinline__ void lds_x_pred(uint32_t saddr, uint32_t pred, uint32_t& r0,
                                            uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -140,6 +155,13 @@ __device__ __forceinline__ void lds_x_pred(uint32_t saddr, uint32_t pred, uint32
 //   EPI_SILU_MUL: W holds gate and up rows interleaved in groups of 8 (tile rows 0..7 = gate rows
 //                 8j..8j+7, rows 8..15 = up rows 8j..8j+7; M = 2 * outputs);
 //                 out[8j+r] = f16( f32(f16(silu(f16(g)))) * f32(f16(u)) ), the silu_mul_kernel chain.
+//   EPI_ALLREDUCE: tensor-parallel K-split layer, GEMV and all-reduce in ONE kernel.  Every CTA
+//                 stores its tile's 16 partial outputs straight into the communication buffer of
+//                 EVERY rank (peer stores over NVLink, overlapping the remaining tiles' math).
+//                 The CTA that finishes last on this GPU publishes "rank r, vector seq complete"
+//                 to all peers, waits (bounded) for theirs, and then does
+//                 out[m] = f16(f32(out[m]) + f32(f16(sum over ranks, fp32, rank order))) for the
+//                 whole vector: `out` is the residual stream, updated in place.
 template <int WARPS, int NACT, int PRO, int EPI>
 __global__ void __launch_bounds__(WARPS * 32, 768 / (WARPS * 32))  // 24 warps per SM resident
 gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
@@ -389,6 +411,20 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
                         out[tile * 8 + r] = __float2half(sl * uf);
                     }
                 }
+            } else if (EPI == EPI_ALLREDUCE) {
+                if ((int)threadIdx.x < ex.world) {
+                    // 16 partial outputs of this tile -> slot [parity][this rank] of rank tid
+                    uint4 v[2];
+                    __half2* hp = reinterpret_cast<__half2*>(v);
+#pragma unroll
+                    for (int r = 0; r < 8; r++)
+                        hp[r] = __floats2half2_rn(pt[2 * r][0], pt[2 * r + 1][0]);
+                    unsigned char* dst = ex.comm[threadIdx.x] +
+                                         push_data_off(ex.comm_n, ex.parity, ex.rank) +
+                                         (size_t)tile * 16 * sizeof(__half);
+                    reinterpret_cast<uint4*>(dst)[0] = v[0];
+                    reinterpret_cast<uint4*>(dst)[1] = v[1];
+                }
             } else if (threadIdx.x < 16 * NACT) {
                 const int r = threadIdx.x & 15, a = threadIdx.x >> 4;
                 float v = pt[r][a];
@@ -414,6 +450,74 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         if (e + 1 < total) do_elem(other, cur);
     }
     if (S > 1) cluster_sync_all();   // no CTA may exit while a peer can still read its shared memory
+
+    if (EPI == EPI_ALLREDUCE) {
+        __shared__ uint32_t s_last, s_seq;
+        unsigned char* mine = ex.comm[ex.rank];
+        uint32_t* errw = reinterpret_cast<uint32_t*>(mine + 4);
+        __threadfence_system();          // this CTA's peer stores before its "finished" count
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t* done = reinterpret_cast<uint32_t*>(mine + NVFP4_PUSH_DONE_OFF);
+            const uint32_t prev = atomicAdd(done, 1u);
+            s_last = (prev == gridDim.x - 1) ? 1u : 0u;
+            if (s_last) {
+                *done = 0u;
+                uint32_t* seqp = reinterpret_cast<uint32_t*>(mine + NVFP4_PUSH_SEQ_OFF);
+                s_seq = *seqp + 1u;
+                *seqp = s_seq;
+                __threadfence_system();  // every CTA's stores (seen through the counter) first
+            }
+        }
+        __syncthreads();
+        if (s_last) {
+            const uint32_t seq = s_seq;
+            const int tid = threadIdx.x;
+            if (tid < ex.world && tid != ex.rank) {
+                uint32_t* pf = reinterpret_cast<uint32_t*>(ex.comm[tid] + NVFP4_PUSH_FLAGS_OFF) +
+                               ex.parity * 8 + ex.rank;
+                asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(pf), "r"(seq) : "memory");
+                const uint32_t* mf = reinterpret_cast<const uint32_t*>(mine + NVFP4_PUSH_FLAGS_OFF) +
+                                     ex.parity * 8 + tid;
+                uint32_t spins = 0, v;
+                do {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(mf) : "memory");
+                    if ((int32_t)(v - seq) >= 0) break;
+                } while (++spins <= NVFP4_PUSH_SPIN_LIMIT);
+                if ((int32_t)(v - seq) < 0) atomicExch(errw, 101u + (uint32_t)tid);
+            }
+            __syncthreads();
+            // out[m] += f16(sum of the ranks' partial vectors), all now in THIS rank's buffer
+            for (int i = tid * 8; i < M; i += WARPS * 32 * 8) {
+                float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+                for (int r = 0; r < ex.world; r++) {
+                    uint4 v;
+                    const void* src = mine + push_data_off(ex.comm_n, ex.parity, r) +
+                                      (size_t)i * sizeof(__half);
+                    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                                 : "l"(src)
+                                 : "memory");
+                    const __half2* hp = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 f = __half22float2(hp[e]);
+                        acc[2 * e] += f.x;
+                        acc[2 * e + 1] += f.y;
+                    }
+                }
+                uint4 hv = *reinterpret_cast<const uint4*>(out + i);
+                __half2* hp = reinterpret_cast<__half2*>(&hv);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(hp[e]);
+                    hp[e] = __floats2half2_rn(f.x + round_f16(acc[2 * e]),
+                                              f.y + round_f16(acc[2 * e + 1]));
+                }
+                *reinterpret_cast<uint4*>(out + i) = hv;
+            }
+        }
+    }
 }
 
 // Generic path for shapes or pointers the tensor-core kernel does not take (K % 128 != 0, or
@@ -592,7 +696,7 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
         GemvPlan plan = plan_gemv(M, K);
         if (g_cfg.warps == 2) plan = {2, 1, (M + 15) / 16 < num_sms() * 12 ? (M + 15) / 16 : num_sms() * 12};
         const int warps = plan.warps;
-        const GemvExtra none = {nullptr, 0.0f, nullptr};
+        GemvExtra none = {};
         if (nact == 1) {
             e = (warps == 8) ? launch_mma<8, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none, plan)
               : (warps == 2) ? launch_mma<2, 1, 0, 0>(packed, scales, a0, a1, out, M, K, st, none, plan)
@@ -635,7 +739,10 @@ int gemv_ex_dispatch(const void* packed, const void* scales, const void* act, vo
     if (epilogue < EPI_STORE || epilogue > EPI_SILU_MUL) return NVFP4_ERR_SHAPE;
     if (epilogue == EPI_RESIDUAL && !residual) return NVFP4_ERR_SHAPE;
     if (epilogue == EPI_SILU_MUL && M % 16 != 0) return NVFP4_ERR_SHAPE;
-    const GemvExtra ex = {(const float*)norm_w1, eps, (const __half*)residual};
+    GemvExtra ex = {};
+    ex.norm_w1 = (const float*)norm_w1;
+    ex.eps = eps;
+    ex.residual = (const __half*)residual;
     cudaStream_t st = (cudaStream_t)stream;
     GemvPlan plan = plan_gemv(M, K);
     if (prologue == PRO_RMSNORM) {
@@ -671,9 +778,59 @@ int gemv_ex_dispatch(const void* packed, const void* scales, const void* act, vo
     return NVFP4_OK;
 }
 
+// Tensor-parallel K-split layer: GEMV + all-reduce + residual add in one kernel.
+int gemv_allreduce_dispatch(const void* packed, const void* scales, const void* act, void* h, int M,
+                            int K, const void* const* bufs, int rank, int world, int n, int parity,
+                            void* stream) {
+    if (K <= 0 || K % 128 != 0 || M <= 0 || M % 16 != 0) return NVFP4_ERR_SHAPE;
+    if (!packed || !scales || !act || !h || !bufs) return NVFP4_ERR_SHAPE;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || n < M || n % 8 != 0)
+        return NVFP4_ERR_SHAPE;
+    if (!aligned(packed, 32) || !aligned(scales, 8) || !aligned(act, 16) || !aligned(h, 16))
+        return NVFP4_ERR_SHAPE;
+    GemvExtra ex = {};
+    for (int r = 0; r < world; r++) {
+        if (!bufs[r]) return NVFP4_ERR_SHAPE;
+        ex.comm[r] = (unsigned char*)bufs[r];
+    }
+    ex.rank = rank;
+    ex.world = world;
+    ex.parity = parity & 1;
+    ex.comm_n = n;
+    const int save = g_cfg.max_split;
+    g_cfg.max_split = 1;                         // the finished-CTA count assumes one CTA per tile
+    GemvPlan plan = plan_gemv(M, K);
+    g_cfg.max_split = save;
+    plan.split = 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    const cudaError_t e =
+        (plan.warps == 8)
+            ? launch_mma<8, 1, 0, EPI_ALLREDUCE>(packed, scales, act, nullptr, h, M, K, st, ex, plan)
+            : launch_mma<4, 1, 0, EPI_ALLREDUCE>(packed, scales, act, nullptr, h, M, K, st, ex, plan);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "launch_nvfp4_gemv_allreduce: %s\n", cudaGetErrorString(e));
+        return NVFP4_ERR_LAUNCH;
+    }
+    return NVFP4_OK;
+}
+
 }  // namespace nvfp4
 
 extern "C" {
+
+// h[M] (fp16, in place) += f16( sum over the ranks of W_r[M, K] . act_r[K] ): a tensor-parallel
+// K-split layer, its all-reduce and the residual add as ONE kernel over NVLink peer memory.
+// bufs: HOST array of `world` device pointers, every rank's communication buffer as mapped here
+// (see nvfp4_comm_buffer_bytes); n: the buffers' vector capacity (n >= M); parity alternates
+// 0, 1, 0, ... over the calls; every rank makes the same sequence of calls.  No counterpart in
+// the reference.  0; -2 bad arguments; -1 launch error.
+int launch_nvfp4_gemv_allreduce(const void* weight_packed, const void* weight_scales,
+                                const void* activation, void* h, int M, int K,
+                                const void* const* bufs, int rank, int world, int n, int parity,
+                                void* stream) {
+    return nvfp4::gemv_allreduce_dispatch(weight_packed, weight_scales, activation, h, M, K, bufs,
+                                          rank, world, n, parity, stream);
+}
 
 // GEMV with optional fused RMSNorm of the activation (prologue = 1) and fused residual add
 // (epilogue = 1) or silu(gate)*up over interleaved gate/up rows (epilogue = 2).  No counterpart in

@@ -112,11 +112,13 @@ class DecodeEngine:
     """Holds the prepared weights and all state of one sequence and replays the step graph."""
 
     def __init__(self, cfg: ModelConfig, device: str = "cuda", tp_rank: int = 0, tp_world: int = 1,
-                 allreduce: str = "peer"):
+                 allreduce: str = "fused"):
         """tp_world > 1: this process holds shard tp_rank of a tensor-parallel group (one process
         per GPU, torch.distributed initialised with the NCCL backend by the caller).
-        allreduce: "peer" = this library's one-shot all-reduce + residual kernel over NVLink peer
-        memory; "nccl" = NCCL all-reduce followed by a residual-add kernel."""
+        allreduce: "fused" = the K-split GEMV, its all-reduce and the residual add are ONE kernel
+        (peer stores per tile, last CTA reduces); "peer" = GEMV, then this library's one-shot
+        all-reduce + residual kernel over NVLink peer memory; "nccl" = GEMV, NCCL all-reduce, then
+        a residual-add kernel."""
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; there is no CPU fallback")
         self.cfg = cfg
@@ -170,42 +172,19 @@ class DecodeEngine:
         self.lm_head = None
         self.allreduce = allreduce if W > 1 else "none"
         self.ar_calls = 0
-        if self.allreduce == "peer":
+        if self.allreduce in ("peer", "fused"):
             self._setup_peer_comm()
 
     def _setup_peer_comm(self):
-        """Allocate this rank's communication buffer, exchange CUDA IPC handles, map the peers'."""
-        import torch.distributed as dist
+        from .comm import PeerComm
 
-        lib, n = self.lib, self.cfg.hidden
-        nbytes = lib.nvfp4_comm_buffer_bytes(n)
-        self.comm_own = lib.gpu_malloc(nbytes)
-        if not self.comm_own or lib.nvfp4_comm_init(vp(self.comm_own), n) != 0:
-            raise RuntimeError("communication buffer allocation failed")
-        hdl = ctypes.create_string_buffer(64)
-        if lib.nvfp4_ipc_get_handle(vp(self.comm_own), hdl) != 0:
-            raise RuntimeError("cudaIpcGetMemHandle failed")
-        handles = [None] * self.world
-        dist.all_gather_object(handles, hdl.raw)
-        ptrs = []
-        for r, raw in enumerate(handles):
-            if r == self.rank:
-                ptrs.append(self.comm_own)
-            else:
-                p = lib.nvfp4_ipc_open_handle(ctypes.create_string_buffer(raw, 64))
-                if not p:
-                    raise RuntimeError(f"cannot map rank {r}'s communication buffer")
-                ptrs.append(p)
-        self.comm_ptrs = (vp * self.world)(*ptrs)
-        self.comm_slot = [self.comm_own + lib.nvfp4_comm_data_offset(n, p) for p in (0, 1)]
-        dist.barrier()
+        self.comm = PeerComm(self.cfg.hidden, self.rank, self.world)
 
     def comm_status(self) -> int:
         """0 if every peer wait of the one-shot all-reduce was answered in time."""
-        if self.allreduce != "peer":
+        if self.allreduce not in ("peer", "fused"):
             return 0
-        torch.cuda.synchronize()
-        return self.lib.nvfp4_comm_status(vp(self.comm_own))
+        return self.comm.status()
 
     # ------------------------------------------------------------------ weights
     def _mat(self, packed: torch.Tensor, scales: torch.Tensor, M: int, K: int) -> _Mat:
@@ -365,13 +344,23 @@ class DecodeEngine:
         if self.world == 1:
             self._gemv(st, m, x, self.h, epi=1, residual=self.h)
             return
-        if self.allreduce == "peer":
-            parity = self.ar_calls & 1
+        if self.allreduce == "fused":
+            _, parity = self.comm.next_slot()
             self.ar_calls += 1
-            self._gemv(st, m, x, self.comm_slot[parity])
-            rc = self.lib.launch_allreduce_residual(vp(self.h.data_ptr()), self.comm_ptrs, self.rank,
-                                                    self.world, self.cfg.hidden, parity, st)
-            assert rc == 0, rc
+            rc = self.lib.launch_nvfp4_gemv_allreduce(
+                vp(m.packed.data_ptr()), vp(m.scales.data_ptr()), vp(x.data_ptr()),
+                vp(self.h.data_ptr()), m.M, m.K, self.comm.ptrs, self.rank, self.world,
+                self.cfg.hidden, parity, st)
+            if rc != 0:
+                raise RuntimeError(f"launch_nvfp4_gemv_allreduce rc={rc}")
+            self.n_launch += 1
+            self.n_collective += 1
+            return
+        if self.allreduce == "peer":
+            slot, parity = self.comm.next_slot()
+            self.ar_calls += 1
+            self._gemv(st, m, x, slot)
+            self.comm.allreduce_residual(self.h, parity, st)
             self.n_launch += 1
             self.n_collective += 1
             return

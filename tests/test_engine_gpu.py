@@ -230,7 +230,7 @@ def test_allreduce_residual_single_rank(lib):
     # world = 1: no peers to wait for; h += f16(own partial vector), alternating data slots
     n = 5120
     nbytes = lib.nvfp4_comm_buffer_bytes(n)
-    assert nbytes == 256 + 4 * n
+    assert nbytes == 256 + 4 * n + 32 * n      # header, pull area [2][n], push area [2][8][n]
     buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
     assert lib.nvfp4_comm_init(ptr(buf), n) == 0
     rng = np.random.default_rng(0)
@@ -251,3 +251,31 @@ def test_allreduce_residual_single_rank(lib):
     assert int(buf[:4].view(torch.int32)) == 4           # the call counter
     assert lib.launch_allreduce_residual(ptr(d_h), bufs, 0, 9, n, 0, stream()) == -1
     assert lib.launch_allreduce_residual(ptr(d_h), bufs, 0, 1, n + 4, 0, stream()) == -1
+
+
+def test_gemv_allreduce_single_rank_equals_residual_epilogue(lib):
+    # world = 1: the fused GEMV + all-reduce + residual kernel must give exactly what the GEMV
+    # with the residual epilogue gives; run twice to alternate the data slots
+    M, K, n = 5120, 6144, 5120
+    w = oc.synthetic_weight(M, K, seed=77)
+    p, s = oc.encode(w)
+    d_p, d_s = dev(p), dev(s)
+    buf = torch.zeros(lib.nvfp4_comm_buffer_bytes(n), dtype=torch.uint8, device="cuda")
+    assert lib.nvfp4_comm_init(ptr(buf), n) == 0
+    bufs = (ctypes.c_void_p * 1)(buf.data_ptr())
+    rng = np.random.default_rng(5)
+    h0 = rng.standard_normal(M).astype(np.float16)
+    h_a, h_b = dev(h0), dev(h0)
+    for call in range(3):
+        x = dev(rng.standard_normal(K).astype(np.float16))
+        rc = lib.launch_nvfp4_gemv_fused(ptr(d_p), ptr(d_s), ptr(x), ptr(h_a), M, K, 0,
+                                         ctypes.c_void_p(0), 1e-6, 1, ptr(h_a), stream())
+        assert rc == 0
+        rc = lib.launch_nvfp4_gemv_allreduce(ptr(d_p), ptr(d_s), ptr(x), ptr(h_b), M, K, bufs, 0, 1,
+                                             n, call & 1, stream())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert torch.equal(h_a, h_b), call
+    assert lib.nvfp4_comm_status(ptr(buf)) == 0
+    assert lib.launch_nvfp4_gemv_allreduce(ptr(d_p), ptr(d_s), ptr(x), ptr(h_b), M + 8, K, bufs, 0,
+                                           1, n, 0, stream()) == -2

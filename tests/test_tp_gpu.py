@@ -31,7 +31,7 @@ def _worker(rank, world, port, q):
     W = do.make_weights(cfg, 1)
     prompt = np.random.default_rng(1).integers(0, cfg.vocab, 8)
     out = {}
-    for mode in ("peer", "nccl"):
+    for mode in ("fused", "peer", "nccl"):
         eng = DecodeEngine(cfg, device=f"cuda:{rank}", tp_rank=rank, tp_world=world, allreduce=mode)
         eng.load_weights(W)
         eager = eng.run(prompt, 16)
@@ -39,7 +39,7 @@ def _worker(rank, world, port, q):
         eng.capture(n_warmup=1)
         graphed = eng.run(prompt, 16)
         out[mode] = (eager, graphed, eng.comm_status(), eng.n_collective)
-    eager, graphed = out["peer"][:2]
+    eager, graphed = out["fused"][:2]
     single = None
     if rank == 0:
         one = DecodeEngine(cfg, device="cuda:0")
@@ -71,8 +71,10 @@ def test_tp2_matches_single_gpu_and_oracle():
     (r0, eager0, graph0, single, out0), (r1, eager1, graph1, _, out1) = res
     assert eager0 == eager1 == graph0 == graph1          # ranks agree; graph replay == eager
     for o in (out0, out1):
-        assert o["peer"][2] == 0                         # no peer wait ever ran out
-        assert o["peer"][3] == o["nccl"][3] == 2 * 4 + 1  # 2 K-split layers per layer + argmax
+        assert o["peer"][2] == 0 and o["fused"][2] == 0   # no peer wait ever ran out
+        assert o["fused"][3] == o["peer"][3] == o["nccl"][3] == 2 * 4 + 1  # K-split layers + argmax
+        assert o["peer"][0] == o["peer"][1]
+        assert o["peer"][1] == o["fused"][1]              # same sum order: identical tokens
         assert o["nccl"][0] == o["nccl"][1]
     # NCCL sums the fp16 partial vectors its own way; allow a near-tie divergence between modes
     nccl = out0["nccl"][1]
