@@ -701,7 +701,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--gen", type=int, default=63)
     ap.add_argument("--vocab", type=int, default=VOCAB)
-    ap.add_argument("--allreduce", default="fused", choices=["fused", "peer", "nccl"],
+    ap.add_argument("--allreduce", default="peer", choices=["fused", "peer", "nccl"],
                     help="with --decode under torchrun: GEMV+all-reduce in one kernel, a separate "
                          "one-shot peer-memory all-reduce kernel, or NCCL")
     ap.add_argument("--fake-context", type=int, default=0,

@@ -59,6 +59,7 @@ __device__ __forceinline__ uint4 ld_relaxed_sys_u4(const void* p) {
 __global__ void __launch_bounds__(1024)
 allreduce_residual_kernel(CommPeers peers, int rank, int world, int n, int parity,
                           __half* __restrict__ h) {
+    pdl_prologue();
     __shared__ uint32_t s_seq;
     unsigned char* mine = peers.buf[rank];
     uint32_t* counter = reinterpret_cast<uint32_t*>(mine);
@@ -195,9 +196,9 @@ int launch_allreduce_residual(void* h, const void* const* bufs, int rank, int wo
     int threads = (n / 8 + 31) / 32 * 32;
     if (threads > 1024) threads = 1024;
     if (threads < 32) threads = 32;
-    nvfp4::allreduce_residual_kernel<<<1, threads, 0, (cudaStream_t)stream>>>(
-        peers, rank, world, n, parity & 1, (__half*)h);
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    return nvfp4::launch_pdl(nvfp4::allreduce_residual_kernel, dim3(1), dim3(threads), 0,
+                             (cudaStream_t)stream, peers, rank, world, n, parity & 1, (__half*)h) ==
+                   cudaSuccess ? 0 : -1;
 }
 
 }  // extern "C"

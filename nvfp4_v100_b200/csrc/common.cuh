@@ -77,4 +77,30 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Programmatic dependent launch.  A kernel that starts with pdl_prologue() may be launched with
+// the programmatic-stream-serialization attribute: it becomes resident while the previous kernel
+// in the stream is still draining, lets ITS successor do the same, and then waits for the
+// previous kernel to complete before touching memory.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+}
+
+// Launch with the attribute (kernels that call pdl_prologue() first thing).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t st, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace nvfp4

@@ -17,6 +17,7 @@ namespace nvfp4 {
 __global__ void __launch_bounds__(256)
 embed_gather_kernel(const __half* __restrict__ table, const long long* __restrict__ tok,
                     __half* __restrict__ out, int hidden, long long vocab) {
+    pdl_prologue();
     long long id = *tok;
     if (id < 0) id = 0;
     if (id >= vocab) id = vocab - 1;
@@ -43,6 +44,7 @@ attn_prep_kernel(const __half* __restrict__ qkv, const float* __restrict__ q_w1,
                  __half* __restrict__ q_out, __half* __restrict__ gate_out,
                  __half* __restrict__ keys, __half* __restrict__ values, int hq, int hkv,
                  int max_len, float eps) {
+    pdl_prologue();
     __shared__ float s_red[8];
     __shared__ float s_n[256];
     const int b = blockIdx.x, d = threadIdx.x, lane = d & 31, warp = d >> 5;
@@ -89,6 +91,7 @@ argmax_advance_kernel(const __half* __restrict__ logits, int vocab, long long* _
                       long long* __restrict__ pos, long long* __restrict__ len,
                       long long* __restrict__ history, long long* __restrict__ hist_count,
                       int hist_cap) {
+    pdl_prologue();
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -160,6 +163,7 @@ argmax_advance_kernel(const __half* __restrict__ logits, int vocab, long long* _
 // layer's partial outputs in tensor-parallel decode.
 __global__ void __launch_bounds__(256)
 residual_add_kernel(__half* __restrict__ h, const __half* __restrict__ y, int n) {
+    pdl_prologue();
     const int i = (blockIdx.x * 256 + threadIdx.x) * 2;
     if (i + 1 < n) {
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(h + i));
@@ -199,6 +203,7 @@ __global__ void pick_global_argmax_kernel(const float* __restrict__ cand, int wo
 __global__ void __launch_bounds__(1024)
 argmax_slice_kernel(const __half* __restrict__ logits, int vocab, long long offset,
                     float* __restrict__ cand) {
+    pdl_prologue();
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -240,9 +245,9 @@ extern "C" {
 // h, y fp16 [n]: h += y (fp32 add, one rounding).  0 / -1.
 int launch_residual_add(void* h, const void* y, int n, void* stream) {
     if (!h || !y || n <= 0) return -1;
-    nvfp4::residual_add_kernel<<<(n + 511) / 512, 256, 0, (cudaStream_t)stream>>>(
-        (__half*)h, (const __half*)y, n);
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    return nvfp4::launch_pdl(nvfp4::residual_add_kernel, dim3((n + 511) / 512), dim3(256), 0,
+                             (cudaStream_t)stream, (__half*)h, (const __half*)y, n) == cudaSuccess
+               ? 0 : -1;
 }
 
 // Tensor-parallel argmax, step 1: cand (fp32 [2]) = (max of logits[0..vocab), offset + argmax).
@@ -270,9 +275,9 @@ int launch_embed_gather(const void* table, const void* tok, void* out, int hidde
                         void* stream) {
     if (!table || !tok || !out || hidden <= 0 || vocab <= 0) return -1;
     const int per = 256 * 8;
-    nvfp4::embed_gather_kernel<<<(hidden + per - 1) / per, 256, 0, (cudaStream_t)stream>>>(
-        (const __half*)table, (const long long*)tok, (__half*)out, hidden, vocab);
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    return nvfp4::launch_pdl(nvfp4::embed_gather_kernel, dim3((hidden + per - 1) / per), dim3(256), 0,
+                             (cudaStream_t)stream, (const __half*)table, (const long long*)tok,
+                             (__half*)out, hidden, vocab) == cudaSuccess ? 0 : -1;
 }
 
 // qkv fp16 [hq*512 + 2*hkv*256]; q_w1, k_w1 fp32 [256] (1 + weight); cos/sin tables fp16
@@ -284,11 +289,11 @@ int launch_attn_prep(const void* qkv, const void* q_w1, const void* k_w1, const 
     if (!qkv || !q_w1 || !k_w1 || !cos_tab || !sin_tab || !pos || !q_out || !gate_out || !keys ||
         !values || hq <= 0 || hkv <= 0 || max_len <= 0)
         return -1;
-    nvfp4::attn_prep_kernel<<<hq + 2 * hkv, 256, 0, (cudaStream_t)stream>>>(
-        (const __half*)qkv, (const float*)q_w1, (const float*)k_w1, (const __half*)cos_tab,
-        (const __half*)sin_tab, (const long long*)pos, (__half*)q_out, (__half*)gate_out,
-        (__half*)keys, (__half*)values, hq, hkv, max_len, eps);
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    return nvfp4::launch_pdl(nvfp4::attn_prep_kernel, dim3(hq + 2 * hkv), dim3(256), 0,
+                             (cudaStream_t)stream, (const __half*)qkv, (const float*)q_w1,
+                             (const float*)k_w1, (const __half*)cos_tab, (const __half*)sin_tab,
+                             (const long long*)pos, (__half*)q_out, (__half*)gate_out, (__half*)keys,
+                             (__half*)values, hq, hkv, max_len, eps) == cudaSuccess ? 0 : -1;
 }
 
 // logits fp16 [vocab]; tok/pos/len/hist_count: device int64 scalars (pos, len, history and
@@ -296,10 +301,10 @@ int launch_attn_prep(const void* qkv, const void* q_w1, const void* k_w1, const 
 int launch_argmax_advance(const void* logits, int vocab, void* tok, void* pos, void* len,
                           void* history, void* hist_count, int hist_cap, void* stream) {
     if (!logits || !tok || vocab <= 0) return -1;
-    nvfp4::argmax_advance_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(
-        (const __half*)logits, vocab, (long long*)tok, (long long*)pos, (long long*)len,
-        (long long*)history, (long long*)hist_count, hist_cap);
-    return cudaGetLastError() == cudaSuccess ? 0 : -1;
+    return nvfp4::launch_pdl(nvfp4::argmax_advance_kernel, dim3(1), dim3(1024), 0,
+                             (cudaStream_t)stream, (const __half*)logits, vocab, (long long*)tok,
+                             (long long*)pos, (long long*)len, (long long*)history,
+                             (long long*)hist_count, hist_cap) == cudaSuccess ? 0 : -1;
 }
 
 }  // extern "C"

@@ -23,6 +23,7 @@ template <int THREADS>
 __global__ void __launch_bounds__(THREADS)
 rmsnorm_kernel(const __half* __restrict__ x, long long row_stride, const float* __restrict__ w1,
                __half* __restrict__ out, int n, float eps) {
+    pdl_prologue();
     __shared__ float s_red[THREADS / 32];
     __shared__ float s_inv;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -90,6 +91,7 @@ __global__ void __launch_bounds__(128)
 rope_qk_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
                const __half* __restrict__ cs, const __half* __restrict__ sn,
                __half* __restrict__ q_out, __half* __restrict__ k_out, int hq) {
+    pdl_prologue();
     const int h = blockIdx.x, d = threadIdx.x;  // d in [0,128): handles d and d+128
     const bool is_q = h < hq;
     const size_t off = (size_t)(is_q ? h : h - hq) * 256;
@@ -112,6 +114,7 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x));
 __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __half* __restrict__ g, const __half* __restrict__ u,
                 __half* __restrict__ out, int n) {
+    pdl_prologue();
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     const float gf = __half2float(g[i]), uf = __half2float(u[i]);
@@ -149,6 +152,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys
                    const __half* __restrict__ values, const long long* __restrict__ cum_len,
                    const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
                    int gqa, float scale) {
+    pdl_prologue();
     extern __shared__ float s_sc[];  // [max_len]
     __shared__ float s_red[ATT_WARPS];
     __shared__ float s_bcast;
@@ -267,6 +271,7 @@ __device__ __forceinline__ float softplus_f(float x) { return (x > 20.0f) ? x : 
 __global__ void __launch_bounds__(256)
 dn_conv_kernel(const __half* __restrict__ mixed, const __half* __restrict__ conv_w,
                __half* __restrict__ conv_state, float* __restrict__ scratch, int conv_dim) {
+    pdl_prologue();
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= conv_dim) return;
     // state and weights of a channel are 4 consecutive halves: one 8-byte load each
@@ -298,6 +303,7 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
               const __half* __restrict__ dt_bias, const __half* __restrict__ norm_w,
               const float* __restrict__ scratch, float* __restrict__ state,
               __half* __restrict__ out, float rms_eps, int key_dim, int rep) {
+    pdl_prologue();
     __shared__ float s_o[DN_DK];
     __shared__ float s_red[8];
     const int h = blockIdx.x, kh = h / rep;  // value head h reads key head h / rep
@@ -374,13 +380,13 @@ int launch_rmsnorm(const void* x, long long row_stride, const void* w1, void* ou
     if (rows <= 0 || n <= 0) return -1;
     if (!x || !w1 || !out) return -1;
     cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
     if (n >= 2048)
-        nvfp4::rmsnorm_kernel<512><<<rows, 512, 0, st>>>((const __half*)x, row_stride,
-                                                         (const float*)w1, (__half*)out, n, eps);
+        e = nvfp4::launch_pdl(nvfp4::rmsnorm_kernel<512>, dim3(rows), dim3(512), 0, st,
+                              (const __half*)x, row_stride, (const float*)w1, (__half*)out, n, eps);
     else
-        nvfp4::rmsnorm_kernel<64><<<rows, 64, 0, st>>>((const __half*)x, row_stride,
-                                                       (const float*)w1, (__half*)out, n, eps);
-    const cudaError_t e = cudaGetLastError();
+        e = nvfp4::launch_pdl(nvfp4::rmsnorm_kernel<64>, dim3(rows), dim3(64), 0, st,
+                              (const __half*)x, row_stride, (const float*)w1, (__half*)out, n, eps);
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 
@@ -388,17 +394,18 @@ int launch_rope_qk(const void* q, const void* k, const void* cs, const void* sn,
                    void* k_out, int hq, int hkv, void* stream) {
     if (hq < 0 || hkv < 0 || hq + hkv <= 0) return -1;
     if (!cs || !sn || (hq > 0 && (!q || !q_out)) || (hkv > 0 && (!k || !k_out))) return -1;
-    nvfp4::rope_qk_kernel<<<hq + hkv, 128, 0, (cudaStream_t)stream>>>(
-        (const __half*)q, (const __half*)k, (const __half*)cs, (const __half*)sn, (__half*)q_out,
-        (__half*)k_out, hq);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    const cudaError_t e = nvfp4::launch_pdl(
+        nvfp4::rope_qk_kernel, dim3(hq + hkv), dim3(128), 0, (cudaStream_t)stream, (const __half*)q,
+        (const __half*)k, (const __half*)cs, (const __half*)sn, (__half*)q_out, (__half*)k_out, hq);
+    return e == cudaSuccess ? 0 : -2;
 }
 
 int launch_silu_mul(const void* g, const void* u, void* out, int n, void* stream) {
     if (n <= 0 || !g || !u || !out) return -1;
-    nvfp4::silu_mul_kernel<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(
-        (const __half*)g, (const __half*)u, (__half*)out, n);
-    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+    const cudaError_t e =
+        nvfp4::launch_pdl(nvfp4::silu_mul_kernel, dim3((n + 255) / 256), dim3(256), 0,
+                          (cudaStream_t)stream, (const __half*)g, (const __half*)u, (__half*)out, n);
+    return e == cudaSuccess ? 0 : -2;
 }
 
 // Heads are the 27B model's: 24 query heads, 4 KV heads, head dim 256.  max_len is the cache's
@@ -421,10 +428,10 @@ static int attn_decode_launch(const void* q, const void* keys, const void* value
             return -2;
         smem_opt_in = true;
     }
-    nvfp4::attn_decode_kernel<<<hq, ATT_THREADS, smem, (cudaStream_t)stream>>>(
+    const cudaError_t e = nvfp4::launch_pdl(
+        nvfp4::attn_decode_kernel, dim3(hq), dim3(ATT_THREADS), smem, (cudaStream_t)stream,
         (const __half*)q, (const __half*)keys, (const __half*)values, (const long long*)cum_len,
         (const __half*)gate, (__half*)out, max_len, hq / hkv, scale);
-    const cudaError_t e = cudaGetLastError();
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 
@@ -452,19 +459,18 @@ static int dn_fused_launch(const void* mixed, const void* z_in, const void* b_in
     const int key_dim = n_kheads * DN_DK;
     const int conv_dim = 2 * key_dim + n_vheads * DN_DK;
     cudaStream_t s = (cudaStream_t)stream;
-    nvfp4::dn_conv_kernel<<<(conv_dim + 255) / 256, 256, 0, s>>>(
-        (const __half*)mixed, (const __half*)conv_w, (__half*)conv_state, (float*)scratch,
-        conv_dim);
-    cudaError_t e = cudaGetLastError();
+    cudaError_t e = nvfp4::launch_pdl(nvfp4::dn_conv_kernel, dim3((conv_dim + 255) / 256), dim3(256),
+                                      0, s, (const __half*)mixed, (const __half*)conv_w,
+                                      (__half*)conv_state, (float*)scratch, conv_dim);
     if (e != cudaSuccess) {
         fprintf(stderr, "dn_conv launch: %s\n", cudaGetErrorString(e));
         return -1;
     }
-    nvfp4::dn_rec_kernel<<<n_vheads, DN_REC_THREADS, 0, s>>>(
-        (const __half*)z_in, (const __half*)b_in, (const __half*)a_in, (const __half*)A_log,
-        (const __half*)dt_bias, (const __half*)norm_w, (const float*)scratch, (float*)state,
-        (__half*)out, rms_eps, key_dim, n_vheads / n_kheads);
-    e = cudaGetLastError();
+    e = nvfp4::launch_pdl(nvfp4::dn_rec_kernel, dim3(n_vheads), dim3(DN_REC_THREADS), 0, s,
+                          (const __half*)z_in, (const __half*)b_in, (const __half*)a_in,
+                          (const __half*)A_log, (const __half*)dt_bias, (const __half*)norm_w,
+                          (const float*)scratch, (float*)state, (__half*)out, rms_eps, key_dim,
+                          n_vheads / n_kheads);
     if (e != cudaSuccess) {
         fprintf(stderr, "dn_rec launch: %s\n", cudaGetErrorString(e));
         return -1;

@@ -112,7 +112,7 @@ class DecodeEngine:
     """Holds the prepared weights and all state of one sequence and replays the step graph."""
 
     def __init__(self, cfg: ModelConfig, device: str = "cuda", tp_rank: int = 0, tp_world: int = 1,
-                 allreduce: str = "fused"):
+                 allreduce: str = "peer"):
         """tp_world > 1: this process holds shard tp_rank of a tensor-parallel group (one process
         per GPU, torch.distributed initialised with the NCCL backend by the caller).
         allreduce: "fused" = the K-split GEMV, its all-reduce and the residual add are ONE kernel
