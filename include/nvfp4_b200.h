@@ -60,6 +60,11 @@ int launch_nvfp4_gemvnl(const void* weight_packed, const void* weight_scales,
 int launch_nvfp4_gemv2(const void* weight_packed, const void* weight_scales, const void* act0,
                        const void* act1, void* output, int M, int K, void* stream);
 
+/* The same with the two activations interleaved as K fp16 pairs (act_i[2k] = act0[k],
+ * act_i[2k + 1] = act1[k]); output[2, M].  kernels/nvfp4_gemv.cu:997-1011. */
+int launch_nvfp4_gemv2i(const void* weight_packed, const void* weight_scales, const void* act_i,
+                        void* output, int M, int K, void* stream);
+
 /* Dense GEMM for more than two tokens: output[M, N] (fp16) = dequant(W)[M, K] . activation[K, N]
  * (fp16, N = tokens, token-minor as the reference's caller prepares it).  Weight x block scale in
  * fp16, fp16 x fp16 products, fp32 accumulation, as the reference's wmma kernel.  Runs on tcgen05

@@ -111,7 +111,7 @@ struct WeightRegs {
 
 // Optional work fused around the dot products (used by the decode engine; the reference-named
 // entry points run with PRO_NONE / EPI_STORE).
-enum { PRO_NONE = 0, PRO_RMSNORM = 1 };
+enum { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_INTERLEAVED = 2 };
 #define PRO_NV 5  // 16-byte activation vectors a thread holds in the RMSNorm prologue
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_ALLREDUCE = 3 };
 struct GemvExtra {
@@ -151,6 +151,8 @@ __device__ __forceinline__ void lds_x_pred(uint32_t saddr, uint32_t pred, uint32
 //   PRO_RMSNORM : the activation is RMS-normalised first, x' = f16(f32(x) * rsqrt(mean(x^2)+eps)
 //                 * w1) — the arithmetic of rmsnorm_kernel — once per CTA into shared memory
 //                 (dynamic, 2K bytes), and the dot products read x' from there.
+//   PRO_INTERLEAVED: (two activations) act0 holds K pairs (a0[k], a1[k]); the CTA splits them
+//                 into two planes of shared memory (dynamic, 4K bytes) and reads x from there.
 //   EPI_RESIDUAL: out[m] = f16(f32(residual[m]) + f32(f16(y[m]))).
 //   EPI_SILU_MUL: W holds gate and up rows interleaved in groups of 8 (tile rows 0..7 = gate rows
 //                 8j..8j+7, rows 8..15 = up rows 8j..8j+7; M = 2 * outputs);
@@ -314,7 +316,22 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         }
         __syncthreads();
     }
-    const uint32_t xs_base = (uint32_t)__cvta_generic_to_shared(xs);
+    if (PRO == PRO_INTERLEAVED) {
+        const uint32_t* ai = reinterpret_cast<const uint32_t*>(act0);  // one u32 = (a0[k], a1[k])
+        for (int i = threadIdx.x * 4; i < K; i += WARPS * 32 * 4) {
+            const uint4 v = *reinterpret_cast<const uint4*>(ai + i);
+            uint2 p0, p1;
+            p0.x = __byte_perm(v.x, v.y, 0x5410);
+            p0.y = __byte_perm(v.z, v.w, 0x5410);
+            p1.x = __byte_perm(v.x, v.y, 0x7632);
+            p1.y = __byte_perm(v.z, v.w, 0x7632);
+            *reinterpret_cast<uint2*>(xs + i) = p0;
+            *reinterpret_cast<uint2*>(xs + K + i) = p1;
+        }
+        __syncthreads();
+    }
+    const uint32_t xs_base = (uint32_t)__cvta_generic_to_shared(xs) +
+                             ((PRO == PRO_INTERLEAVED && g >= 4) ? (uint32_t)K * 2u : 0u);
 
     uint32_t xr[2][8];  // two passes of activation registers (zero where this lane supplies none)
 #pragma unroll
@@ -342,7 +359,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         const int kx = max(0, min(kc, K - 64));
         const __half* xptr = xsrc + kx;
         auto load_x = [&](int q, uint32_t (&x)[8]) {
-            if (PRO == PRO_RMSNORM) {
+            if (PRO != PRO_NONE) {
                 const uint32_t a = xs_base + (uint32_t)(kx + 16 * q) * 2u;
                 lds_x_pred(a, xp, x[0], x[1], x[2], x[3]);
                 lds_x_pred(a + 16u, xp, x[4], x[5], x[6], x[7]);
@@ -523,7 +540,8 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
 // Generic path for shapes or pointers the tensor-core kernel does not take (K % 128 != 0, or
 // weaker alignment): one warp per row, 16-byte loads, fp32 FMA.  K % 32 == 0, packed and
 // activations 16-byte aligned, scales 2-byte aligned.
-template <int NACT>
+// ILV (two activations): act0 holds K pairs (a0[k], a1[k]) instead of two separate vectors.
+template <int NACT, bool ILV = false>
 __global__ void __launch_bounds__(256)
 gemv_generic_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                     const __half* __restrict__ act0, const __half* __restrict__ act1,
@@ -549,8 +567,19 @@ gemv_generic_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restric
             for (int j = 0; j < 4; j++) {
                 uint32_t h[4];
                 e2m1x8_to_half2x4(w[j], h[0], h[1], h[2], h[3]);
-                const uint4 xv = __ldg(xp + j);
-                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+                uint32_t xw[4];
+                if (ILV) {
+                    const uint4* ip = reinterpret_cast<const uint4*>(act0 + (size_t)c * 64) + 2 * j;
+                    const uint4 lo = __ldg(ip), hi = __ldg(ip + 1);
+                    const uint32_t sel = a ? 0x7632u : 0x5410u;
+                    xw[0] = __byte_perm(lo.x, lo.y, sel);
+                    xw[1] = __byte_perm(lo.z, lo.w, sel);
+                    xw[2] = __byte_perm(hi.x, hi.y, sel);
+                    xw[3] = __byte_perm(hi.z, hi.w, sel);
+                } else {
+                    const uint4 xv = __ldg(xp + j);
+                    xw[0] = xv.x; xw[1] = xv.y; xw[2] = xv.z; xw[3] = xv.w;
+                }
 #pragma unroll
                 for (int p = 0; p < 4; p++) {
                     const float2 wf = __half22float2(*reinterpret_cast<const __half2*>(&h[p]));
@@ -635,7 +664,7 @@ template <int WARPS, int NACT, int PRO, int EPI>
 static cudaError_t launch_mma(const void* packed, const void* scales, const void* a0, const void* a1,
                               void* out, int M, int K, cudaStream_t st, const GemvExtra& ex,
                               const GemvPlan& plan) {
-    const int smem = (PRO == PRO_RMSNORM) ? K * 2 : 0;
+    const int smem = (PRO == PRO_RMSNORM) ? K * 2 : (PRO == PRO_INTERLEAVED) ? K * 4 : 0;
     static int max_smem_set = 0;
     if (smem > 48 * 1024 && smem > max_smem_set) {
         if (cudaFuncSetAttribute(gemv_mma_kernel<WARPS, NACT, PRO, EPI>,
@@ -719,6 +748,36 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
     }
     if (e != cudaSuccess) {
         fprintf(stderr, "%s launch: %s\n", who, cudaGetErrorString(e));
+        return NVFP4_ERR_LAUNCH;
+    }
+    return NVFP4_OK;
+}
+
+// Two activations stored as K (a0[k], a1[k]) pairs; out[m] = W a0, out[M + m] = W a1.
+int gemv2i_dispatch(const void* packed, const void* scales, const void* act_i, void* out, int M,
+                    int K, void* stream) {
+    if (K <= 0 || K % (NVFP4_BLOCK * 2) != 0) return NVFP4_ERR_SHAPE;
+    if (M <= 0 || !packed || !scales || !act_i || !out) return NVFP4_ERR_SHAPE;
+    if (!aligned(packed, 16) || !aligned(act_i, 16) || !aligned(scales, 2) || !aligned(out, 2))
+        return NVFP4_ERR_SHAPE;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    const bool fast = !g_cfg.force_generic && (K % 128 == 0) && aligned(packed, 32) &&
+                      aligned(scales, 8) && K * 4 <= 200 * 1024;
+    if (fast) {
+        GemvPlan plan = plan_gemv(M, K);
+        GemvExtra none = {};
+        e = (plan.warps == 8)
+                ? launch_mma<8, 2, PRO_INTERLEAVED, 0>(packed, scales, act_i, act_i, out, M, K, st, none, plan)
+                : launch_mma<4, 2, PRO_INTERLEAVED, 0>(packed, scales, act_i, act_i, out, M, K, st, none, plan);
+    } else {
+        gemv_generic_kernel<2, true><<<(unsigned)((M + 7) / 8), 256, 0, st>>>(
+            (const uint8_t*)packed, (const uint8_t*)scales, (const __half*)act_i,
+            (const __half*)act_i, (__half*)out, M, K);
+        e = cudaGetLastError();
+    }
+    if (e != cudaSuccess) {
+        fprintf(stderr, "launch_nvfp4_gemv2i launch: %s\n", cudaGetErrorString(e));
         return NVFP4_ERR_LAUNCH;
     }
     return NVFP4_OK;
@@ -871,6 +930,13 @@ int launch_nvfp4_gemv2(const void* weight_packed, const void* weight_scales, con
                        const void* act1, void* output, int M, int K, void* stream) {
     return nvfp4::gemv_dispatch(weight_packed, weight_scales, act0, act1, output, M, K, stream, 2,
                                 "launch_nvfp4_gemv2");
+}
+
+// reference: kernels/nvfp4_gemv.cu:997-1011 (launch_nvfp4_gemv2i): two activations interleaved
+// as K (a0[k], a1[k]) fp16 pairs; output [2, M].
+int launch_nvfp4_gemv2i(const void* weight_packed, const void* weight_scales, const void* act_i,
+                        void* output, int M, int K, void* stream) {
+    return nvfp4::gemv2i_dispatch(weight_packed, weight_scales, act_i, output, M, K, stream);
 }
 
 // Tuning hook (no counterpart in the reference): warps per CTA (0 = auto, 2/4/8), resident CTAs

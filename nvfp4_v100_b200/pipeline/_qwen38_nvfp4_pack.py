@@ -1,15 +1,23 @@
 """Container writer: fp16 state dict -> ``nvfp4_packed.bin`` + ``nvfp4_index.json`` +
-``fp16_embed.npy`` + ``fp32_misc.npz``, the on-disk format the decode engine bridge loads.
+``fp16_embed.npy`` + ``fp32_misc.npz``, the on-disk format the decode engine bridge loads
+(reference: pipeline/_qwen38_nvfp4_pack.py:95-133 for the layout, :34-67 for the quantiser).
 
-Mirrors the reference's offline packer (pipeline/_qwen38_nvfp4_pack.py:34-67 quantiser,
-:95-133 container layout): every 2-D tensor except the embedding is quantised row-wise (block max
-in float64 -> scale exponent ceil(log2(max/6)) clipped to +-127, normalise in float64 -> float32,
-nearest E2M1 code with ties to the smaller code, -0 stored as +0, two nibbles per byte) and
-written as its packed bytes immediately followed by its scale bytes; the index records
-``{M, K, packed_off, packed_bytes, scales_off, scales_bytes, fmt}`` per tensor name; non-2-D
-tensors go to ``fp32_misc.npz``.  The reference reads sharded safetensors of a real checkpoint;
-here the source is any mapping name -> array (synthetic weights), so a container can be produced
-without the checkpoint.  This is an offline CPU tool, not part of the GPU hot path.
+Every 2-D tensor except the embedding is quantised row-wise and written as its packed bytes
+immediately followed by its scale bytes; the index records ``{M, K, packed_off, packed_bytes,
+scales_off, scales_bytes, fmt}`` per tensor name; non-2-D tensors go to ``fp32_misc.npz``.  The
+reference reads sharded safetensors of a real checkpoint; here the source is any mapping
+name -> array (synthetic weights), so a container can be produced without the checkpoint.
+
+The quantiser below produces the reference's bytes by exact arithmetic instead of logarithms
+and table searches (``tests/test_oracle_codec.py`` compares it with the golden vectors): it is the
+host statement of what ``launch_nvfp4_encode`` does on the device.
+  scale : the block maximum is m * 2^x with 0.5 <= m < 1 (``frexp``, exact); the smallest e with
+          6 * 2^e >= max is x - 3 when m <= 0.75 and x - 2 otherwise; byte = e + 127; an all-zero
+          block gets e = 0; e is clipped to [-127, 127].
+  code  : |value| * 2^-e (exact) is compared with the seven midpoints between code points; the
+          code is the number of midpoints strictly below it, so a value on a midpoint takes the
+          smaller code.  The sign bit is set for values below zero only (-0 stores as +0).
+This is an offline tool, not part of the GPU hot path.
 """
 from __future__ import annotations
 
@@ -23,32 +31,40 @@ BLOCK = 16
 BIAS = 127
 ROW_CHUNK = 4096
 FMT = "nvfp4_v2_embedded_sign"
-_EDGES = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=np.float32)
+_MIDPOINTS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
 
 
 def encode_block_scales(max_abs_f64: np.ndarray):
-    with np.errstate(divide="ignore", invalid="ignore"):
-        scale_exp = np.ceil(np.log2(max_abs_f64 / E2M1_MAX_ABS))
-    scale_exp = np.where(max_abs_f64 == 0.0, 0.0, scale_exp)
-    scale_exp = np.clip(scale_exp, -127, 127)
-    return (scale_exp + BIAS).astype(np.uint8), scale_exp
+    """Block maxima -> (scale bytes uint8, scale exponents float64)."""
+    peak = np.asarray(max_abs_f64, dtype=np.float64)
+    mant, expo = np.frexp(peak)
+    e = expo - np.where(mant <= 0.75, 3, 2)
+    e = np.where(peak > 0.0, e, 0)
+    e = np.where(np.isinf(peak), 127, e)
+    e = np.clip(e, -127, 127)
+    return (e + BIAS).astype(np.uint8), e.astype(np.float64)
 
 
 def e2m1_codes_rtn(abs_x: np.ndarray) -> np.ndarray:
-    return np.searchsorted(_EDGES, np.clip(abs_x, 0.0, 6.0), side="left").astype(np.uint8)
+    """|normalised value| -> 3-bit code, nearest code point, a tie goes to the smaller code."""
+    a = np.asarray(abs_x)
+    code = np.zeros(a.shape, dtype=np.uint8)
+    for mid in _MIDPOINTS:
+        code += a > mid
+    return code
 
 
 def encode_rows(w_f32: np.ndarray):
     """(rows, K) float32 -> packed (rows, K/2) uint8, scale bytes (rows, K/16) uint8."""
-    M, K = w_f32.shape
-    assert K % BLOCK == 0
-    blocks = w_f32.reshape(M, K // BLOCK, BLOCK)
-    max_abs = np.abs(blocks).max(axis=-1).astype(np.float64)
-    sbytes, sexp = encode_block_scales(max_abs)
-    norm = (blocks / np.exp2(sexp)[..., None]).astype(np.float32).reshape(M, K)
-    signs = (norm < 0).astype(np.uint8)
-    nib = (signs << 3) | e2m1_codes_rtn(np.abs(norm))
-    return (nib[:, 0::2] & 0x0F) | ((nib[:, 1::2] & 0x0F) << 4), sbytes
+    rows, K = w_f32.shape
+    if K % BLOCK:
+        raise ValueError(f"K = {K} is not a multiple of {BLOCK}")
+    blk = np.asarray(w_f32, dtype=np.float64).reshape(rows, K // BLOCK, BLOCK)
+    sbytes, e = encode_block_scales(np.abs(blk).max(axis=2))
+    unit = np.ldexp(blk, -e.astype(np.int64)[..., None]).astype(np.float32).reshape(rows, K)
+    nibble = e2m1_codes_rtn(np.abs(unit)) | ((unit < 0).astype(np.uint8) << 3)
+    pairs = nibble.reshape(rows, K // 2, 2)
+    return pairs[..., 0] | (pairs[..., 1] << 4), sbytes
 
 
 def pack_tensors(tensors: dict, out_dir: str, prequantised: dict | None = None) -> dict:

@@ -41,6 +41,20 @@ def gemv2(lib, packed, scales, act0, act1):
     return rc, o[:2 * M].reshape(2, M)
 
 
+def gemv2i(lib, packed, scales, act0, act1):
+    """launch_nvfp4_gemv2i: the two activations travel as K (a0[k], a1[k]) pairs."""
+    M, K = packed.shape[0], packed.shape[1] * 2
+    d_p, d_s = dev(packed), dev(scales)
+    inter = np.stack([act0.astype(np.float16), act1.astype(np.float16)], axis=1).reshape(-1)
+    d_a = dev(np.ascontiguousarray(inter))
+    out = torch.full((2 * M + 8,), float("nan"), dtype=torch.float16, device="cuda")
+    rc = lib.launch_nvfp4_gemv2i(ptr(d_p), ptr(d_s), ptr(d_a), ptr(out), M, K, stream())
+    torch.cuda.synchronize()
+    o = out.cpu().numpy()
+    assert np.isnan(o[2 * M:]).all()
+    return rc, o[:2 * M].reshape(2, M)
+
+
 def ulp_diff_f16(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     """Distance in fp16 representable steps between two fp16 arrays (sign-magnitude aware)."""
     def key(x):

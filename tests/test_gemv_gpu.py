@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 
 from oracle import nvfp4_codec_oracle as oc
-from tests.gpu_util import gemv, gemv2
+from tests.gpu_util import gemv, gemv2, gemv2i
 
 pytestmark = pytest.mark.gpu
 
@@ -173,6 +173,22 @@ def test_gemv2_two_activations(lib):
         assert rc == 0
         check(y[0], p, s, a0)
         check(y[1], p, s, a1)
+
+
+def test_gemv2i_interleaved_activations(lib):
+    # reference: kernels/nvfp4_gemv.cu:997-1011; shapes cover the tensor-core kernel with 4 and 8
+    # warps, the generic kernel (K % 128 != 0) and a ragged last row tile
+    for M, K in ((48, 256), (100, 5120), (31, 96), (5120, 6144), (1030, 17408)):
+        w = oc.synthetic_weight(M, K, seed=M + 3)
+        p, s = oc.encode(w)
+        a0, a1 = oc.synthetic_act(K, seed=5), oc.synthetic_act(K, seed=6)
+        rc, y = gemv2i(lib, p, s, a0, a1)
+        assert rc == 0
+        check(y[0], p, s, a0)
+        check(y[1], p, s, a1)
+        rc2, y2 = gemv2(lib, p, s, a0, a1)
+        assert rc2 == 0 and np.array_equal(y.view(np.uint16), y2.view(np.uint16))
+    assert lib.launch_nvfp4_gemv2i(None, None, None, None, 16, 48, None) == -2
 
 
 def test_config1_full_size(lib):

@@ -94,3 +94,32 @@ def test_empty_and_shapes():
     assert p.shape == (0, 16) and s.shape == (0, 2)
     p, s = oc.encode(np.zeros((3, 16), dtype=np.float16))
     assert np.all(s == 127) and np.all(p == 0)
+
+
+def test_container_quantiser_matches_golden(golden):
+    """The container writer's exact-arithmetic quantiser (frexp scale rule, midpoint counting)
+    against the reference codec's bytes, and its packed-embedding reader against the reference's
+    decoded rows."""
+    import os
+    import tempfile
+
+    from nvfp4_v100_b200.pipeline import _qwen38_nvfp4_pack as pk
+
+    for key in ["edge"] + [f"m{i}" for i in range(int(golden["n_mats"]))]:
+        p, s = pk.encode_rows(golden[key + "_in"].astype(np.float32))
+        assert np.array_equal(p, golden[key + "_packed"]), key
+        assert np.array_equal(s, golden[key + "_scales"]), key
+    vals = np.arange(0, 0x7C00, dtype=np.uint16).view(np.float16).astype(np.float64)
+    assert np.array_equal(pk.encode_block_scales(vals)[0], golden["scale_all"])
+    for j, e in enumerate(golden["code_exps"]):
+        a = (vals * 2.0 ** int(e)).astype(np.float32)
+        assert np.array_equal(pk.e2m1_codes_rtn(a), golden["code_all"][j]), int(e)
+
+    from nvfp4_v100_b200.pipeline._qwen38_infer import PackedEmb
+
+    with tempfile.TemporaryDirectory() as d:
+        np.save(os.path.join(d, "p.npy"), golden["emb_packed"])
+        np.save(os.path.join(d, "s.npy"), golden["emb_scales"])
+        emb = PackedEmb(os.path.join(d, "p.npy"), os.path.join(d, "s.npy"))
+        rows = emb[golden["emb_idx"]].numpy()
+        assert np.array_equal(rows.view(np.uint16), golden["emb_rows"].view(np.uint16))
