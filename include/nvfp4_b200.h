@@ -217,6 +217,16 @@ int nvfp4_comm_status(const void* my_buf);
 int launch_allreduce_residual(void* h, const void* const* bufs, int rank, int world, int n,
                               int parity, void* stream);
 
+/* Quantiser on the device: src fp16 [M, K] row-major -> packed [M, K/2] + scales [M, K/16], byte
+ * for byte what the reference's CPU codec produces (scale exponent ceil(log2(max/6)), zero block
+ * -> byte 127, nearest code with ties to the smaller code, -0 -> +0): codec/nvfp4_codec.py:166-245,
+ * codec/nvfp4_codec_fast.py:19-53, pipeline/_qwen38_nvfp4_pack.py:34-67.  The reference has no GPU
+ * entry for this; it makes container production and activation quantisation a stream-speed step.
+ * K % 16 == 0, src 16-byte aligned, packed 8-byte aligned.  Asynchronous, capturable.
+ * 0; -2 bad shape or pointer; -1 launch error. */
+int launch_nvfp4_encode(const void* src_fp16, void* packed, void* scales, int M, int K,
+                        void* stream);
+
 /* The DeltaNet step without a caller-provided workspace.  It has no counterpart in the reference,
  * whose caller always allocates the scratch tensor itself.  It exists for callers that cannot
  * allocate device memory at the point of the call: code that runs after all device memory has

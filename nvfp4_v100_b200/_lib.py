@@ -63,6 +63,7 @@ SIGNATURES = {
     "launch_allreduce_residual": ([_vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _vp], _i),
     "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
     "launch_dn_fused_heads": ([_vp] * 12 + [_i, _i, _f, _vp], _i),
+    "launch_nvfp4_encode": ([_vp, _vp, _vp, _i, _i, _vp], _i),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),
 }
 

@@ -1,0 +1,108 @@
+"""launch_nvfp4_encode (device quantiser) against the codec oracle and the reference codec's golden
+bytes: bit-exact, including the exhaustive scale and rounding rules."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_codec_oracle as oc
+from tests.gpu_util import ptr, stream
+
+pytestmark = pytest.mark.gpu
+
+
+def encode_gpu(lib, w16: np.ndarray):
+    M, K = w16.shape
+    src = torch.from_numpy(np.ascontiguousarray(w16)).cuda()
+    packed = torch.full((M * K // 2 + 16,), 0xAB, dtype=torch.uint8, device="cuda")
+    scales = torch.full((M * K // 16 + 16,), 0xCD, dtype=torch.uint8, device="cuda")
+    rc = lib.launch_nvfp4_encode(ptr(src), ptr(packed), ptr(scales), M, K, stream())
+    torch.cuda.synchronize()
+    assert rc == 0
+    p, s = packed.cpu().numpy(), scales.cpu().numpy()
+    assert (p[M * K // 2:] == 0xAB).all() and (s[M * K // 16:] == 0xCD).all()   # canaries
+    return p[:M * K // 2].reshape(M, K // 2), s[:M * K // 16].reshape(M, K // 16)
+
+
+def test_golden_matrices(lib, golden):
+    for key in ["edge"] + [f"m{i}" for i in range(int(golden["n_mats"]))]:
+        p, s = encode_gpu(lib, golden[key + "_in"])
+        assert np.array_equal(p, golden[key + "_packed"]), key
+        assert np.array_equal(s, golden[key + "_scales"]), key
+
+
+def test_scale_rule_every_fp16_maximum(lib, golden):
+    # one block per finite fp16 magnitude: that value once, zeros elsewhere
+    vals = np.arange(0, 0x7C00, dtype=np.uint16).view(np.float16)
+    w = np.zeros((len(vals), 16), dtype=np.float16)
+    w[:, 5] = vals
+    _, s = encode_gpu(lib, w)
+    assert np.array_equal(s[:, 0], golden["scale_all"])
+
+
+def test_rounding_rule_every_fp16_value(lib):
+    # blocks whose maximum pins the scale at 2^e; the other 15 slots sweep all fp16 values that
+    # do not exceed the maximum (both signs), so every value / scale combination is visited
+    allv = np.arange(0, 0x10000, dtype=np.uint32).astype(np.uint16).view(np.float16)
+    finite = allv[np.isfinite(allv)]
+    for top in (6.0, 3.0, 0.046875, 1536.0, 6.1e-5, 65504.0):
+        cand = finite[np.abs(finite.astype(np.float32)) <= top]
+        n = -(-len(cand) // 15)
+        w = np.zeros((n, 16), dtype=np.float16)
+        w[:, 0] = top
+        body = np.zeros(n * 15, dtype=np.float16)
+        body[:len(cand)] = cand
+        w[:, 1:] = body.reshape(n, 15)
+        p, s = encode_gpu(lib, w)
+        rp, rs = oc.encode(w)
+        assert np.array_equal(s, rs), top
+        assert np.array_equal(p, rp), top
+
+
+def test_shapes_and_model_statistics(lib):
+    for M, K, sigma, seed in ((1, 16, 1.0, 0), (7, 48, 0.02, 1), (100, 5120, 0.02, 2),
+                              (5120, 5120, 0.02, 3), (3, 17408, 1.0, 4)):
+        w = oc.synthetic_weight(M, K, seed=seed, sigma=sigma)
+        p, s = encode_gpu(lib, w)
+        rp, rs = oc.encode(w)
+        assert np.array_equal(p, rp) and np.array_equal(s, rs), (M, K)
+    # re-quantising dequantised values (many exact ties and negative zeros; a block whose
+    # largest code fell below 6 moves to a smaller scale): still the codec's bytes, and after
+    # that one step the representation is stable
+    w = oc.synthetic_weight(64, 1024, seed=9)
+    p, s = encode_gpu(lib, w)
+    d = oc.decode(p, s)
+    p2, s2 = encode_gpu(lib, d)
+    rp2, rs2 = oc.encode(d)
+    assert np.array_equal(p2, rp2) and np.array_equal(s2, rs2)
+    assert np.array_equal(oc.decode(p2, s2).view(np.uint16) & 0x7FFF, d.view(np.uint16) & 0x7FFF)
+
+
+def test_non_finite_inputs_follow_the_cpu_arithmetic(lib):
+    w = oc.synthetic_weight(4, 64, seed=5, sigma=1.0)
+    w[0, 3] = np.inf
+    w[1, 20] = -np.inf
+    w[2, 40] = np.nan
+    p, s = encode_gpu(lib, w)
+    with np.errstate(all="ignore"):
+        rp, rs = oc.encode(w)
+    assert np.array_equal(s, rs) and np.array_equal(p, rp)
+    assert s[0, 0] == 254 and s[2, 2] == 127
+
+
+def test_argument_checks(lib):
+    assert lib.launch_nvfp4_encode(None, None, None, 4, 64, None) == -2
+    x = torch.zeros(64, dtype=torch.float16, device="cuda")
+    o = torch.zeros(64, dtype=torch.uint8, device="cuda")
+    assert lib.launch_nvfp4_encode(ptr(x), ptr(o), ptr(o), 1, 24, stream()) == -2
+    assert lib.launch_nvfp4_encode(ptr(x), ptr(o), ptr(o), 0, 16, stream()) == -2
+
+
+def test_encoded_weights_feed_the_gemv(lib):
+    from tests.gpu_util import gemv
+    w = oc.synthetic_weight(96, 1024, seed=11)
+    p, s = encode_gpu(lib, w)
+    a = oc.synthetic_act(1024, seed=12)
+    rc, y = gemv(lib, p, s, a)
+    assert rc == 0
+    ref = oc.gemv_f64(p, s, a)
+    assert oc.rel_error_floored(y, ref).max() <= 1e-3

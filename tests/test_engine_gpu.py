@@ -253,6 +253,31 @@ def test_allreduce_residual_single_rank(lib):
     assert lib.launch_allreduce_residual(ptr(d_h), bufs, 0, 1, n + 4, 0, stream()) == -1
 
 
+def test_allreduce_missing_peer_reports_status_and_returns(lib):
+    # Failure detection without a GPU fault: rank 0 of a 2-rank group whose peer never announces
+    # its vector (the "peer" is a second, idle buffer on this GPU).  The kernel's wait is bounded:
+    # it gives up, records which peer was missing in the error word, finishes, and the context
+    # stays usable for the next launch.
+    n = 1024
+    mine = torch.zeros(lib.nvfp4_comm_buffer_bytes(n), dtype=torch.uint8, device="cuda")
+    idle = torch.zeros_like(mine)
+    assert lib.nvfp4_comm_init(ptr(mine), n) == 0 and lib.nvfp4_comm_init(ptr(idle), n) == 0
+    bufs = (ctypes.c_void_p * 2)(mine.data_ptr(), idle.data_ptr())
+    h = dev(np.ones(n, dtype=np.float16))
+    assert lib.nvfp4_comm_status(ptr(mine)) == 0
+    assert lib.launch_allreduce_residual(ptr(h), bufs, 0, 2, n, 0, stream()) == 0
+    torch.cuda.synchronize()                              # returns: the wait ran out
+    assert lib.nvfp4_comm_status(ptr(mine)) == 2          # 1 + rank of the peer that never came
+    assert int(idle[64:68].view(torch.int32)) == 1        # our announcement reached the peer
+    # the context is intact: a single-rank call on a fresh buffer still works
+    solo = torch.zeros_like(mine)
+    assert lib.nvfp4_comm_init(ptr(solo), n) == 0
+    one = (ctypes.c_void_p * 1)(solo.data_ptr())
+    assert lib.launch_allreduce_residual(ptr(h), one, 0, 1, n, 0, stream()) == 0
+    torch.cuda.synchronize()
+    assert lib.nvfp4_comm_status(ptr(solo)) == 0
+
+
 def test_gemv_allreduce_single_rank_equals_residual_epilogue(lib):
     # world = 1: the fused GEMV + all-reduce + residual kernel must give exactly what the GEMV
     # with the residual epilogue gives; run twice to alternate the data slots

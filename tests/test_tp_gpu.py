@@ -1,5 +1,6 @@
-"""Tensor-parallel decode on 2 GPUs (one process per GPU, NCCL) against the single-GPU engine
-and the CPU oracle, small configuration.  Skipped on a box with fewer than two GPUs.
+"""Tensor-parallel decode on 2, 4 and 8 GPUs (one process per GPU, NCCL) against the single-GPU
+engine and the CPU oracle, small configuration with as many attention heads as ranks and a single
+KV head (replicated on every rank).  A case is skipped on a box with fewer GPUs than ranks.
 
 TP changes the summation order of every K-split layer (fp16 partial vectors are all-reduced), so
 logits agree to reassociation noise only; tokens are compared with the margin rule of
@@ -12,9 +13,12 @@ import torch
 import torch.multiprocessing as mp
 
 pytestmark = pytest.mark.gpu
-SMALL_TP = dict(hidden=256, inter=512, vocab=1008, n_layers=4, hq=2, hkv=1, dn_kheads=2,
-                dn_vheads=4, max_len=64)
 MARGIN = 4e-3
+
+
+def small_tp(world):
+    return dict(hidden=256, inter=1024, vocab=1008, n_layers=4, hq=world, hkv=1, dn_kheads=world,
+                dn_vheads=2 * world, max_len=64)
 
 
 def _worker(rank, world, port, q):
@@ -27,7 +31,7 @@ def _worker(rank, world, port, q):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world,
                             device_id=torch.device("cuda", rank))
-    cfg = ModelConfig(**SMALL_TP)
+    cfg = ModelConfig(**small_tp(world))
     W = do.make_weights(cfg, 1)
     prompt = np.random.default_rng(1).integers(0, cfg.vocab, 8)
     out = {}
@@ -53,24 +57,26 @@ def _worker(rank, world, port, q):
     os._exit(0)     # skip communicator teardown (graph still holds NCCL kernels)
 
 
-def test_tp2_matches_single_gpu_and_oracle():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_matches_single_gpu_and_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     from nvfp4_v100_b200.engine import ModelConfig, rope_tables
     from oracle import decode_oracle as do
 
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = 29600 + (os.getpid() % 1000)
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = sorted(q.get(timeout=300) for _ in range(2))
+    res = sorted(q.get(timeout=300) for _ in range(world))
     for p in procs:
         p.join(timeout=60)
-    (r0, eager0, graph0, single, out0), (r1, eager1, graph1, _, out1) = res
-    assert eager0 == eager1 == graph0 == graph1          # ranks agree; graph replay == eager
-    for o in (out0, out1):
+    _, eager0, graph0, single, out0 = res[0]
+    for _, eager, graphed, _, _ in res:
+        assert eager == graphed == eager0 == graph0      # ranks agree; graph replay == eager
+    for o in [r[4] for r in res]:
         assert o["peer"][2] == 0 and o["fused"][2] == 0   # no peer wait ever ran out
         assert o["fused"][3] == o["peer"][3] == o["nccl"][3] == 2 * 4 + 1  # K-split layers + argmax
         assert o["peer"][0] == o["peer"][1]
@@ -78,11 +84,11 @@ def test_tp2_matches_single_gpu_and_oracle():
         assert o["nccl"][0] == o["nccl"][1]
     # NCCL sums the fp16 partial vectors its own way; allow a near-tie divergence between modes
     nccl = out0["nccl"][1]
-    cfg = ModelConfig(**SMALL_TP)
+    cfg = ModelConfig(**small_tp(world))
     cos, sin = rope_tables(cfg)
     prompt = np.random.default_rng(1).integers(0, cfg.vocab, 8)
     want, _, margins = do.OracleModel(cfg, do.make_weights(cfg, 1), cos, sin).run(prompt, 16)
-    for name, got in (("tp2", graph0), ("tp2-nccl", nccl), ("single", single)):
+    for name, got in ((f"tp{world}", graph0), (f"tp{world}-nccl", nccl), ("single", single)):
         for i in range(16):
             if got[i] != want[i]:
                 assert margins[i] < MARGIN, (name, i, got[i], want[i], margins[i])
