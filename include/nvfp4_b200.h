@@ -217,6 +217,43 @@ int nvfp4_comm_status(const void* my_buf);
 int launch_allreduce_residual(void* h, const void* const* bufs, int rank, int world, int n,
                               int parity, void* stream);
 
+/* Chunked prefill (no counterpart in the reference, which prefills through the third-party model
+ * code with launch_nvfp4_gemmtc_v5 as its Linear: pipeline/_qwen38_infer.py:796-809).  A chunk's
+ * activations are token-major [tokens][features] between operators and token-minor
+ * [features][tokens] at the GEMM; every operator keeps the arithmetic of its decode-step twin.
+ *   launch_transpose_f16   dst[c][r] = src[r][c] (r < R, c < C); dst rows ld_dst >= R long, tail zeroed
+ *   launch_add_transposed  h[t][c] += dT[c][t] (fp32 add, one rounding): residual add from a GEMM output
+ *   launch_embed_rows      out[t][:] = table[ids[t]], ids device int64 [n]
+ *   launch_silu_mul_rows   gu token-minor [2*inter][N], gate/up rows interleaved by 8 -> act [inter][N]
+ *   launch_attn_prep_tokens  launch_attn_prep for the n_tokens rows of a chunk starting at position
+ *                          pos0 (host int); qkv token-major, ld halves per row; q_out/gate_out
+ *                          token-major [n_tokens][hq*256]; token i writes cache row pos0 + i
+ *   launch_attn_prefill    causal attention, decode arithmetic: token i attends to cache rows
+ *                          [0, len0 + i); q, gate, out token-major [n_tokens][hq*256]
+ *   launch_dn_prefill      one Gated-DeltaNet layer over n tokens: x token-major [n][ld], row =
+ *                          [mixed | z | b | a]; conv window and recurrent state carried in
+ *                          conv_state / state; out token-major [n][nv*128]; work: 256-byte aligned
+ *                          scratch of nvfp4_dn_prefill_work_bytes(n, nk, nv) bytes
+ * All return 0, -1 for bad arguments (launch_attn_prefill: -2), or a launch error code. */
+int launch_transpose_f16(const void* src, long long ld_src, void* dst, long long ld_dst, int R,
+                         int C, void* stream);
+int launch_add_transposed(void* h, const void* dT, long long ldT, int n, int C, void* stream);
+int launch_embed_rows(const void* table, const void* ids, void* out, int n, int hidden,
+                      long long vocab, void* stream);
+int launch_silu_mul_rows(const void* gu, void* act, int inter, int N, void* stream);
+int launch_attn_prep_tokens(const void* qkv, long long ld, const void* q_w1, const void* k_w1,
+                            const void* cos_tab, const void* sin_tab, int pos0, int n_tokens,
+                            void* q_out, void* gate_out, void* keys, void* values, int hq, int hkv,
+                            int max_len, float eps, void* stream);
+int launch_attn_prefill(const void* q, const void* keys, const void* values, int len0,
+                        int n_tokens, const void* gate, void* out, int max_len, int hq, int hkv,
+                        float scale, void* stream);
+long long nvfp4_dn_prefill_work_bytes(int n, int nk, int nv);
+int launch_dn_prefill(const void* x, long long ld, const void* conv_w, void* conv_state,
+                      const void* A_log, const void* dt_bias, const void* norm_w, void* state,
+                      void* work, long long work_bytes, void* out, int n, int nk, int nv,
+                      float rms_eps, void* stream);
+
 /* Quantiser on the device: src fp16 [M, K] row-major -> packed [M, K/2] + scales [M, K/16], byte
  * for byte what the reference's CPU codec produces (scale exponent ceil(log2(max/6)), zero block
  * -> byte 127, nearest code with ties to the smaller code, -0 -> +0): codec/nvfp4_codec.py:166-245,

@@ -63,6 +63,14 @@ SIGNATURES = {
     "launch_allreduce_residual": ([_vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _vp], _i),
     "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
     "launch_dn_fused_heads": ([_vp] * 12 + [_i, _i, _f, _vp], _i),
+    "launch_transpose_f16": ([_vp, _ll, _vp, _ll, _i, _i, _vp], _i),
+    "launch_add_transposed": ([_vp, _vp, _ll, _i, _i, _vp], _i),
+    "launch_embed_rows": ([_vp, _vp, _vp, _i, _i, _ll, _vp], _i),
+    "launch_silu_mul_rows": ([_vp, _vp, _i, _i, _vp], _i),
+    "launch_attn_prep_tokens": ([_vp, _ll] + [_vp] * 4 + [_i, _i] + [_vp] * 4 + [_i, _i, _i, _f, _vp], _i),
+    "launch_attn_prefill": ([_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _f, _vp], _i),
+    "nvfp4_dn_prefill_work_bytes": ([_i, _i, _i], _ll),
+    "launch_dn_prefill": ([_vp, _ll] + [_vp] * 7 + [_ll, _vp, _i, _i, _i, _f, _vp], _i),
     "launch_nvfp4_encode": ([_vp, _vp, _vp, _i, _i, _vp], _i),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),
 }

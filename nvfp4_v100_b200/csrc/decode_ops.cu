@@ -37,18 +37,14 @@ embed_gather_kernel(const __half* __restrict__ table, const long long* __restric
 //   value head j : values[j][*pos] = v_j
 // RMSNorm and RoPE use exactly the arithmetic of rmsnorm_kernel and rope_qk_kernel, including the
 // fp16 rounding between them.
-__global__ void __launch_bounds__(256)
-attn_prep_kernel(const __half* __restrict__ qkv, const float* __restrict__ q_w1,
-                 const float* __restrict__ k_w1, const __half* __restrict__ cos_tab,
-                 const __half* __restrict__ sin_tab, const long long* __restrict__ pos_ptr,
-                 __half* __restrict__ q_out, __half* __restrict__ gate_out,
-                 __half* __restrict__ keys, __half* __restrict__ values, int hq, int hkv,
-                 int max_len, float eps) {
-    pdl_prologue();
+__device__ __forceinline__ void attn_prep_one_token(
+    const __half* __restrict__ qkv, const float* __restrict__ q_w1, const float* __restrict__ k_w1,
+    const __half* __restrict__ cos_tab, const __half* __restrict__ sin_tab, long long pos,
+    __half* __restrict__ q_out, __half* __restrict__ gate_out, __half* __restrict__ keys,
+    __half* __restrict__ values, int hq, int hkv, int max_len, float eps) {
     __shared__ float s_red[8];
     __shared__ float s_n[256];
     const int b = blockIdx.x, d = threadIdx.x, lane = d & 31, warp = d >> 5;
-    long long pos = *pos_ptr;
     if (pos < 0) pos = 0;
     if (pos >= max_len) pos = max_len - 1;  // never index past the cache or the tables
     const __half* kbase = qkv + (size_t)hq * 512;
@@ -82,6 +78,35 @@ attn_prep_kernel(const __half* __restrict__ qkv, const float* __restrict__ q_w1,
     } else {
         keys[((size_t)(b - hq) * max_len + pos) * 256 + d] = r;
     }
+}
+
+// Decode: the position is read from device memory.
+__global__ void __launch_bounds__(256)
+attn_prep_kernel(const __half* __restrict__ qkv, const float* __restrict__ q_w1,
+                 const float* __restrict__ k_w1, const __half* __restrict__ cos_tab,
+                 const __half* __restrict__ sin_tab, const long long* __restrict__ pos_ptr,
+                 __half* __restrict__ q_out, __half* __restrict__ gate_out,
+                 __half* __restrict__ keys, __half* __restrict__ values, int hq, int hkv,
+                 int max_len, float eps) {
+    pdl_prologue();
+    attn_prep_one_token(qkv, q_w1, k_w1, cos_tab, sin_tab, *pos_ptr, q_out, gate_out, keys, values,
+                        hq, hkv, max_len, eps);
+}
+
+// Prefill: token blockIdx.y of a chunk starting at position pos0; qkv is token-major with `ld`
+// halves between token rows, q_out / gate_out token-major [tokens][hq * 256].
+__global__ void __launch_bounds__(256)
+attn_prep_tokens_kernel(const __half* __restrict__ qkv, long long ld,
+                        const float* __restrict__ q_w1, const float* __restrict__ k_w1,
+                        const __half* __restrict__ cos_tab, const __half* __restrict__ sin_tab,
+                        int pos0, __half* __restrict__ q_out, __half* __restrict__ gate_out,
+                        __half* __restrict__ keys, __half* __restrict__ values, int hq, int hkv,
+                        int max_len, float eps) {
+    pdl_prologue();
+    const size_t t = blockIdx.y;
+    attn_prep_one_token(qkv + t * (size_t)ld, q_w1, k_w1, cos_tab, sin_tab,
+                        (long long)pos0 + (long long)t, q_out + t * (size_t)hq * 256,
+                        gate_out + t * (size_t)hq * 256, keys, values, hq, hkv, max_len, eps);
 }
 
 // next = argmax(logits) (lowest index among equal maxima); also records the token and advances
@@ -294,6 +319,25 @@ int launch_attn_prep(const void* qkv, const void* q_w1, const void* k_w1, const 
                              (const float*)k_w1, (const __half*)cos_tab, (const __half*)sin_tab,
                              (const long long*)pos, (__half*)q_out, (__half*)gate_out, (__half*)keys,
                              (__half*)values, hq, hkv, max_len, eps) == cudaSuccess ? 0 : -1;
+}
+
+// The same for the n_tokens tokens of a prefill chunk that starts at position pos0 (host value):
+// qkv token-major with `ld` halves between rows; q_out, gate_out token-major [n_tokens][hq*256];
+// token i writes cache row pos0 + i.  0, or -1 bad args / launch error.
+int launch_attn_prep_tokens(const void* qkv, long long ld, const void* q_w1, const void* k_w1,
+                            const void* cos_tab, const void* sin_tab, int pos0, int n_tokens,
+                            void* q_out, void* gate_out, void* keys, void* values, int hq, int hkv,
+                            int max_len, float eps, void* stream) {
+    if (!qkv || !q_w1 || !k_w1 || !cos_tab || !sin_tab || !q_out || !gate_out || !keys || !values ||
+        hq <= 0 || hkv <= 0 || max_len <= 0 || n_tokens <= 0 || n_tokens > 65535 || pos0 < 0 ||
+        pos0 + n_tokens > max_len || ld < (long long)hq * 512 + 2LL * hkv * 256)
+        return -1;
+    return nvfp4::launch_pdl(nvfp4::attn_prep_tokens_kernel, dim3(hq + 2 * hkv, n_tokens),
+                             dim3(256), 0, (cudaStream_t)stream, (const __half*)qkv, ld,
+                             (const float*)q_w1, (const float*)k_w1, (const __half*)cos_tab,
+                             (const __half*)sin_tab, pos0, (__half*)q_out, (__half*)gate_out,
+                             (__half*)keys, (__half*)values, hq, hkv, max_len, eps) == cudaSuccess
+               ? 0 : -1;
 }
 
 // logits fp16 [vocab]; tok/pos/len/hist_count: device int64 scalars (pos, len, history and

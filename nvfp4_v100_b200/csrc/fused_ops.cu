@@ -147,22 +147,20 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     }
 }
 
-__global__ void __launch_bounds__(ATT_THREADS)
-attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys,
-                   const __half* __restrict__ values, const long long* __restrict__ cum_len,
-                   const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
-                   int gqa, float scale) {
-    pdl_prologue();
+// One query head against the first L cache rows of its KV head; q, gate and out point at the
+// head-major [heads][256] vectors of ONE token.
+__device__ __forceinline__ void attn_one_query(const __half* __restrict__ q,
+                                               const __half* __restrict__ keys,
+                                               const __half* __restrict__ values, int L,
+                                               const __half* __restrict__ gate,
+                                               __half* __restrict__ out, int max_len, int gqa,
+                                               float scale) {
     extern __shared__ float s_sc[];  // [max_len]
     __shared__ float s_red[ATT_WARPS];
     __shared__ float s_bcast;
     __shared__ float s_o[ATT_WARPS][ATT_D];
     const int h = blockIdx.x, kv = h / gqa;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
-    long long L64 = *cum_len;
-    if (L64 > max_len) L64 = max_len;  // never index past the cache
-    if (L64 < 0) L64 = 0;
-    const int L = (int)L64;
 
     float qf[8];
     unpack8(*reinterpret_cast<const uint4*>(q + (size_t)h * ATT_D + lane * 8), qf);
@@ -251,6 +249,33 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys
     const float gt = __half2float(gate[(size_t)h * ATT_D + t]);
     const float sg = round_f16(1.0f / (1.0f + expf(-gt)));
     out[(size_t)h * ATT_D + t] = __float2half(a * sg);
+}
+
+// Decode: one token, length read from device memory.
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys,
+                   const __half* __restrict__ values, const long long* __restrict__ cum_len,
+                   const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
+                   int gqa, float scale) {
+    pdl_prologue();
+    long long L64 = *cum_len;
+    if (L64 > max_len) L64 = max_len;  // never index past the cache
+    if (L64 < 0) L64 = 0;
+    attn_one_query(q, keys, values, (int)L64, gate, out, max_len, gqa, scale);
+}
+
+// Prefill: token blockIdx.y of a chunk whose first token sees len0 cache rows (itself included);
+// token i sees len0 + i.  q, gate, out are token-major [tokens][heads * 256].
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_prefill_kernel(const __half* __restrict__ q, const __half* __restrict__ keys,
+                    const __half* __restrict__ values, int len0,
+                    const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
+                    int gqa, float scale) {
+    pdl_prologue();
+    const size_t row = (size_t)blockIdx.y * gridDim.x * ATT_D;
+    int L = len0 + (int)blockIdx.y;
+    if (L > max_len) L = max_len;
+    attn_one_query(q + row, keys, values, L, gate + row, out + row, max_len, gqa, scale);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -431,6 +456,31 @@ static int attn_decode_launch(const void* q, const void* keys, const void* value
     const cudaError_t e = nvfp4::launch_pdl(
         nvfp4::attn_decode_kernel, dim3(hq), dim3(ATT_THREADS), smem, (cudaStream_t)stream,
         (const __half*)q, (const __half*)keys, (const __half*)values, (const long long*)cum_len,
+        (const __half*)gate, (__half*)out, max_len, hq / hkv, scale);
+    return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+// Causal attention of a prefill chunk with the decode kernel's arithmetic: token i of the chunk
+// (i < n_tokens) attends to cache rows [0, len0 + i), which must already hold the chunk's own
+// keys and values.  q, gate, out: token-major [n_tokens][hq * 256].  Grid (hq, n_tokens).
+int launch_attn_prefill(const void* q, const void* keys, const void* values, int len0,
+                        int n_tokens, const void* gate, void* out, int max_len, int hq, int hkv,
+                        float scale, void* stream) {
+    static int smem_set = 0;
+    if (max_len <= 0 || max_len > 47104 || n_tokens <= 0 || n_tokens > 65535) return -2;
+    if (len0 < 1 || len0 + n_tokens - 1 > max_len) return -2;
+    if (!q || !keys || !values || !gate || !out) return -2;
+    if (hq <= 0 || hkv <= 0 || hq % hkv != 0) return -2;
+    const int smem = (len0 + n_tokens - 1) * (int)sizeof(float);
+    if (smem > 40 * 1024 && smem > smem_set) {
+        if (cudaFuncSetAttribute(nvfp4::attn_prefill_kernel,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+            return -2;
+        smem_set = smem;
+    }
+    const cudaError_t e = nvfp4::launch_pdl(
+        nvfp4::attn_prefill_kernel, dim3(hq, n_tokens), dim3(ATT_THREADS), (size_t)smem,
+        (cudaStream_t)stream, (const __half*)q, (const __half*)keys, (const __half*)values, len0,
         (const __half*)gate, (__half*)out, max_len, hq / hkv, scale);
     return (e == cudaSuccess) ? 0 : (int)e;
 }

@@ -194,17 +194,35 @@ class DecodeEngine:
         assert packed.data_ptr() % 32 == 0 and scales.data_ptr() % 8 == 0
         return _Mat(packed, scales, M, K)
 
-    def load_random(self, seed: int = 0):
-        """Random E2M1 bytes and scale bytes in [118, 122] (what N(0, 0.02^2) weights produce),
-        fp16 embedding ~N(0, 0.02^2), unit norm weights: the throughput workload."""
+    def load_random(self, seed: int = 0, quantise: bool = True):
+        """The throughput workload: seeded fp16 weights ~N(0, 0.02^2) drawn on the device and
+        quantised there with ``launch_nvfp4_encode`` (``quantise=False``: random E2M1 bytes with
+        scale bytes in [118, 122], the range those weights produce), fp16 embedding
+        ~N(0, 0.02^2), unit norm weights."""
         c = self.cfg
         g = torch.Generator(device=self.dev)
         g.manual_seed(seed * 64 + self.rank)
+        vp = ctypes.c_void_p
 
         def rnd(M, K):
-            p = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device=self.dev, generator=g)
-            s = torch.randint(118, 123, (M * K // 16,), dtype=torch.uint8, device=self.dev,
-                              generator=g)
+            if not quantise:
+                p = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device=self.dev,
+                                  generator=g)
+                s = torch.randint(118, 123, (M * K // 16,), dtype=torch.uint8, device=self.dev,
+                                  generator=g)
+                return self._mat(p, s, M, K)
+            p = torch.empty(M * K // 2, dtype=torch.uint8, device=self.dev)
+            s = torch.empty(M * K // 16, dtype=torch.uint8, device=self.dev)
+            st = vp(torch.cuda.current_stream(self.dev).cuda_stream)
+            step = max(1, (1 << 28) // K)               # at most 512 MB of fp16 at a time
+            for r0 in range(0, M, step):
+                r1 = min(M, r0 + step)
+                w = (torch.randn((r1 - r0, K), device=self.dev, generator=g) * 0.02).half()
+                rc = self.lib.launch_nvfp4_encode(
+                    vp(w.data_ptr()), vp(p.data_ptr() + r0 * (K // 2)),
+                    vp(s.data_ptr() + r0 * (K // 16)), r1 - r0, K, st)
+                if rc != 0:
+                    raise RuntimeError(f"launch_nvfp4_encode rc={rc}")
             return self._mat(p, s, M, K)
 
         ones = lambda n: torch.ones(n, dtype=torch.float32, device=self.dev)
@@ -518,10 +536,119 @@ class DecodeEngine:
         else:
             self.enqueue_step()
 
-    def run(self, prompt, n_gen: int):
-        """Feed the prompt token by token through the step (teacher forced), then generate n_gen
-        tokens greedily.  Returns the generated token ids (host list)."""
+    # ------------------------------------------------------------------ chunked prefill
+    def _prefill_buffers(self, chunk: int):
+        """Scratch for one chunk of up to ``chunk`` tokens (allocated once, reused)."""
+        if getattr(self, "_pf", None) is not None and self._pf["chunk"] >= chunk:
+            return self._pf
+        c = self.cfg
+        f16 = torch.float16
+        np_max = (chunk + 7) // 8 * 8
+        m_in = max(self.hq_l * 2 * HEAD_DIM + 2 * self.hkv_l * HEAD_DIM,
+                   self.conv_l + self.nv_l * DN_DIM + 2 * self.nv_l)
+        k_max = max(c.hidden, self.hq_l * HEAD_DIM, self.nv_l * DN_DIM)
+        m_max = max(m_in, 2 * self.inter_l, c.hidden)
+        e = lambda *shape, dt=f16: torch.empty(*shape, dtype=dt, device=self.dev)
+        work = int(self.lib.nvfp4_dn_prefill_work_bytes(chunk, max(1, self.nk_l), max(1, self.nv_l)))
+        self._pf = dict(
+            chunk=chunk, ids=e(chunk, dt=torch.int64),
+            h=e(chunk * c.hidden), xn=e(chunk * c.hidden),
+            xT=e(k_max * np_max), yT=e(m_max * np_max), y=e(chunk * m_in),
+            actT=e(self.inter_l * np_max), dT=e(c.hidden * np_max),
+            q=e(chunk * self.hq_l * HEAD_DIM), gate=e(chunk * self.hq_l * HEAD_DIM),
+            mix=e(chunk * max(self.hq_l * HEAD_DIM, self.nv_l * DN_DIM)),
+            work=e(work, dt=torch.uint8), work_bytes=work)
+        return self._pf
+
+    def prefill(self, tokens, chunk: int = 512, start: int = 0):
+        """Run ``tokens`` (host ints) through the model in chunks of up to ``chunk`` tokens with the
+        tensor-core GEMM as every projection, filling the KV caches, conv windows and recurrent
+        states for positions start .. start + len(tokens) - 1.  Leaves the engine ready to process
+        the token at the next position (``tok`` is the caller's to set).  Single GPU only; the
+        reference's flow is pipeline/_qwen38_infer.py:796-809 (512-token chunks through the
+        third-party model code)."""
+        if self.world != 1:
+            raise RuntimeError("chunked prefill is single-GPU; tensor-parallel engines feed the "
+                               "prompt through the decode step")
+        c, lib = self.cfg, self.lib
+        total = len(tokens)
+        if start + total > c.max_len:
+            raise ValueError("prompt longer than the cache")
+        B = self._prefill_buffers(min(chunk, max(total, 1)))
+        st = vp(torch.cuda.current_stream().cuda_stream)
+        H = c.hidden
+        ptr = lambda t: vp(t.data_ptr())
+
+        def ok(rc, what):
+            if rc != 0:
+                raise RuntimeError(f"{what} rc={rc}")
+
+        def rmsnorm(w1, n):
+            ok(lib.launch_rmsnorm(ptr(B["h"]), H, ptr(w1), ptr(B["xn"]), n, H, float(c.rms_eps), st),
+               "launch_rmsnorm")
+
+        def to_gemm(src, n, feat, Np):          # token-major [n][feat] -> xT [feat][Np]
+            ok(lib.launch_transpose_f16(ptr(src), feat, ptr(B["xT"]), Np, n, feat, st), "transpose")
+
+        def gemm(m: _Mat, act, out, Np):
+            ok(lib.launch_nvfp4_gemmtc_v5(ptr(m.packed), ptr(m.scales), ptr(act), ptr(out), m.M, Np,
+                                          m.K, st), "launch_nvfp4_gemmtc_v5")
+
+        for lo in range(0, total, B["chunk"]):
+            n = min(B["chunk"], total - lo)
+            Np = (n + 7) // 8 * 8
+            p0 = start + lo
+            B["ids"][:n].copy_(torch.as_tensor(np.asarray(tokens[lo:lo + n], dtype=np.int64)))
+            ok(lib.launch_embed_rows(ptr(self.embed), ptr(B["ids"]), ptr(B["h"]), n, H, c.vocab, st),
+               "launch_embed_rows")
+            for L in self.layers:
+                e = L.extra
+                rmsnorm(L.in_w1, n)
+                to_gemm(B["xn"], n, H, Np)
+                gemm(L.w_in, B["xT"], B["yT"], Np)
+                m_in = L.w_in.M
+                ok(lib.launch_transpose_f16(ptr(B["yT"]), Np, ptr(B["y"]), m_in, m_in, n, st),
+                   "transpose")
+                if L.attn:
+                    ok(lib.launch_attn_prep_tokens(
+                        ptr(B["y"]), m_in, ptr(e["q_w1"]), ptr(e["k_w1"]), ptr(self.cos),
+                        ptr(self.sin), p0, n, ptr(B["q"]), ptr(B["gate"]), ptr(e["keys"]),
+                        ptr(e["values"]), self.hq_l, self.hkv_l, c.max_len, float(c.rms_eps), st),
+                       "launch_attn_prep_tokens")
+                    ok(lib.launch_attn_prefill(
+                        ptr(B["q"]), ptr(e["keys"]), ptr(e["values"]), p0 + 1, n, ptr(B["gate"]),
+                        ptr(B["mix"]), c.max_len, self.hq_l, self.hkv_l, float(HEAD_DIM) ** -0.5,
+                        st), "launch_attn_prefill")
+                else:
+                    ok(lib.launch_dn_prefill(
+                        ptr(B["y"]), m_in, ptr(e["conv_w"]), ptr(e["conv_state"]), ptr(e["A_log"]),
+                        ptr(e["dt_bias"]), ptr(e["norm_w"]), ptr(e["state"]), ptr(B["work"]),
+                        B["work_bytes"], ptr(B["mix"]), n, self.nk_l, self.nv_l, float(c.rms_eps),
+                        st), "launch_dn_prefill")
+                to_gemm(B["mix"], n, L.w_out.K, Np)
+                gemm(L.w_out, B["xT"], B["dT"], Np)
+                ok(lib.launch_add_transposed(ptr(B["h"]), ptr(B["dT"]), Np, n, H, st), "add")
+                rmsnorm(L.post_w1, n)
+                to_gemm(B["xn"], n, H, Np)
+                gemm(L.w_gu, B["xT"], B["yT"], Np)
+                ok(lib.launch_silu_mul_rows(ptr(B["yT"]), ptr(B["actT"]), self.inter_l, Np, st),
+                   "launch_silu_mul_rows")
+                gemm(L.w_down, B["actT"], B["dT"], Np)
+                ok(lib.launch_add_transposed(ptr(B["h"]), ptr(B["dT"]), Np, n, H, st), "add")
+        self.pos.fill_(start + total)
+        self.len.fill_(start + total + 1)
+        if lib.nvfp4_gemm_status(0) != 0:
+            raise RuntimeError("a bounded wait inside the tensor-core GEMM ran out")
+
+    def run(self, prompt, n_gen: int, native_prefill: bool = False):
+        """Feed the prompt, then generate n_gen tokens greedily; returns the generated token ids
+        (host list).  The prompt goes token by token through the decode step (teacher forced), or
+        with ``native_prefill`` all but its last token through :meth:`prefill`."""
         self.reset(int(prompt[0]))
+        if native_prefill and len(prompt) > 1:
+            self.prefill([int(t) for t in prompt[:-1]])
+            self.tok.fill_(int(prompt[-1]))
+            prompt = prompt[-1:]
         for t in range(1, len(prompt)):
             self.step()
             self.tok.fill_(int(prompt[t]))      # overwrite the model's own prediction

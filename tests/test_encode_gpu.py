@@ -106,3 +106,23 @@ def test_encoded_weights_feed_the_gemv(lib):
     assert rc == 0
     ref = oc.gemv_f64(p, s, a)
     assert oc.rel_error_floored(y, ref).max() <= 1e-3
+
+
+def test_container_written_on_the_gpu_equals_the_host_container(lib, tmp_path):
+    from nvfp4_v100_b200.pipeline import _qwen38_nvfp4_pack as pk
+
+    rng = np.random.default_rng(21)
+    tensors = {
+        "model.language_model.layers.0.mlp.gate_proj.weight": oc.synthetic_weight(96, 256, 1),
+        "model.language_model.layers.0.mlp.down_proj.weight": oc.synthetic_weight(256, 96 + 32, 2),
+        "model.language_model.layers.0.input_layernorm.weight": rng.standard_normal(256).astype(np.float32),
+        "model.language_model.embed_tokens.weight": oc.synthetic_weight(50, 256, 3),
+        "lm_head.weight": oc.synthetic_weight(50, 256, 4),
+    }
+    host_dir, gpu_dir = str(tmp_path / "host"), str(tmp_path / "gpu")
+    ih = pk.pack_tensors(tensors, host_dir)
+    ig = pk.pack_tensors(tensors, gpu_dir, device="cuda")
+    assert ih == ig and len(ih) == 3
+    for name in ("nvfp4_packed.bin", "nvfp4_index.json", "fp16_embed.npy"):
+        with open(f"{host_dir}/{name}", "rb") as a, open(f"{gpu_dir}/{name}", "rb") as b:
+            assert a.read() == b.read(), name
