@@ -40,6 +40,7 @@ constexpr int GEMM_BK = 64;
 constexpr int GEMM_STAGES = 4;
 constexpr int GEMM_PRODUCER_WARPS = 8;   // weight-dequant warps (two threads per weight row)
 constexpr int GEMM_THREADS = 64 + 32 * GEMM_PRODUCER_WARPS;
+constexpr int GEMM_WPF = 4;               // K steps the weight loads run ahead of their use
 constexpr uint32_t GEMM_SPIN_LIMIT = 1u << 24;
 
 __device__ int g_gemm_status = 0;  // 0 ok; otherwise 1 + id of the wait that ran out
@@ -163,6 +164,8 @@ __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                           const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                           __half* __restrict__ out, int M, int N, int K) {
+    // (two stages and two CTAs per SM for the 256-token tile measured 8 % slower than this)
+    constexpr int ST = GEMM_STAGES;
     constexpr int A_BYTES = GEMM_BM * 128;          // 16 KB
     constexpr int B_BOX = GEMM_BK * 128;            // 8 KB: 64 k rows of 64 tokens
     constexpr int B_BYTES = (BN / 64) * B_BOX;
@@ -171,10 +174,10 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~(uintptr_t)1023);
     uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem + GEMM_STAGES * A_BYTES;
-    __shared__ __align__(8) uint64_t bar_full_b[GEMM_STAGES];   // TMA bytes landed
-    __shared__ __align__(8) uint64_t bar_full_a[GEMM_STAGES];   // 128 weight rows written
-    __shared__ __align__(8) uint64_t bar_empty[GEMM_STAGES];    // MMAs that read the stage retired
+    uint8_t* smem_b = smem + ST * A_BYTES;
+    __shared__ __align__(8) uint64_t bar_full_b[ST];   // TMA bytes landed
+    __shared__ __align__(8) uint64_t bar_full_a[ST];   // 128 weight rows written
+    __shared__ __align__(8) uint64_t bar_empty[ST];    // MMAs that read the stage retired
     __shared__ __align__(8) uint64_t bar_accum;                 // whole accumulation retired
     __shared__ uint32_t s_tmem;
 
@@ -183,7 +186,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
     const int ksteps = K / GEMM_BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < GEMM_STAGES; s++) {
+        for (int s = 0; s < ST; s++) {
             mbar_init(smem_u32(&bar_full_b[s]), 1);
             mbar_init(smem_u32(&bar_full_a[s]), 32 * GEMM_PRODUCER_WARPS);
             mbar_init(smem_u32(&bar_empty[s]), 1);
@@ -205,8 +208,8 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
         if (lane == 0) {
             bool ok = true;
             for (int it = 0; it < ksteps && ok; it++) {
-                const int s = it % GEMM_STAGES;
-                const uint32_t ph = (uint32_t)(it / GEMM_STAGES) & 1u;
+                const int s = it % ST;
+                const uint32_t ph = (uint32_t)(it / ST) & 1u;
                 ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 0);
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&bar_full_b[s]);
@@ -225,8 +228,8 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                                    ((uint32_t)(GEMM_BM >> 4) << 24);
             bool ok = true;
             for (int it = 0; it < ksteps && ok; it++) {
-                const int s = it % GEMM_STAGES;
-                const uint32_t ph = (uint32_t)(it / GEMM_STAGES) & 1u;
+                const int s = it % ST;
+                const uint32_t ph = (uint32_t)(it / ST) & 1u;
                 ok = mbar_wait(smem_u32(&bar_full_a[s]), ph, 1) &&
                      mbar_wait(smem_u32(&bar_full_b[s]), ph, 2);
                 if (!ok) break;
@@ -255,12 +258,31 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
         const uint8_t* prow = packed + (size_t)row * (size_t)(K >> 1) + half * 16;
         const uint8_t* srow = scales + (size_t)row * (size_t)(K >> 4) + half * 2;
         bool ok = true;
-        for (int it = 0; it < ksteps; it++) {
-            const int s = it % GEMM_STAGES;
-            const uint32_t ph = (uint32_t)(it / GEMM_STAGES) & 1u;
-            // 16 packed bytes (32 weights = 2 scale blocks) of this K step
-            const uint4 p0 = ld_stream_u4(prow + (size_t)it * 32);
-            const uint32_t sc2 = __ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)it * 4));
+        // 16 packed bytes (32 weights = 2 scale blocks) per K step, requested GEMM_WPF steps ahead
+        // of their use: the weight stream comes from HBM and its latency is longer than the
+        // tensor core needs for one K step
+        uint4 pw[GEMM_WPF];
+        uint32_t ps[GEMM_WPF];
+#pragma unroll
+        for (int u = 0; u < GEMM_WPF; u++) {
+            if (u < ksteps) {
+                pw[u] = ld_stream_u4(prow + (size_t)u * 32);
+                ps[u] = __ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)u * 4));
+            }
+        }
+        for (int it0 = 0; it0 < ksteps; it0 += GEMM_WPF) {
+#pragma unroll
+        for (int u = 0; u < GEMM_WPF; u++) {
+            const int it = it0 + u;
+            if (it >= ksteps) break;
+            const int s = it % ST;
+            const uint32_t ph = (uint32_t)(it / ST) & 1u;
+            const uint4 p0 = pw[u];
+            const uint32_t sc2 = ps[u];
+            if (it + GEMM_WPF < ksteps) {
+                pw[u] = ld_stream_u4(prow + (size_t)(it + GEMM_WPF) * 32);
+                ps[u] = __ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)(it + GEMM_WPF) * 4));
+            }
             if (ok) ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 3);
             const uint32_t w[4] = {p0.x, p0.y, p0.z, p0.w};
             uint8_t* arow = smem_a + s * A_BYTES + r * 128;
@@ -283,6 +305,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
             }
             fence_proxy_async_smem();     // make the generic-proxy writes visible to the tensor core
             mbar_arrive(smem_u32(&bar_full_a[s]));
+        }
         }
 
         // ---------------- epilogue: TMEM -> registers -> fp16 out[m][n] ----------------

@@ -237,104 +237,160 @@ dn_prep_kernel(const __half* __restrict__ conv_out, int conv_dim, const __half* 
     }
 }
 
-// The recurrence over the chunk.  CTA = 4 warps = 32 state rows of one value head; a warp owns 8
-// rows: lane group gi = lane >> 3 owns rows 2 gi and 2 gi + 1 of the warp's 8, lane sub = lane & 7
-// owns dims 16 sub .. 16 sub + 15 of them.  The next token's operands are loaded while the
-// current token is computed.  o[t][h*128 + row] = f16(S_t[row] . q_t).
+// The recurrence over the chunk.  CTA = 4 warps = 16 state rows of one value head (384 CTAs for
+// the full model: two or three per SM); a warp owns 4 rows, one per 8-lane group gi = lane >> 3;
+// lane sub = lane & 7 owns dims 32 j + 4 sub .. + 3 (j = 0..3) of its row, so the 8 lanes of a
+// group read one contiguous 128-byte piece of a vector at a time.  The operands of SCAN_TB tokens (the head's
+// normalised k and q, this CTA's 32 values of v, beta and decay) are staged in shared memory by
+// cp.async, double buffered, so the sequential chain never waits on global memory.
+// o[t][h*128 + row] = f16(S_t[row] . q_t).
 #define SCAN_WARPS 4
+#define SCAN_RPG 1                          // state rows per 8-lane group
+#define SCAN_ROWS (SCAN_WARPS * 4 * SCAN_RPG)
+#define SCAN_TB 16
+
+struct ScanStage {
+    float k[SCAN_TB][PF_DK];
+    float q[SCAN_TB][PF_DK];
+    __half v[SCAN_TB][SCAN_ROWS];
+    float2 be[SCAN_TB];
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gsrc) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
 __global__ void __launch_bounds__(SCAN_WARPS * 32)
 dn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
                const float2* __restrict__ be, const __half* __restrict__ conv_out, int conv_dim,
                float* __restrict__ state, __half* __restrict__ o_out, int nk, int nv, int n) {
     pdl_prologue();
-    const int per_head = PF_DK / (SCAN_WARPS * 8);           // CTAs per value head
+    __shared__ __align__(16) ScanStage stage[2];
+    const int per_head = PF_DK / SCAN_ROWS;                  // CTAs per value head
     const int h = blockIdx.x / per_head, part = blockIdx.x % per_head;
     const int kh = h / (nv / nk);
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gi = lane >> 3, sub = lane & 7;
-    const int row0 = part * (SCAN_WARPS * 8) + warp * 8 + gi * 2;   // rows row0, row0 + 1
+    const int lrow = (warp * 4 + gi) * SCAN_RPG;             // first of this lane's rows, in the CTA
+    const int row0 = part * SCAN_ROWS + lrow;
     const int key_dim = nk * PF_DK;
 
-    float S[2][16];
-    float* sp = state + ((size_t)h * PF_DK + row0) * PF_DK + sub * 16;
+    // stage the operands of tokens [t0, t0 + SCAN_TB) (clamped to the chunk) into buffer b
+    auto issue = [&](int t0, int b) {
+        ScanStage& s = stage[b];
+        for (int i = tid; i < SCAN_TB * (PF_DK / 4); i += SCAN_WARPS * 32) {   // 16-byte pieces
+            const int tt = i / (PF_DK / 4), c = i % (PF_DK / 4);
+            const int t = min(t0 + tt, n - 1);
+            const size_t o = ((size_t)t * nk + kh) * PF_DK + c * 4;
+            cp_async_16(&s.k[tt][c * 4], kn + o);
+            cp_async_16(&s.q[tt][c * 4], qn + o);
+        }
+        if (tid < SCAN_TB * (SCAN_ROWS / 8)) {
+            const int tt = tid / (SCAN_ROWS / 8), c = tid % (SCAN_ROWS / 8);
+            const int t = min(t0 + tt, n - 1);
+            cp_async_16(&s.v[tt][c * 8], conv_out + (size_t)t * conv_dim + 2 * key_dim + h * PF_DK +
+                                             part * SCAN_ROWS + c * 8);
+        }
+        if (tid >= 64 && tid < 64 + SCAN_TB) {
+            const int tt = tid - 64;
+            s.be[tt] = __ldg(be + (size_t)min(t0 + tt, n - 1) * nv + h);
+        }
+        cp_async_commit();
+    };
+
+    float S[SCAN_RPG][16];
+    float* sp = state + ((size_t)h * PF_DK + row0) * PF_DK + sub * 4;
 #pragma unroll
-    for (int r = 0; r < 2; r++)
+    for (int r = 0; r < SCAN_RPG; r++)
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            const float4 v = *reinterpret_cast<const float4*>(sp + (size_t)r * PF_DK + j * 4);
+            const float4 v = *reinterpret_cast<const float4*>(sp + (size_t)r * PF_DK + j * 32);
             S[r][4 * j] = v.x; S[r][4 * j + 1] = v.y; S[r][4 * j + 2] = v.z; S[r][4 * j + 3] = v.w;
         }
 
-    float kc[16], qc[16], kx[16], qx[16];
-    float2 bec, bex;
-    float vc[2], vx[2];
-    auto load = [&](int t, float (&k)[16], float (&q)[16], float2& b, float (&v)[2]) {
-        const size_t o = ((size_t)t * nk + kh) * PF_DK + sub * 16;
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const float4 a = __ldg(reinterpret_cast<const float4*>(kn + o + j * 4));
-            const float4 c = __ldg(reinterpret_cast<const float4*>(qn + o + j * 4));
-            k[4 * j] = a.x; k[4 * j + 1] = a.y; k[4 * j + 2] = a.z; k[4 * j + 3] = a.w;
-            q[4 * j] = c.x; q[4 * j + 1] = c.y; q[4 * j + 2] = c.z; q[4 * j + 3] = c.w;
+    const int nblk = (n + SCAN_TB - 1) / SCAN_TB;
+    if (nblk > 0) issue(0, 0);
+    for (int blk = 0; blk < nblk; blk++) {
+        const int cur = blk & 1;
+        if (blk + 1 < nblk) {
+            issue((blk + 1) * SCAN_TB, cur ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
         }
-        b = __ldg(be + (size_t)t * nv + h);
-        const __half2 vv = *reinterpret_cast<const __half2*>(
-            conv_out + (size_t)t * conv_dim + 2 * key_dim + h * PF_DK + row0);
-        v[0] = __low2float(vv);
-        v[1] = __high2float(vv);
-    };
-    if (n > 0) load(0, kc, qc, bec, vc);
-    for (int t = 0; t < n; t++) {
-        if (t + 1 < n) load(t + 1, kx, qx, bex, vx);
-        const float beta = bec.x, eg = bec.y;
-        float kvp[2], od[2];
+        __syncthreads();
+        const ScanStage& s = stage[cur];
+        const int tcount = min(SCAN_TB, n - blk * SCAN_TB);
+        for (int tt = 0; tt < tcount; tt++) {
+            float kc[16], qc[16];
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-            float a = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 16; j++) {
-                S[r][j] *= eg;
-                a = fmaf(S[r][j], kc[j], a);
+            for (int j = 0; j < 4; j++) {
+                const float4 a = *reinterpret_cast<const float4*>(&s.k[tt][j * 32 + sub * 4]);
+                const float4 c = *reinterpret_cast<const float4*>(&s.q[tt][j * 32 + sub * 4]);
+                kc[4 * j] = a.x; kc[4 * j + 1] = a.y; kc[4 * j + 2] = a.z; kc[4 * j + 3] = a.w;
+                qc[4 * j] = c.x; qc[4 * j + 1] = c.y; qc[4 * j + 2] = c.z; qc[4 * j + 3] = c.w;
             }
-            kvp[r] = a;
-        }
+            const float2 bd = s.be[tt];
+            const float beta = bd.x, eg = bd.y;
+            float vr[SCAN_RPG], kvp[SCAN_RPG], od[SCAN_RPG];
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-            kvp[0] += __shfl_xor_sync(0xffffffffu, kvp[0], o);
-            kvp[1] += __shfl_xor_sync(0xffffffffu, kvp[1], o);
-        }
+            for (int r = 0; r < SCAN_RPG; r++) vr[r] = __half2float(s.v[tt][lrow + r]);
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-            const float delta = (vc[r] - kvp[r]) * beta;
-            float a = 0.0f;
+            for (int r = 0; r < SCAN_RPG; r++) {
+                float a[4];
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                S[r][j] = fmaf(kc[j], delta, S[r][j]);
-                a = fmaf(S[r][j], qc[j], a);
+                for (int j = 0; j < 4; j++) {            // four independent partial sums
+                    S[r][4 * j] *= eg; S[r][4 * j + 1] *= eg; S[r][4 * j + 2] *= eg; S[r][4 * j + 3] *= eg;
+                    a[j] = S[r][4 * j] * kc[4 * j];
+                    a[j] = fmaf(S[r][4 * j + 1], kc[4 * j + 1], a[j]);
+                    a[j] = fmaf(S[r][4 * j + 2], kc[4 * j + 2], a[j]);
+                    a[j] = fmaf(S[r][4 * j + 3], kc[4 * j + 3], a[j]);
+                }
+                kvp[r] = (a[0] + a[1]) + (a[2] + a[3]);
             }
-            od[r] = a;
-        }
 #pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-            od[0] += __shfl_xor_sync(0xffffffffu, od[0], o);
-            od[1] += __shfl_xor_sync(0xffffffffu, od[1], o);
-        }
-        if (sub == 0)
-            *reinterpret_cast<__half2*>(o_out + ((size_t)t * nv + h) * PF_DK + row0) =
-                __floats2half2_rn(od[0], od[1]);
-        if (t + 1 < n) {
+            for (int o = 1; o < 8; o <<= 1)
 #pragma unroll
-            for (int j = 0; j < 16; j++) { kc[j] = kx[j]; qc[j] = qx[j]; }
-            bec = bex;
-            vc[0] = vx[0];
-            vc[1] = vx[1];
+                for (int r = 0; r < SCAN_RPG; r++) kvp[r] += __shfl_xor_sync(0xffffffffu, kvp[r], o);
+#pragma unroll
+            for (int r = 0; r < SCAN_RPG; r++) {
+                const float delta = (vr[r] - kvp[r]) * beta;
+                float a[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) S[r][4 * j + e] = fmaf(kc[4 * j + e], delta, S[r][4 * j + e]);
+                    a[j] = S[r][4 * j] * qc[4 * j];
+                    a[j] = fmaf(S[r][4 * j + 1], qc[4 * j + 1], a[j]);
+                    a[j] = fmaf(S[r][4 * j + 2], qc[4 * j + 2], a[j]);
+                    a[j] = fmaf(S[r][4 * j + 3], qc[4 * j + 3], a[j]);
+                }
+                od[r] = (a[0] + a[1]) + (a[2] + a[3]);
+            }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1)
+#pragma unroll
+                for (int r = 0; r < SCAN_RPG; r++) od[r] += __shfl_xor_sync(0xffffffffu, od[r], o);
+            if (sub == 0) {
+#pragma unroll
+                for (int r = 0; r < SCAN_RPG; r++)
+                    o_out[((size_t)(blk * SCAN_TB + tt) * nv + h) * PF_DK + row0 + r] =
+                        __float2half(od[r]);
+            }
         }
+        __syncthreads();     // everyone is done with this buffer before it is refilled
     }
 #pragma unroll
-    for (int r = 0; r < 2; r++)
+    for (int r = 0; r < SCAN_RPG; r++)
 #pragma unroll
         for (int j = 0; j < 4; j++)
-            *reinterpret_cast<float4*>(sp + (size_t)r * PF_DK + j * 4) =
+            *reinterpret_cast<float4*>(sp + (size_t)r * PF_DK + j * 32) =
                 make_float4(S[r][4 * j], S[r][4 * j + 1], S[r][4 * j + 2], S[r][4 * j + 3]);
 }
 
@@ -456,7 +512,7 @@ int launch_dn_prefill(const void* x, long long ld, const void* conv_w, void* con
                                  st, (const __half*)conv_out, conv_dim, xh, ld,
                                  (const __half*)A_log, (const __half*)dt_bias, qn, kn, be, nk,
                                  nv) == cudaSuccess;
-    ok = ok && nvfp4::launch_pdl(nvfp4::dn_scan_kernel, dim3(nv * (PF_DK / (SCAN_WARPS * 8))),
+    ok = ok && nvfp4::launch_pdl(nvfp4::dn_scan_kernel, dim3(nv * (PF_DK / SCAN_ROWS)),
                                  dim3(SCAN_WARPS * 32), 0, st, (const float*)qn, (const float*)kn,
                                  (const float2*)be, (const __half*)conv_out, conv_dim,
                                  (float*)state, o16, nk, nv, n) == cudaSuccess;
