@@ -264,20 +264,6 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys
     attn_one_query(q, keys, values, (int)L64, gate, out, max_len, gqa, scale);
 }
 
-// Prefill: token blockIdx.y of a chunk whose first token sees len0 cache rows (itself included);
-// token i sees len0 + i.  q, gate, out are token-major [tokens][heads * 256].
-__global__ void __launch_bounds__(ATT_THREADS)
-attn_prefill_kernel(const __half* __restrict__ q, const __half* __restrict__ keys,
-                    const __half* __restrict__ values, int len0,
-                    const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
-                    int gqa, float scale) {
-    pdl_prologue();
-    const size_t row = (size_t)blockIdx.y * gridDim.x * ATT_D;
-    int L = len0 + (int)blockIdx.y;
-    if (L > max_len) L = max_len;
-    attn_one_query(q + row, keys, values, L, gate + row, out + row, max_len, gqa, scale);
-}
-
 // ---------------------------------------------------------------------------------------------
 // Gated DeltaNet decode step (head dim 128, conv kernel 4; 16 key / 48 value heads in the full
 // model, fewer on a tensor-parallel shard).
@@ -396,6 +382,162 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
     }
 }
 
+// Prefill attention for ATT_G consecutive tokens of one query head per CTA: the tokens share
+// every key and value row they load (token g of the group sees L0 + g rows).  Per token the
+// arithmetic and its order are those of attn_one_query — same key-to-warp assignment, same
+// reduction trees — so a chunk gives bit-identical outputs to token-by-token decode.
+#define ATT_G 4
+__global__ void __launch_bounds__(ATT_THREADS)
+attn_prefill_group_kernel(const __half* __restrict__ q, const __half* __restrict__ keys,
+                          const __half* __restrict__ values, int len0, int n_tokens,
+                          const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
+                          int gqa, float scale, int lcap) {
+    pdl_prologue();
+    extern __shared__ float s_sc[];                 // [ATT_G][lcap]
+    __shared__ float s_q[ATT_G][ATT_D];
+    __shared__ float s_red[ATT_G][ATT_WARPS];
+    __shared__ float s_bcast[ATT_G];
+    __shared__ float s_o[ATT_WARPS][ATT_D];
+    const int h = blockIdx.x, kv = h / gqa, hq = gridDim.x;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int tok0 = blockIdx.y * ATT_G;
+    int Lg[ATT_G];
+#pragma unroll
+    for (int g = 0; g < ATT_G; g++) {
+        const int tok = tok0 + g;
+        int L = (tok < n_tokens) ? len0 + tok : 0;   // 0 rows: the token does not exist
+        Lg[g] = min(L, max_len);
+    }
+    int Lmax = 0;
+#pragma unroll
+    for (int g = 0; g < ATT_G; g++) Lmax = max(Lmax, Lg[g]);
+    if (t < ATT_D) {
+#pragma unroll
+        for (int g = 0; g < ATT_G; g++)
+            s_q[g][t] = (Lg[g] > 0)
+                            ? __half2float(q[((size_t)(tok0 + g) * hq + h) * ATT_D + t]) : 0.0f;
+    }
+    __syncthreads();
+
+    const __half* kbase = keys + (size_t)kv * (size_t)max_len * ATT_D + lane * 8;
+    float m[ATT_G];
+#pragma unroll
+    for (int g = 0; g < ATT_G; g++) m[g] = -3.4e38f;
+    for (int i0 = warp; i0 < Lmax; i0 += ATT_WARPS * 2) {
+        uint4 kr[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int i = i0 + u * ATT_WARPS;
+            kr[u] = (i < Lmax) ? *reinterpret_cast<const uint4*>(kbase + (size_t)i * ATT_D)
+                               : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int i = i0 + u * ATT_WARPS;
+            float kf[8];
+            unpack8(kr[u], kf);
+#pragma unroll
+            for (int g = 0; g < ATT_G; g++) {
+                const float4 qa = *reinterpret_cast<const float4*>(&s_q[g][lane * 8]);
+                const float4 qb = *reinterpret_cast<const float4*>(&s_q[g][lane * 8 + 4]);
+                float acc = 0.0f;
+                acc = fmaf(qa.x, kf[0], acc); acc = fmaf(qa.y, kf[1], acc);
+                acc = fmaf(qa.z, kf[2], acc); acc = fmaf(qa.w, kf[3], acc);
+                acc = fmaf(qb.x, kf[4], acc); acc = fmaf(qb.y, kf[5], acc);
+                acc = fmaf(qb.z, kf[6], acc); acc = fmaf(qb.w, kf[7], acc);
+                acc = warp_sum(acc) * scale;
+                if (i < Lg[g]) {
+                    if (lane == 0) s_sc[(size_t)g * lcap + i] = acc;
+                    m[g] = fmaxf(m[g], acc);
+                }
+            }
+        }
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < ATT_G; g++) s_red[g][warp] = m[g];
+    }
+    __syncthreads();
+    if (warp < ATT_G) {
+        float v = s_red[warp][lane];                // ATT_WARPS == 32 values per token
+        v = warp_max(v);
+        if (lane == 0) s_bcast[warp] = v;
+    }
+    __syncthreads();
+    float l[ATT_G];
+#pragma unroll
+    for (int g = 0; g < ATT_G; g++) {
+        const float mg = s_bcast[g];
+        float a = 0.0f;
+        for (int i = t; i < Lg[g]; i += ATT_THREADS) {
+            const float e = expf(s_sc[(size_t)g * lcap + i] - mg);
+            s_sc[(size_t)g * lcap + i] = e;
+            a += e;
+        }
+        l[g] = warp_sum(a);
+    }
+    __syncthreads();
+    if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < ATT_G; g++) s_red[g][warp] = l[g];
+    }
+    __syncthreads();
+    if (warp < ATT_G) {
+        float v = s_red[warp][lane];
+        v = warp_sum(v);
+        if (lane == 0) s_bcast[warp] = 1.0f / v;
+    }
+    __syncthreads();
+    float inv_l[ATT_G];
+#pragma unroll
+    for (int g = 0; g < ATT_G; g++) inv_l[g] = s_bcast[g];
+
+    const __half* vbase = values + (size_t)kv * (size_t)max_len * ATT_D + lane * 8;
+    float o[ATT_G][8];
+#pragma unroll
+    for (int g = 0; g < ATT_G; g++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) o[g][j] = 0.0f;
+    for (int i0 = warp; i0 < Lmax; i0 += ATT_WARPS * 2) {
+        uint4 vr[2];
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int i = i0 + u * ATT_WARPS;
+            vr[u] = (i < Lmax) ? *reinterpret_cast<const uint4*>(vbase + (size_t)i * ATT_D)
+                               : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int i = i0 + u * ATT_WARPS;
+            float vf[8];
+            unpack8(vr[u], vf);
+#pragma unroll
+            for (int g = 0; g < ATT_G; g++) {
+                const float p = (i < Lg[g]) ? s_sc[(size_t)g * lcap + i] * inv_l[g] : 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) o[g][j] = fmaf(p, vf[j], o[g][j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < ATT_G; g++) {
+        __syncthreads();                            // s_o free (first round: nothing pending)
+#pragma unroll
+        for (int j = 0; j < 8; j++) s_o[warp][lane * 8 + j] = o[g][j];
+        __syncthreads();
+        if (t < ATT_D && Lg[g] > 0) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int w = 0; w < ATT_WARPS; w++) acc += s_o[w][t];
+            const size_t idx = ((size_t)(tok0 + g) * hq + h) * ATT_D + t;
+            const float a = round_f16(acc);
+            const float gt = __half2float(gate[idx]);
+            const float sg = round_f16(1.0f / (1.0f + expf(-gt)));
+            out[idx] = __float2half(a * sg);
+        }
+    }
+}
+
 }  // namespace nvfp4
 
 extern "C" {
@@ -471,17 +613,20 @@ int launch_attn_prefill(const void* q, const void* keys, const void* values, int
     if (len0 < 1 || len0 + n_tokens - 1 > max_len) return -2;
     if (!q || !keys || !values || !gate || !out) return -2;
     if (hq <= 0 || hkv <= 0 || hq % hkv != 0) return -2;
-    const int smem = (len0 + n_tokens - 1) * (int)sizeof(float);
-    if (smem > 40 * 1024 && smem > smem_set) {
-        if (cudaFuncSetAttribute(nvfp4::attn_prefill_kernel,
+    const int lcap = len0 + n_tokens - 1;
+    const int smem = ATT_G * lcap * (int)sizeof(float);
+    if (smem > 150 * 1024) return -2;
+    if (smem > 8 * 1024 && smem > smem_set) {
+        if (cudaFuncSetAttribute(nvfp4::attn_prefill_group_kernel,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return -2;
         smem_set = smem;
     }
     const cudaError_t e = nvfp4::launch_pdl(
-        nvfp4::attn_prefill_kernel, dim3(hq, n_tokens), dim3(ATT_THREADS), (size_t)smem,
-        (cudaStream_t)stream, (const __half*)q, (const __half*)keys, (const __half*)values, len0,
-        (const __half*)gate, (__half*)out, max_len, hq / hkv, scale);
+        nvfp4::attn_prefill_group_kernel, dim3(hq, (n_tokens + ATT_G - 1) / ATT_G),
+        dim3(ATT_THREADS), (size_t)smem, (cudaStream_t)stream, (const __half*)q,
+        (const __half*)keys, (const __half*)values, len0, n_tokens, (const __half*)gate,
+        (__half*)out, max_len, hq / hkv, scale, lcap);
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 

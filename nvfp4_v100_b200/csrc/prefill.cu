@@ -16,7 +16,8 @@
 //       the recurrence S_t = S_{t-1} e^{g_t} + k_t (v_t - S_{t-1} e^{g_t} k_t) beta_t, o_t = S_t q_t
 //       run sequentially over the chunk with every state row in registers (rows are independent:
 //       8 lanes own a row, 16 dims each; 6144 rows of the full model are 768 warps); gated norm.
-// Attention uses attn_prep_tokens_kernel (decode_ops.cu) and attn_prefill_kernel (fused_ops.cu).
+// Attention uses attn_prep_tokens_kernel (decode_ops.cu) and attn_prefill_group_kernel
+// (fused_ops.cu).
 #include <cstdio>
 
 #include "common.cuh"
