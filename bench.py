@@ -527,8 +527,12 @@ def run_gemm(args):
         tf_peak, tf_kind = 1590.0, "fallback"
     hbm_peak, hbm_kind = measured_peak()
     rows = []
-    for tokens in (32, 8192):
-        for M, K in ((6144, HIDDEN), (INTER, HIDDEN), (HIDDEN, HIDDEN), (HIDDEN, INTER)):
+    token_counts = (args.tokens,) if args.tokens else (32, 8192)
+    shapes = ((6144, HIDDEN), (INTER, HIDDEN), (HIDDEN, HIDDEN), (HIDDEN, INTER))
+    if args.only:
+        shapes = (tuple(int(v) for v in args.only.lower().split("x")),)
+    for tokens in token_counts:
+        for M, K in shapes:
             p = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device="cuda")
             s = torch.randint(118, 123, (M * K // 16,), dtype=torch.uint8, device="cuda")
             a = torch.randn(K, tokens, device="cuda").to(torch.float16)
@@ -598,6 +602,8 @@ def run_decode(args, quiet=False):
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = ModelConfig(max_len=1024, vocab=args.vocab)
+    if args.layers:
+        cfg.n_layers = args.layers          # profiling aid: full width, reduced depth
     eng = DecodeEngine(cfg, device=f"cuda:{local}", tp_rank=rank, tp_world=world,
                        allreduce=args.allreduce)
     eng.load_random(seed=0)
@@ -722,6 +728,10 @@ def main():
     ap.add_argument("--decode", action="store_true",
                     help="27B-shape decode tok/s (512-token prompt, 63 tokens) instead of the mix")
     ap.add_argument("--prompt-len", type=int, default=512)
+    ap.add_argument("--layers", type=int, default=0,
+                    help="with --decode: use this many layers (profiling aid; 0 = the full 64)")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="with --gemm: a single token count instead of 32 and 8192")
     ap.add_argument("--gen", type=int, default=63)
     ap.add_argument("--vocab", type=int, default=VOCAB)
     ap.add_argument("--allreduce", default="peer", choices=["fused", "peer", "nccl"],
