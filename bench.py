@@ -538,10 +538,19 @@ def run_gemm(args):
             a = torch.randn(K, tokens, device="cuda").to(torch.float16)
             o = torch.zeros(M, tokens, dtype=torch.float16, device="cuda")
             st = vp(torch.cuda.current_stream().cuda_stream)
+            if args.w4a4:       # activations token-major, quantised per block along K on the fly
+                a_tm = torch.randn(tokens, K, device="cuda").to(torch.float16)
+                work = torch.empty(K * tokens, dtype=torch.float16, device="cuda")
 
             def launch():
-                rc = lib.launch_nvfp4_gemmtc_v5(vp(p.data_ptr()), vp(s.data_ptr()), vp(a.data_ptr()),
-                                                vp(o.data_ptr()), M, tokens, K, st)
+                if args.w4a4:
+                    rc = lib.launch_nvfp4_gemm_w4a4(vp(p.data_ptr()), vp(s.data_ptr()),
+                                                    vp(a_tm.data_ptr()), vp(o.data_ptr()),
+                                                    vp(work.data_ptr()), M, tokens, K, st)
+                else:
+                    rc = lib.launch_nvfp4_gemmtc_v5(vp(p.data_ptr()), vp(s.data_ptr()),
+                                                    vp(a.data_ptr()), vp(o.data_ptr()), M, tokens,
+                                                    K, st)
                 assert rc == 0, rc
 
             for _ in range(3):
@@ -568,7 +577,10 @@ def run_gemm(args):
                   f"({100 * flops / best / 1e6 / tf_peak:4.1f}% of {tf_kind} {tf_peak:.0f}) "
                   f"{nbytes / best / 1e3:7.0f} GB/s", file=sys.stderr, flush=True)
     print(json.dumps({"metric": "nvfp4_gemm_tflops", "unit": "TFLOP/s", "n_gpus": 1, "dtype": "f16",
-                      "kernel": "gemm_w4a16_tcgen05_kernel (W4A16: fp16 activations, fp32 accumulation in TMEM)",
+                      "kernel": ("quant_dequant_T_kernel + gemm_w4a16_tcgen05_kernel (W4A4 values, fp16 "
+                                 "tensor path, fp32 accumulation in TMEM)" if args.w4a4 else
+                                 "gemm_w4a16_tcgen05_kernel (W4A16: fp16 activations, fp32 "
+                                 "accumulation in TMEM)"),
                       "status": lib.nvfp4_gemm_status(0), "shapes": rows}), flush=True)
 
 
@@ -730,6 +742,8 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--layers", type=int, default=0,
                     help="with --decode: use this many layers (profiling aid; 0 = the full 64)")
+    ap.add_argument("--w4a4", action="store_true",
+                    help="with --gemm: quantise the activations to NVFP4 on the fly (W4A4 values)")
     ap.add_argument("--tokens", type=int, default=0,
                     help="with --gemm: a single token count instead of 32 and 8192")
     ap.add_argument("--gen", type=int, default=63)

@@ -264,6 +264,29 @@ int launch_dn_prefill(const void* x, long long ld, const void* conv_w, void* con
 int launch_nvfp4_encode(const void* src_fp16, void* packed, void* scales, int M, int K,
                         void* stream);
 
+/* Dequantiser on the device: out[r][0..K) fp16 = row ids[r] of an NVFP4 table (packed
+ * [table_rows][K/2], scales [table_rows][K/16]); ids a device int64 array, or NULL for rows
+ * 0..n_rows-1.  Bit for bit the reference's CPU decoder (code point x 2^(byte-127) in float64, one
+ * rounding to fp16): codec/nvfp4_codec.py:248-275, pipeline/_qwen38_infer.py:117-128 (the packed
+ * embedding table, which the reference decodes on the host per token).  K % 16 == 0; packed 8-byte,
+ * out 16-byte aligned.  0; -2 bad arguments; -1 launch error. */
+int launch_nvfp4_decode_rows(const void* packed, const void* scales, const void* ids, void* out,
+                             int n_rows, int K, long long table_rows, void* stream);
+
+/* W4A4 (both operands in the reference's block-16 E8M0 format).  launch_nvfp4_quant_dequant_T:
+ * dst[k][t] = dequantise(quantise(src[t][:]))[k], the codec applied per token row along K, written
+ * token-minor (rows ld_dst >= n long, tail zeroed).  launch_nvfp4_gemm_w4a4: that, into `work`
+ * (fp16, K * N elements, N = n_tokens rounded up to 8), then launch_nvfp4_gemmtc_v5: out[M, N] =
+ * dequant(W) . dequant(quant(act))^T with fp32 accumulation.  fp16 holds every FP4 value times its
+ * power-of-two scale exactly, so the result is what a block-scaled FP4 x FP4 tensor-core product
+ * accumulating in fp32 gives; it runs at the fp16 tensor rate, not the FP4 rate.  No counterpart
+ * in the reference, which is W4A16 throughout.  0; -2 bad arguments; else a launch error. */
+int launch_nvfp4_quant_dequant_T(const void* src, long long ld_src, void* dst, long long ld_dst,
+                                 int n, int K, void* stream);
+int launch_nvfp4_gemm_w4a4(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
+                           const void* d_activation, void* d_output, void* work, int M,
+                           int n_tokens, int K, void* stream);
+
 /* The DeltaNet step without a caller-provided workspace.  It has no counterpart in the reference,
  * whose caller always allocates the scratch tensor itself.  It exists for callers that cannot
  * allocate device memory at the point of the call: code that runs after all device memory has

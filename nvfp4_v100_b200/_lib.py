@@ -71,6 +71,9 @@ SIGNATURES = {
     "launch_attn_prefill": ([_vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _f, _vp], _i),
     "nvfp4_dn_prefill_work_bytes": ([_i, _i, _i], _ll),
     "launch_dn_prefill": ([_vp, _ll] + [_vp] * 7 + [_ll, _vp, _i, _i, _i, _f, _vp], _i),
+    "launch_nvfp4_decode_rows": ([_vp, _vp, _vp, _vp, _i, _i, _ll, _vp], _i),
+    "launch_nvfp4_quant_dequant_T": ([_vp, _ll, _vp, _ll, _i, _i, _vp], _i),
+    "launch_nvfp4_gemm_w4a4": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "launch_nvfp4_encode": ([_vp, _vp, _vp, _i, _i, _vp], _i),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),
 }

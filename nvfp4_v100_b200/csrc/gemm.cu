@@ -420,6 +420,9 @@ static cudaError_t launch_tc(const CUtensorMap& map, const uint8_t* packed, cons
 
 extern "C" {
 
+int launch_nvfp4_quant_dequant_T(const void* src, long long ld_src, void* dst, long long ld_dst,
+                                 int n, int K, void* stream);
+
 // out[M, N] (fp16) = dequant(W)[M, K] . act[K, N] (fp16, token-minor).  Returns 0 or the
 // cudaError_t of the launch, as the reference does; -2 for a shape no kernel takes (K % 16 != 0,
 // non-positive sizes, NULL pointers).
@@ -459,6 +462,23 @@ int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weig
                                                      d_output, M, N, K);
     const cudaError_t e = cudaGetLastError();
     return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+// W4A4 product with the reference format on both sides: out[M, N] = dequant(W) .
+// dequant(quant(act))^T, activations token-major [n_tokens][K] fp16, quantised per 16-element
+// block along K by the codec's rule.  work: fp16 scratch of K * N elements, N = n_tokens rounded
+// up to a multiple of 8 = the row length of `out`.  Two launches: launch_nvfp4_quant_dequant_T
+// into work, then the tensor-core GEMM (fp16 operands hold the FP4 values exactly; fp32
+// accumulation).  0, -2 for bad arguments, or a launch error code.
+int launch_nvfp4_gemm_w4a4(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
+                           const void* d_activation, void* d_output, void* work, int M,
+                           int n_tokens, int K, void* stream) {
+    if (!work || n_tokens <= 0) return NVFP4_ERR_SHAPE;
+    const int N = (n_tokens + 7) / 8 * 8;
+    const int rc = launch_nvfp4_quant_dequant_T(d_activation, K, work, N, n_tokens, K, stream);
+    if (rc != 0) return rc;
+    return launch_nvfp4_gemmtc_v5(d_weight_packed, d_weight_scales, (const __half*)work,
+                                  (__half*)d_output, M, N, K, stream);
 }
 
 // 0 if no bounded wait inside the tensor-core GEMM has run out since the library was loaded (or

@@ -190,8 +190,9 @@ class PackedEmb:
 
 class QEmbedding(nn.Module):
     """Token embedding.  ``weight_cpu`` is the host table the reference's callers index
-    (``GraphDecoder.step(tok, model.model.embed_tokens.weight_cpu)``); a dense fp16 table is also
-    copied to the device once, and lookups are gathered there."""
+    (``GraphDecoder.step(tok, model.model.embed_tokens.weight_cpu)``).  The table is also copied to
+    the device once — as fp16, or as its packed and scale bytes when it is a ``PackedEmb`` — and
+    lookups are gathered (and dequantised by ``launch_nvfp4_decode_rows``) there."""
 
     def __init__(self, weight_cpu):
         super().__init__()
@@ -200,16 +201,29 @@ class QEmbedding(nn.Module):
         self._table = None
 
     def device_table(self):
-        if self._table is None and torch.is_tensor(self.weight_cpu):
-            self._table = self.weight_cpu.to(device="cuda", dtype=torch.float16)
+        if self._table is None:
+            w = self.weight_cpu
+            if torch.is_tensor(w):
+                self._table = w.to(device="cuda", dtype=torch.float16)
+            else:                                     # PackedEmb: keep it packed on the device too
+                self._table = (torch.from_numpy(np.ascontiguousarray(w.packed)).cuda(),
+                               torch.from_numpy(np.ascontiguousarray(w.scales)).cuda())
         return self._table
 
     def forward(self, ids):
         table = self.device_table()
-        if table is not None:
-            return table.index_select(0, ids.reshape(-1).to(table.device)).view(*ids.shape, -1)
-        rows = self.weight_cpu[ids.detach().reshape(-1).cpu()]         # packed table: host decode
-        return rows.to("cuda").view(*ids.shape, -1)
+        flat = ids.reshape(-1).to(device="cuda", dtype=torch.int64)
+        if torch.is_tensor(table):
+            return table.index_select(0, flat).view(*ids.shape, -1)
+        packed, scales = table
+        out = torch.empty((flat.numel(), self.embedding_dim), dtype=torch.float16, device="cuda")
+        for lo in range(0, flat.numel(), 32768):
+            part = flat[lo:lo + 32768]
+            _ok(GEMV.launch_nvfp4_decode_rows(_p(packed), _p(scales), _p(part), _p(out[lo:]),
+                                              part.numel(), self.embedding_dim,
+                                              self.num_embeddings, _cur_stream()),
+                "launch_nvfp4_decode_rows")
+        return out.view(*ids.shape, -1)
 
 
 class QLinear(nn.Module):

@@ -126,3 +126,52 @@ def test_container_written_on_the_gpu_equals_the_host_container(lib, tmp_path):
     for name in ("nvfp4_packed.bin", "nvfp4_index.json", "fp16_embed.npy"):
         with open(f"{host_dir}/{name}", "rb") as a, open(f"{gpu_dir}/{name}", "rb") as b:
             assert a.read() == b.read(), name
+
+
+def decode_gpu(lib, p, s, ids=None):
+    d_p, d_s = torch.from_numpy(np.ascontiguousarray(p)).cuda(), torch.from_numpy(np.ascontiguousarray(s)).cuda()
+    n = p.shape[0] if ids is None else len(ids)
+    K = p.shape[1] * 2
+    d_ids = None if ids is None else torch.from_numpy(np.asarray(ids, dtype=np.int64)).cuda()
+    out = torch.full((n * K + 16,), 3.0, dtype=torch.float16, device="cuda")
+    rc = lib.launch_nvfp4_decode_rows(ptr(d_p), ptr(d_s), None if ids is None else ptr(d_ids),
+                                      ptr(out), n, K, p.shape[0], stream())
+    torch.cuda.synchronize()
+    assert rc == 0
+    o = out.cpu().numpy()
+    assert (o[n * K:] == 3.0).all()
+    return o[:n * K].reshape(n, K)
+
+
+def test_decode_rows_bit_exact(lib, golden):
+    # the reference decoder's rows (golden), every packed byte under every scale byte, gathers
+    d = decode_gpu(lib, golden["emb_packed"], golden["emb_scales"], golden["emb_idx"])
+    assert np.array_equal(d.view(np.uint16), golden["emb_rows"].view(np.uint16))
+    for i in range(int(golden["n_mats"])):
+        d = decode_gpu(lib, golden[f"m{i}_packed"], golden[f"m{i}_scales"])
+        assert np.array_equal(d.view(np.uint16), golden[f"m{i}_dec"].view(np.uint16)), i
+    # 256 scale bytes x (256 packed bytes in 32 blocks of 8 bytes): row r uses scale byte r
+    p = np.tile(np.arange(256, dtype=np.uint8), (256, 1))
+    s = np.repeat(np.arange(256, dtype=np.uint8)[:, None], 32, axis=1)
+    got = decode_gpu(lib, p, s)
+    with np.errstate(over="ignore"):
+        want = oc.decode(p, s)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+    assert lib.launch_nvfp4_decode_rows(None, None, None, None, 1, 16, 1, None) == -2
+
+
+def test_packed_embedding_lookup_on_the_device(lib, tmp_path):
+    from nvfp4_v100_b200.pipeline import _qwen38_infer as Q
+
+    w = oc.synthetic_weight(300, 256, seed=8)
+    p, s = oc.encode(w)
+    np.save(tmp_path / "p.npy", p)
+    np.save(tmp_path / "s.npy", s)
+    emb = Q.QEmbedding(Q.PackedEmb(str(tmp_path / "p.npy"), str(tmp_path / "s.npy")))
+    ids = torch.tensor([[5, 299, 0, 5]], device="cuda")
+    got = emb(ids)
+    assert got.shape == (1, 4, 256) and got.dtype == torch.float16
+    want = oc.decode(p, s)[[5, 299, 0, 5]]
+    assert np.array_equal(got[0].cpu().numpy().view(np.uint16), want.view(np.uint16))
+    dense = Q.QEmbedding(torch.from_numpy(oc.decode(p, s)))
+    assert torch.equal(dense(ids), got)

@@ -91,3 +91,42 @@ def test_argument_validation(lib):
     assert lib.launch_nvfp4_gemmtc_v5(one, one, one, one, 0, 8, 64, None) == -2
     assert lib.launch_nvfp4_gemmtc_v5(None, one, one, one, 16, 8, 64, None) == -2
     assert lib.get_kernel_shared_mem_bytes() > 64 * 1024
+
+
+def test_w4a4_activation_quantisation_and_product(lib):
+    # BASELINE configuration 5 semantics: activations quantised per 16-element block along K with
+    # the codec, both operands dequantised, fp32-accumulated product.  Oracle: the codec on the
+    # CPU for both operands, float64 matmul.
+    import ctypes
+
+    rng = np.random.default_rng(5)
+    for M, n, K in ((256, 32, 512), (384, 13, 1024), (128, 70, 5120)):
+        w = oc.synthetic_weight(M, K, seed=M + n)
+        p, s = oc.encode(w)
+        act = rng.standard_normal((n, K)).astype(np.float16)
+        act[0, :16] = 0
+        act[1 % n, 16:32] *= 100
+        ap, asc = oc.encode(act)
+        aq = oc.decode_f64(ap, asc)                                  # [n, K]
+        N = (n + 7) // 8 * 8
+        d_act = torch.from_numpy(act).cuda()
+        work = torch.full((K * N + 8,), 9.0, dtype=torch.float16, device="cuda")
+        rc = lib.launch_nvfp4_quant_dequant_T(ptr(d_act), K, ptr(work), N, n, K, stream())
+        torch.cuda.synchronize()
+        assert rc == 0
+        got = work.cpu().numpy()
+        assert (got[K * N:] == 9.0).all()
+        got = got[:K * N].reshape(K, N)
+        assert np.array_equal(got[:, :n].astype(np.float64), aq.T) and (got[:, n:] == 0).all()
+
+        d_p, d_s = torch.from_numpy(p).cuda(), torch.from_numpy(s).cuda()
+        out = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+        rc = lib.launch_nvfp4_gemm_w4a4(ptr(d_p), ptr(d_s), ptr(d_act), ptr(out), ptr(work), M, n, K,
+                                        stream())
+        torch.cuda.synchronize()
+        assert rc == 0 and lib.nvfp4_gemm_status(0) == 0
+        ref = oc.decode_f64(p, s) @ aq.T                              # [M, n]
+        y = out.cpu().numpy()[:, :n]
+        assert oc.rel_error_floored(y, ref).max() <= 2e-3 * max(1.0, (K / 4096) ** 0.5), (M, n, K)
+    assert lib.launch_nvfp4_gemm_w4a4(ptr(d_p), ptr(d_s), ptr(d_act), ptr(out), None, M, n, K,
+                                      stream()) == -2
