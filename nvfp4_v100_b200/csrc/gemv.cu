@@ -657,6 +657,14 @@ static GemvPlan plan_gemv(int M, int K) {
             }
         }
     }
+    // Measured exception to the equal-shares rule: when the tiles left over after whole rounds
+    // are few (at most a third of the slots), filling every slot and letting a few CTAs run one
+    // extra tile on an otherwise idle machine is faster than shrinking the grid for all rounds
+    // (896 tiles on 444 slots: 14.0 us against 14.9 us).
+    if (best.split == 1 && !g_cfg.force_split) {
+        const int slots = num_sms() * (24 / best.warps);
+        if (ntiles > slots && (ntiles % slots) * 3 <= slots) best.grid = slots;
+    }
     return best;
 }
 
@@ -674,7 +682,12 @@ static cudaError_t launch_mma(const void* packed, const void* scales, const void
     }
     const int ntiles = (M + 15) / 16;
     int grid = plan.grid;
-    if (g_cfg.ctas_per_sm > 0) {
+    if (g_cfg.ctas_per_sm > 64) {          // tuning: an exact grid size
+        grid = g_cfg.ctas_per_sm;
+        if (grid > ntiles * plan.split) grid = ntiles * plan.split;
+        grid -= grid % plan.split;
+        if (grid < plan.split) grid = plan.split;
+    } else if (g_cfg.ctas_per_sm > 0) {
         grid = num_sms() * g_cfg.ctas_per_sm;
         if (grid > ntiles * plan.split) grid = ntiles * plan.split;
         grid -= grid % plan.split;
