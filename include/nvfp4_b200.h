@@ -80,7 +80,7 @@ int get_kernel_shared_mem_bytes(void);                          /* kernels/nvfp4
 int nvfp4_gemm_status(int reset);
 
 /* Tuning hook; no counterpart in the reference.  warps per CTA (0 = auto, 2, 4 or 8), resident
- * CTAs per SM used to size the grid (0 = occupancy calculator), flags: bit 0 routes every GEMV to
+ * CTAs per SM used to size the grid (0 = planner; above 64 = an exact grid size), flags: bit 0 routes every GEMV to
  * the non-tensor-core kernel, bit 1 turns programmatic dependent launch off, bits 4..6 cap and
  * bits 8..10 force the cluster K split (1, 2 or 4 CTAs per row tile; 0 = planner decides).
  * Process-wide, not thread-safe.  Returns 0 or -2. */
