@@ -634,7 +634,7 @@ def run_decode(args, quiet=False):
 
     barrier()
     native_prefill_ms = None
-    if world == 1 and not args.fake_context and len(prompt) > 1:
+    if not args.fake_context and len(prompt) > 1:
         # chunked prefill through the tensor-core GEMM (512-token chunks, the reference's chunk
         # size); one untimed pass first (one-time attribute and tensor-map set-up), then timed
         head = [int(t) for t in prompt[:-1]]
@@ -646,7 +646,7 @@ def run_decode(args, quiet=False):
         p0.record()
         eng.prefill(head)
         p1.record()
-        torch.cuda.synchronize()
+        barrier()
         prefill_s = time.perf_counter() - t0
         native_prefill_ms = p0.elapsed_time(p1)
         eng.tok.fill_(int(prompt[-1]))
@@ -676,9 +676,11 @@ def run_decode(args, quiet=False):
     barrier()
     e2e_s = time.perf_counter() - t0
     if world > 1:
-        tm = torch.tensor([ms, e2e_s, prefill_s], dtype=torch.float64, device="cuda")
+        tm = torch.tensor([ms, e2e_s, prefill_s, native_prefill_ms or 0.0], dtype=torch.float64,
+                          device="cuda")
         dist.all_reduce(tm, op=dist.ReduceOp.MAX)
-        ms, e2e_s, prefill_s = (float(x) for x in tm)
+        ms, e2e_s, prefill_s, npm = (float(x) for x in tm)
+        native_prefill_ms = npm if native_prefill_ms else None
     res = None
     if rank == 0:
         peak, peak_kind = measured_peak()

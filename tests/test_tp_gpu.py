@@ -43,6 +43,8 @@ def _worker(rank, world, port, q):
         eng.capture(n_warmup=1)
         graphed = eng.run(prompt, 16)
         out[mode] = (eager, graphed, eng.comm_status(), eng.n_collective)
+        if mode == "peer":      # chunked prefill on the shards, then the same step graph
+            out["prefill"] = eng.run(prompt, 16, native_prefill=True)
     eager, graphed = out["fused"][:2]
     single = None
     if rank == 0:
@@ -88,7 +90,10 @@ def test_tp_matches_single_gpu_and_oracle(world):
     cos, sin = rope_tables(cfg)
     prompt = np.random.default_rng(1).integers(0, cfg.vocab, 8)
     want, _, margins = do.OracleModel(cfg, do.make_weights(cfg, 1), cos, sin).run(prompt, 16)
-    for name, got in ((f"tp{world}", graph0), (f"tp{world}-nccl", nccl), ("single", single)):
+    for r in res:
+        assert r[4]["prefill"] == out0["prefill"]            # ranks agree
+    for name, got in ((f"tp{world}", graph0), (f"tp{world}-nccl", nccl), ("single", single),
+                      (f"tp{world}-prefill", out0["prefill"])):
         for i in range(16):
             if got[i] != want[i]:
                 assert margins[i] < MARGIN, (name, i, got[i], want[i], margins[i])
