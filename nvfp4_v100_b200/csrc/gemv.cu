@@ -206,9 +206,6 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
             if (sbytes) prefetch_l2_bulk(scales + (size_t)r0 * srow, (uint32_t)sbytes);
         }
     }
-    pdl_wait();
-
-
     // Per-warp work sequence: for each of this CTA's row tiles, nsw K steps (step = warp + k *
     // WARPS; a step past the end of the row loads nothing and contributes zero, so every warp
     // runs the same count and meets the others at each tile's reduction).  The register prefetch
@@ -246,11 +243,14 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         }
     };
 
+    // The first weight loads are issued before waiting for the previous kernel: weights are never
+    // written by a kernel of the step, so only the activation reads have to come after the wait.
     WeightRegs cur;
     if (my_tiles > 0) {
         set_load_tile(0);
-        load_w(0, cur);  // in flight while the activation is prepared
+        load_w(0, cur);  // in flight while the previous kernel drains and the activation is prepared
     }
+    pdl_wait();
 
     if (PRO == PRO_RMSNORM) {
         // Every thread keeps its share of x in registers between the two phases and issues all
