@@ -282,7 +282,11 @@ __device__ __forceinline__ float softplus_f(float x) { return (x > 20.0f) ? x : 
 __global__ void __launch_bounds__(256)
 dn_conv_kernel(const __half* __restrict__ mixed, const __half* __restrict__ conv_w,
                __half* __restrict__ conv_state, float* __restrict__ scratch, int conv_dim) {
-    pdl_prologue();
+    // Wait first, then let the next kernel start: dn_rec_kernel reads the recurrent state before
+    // its own wait, which is safe only once everything before this kernel — possibly a
+    // dn_rec_kernel on the same state, when two tokens are processed back to back — has finished.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= conv_dim) return;
     // state and weights of a channel are 4 consecutive halves: one 8-byte load each
@@ -314,11 +318,19 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
               const __half* __restrict__ dt_bias, const __half* __restrict__ norm_w,
               const float* __restrict__ scratch, float* __restrict__ state,
               __half* __restrict__ out, float rms_eps, int key_dim, int rep) {
-    pdl_prologue();
     __shared__ float s_o[DN_DK];
     __shared__ float s_red[8];
     const int h = blockIdx.x, kh = h / rep;  // value head h reads key head h / rep
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    // The recurrent state was last written by this kernel's own launch of the previous step, so
+    // its 64 KB per head are requested before waiting for the previous kernel in the stream;
+    // everything that kernel produces (conv output, z, b, a) is read after the wait.
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    float* Sbase = state + ((size_t)h * DN_DK + (size_t)warp * 8) * DN_DK + lane * 4;
+    float4 S[8];
+#pragma unroll
+    for (int r = 0; r < 8; r++) S[r] = *reinterpret_cast<const float4*>(Sbase + (size_t)r * DN_DK);
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
     const float beta = round_f16(1.0f / (1.0f + expf(-__half2float(b_in[h]))));
     const float gdec = -expf(__half2float(A_log[h])) *
@@ -336,10 +348,6 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
     kv.x *= inv_k; kv.y *= inv_k; kv.z *= inv_k; kv.w *= inv_k;
 
     // rows j = warp*8 .. warp*8+7 of S_t[h][j][:]
-    float* Sbase = state + ((size_t)h * DN_DK + (size_t)warp * 8) * DN_DK + lane * 4;
-    float4 S[8];
-#pragma unroll
-    for (int r = 0; r < 8; r++) S[r] = *reinterpret_cast<const float4*>(Sbase + (size_t)r * DN_DK);
 #pragma unroll
     for (int r = 0; r < 8; r++) {
         const int j = warp * 8 + r;

@@ -184,7 +184,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
     const size_t prow = (size_t)(K >> 1), srow = (size_t)(K >> 4);
     // Lane (g,t) supplies column g of B with the activation of K chunk t when (g & 3) == t.
     const bool supplies = ((g & 3) == t) && (g < 4 || NACT == 2);
-    const __half* xsrc = (g < 4 || NACT == 1) ? act0 : act1;
+    const __half* xsrc = (g < 4 || NACT == 1) ? act0 : act1;   // re-derived after the wait below
 
     // ---- prologue that does not depend on the previous kernel: L2 prefetch of the first tile ----
     pdl_launch_dependents();
@@ -251,6 +251,10 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         load_w(0, cur);  // in flight while the previous kernel drains and the activation is prepared
     }
     pdl_wait();
+    // The activation loads in the main loop are plain (non-volatile) asm statements, which the
+    // compiler is free to move above the wait; taking their base pointer through an asm statement
+    // that is ordered after the wait pins them behind it.
+    asm volatile("" : "+l"(xsrc));
 
     if (PRO == PRO_RMSNORM) {
         // Every thread keeps its share of x in registers between the two phases and issues all
@@ -330,8 +334,9 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
         }
         __syncthreads();
     }
-    const uint32_t xs_base = (uint32_t)__cvta_generic_to_shared(xs) +
-                             ((PRO == PRO_INTERLEAVED && g >= 4) ? (uint32_t)K * 2u : 0u);
+    uint32_t xs_base = (uint32_t)__cvta_generic_to_shared(xs) +
+                       ((PRO == PRO_INTERLEAVED && g >= 4) ? (uint32_t)K * 2u : 0u);
+    asm volatile("" : "+r"(xs_base));   // same for the shared-memory reads and the barrier above
 
     uint32_t xr[2][8];  // two passes of activation registers (zero where this lane supplies none)
 #pragma unroll
