@@ -161,6 +161,18 @@ int launch_nvfp4_gemv_fused(const void* weight_packed, const void* weight_scales
                             const void* norm_w1, float eps, int epilogue, const void* residual,
                             void* stream);
 
+/* launch_attn_decode_heads with the keys of every head split over eight CTAs (no counterpart in
+ * the reference): each warp requests its key AND value rows at once, partial softmax results are
+ * combined in shared memory, then by the last CTA of a head to finish (in split order, so the
+ * result does not depend on arrival order).  scratch: nvfp4_attn_split_scratch_bytes(hq) bytes,
+ * 16-byte aligned, zeroed once before first use; calls sharing it must not overlap.  Results
+ * match launch_attn_decode_heads to the last fp32 bit before the fp16 rounding.
+ * 0; -2 bad arguments; else the launch error. */
+long long nvfp4_attn_split_scratch_bytes(int hq);
+int launch_attn_decode_split(const void* q, const void* keys, const void* values,
+                             const void* cum_len, const void* gate, void* out, void* scratch,
+                             int max_len, int hq, int hkv, float scale, void* stream);
+
 /* out[hidden] = table[*tok] — table fp16 [vocab, hidden], tok a device int64.  0 / -1. */
 int launch_embed_gather(const void* table, const void* tok, void* out, int hidden, long long vocab,
                         void* stream);

@@ -45,6 +45,8 @@ SIGNATURES = {
     "launch_attn_decode": ([_vp] * 6 + [_i, _f, _vp], _i),
     "launch_attn_decode_heads": ([_vp] * 6 + [_i, _i, _i, _f, _vp], _i),
     "launch_nvfp4_gemv_fused": ([_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _f, _i, _vp, _vp], _i),
+    "nvfp4_attn_split_scratch_bytes": ([_i], _ll),
+    "launch_attn_decode_split": ([_vp] * 7 + [_i, _i, _i, _f, _vp], _i),
     "launch_embed_gather": ([_vp, _vp, _vp, _i, _ll, _vp], _i),
     "launch_attn_prep": ([_vp] * 10 + [_i, _i, _i, _f, _vp], _i),
     "launch_argmax_advance": ([_vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp], _i),

@@ -390,6 +390,139 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
     }
 }
 
+// Decode attention split over the keys (flash-decoding): ATS_SPLIT CTAs per query head, each
+// taking every ATS_SPLIT-th block of ATS_WARPS keys.  A warp requests up to ATS_ROWS key rows AND
+// the matching value rows at once (values do not depend on the scores), so a context of up to
+// ATS_SPLIT * ATS_WARPS * ATS_ROWS = 768 keys costs one memory round trip instead of one per
+// four keys; longer contexts loop.  Each warp keeps a running (max, sum, weighted values); warps
+// combine through shared memory, CTAs through a scratch buffer in global memory, and the CTA
+// that arrives last at the head's counter (in whatever order the CTAs finish, the partials are
+// combined in split order, so the result is deterministic) applies 1/sum, rounds to fp16 and
+// multiplies by sigmoid(gate) as attn_one_query does.  Scores use the same fma chain; the
+// softmax is rescaled per part, so results can differ from attn_one_query in the last fp32 bit
+// before the fp16 rounding.
+#define ATS_SPLIT 8
+#define ATS_WARPS 16
+#define ATS_ROWS 6
+#define ATS_PART (ATT_D + 4)    // floats per partial: 256 weighted values, max, sum, padding
+
+__global__ void __launch_bounds__(ATS_WARPS * 32)
+attn_decode_split_kernel(const __half* __restrict__ q, const __half* __restrict__ keys,
+                         const __half* __restrict__ values, const long long* __restrict__ cum_len,
+                         const __half* __restrict__ gate, __half* __restrict__ out,
+                         float* __restrict__ part, unsigned int* __restrict__ counters,
+                         int max_len, int gqa, float scale) {
+    pdl_prologue();
+    __shared__ float s_part[ATS_WARPS][ATS_PART];
+    __shared__ unsigned int s_last;
+    const int h = blockIdx.x, sp = blockIdx.y, kv = h / gqa;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    long long L64 = *cum_len;
+    if (L64 > max_len) L64 = max_len;
+    if (L64 < 0) L64 = 0;
+    const int L = (int)L64;
+
+    float qf[8];
+    unpack8(*reinterpret_cast<const uint4*>(q + (size_t)h * ATT_D + lane * 8), qf);
+    const __half* kbase = keys + (size_t)kv * (size_t)max_len * ATT_D + lane * 8;
+    const __half* vbase = values + (size_t)kv * (size_t)max_len * ATT_D + lane * 8;
+    float m = -3.4e38f, l = 0.0f;
+    float o[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    // key i belongs to split (i / ATS_WARPS) % ATS_SPLIT and warp i % ATS_WARPS
+    const int stride = ATS_SPLIT * ATS_WARPS;
+    for (int i0 = sp * ATS_WARPS + warp; i0 < L; i0 += stride * ATS_ROWS) {
+        uint4 kr[ATS_ROWS], vr[ATS_ROWS];
+#pragma unroll
+        for (int u = 0; u < ATS_ROWS; u++) {
+            const int i = i0 + u * stride;
+            const bool ok = i < L;
+            kr[u] = ok ? *reinterpret_cast<const uint4*>(kbase + (size_t)i * ATT_D)
+                       : make_uint4(0u, 0u, 0u, 0u);
+            vr[u] = ok ? *reinterpret_cast<const uint4*>(vbase + (size_t)i * ATT_D)
+                       : make_uint4(0u, 0u, 0u, 0u);
+        }
+        float sc[ATS_ROWS];
+        float mb = m;
+#pragma unroll
+        for (int u = 0; u < ATS_ROWS; u++) {
+            float kf[8];
+            unpack8(kr[u], kf);
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc = fmaf(qf[j], kf[j], acc);
+            acc = warp_sum(acc) * scale;
+            sc[u] = (i0 + u * stride < L) ? acc : -3.4e38f;
+            mb = fmaxf(mb, sc[u]);
+        }
+        const float corr = expf(m - mb);          // 0 on the first batch (m = -3.4e38)
+        l *= corr;
+#pragma unroll
+        for (int j = 0; j < 8; j++) o[j] *= corr;
+        m = mb;
+#pragma unroll
+        for (int u = 0; u < ATS_ROWS; u++) {
+            const float p = (i0 + u * stride < L) ? expf(sc[u] - m) : 0.0f;
+            l += p;
+            float vf[8];
+            unpack8(vr[u], vf);
+#pragma unroll
+            for (int j = 0; j < 8; j++) o[j] = fmaf(p, vf[j], o[j]);
+        }
+    }
+    // ---- warps -> CTA partial ----
+#pragma unroll
+    for (int j = 0; j < 8; j++) s_part[warp][lane * 8 + j] = o[j];
+    if (lane == 0) {
+        s_part[warp][ATT_D] = m;
+        s_part[warp][ATT_D + 1] = l;
+    }
+    __syncthreads();
+    float* mine = part + ((size_t)h * ATS_SPLIT + sp) * ATS_PART;
+    if (t < ATT_D) {
+        float M = -3.4e38f;
+#pragma unroll
+        for (int w = 0; w < ATS_WARPS; w++) M = fmaxf(M, s_part[w][ATT_D]);
+        float acc = 0.0f, ls = 0.0f;
+#pragma unroll
+        for (int w = 0; w < ATS_WARPS; w++) {
+            const float f = expf(s_part[w][ATT_D] - M);     // warps without keys: exp(-huge) = 0
+            acc = fmaf(s_part[w][t], f, acc);
+            ls = fmaf(s_part[w][ATT_D + 1], f, ls);
+        }
+        mine[t] = acc;
+        if (t == 0) {
+            mine[ATT_D] = M;
+            mine[ATT_D + 1] = ls;
+        }
+    }
+    // ---- CTAs -> head: the last CTA to arrive combines the parts in split order ----
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        const unsigned int prev = atomicAdd(counters + h, 1u);
+        s_last = (prev == ATS_SPLIT - 1) ? 1u : 0u;
+        if (s_last) counters[h] = 0u;                       // ready for the next launch
+    }
+    __syncthreads();
+    if (!s_last || t >= ATT_D) return;
+    __threadfence();
+    const float* ph = part + (size_t)h * ATS_SPLIT * ATS_PART;
+    float M = -3.4e38f;
+#pragma unroll
+    for (int s = 0; s < ATS_SPLIT; s++) M = fmaxf(M, __ldcg(ph + s * ATS_PART + ATT_D));
+    float acc = 0.0f, ls = 0.0f;
+#pragma unroll
+    for (int s = 0; s < ATS_SPLIT; s++) {
+        const float f = expf(__ldcg(ph + s * ATS_PART + ATT_D) - M);
+        acc = fmaf(__ldcg(ph + s * ATS_PART + t), f, acc);
+        ls = fmaf(__ldcg(ph + s * ATS_PART + ATT_D + 1), f, ls);
+    }
+    const float a = round_f16(acc * (1.0f / ls));
+    const float gt = __half2float(gate[(size_t)h * ATT_D + t]);
+    const float sg = round_f16(1.0f / (1.0f + expf(-gt)));
+    out[(size_t)h * ATT_D + t] = __float2half(a * sg);
+}
+
 // Prefill attention for ATT_G consecutive tokens of one query head per CTA: the tokens share
 // every key and value row they load (token g of the group sees L0 + g rows).  Per token the
 // arithmetic and its order are those of attn_one_query — same key-to-warp assignment, same
@@ -635,6 +768,32 @@ int launch_attn_prefill(const void* q, const void* keys, const void* values, int
         dim3(ATT_THREADS), (size_t)smem, (cudaStream_t)stream, (const __half*)q,
         (const __half*)keys, (const __half*)values, len0, n_tokens, (const __half*)gate,
         (__half*)out, max_len, hq / hkv, scale, lcap);
+    return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+// Bytes of scratch launch_attn_decode_split needs for hq query heads (partials + one counter per
+// head); the counters (the last hq * 4 bytes ... see the launcher) must be zero before first use.
+long long nvfp4_attn_split_scratch_bytes(int hq) {
+    if (hq <= 0) return -1;
+    return (long long)hq * ATS_SPLIT * ATS_PART * 4 + (long long)hq * 4;
+}
+
+// launch_attn_decode_heads with the keys split over eight CTAs per head.  scratch: device buffer
+// of nvfp4_attn_split_scratch_bytes(hq) bytes, 16-byte aligned, zeroed once by the caller (the
+// kernel leaves its counters at zero).  Calls that share a scratch buffer must not overlap.
+// 0; -2 bad arguments; else the launch error.
+int launch_attn_decode_split(const void* q, const void* keys, const void* values,
+                             const void* cum_len, const void* gate, void* out, void* scratch,
+                             int max_len, int hq, int hkv, float scale, void* stream) {
+    if (max_len <= 0 || !q || !keys || !values || !cum_len || !gate || !out || !scratch) return -2;
+    if (hq <= 0 || hkv <= 0 || hq % hkv != 0 || ((uintptr_t)scratch & 15)) return -2;
+    float* part = (float*)scratch;
+    unsigned int* counters = (unsigned int*)(part + (size_t)hq * ATS_SPLIT * ATS_PART);
+    const cudaError_t e = nvfp4::launch_pdl(
+        nvfp4::attn_decode_split_kernel, dim3(hq, ATS_SPLIT), dim3(ATS_WARPS * 32), 0,
+        (cudaStream_t)stream, (const __half*)q, (const __half*)keys, (const __half*)values,
+        (const long long*)cum_len, (const __half*)gate, (__half*)out, part, counters, max_len,
+        hq / hkv, scale);
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 

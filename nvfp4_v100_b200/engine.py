@@ -151,6 +151,7 @@ class DecodeEngine:
         self.q_out = z(self.hq_l * HEAD_DIM)
         self.gate_out = z(self.hq_l * HEAD_DIM)
         self.attn_out = z(self.hq_l * HEAD_DIM)
+        self.attn_scratch = z(int(self.lib.nvfp4_attn_split_scratch_bytes(self.hq_l)), dt=torch.uint8)
         self.dn_in = z(self.conv_l + self.nv_l * DN_DIM + 2 * self.nv_l)
         self.dn_out = z(self.nv_l * DN_DIM)
         self.dn_scratch = z(self.conv_l, dt=f32)
@@ -417,11 +418,11 @@ class DecodeEngine:
                     vp(e["keys"].data_ptr()), vp(e["values"].data_ptr()), self.hq_l, self.hkv_l,
                     c.max_len, float(c.rms_eps), st)
                 assert rc == 0, rc
-                rc = lib.launch_attn_decode_heads(
+                rc = lib.launch_attn_decode_split(
                     vp(self.q_out.data_ptr()), vp(e["keys"].data_ptr()), vp(e["values"].data_ptr()),
                     vp(self.len.data_ptr()), vp(self.gate_out.data_ptr()),
-                    vp(self.attn_out.data_ptr()), c.max_len, self.hq_l, self.hkv_l,
-                    float(HEAD_DIM) ** -0.5, st)
+                    vp(self.attn_out.data_ptr()), vp(self.attn_scratch.data_ptr()), c.max_len,
+                    self.hq_l, self.hkv_l, float(HEAD_DIM) ** -0.5, st)
                 assert rc == 0, rc
                 self.n_launch += 2
                 self._row_parallel(st, L.w_out, self.attn_out)

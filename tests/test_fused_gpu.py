@@ -210,3 +210,34 @@ def test_dn_fused_heads_rejects_bad_counts(lib):
     args = [one] * 12
     assert lib.launch_dn_fused_heads(*args, 0, 3, 1e-6, None) == -1
     assert lib.launch_dn_fused_heads(*args, 4, 6, 1e-6, None) == -1
+
+
+@pytest.mark.parametrize("hq,hkv,max_len", [(4, 2, 3072), (6, 1, 1024)])
+def test_attn_decode_split_matches_single_cta_kernel(lib, hq, hkv, max_len):
+    # keys split over eight CTAs per head, partial softmax results combined: same result as the
+    # one-CTA kernel up to the last fp32 bit before the fp16 rounding; the head counters must be
+    # back at zero after every call
+    rng = np.random.default_rng(hq * 10 + hkv)
+    keys = dev(rng.standard_normal((hkv, max_len, 256)).astype(np.float16))
+    values = dev(rng.standard_normal((hkv, max_len, 256)).astype(np.float16))
+    nbytes = lib.nvfp4_attn_split_scratch_bytes(hq)
+    scratch = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    scale = 256 ** -0.5
+    for L in (1, 2, 15, 16, 17, 127, 128, 129, 575, 769, 1000, max_len):
+        q = dev((rng.standard_normal(hq * 256) * 2).astype(np.float16))
+        gate = dev(rng.standard_normal(hq * 256).astype(np.float16))
+        ln = dev(np.array([L], dtype=np.int64))
+        a = torch.zeros(hq * 256, dtype=torch.float16, device="cuda")
+        b = torch.zeros_like(a)
+        assert lib.launch_attn_decode_heads(ptr(q), ptr(keys), ptr(values), ptr(ln), ptr(gate),
+                                            ptr(a), max_len, hq, hkv, scale, stream()) == 0
+        assert lib.launch_attn_decode_split(ptr(q), ptr(keys), ptr(values), ptr(ln), ptr(gate),
+                                            ptr(b), ptr(scratch), max_len, hq, hkv, scale,
+                                            stream()) == 0
+        torch.cuda.synchronize()
+        steps = ulp_diff_f16(a.cpu().numpy(), b.cpu().numpy())
+        # the fp16-rounded sum can move one step; the product with the rounded gate one more
+        assert steps.max() <= 2 and (steps == 0).mean() > 0.98, (L, steps.max(), (steps == 0).mean())
+        assert int(scratch[-4 * hq:].view(torch.int32).abs().sum()) == 0
+    assert lib.launch_attn_decode_split(ptr(q), ptr(keys), ptr(values), ptr(ln), ptr(gate), ptr(b),
+                                        None, max_len, hq, hkv, scale, stream()) == -2
