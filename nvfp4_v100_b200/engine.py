@@ -32,7 +32,7 @@ CONV_K = 4
 
 @dataclass
 class ModelConfig:
-    """Shapes of the decoder.  Defaults are the reference's 27B model (SURVEY: hidden 5120,
+    """Shapes of the decoder.  Defaults are the reference's 27B model (hidden 5120,
     intermediate 17408, 24 q / 4 kv heads x 256, DeltaNet 16 key / 48 value heads x 128,
     q projection with per-head output gate, every 4th layer full attention)."""
     hidden: int = 5120

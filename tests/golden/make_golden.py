@@ -2,7 +2,7 @@
 
 Run once, in a checkout that has the reference mounted:
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <reference checkout>
 
 The reference tree is only read (its ``codec/`` directory is put on ``sys.path``); nothing is
 copied from it.  The resulting ``.npz`` travels with the repository, so the tests that use it
