@@ -11,7 +11,7 @@ written against the reference runs against this package unchanged:
                 ``refresh_deltanet_state`` ``prefill``
   operators     ``patch_fused_deltanet`` ``patch_attn_decode`` ``patch_rmsnorm`` ``patch_rope``
                 ``patch_mlp_silu_mul``   (the last two: experiments/_qwen38_p9_fuse.py:48-116)
-  step graph    ``GraphDecoder``
+  step graph    ``GraphDecoder`` ``GraphDecoder2``
 
 How it is built here (the reference's behaviour in brackets where it differs):
   * one shared library, bound once through ``nvfp4_v100_b200._lib`` with its signature table
@@ -733,3 +733,63 @@ class GraphDecoder:
     def step_logits(self, tok_id, emb_w):
         self._replay(tok_id, emb_w)
         return int(self.static_next.item()), self.static_logits
+
+
+class GraphDecoder2:
+    """Two tokens per replay, for speculative verification: the graph runs the model on
+    [tokA, tokB] at positions [p, p + 1]; ``static_next[0]`` / ``static_logits[0]`` are the
+    prediction after tokA (which accepts or rejects the draft tokB), index 1 the prediction after
+    tokB (the bonus token when the draft is accepted).  Every QLinear takes the two-activation
+    GEMV, the DeltaNet layers two fused steps (with a state backup for a rejected draft); attention,
+    norms, rotary and the MLP product fall back to the model code for two tokens.
+    ``static_pos`` (device int64 [2] = [p, p + 1]) is shared with a ``GraphDecoder`` and advanced
+    by one per replay; the caller re-aligns it every round.
+    Reference: pipeline/_qwen38_infer.py:732-773."""
+
+    def __init__(self, model, cache, first_pos, hid, static_pos, n_warmup=3):
+        dev = "cuda"
+        self.first_pos = first_pos
+        self.static_pos = static_pos
+        self.static_embeds = torch.zeros(1, 2, hid, dtype=torch.float16, device=dev)
+        self.static_logits = torch.zeros(2, model.lm_head.M, dtype=torch.float16, device=dev)
+        self.static_next = torch.zeros(2, dtype=torch.long, device=dev)
+        self._pins = [torch.empty(hid, dtype=torch.float16, pin_memory=True) for _ in range(2)]
+        self._tables = {}
+
+        def body():
+            both = model(inputs_embeds=self.static_embeds, past_key_values=cache, use_cache=True,
+                         cache_position=self.static_pos).logits[0, -2:, :]
+            self.static_logits.copy_(both)
+            self.static_next.copy_(both.argmax(dim=-1))
+            self.static_pos.add_(1)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.no_grad(), torch.cuda.stream(side):
+            for _ in range(n_warmup):
+                body()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.no_grad(), torch.cuda.graph(self.graph):
+            body()
+
+    def _put(self, slot, tok_id, emb_w):
+        dst = self.static_embeds[0, slot]
+        if torch.is_tensor(emb_w) and emb_w.dtype == torch.float16:
+            key = id(emb_w)
+            if key not in self._tables:
+                self._tables[key] = emb_w.to("cuda")
+            dst.copy_(self._tables[key][tok_id])
+        else:
+            self._pins[slot].copy_(emb_w[tok_id])
+            dst.copy_(self._pins[slot], non_blocking=True)
+
+    def step2(self, tokA, tokB, emb_w):
+        """Replay on (tokA, tokB); returns (argmax int64 [2], logits fp16 [2, V]), both device
+        tensors that the next replay overwrites."""
+        self._put(0, tokA, emb_w)
+        self._put(1, tokB, emb_w)
+        self.graph.replay()
+        return self.static_next, self.static_logits
+

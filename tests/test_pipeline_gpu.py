@@ -123,6 +123,27 @@ def test_patched_graph_stack_matches_eager_stack(lib, tmp_path):
             cur = dec.step(cur, emb_w)
             toks_b.append(cur)
 
+    # ---- two tokens per replay (speculative verify): positions [p, p + 1] from the same state ----
+    restore_all(model, cache, snap, L, Q)
+    for m, (c, s) in zip(mods, vf_snap):
+        m._vf_conv.copy_(c)
+        m._vf_S.copy_(s)
+    pos2 = torch.tensor([L, L + 1], device="cuda")
+    dec2 = Q.GraphDecoder2(model, cache, L, cfg.hidden, pos2, n_warmup=1)
+    restore_all(model, cache, snap, L, Q)
+    for m, (c, s) in zip(mods, vf_snap):
+        m._vf_conv.copy_(c)
+        m._vf_S.copy_(s)
+    pos2.copy_(torch.tensor([L, L + 1]))
+    torch.cuda.synchronize()
+    nxt2, lg2 = dec2.step2(toks_b[0], toks_b[1], emb_w)
+    nxt2 = nxt2.cpu().tolist()
+    # after tokA the model must predict what the one-token decoder predicted (tokB), and after
+    # tokB the decoder's third token, unless the eager margin there is a near-tie
+    for got, want_tok, margin in ((nxt2[0], toks_b[1], margins[0]), (nxt2[1], toks_b[2], margins[1])):
+        assert got == want_tok or margin < MARGIN, (nxt2, toks_b[:3], margins[:2])
+    assert torch.isfinite(lg2.float()).all() and pos2.cpu().tolist() == [L + 1, L + 2]
+
     matched = 0
     for i in range(1, n_gen + 1):
         if toks_a[i] == toks_b[i]:
