@@ -28,7 +28,9 @@ __device__ __forceinline__ uint32_t e2m1_code_of(float a) {
 __global__ void __launch_bounds__(256)
 encode_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed,
               uint8_t* __restrict__ scales, long long nblocks) {
-    pdl_prologue();
+    // Waits for its predecessor but does NOT let its successor start early: what it writes are
+    // weights, and the GEMV requests weights before waiting for the kernel in front of it.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += stride) {
         const uint4 v0 = __ldg(src + 2 * b), v1 = __ldg(src + 2 * b + 1);
