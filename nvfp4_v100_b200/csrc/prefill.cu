@@ -250,6 +250,23 @@ dn_prep_kernel(const __half* __restrict__ conv_out, int conv_dim, const __half* 
 #define SCAN_ROWS (SCAN_WARPS * 4 * SCAN_RPG)
 #define SCAN_TB 16
 
+// packed fp32 pair arithmetic (two IEEE fp32 operations per instruction)
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+          "l"(*reinterpret_cast<unsigned long long*>(&c)));
+    return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;"
+        : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+        : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)));
+    return d;
+}
+
 struct ScanStage {
     float k[SCAN_TB][PF_DK];
     float q[SCAN_TB][PF_DK];
@@ -305,7 +322,7 @@ dn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
         cp_async_commit();
     };
 
-    float S[SCAN_RPG][16];
+    __align__(8) float S[SCAN_RPG][16];
     float* sp = state + ((size_t)h * PF_DK + row0) * PF_DK + sub * 4;
 #pragma unroll
     for (int r = 0; r < SCAN_RPG; r++)
@@ -329,31 +346,34 @@ dn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
         const ScanStage& s = stage[cur];
         const int tcount = min(SCAN_TB, n - blk * SCAN_TB);
         for (int tt = 0; tt < tcount; tt++) {
-            float kc[16], qc[16];
+            // the row's 16 state values, k and q as 8 fp32 pairs: packed fp32x2 multiply-adds
+            // halve the instruction count of the scan, which is issue-bound
+            float2 kc[8], qc[8];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const float4 a = *reinterpret_cast<const float4*>(&s.k[tt][j * 32 + sub * 4]);
                 const float4 c = *reinterpret_cast<const float4*>(&s.q[tt][j * 32 + sub * 4]);
-                kc[4 * j] = a.x; kc[4 * j + 1] = a.y; kc[4 * j + 2] = a.z; kc[4 * j + 3] = a.w;
-                qc[4 * j] = c.x; qc[4 * j + 1] = c.y; qc[4 * j + 2] = c.z; qc[4 * j + 3] = c.w;
+                kc[2 * j] = make_float2(a.x, a.y); kc[2 * j + 1] = make_float2(a.z, a.w);
+                qc[2 * j] = make_float2(c.x, c.y); qc[2 * j + 1] = make_float2(c.z, c.w);
             }
             const float2 bd = s.be[tt];
-            const float beta = bd.x, eg = bd.y;
+            const float beta = bd.x;
+            const float2 eg2 = make_float2(bd.y, bd.y);
             float vr[SCAN_RPG], kvp[SCAN_RPG], od[SCAN_RPG];
 #pragma unroll
             for (int r = 0; r < SCAN_RPG; r++) vr[r] = __half2float(s.v[tt][lrow + r]);
 #pragma unroll
             for (int r = 0; r < SCAN_RPG; r++) {
-                float a[4];
+                float2* S2 = reinterpret_cast<float2*>(S[r]);
+                float2 a[4];
 #pragma unroll
-                for (int j = 0; j < 4; j++) {            // four independent partial sums
-                    S[r][4 * j] *= eg; S[r][4 * j + 1] *= eg; S[r][4 * j + 2] *= eg; S[r][4 * j + 3] *= eg;
-                    a[j] = S[r][4 * j] * kc[4 * j];
-                    a[j] = fmaf(S[r][4 * j + 1], kc[4 * j + 1], a[j]);
-                    a[j] = fmaf(S[r][4 * j + 2], kc[4 * j + 2], a[j]);
-                    a[j] = fmaf(S[r][4 * j + 3], kc[4 * j + 3], a[j]);
+                for (int j = 0; j < 4; j++) {            // four independent partial sums (pairs)
+                    S2[2 * j] = fmul2(S2[2 * j], eg2);
+                    S2[2 * j + 1] = fmul2(S2[2 * j + 1], eg2);
+                    a[j] = fmul2(S2[2 * j], kc[2 * j]);
+                    a[j] = ffma2(S2[2 * j + 1], kc[2 * j + 1], a[j]);
                 }
-                kvp[r] = (a[0] + a[1]) + (a[2] + a[3]);
+                kvp[r] = ((a[0].x + a[0].y) + (a[1].x + a[1].y)) + ((a[2].x + a[2].y) + (a[3].x + a[3].y));
             }
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1)
@@ -361,18 +381,18 @@ dn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
                 for (int r = 0; r < SCAN_RPG; r++) kvp[r] += __shfl_xor_sync(0xffffffffu, kvp[r], o);
 #pragma unroll
             for (int r = 0; r < SCAN_RPG; r++) {
+                float2* S2 = reinterpret_cast<float2*>(S[r]);
                 const float delta = (vr[r] - kvp[r]) * beta;
-                float a[4];
+                const float2 d2 = make_float2(delta, delta);
+                float2 a[4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) {
-#pragma unroll
-                    for (int e = 0; e < 4; e++) S[r][4 * j + e] = fmaf(kc[4 * j + e], delta, S[r][4 * j + e]);
-                    a[j] = S[r][4 * j] * qc[4 * j];
-                    a[j] = fmaf(S[r][4 * j + 1], qc[4 * j + 1], a[j]);
-                    a[j] = fmaf(S[r][4 * j + 2], qc[4 * j + 2], a[j]);
-                    a[j] = fmaf(S[r][4 * j + 3], qc[4 * j + 3], a[j]);
+                    S2[2 * j] = ffma2(kc[2 * j], d2, S2[2 * j]);
+                    S2[2 * j + 1] = ffma2(kc[2 * j + 1], d2, S2[2 * j + 1]);
+                    a[j] = fmul2(S2[2 * j], qc[2 * j]);
+                    a[j] = ffma2(S2[2 * j + 1], qc[2 * j + 1], a[j]);
                 }
-                od[r] = (a[0] + a[1]) + (a[2] + a[3]);
+                od[r] = ((a[0].x + a[0].y) + (a[1].x + a[1].y)) + ((a[2].x + a[2].y) + (a[3].x + a[3].y));
             }
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1)
