@@ -11,8 +11,9 @@ experiments/_bench_gemv_real_shapes.py:67) divided by device time.
 
   value    steps are replayed from a CUDA graph with all inputs resident in HBM.
   e2e      the same step through the C ABI with HOST activations and HOST results: every step
-           copies the 497 activation vectors from pinned host memory to the device, launches the
-           GEMVs and copies the 497 result vectors back; copies are inside the timed region.
+           copies the 497 activation vectors (one arena, one copy) from pinned host memory to the
+           device, replays the captured GEMV launches and copies the 497 result vectors (one
+           arena, one copy) back; copies are inside the timed region.
   roofline the GEMV kernel against the measured HBM copy bandwidth (MEASURED_PEAKS.json).
   cpu_baseline  the CPU oracle (vectorised codec decode + fp32 torch matvec) timed on this host.
 
@@ -245,15 +246,23 @@ def run_ours(args):
     g.manual_seed(1234 + rank)
     layers = []
     total_alg = 0
-    for name, M, K, split in gemvs:
-        m, k = shard(M, K, split, world, rank)
-        if m == 0:
-            continue
+    shapes = [(name, *shard(M, K, split, world, rank), split) for name, M, K, split in gemvs]
+    shapes = [s_ for s_ in shapes if s_[1] > 0]
+    # every activation and every result lives in one device arena each (256-byte aligned slices),
+    # so that the end-to-end pass moves them with ONE copy per direction and step
+    pad = lambda n: (n + 127) // 128 * 128
+    act_arena = torch.zeros(sum(pad(k) for _, _, k, _ in shapes), dtype=torch.float16, device="cuda")
+    out_arena = torch.zeros(sum(pad(m) for _, m, _, _ in shapes), dtype=torch.float16, device="cuda")
+    a_off = o_off = 0
+    for name, m, k, split in shapes:
         packed = torch.randint(0, 256, (m * k // 2,), dtype=torch.uint8, device="cuda", generator=g)
         scales = torch.randint(118, 123, (m * k // 16,), dtype=torch.uint8, device="cuda",
                                generator=g)
-        act = torch.randn(k, dtype=torch.float32, device="cuda", generator=g).to(torch.float16)
-        out = torch.zeros(m, dtype=torch.float16, device="cuda")
+        act = act_arena[a_off:a_off + k]
+        act.copy_(torch.randn(k, dtype=torch.float32, device="cuda", generator=g).to(torch.float16))
+        out = out_arena[o_off:o_off + m]
+        a_off += pad(k)
+        o_off += pad(m)
         layers.append((name, m, k, split, packed, scales, act, out))
         total_alg += gemv_bytes(m, k)
     n_launch = len(layers)
@@ -322,19 +331,22 @@ def run_ours(args):
     ms = ev0.elapsed_time(ev1)
 
     # ---- end to end: host activations in, host results out, every step ----
-    h_act = [torch.empty(l[2], dtype=torch.float16).pin_memory() for l in layers]
-    h_out = [torch.empty(l[1], dtype=torch.float16).pin_memory() for l in layers]
-    for h, l in zip(h_act, layers):
-        h.copy_(l[6])
-    h2d = sum(h.numel() * 2 for h in h_act)
-    d2h = sum(h.numel() * 2 for h in h_out)
+    # One copy of the activation arena from pinned host memory, the captured step (the same C-ABI
+    # launches), one copy of the result arena back (plus the residual vector when K-split layers
+    # are all-reduced into it): what a caller with host buffers does per step.
+    h_act = torch.empty_like(act_arena, device="cpu").pin_memory()
+    h_out = torch.empty_like(out_arena, device="cpu").pin_memory()
+    h_act.copy_(act_arena)
+    h_res = torch.empty(HIDDEN, dtype=torch.float16).pin_memory() if comm is not None else None
+    h2d = sum(l[2] for l in layers) * 2
+    d2h = sum(l[1] for l in layers) * 2
 
     def e2e_step():
-        st = vp(torch.cuda.current_stream().cuda_stream)
-        for (name, m, k, split, packed, scales, act, out), ha, ho in zip(layers, h_act, h_out):
-            act.copy_(ha, non_blocking=True)
-            gemv(name, m, k, split, packed, scales, act, out, st)
-            ho.copy_(resid if (comm is not None and split == "row") else out, non_blocking=True)
+        act_arena.copy_(h_act, non_blocking=True)
+        graph.replay()
+        h_out.copy_(out_arena, non_blocking=True)
+        if h_res is not None:
+            h_res.copy_(resid, non_blocking=True)
 
     e2e_steps = max(1, min(args.steps, 5))
     e2e_step()
