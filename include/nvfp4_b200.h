@@ -86,6 +86,28 @@ int nvfp4_gemm_status(int reset);
  * Process-wide, not thread-safe.  Returns 0 or -2. */
 int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int flags);
 
+/* The batch-1 GEMV streams its weights through a shared-memory ring filled by bulk asynchronous
+ * copies (K % 256 == 0, weight_scales 16-byte aligned; other shapes use the register-streaming
+ * kernel).  Both are no counterpart of anything in the reference.
+ * nvfp4_gemv_status: 0 if no bounded wait inside the ring kernel ever ran out; 1 + wait id
+ * otherwise (0 producer waiting for a free stage, 1 consumer waiting for a stage's bytes, 3 final
+ * drain).  reset != 0 clears it.  Synchronous.
+ * nvfp4_b200_gemv_stream_config: tuning hook.  consumer warps per CTA (0 = 16; 8, 12, 16),
+ * shared-memory budget per CTA in KB (0 = 100, at most 108), target stage size in KB (0 = 24),
+ * minimum ring stages (0 = 3), CTAs per SM that size the grid (0 = 1; 1, 2), late (0 automatic,
+ * 1 / -1 force / forbid the register-saving second-half load), disable != 0 routes every GEMV to
+ * the register-streaming kernel.  Process-wide, not thread-safe.  Returns 0 or -2.
+ *
+ * Contract of every GEMV launcher under programmatic dependent launch (on by default): weights,
+ * scales and norm weights may be read BEFORE the previous kernel in the stream has finished, so
+ * they must not be written by a kernel launched earlier in the same stream without a full
+ * dependency in between (an event, a synchronisation, or a launch with bit 1 of
+ * nvfp4_b200_gemv_config's flags set).  Activations, residuals and outputs are only touched after
+ * the previous kernel has completed. */
+int nvfp4_gemv_status(int reset);
+int nvfp4_b200_gemv_stream_config(int warps, int smem_kb, int stage_kb, int min_stages,
+                                  int ctas_per_sm, int late, int disable);
+
 /* ---------------------------------------------------------------------------------------------
  * Zero-centred RMSNorm: out[r, :] = f16( f32(x[r, :]) * rsqrt(mean(x^2) + eps) * w1 ).
  * x fp16, row r starts at x + r*row_stride (elements); w1 fp32 [n] = 1 + weight; out fp16

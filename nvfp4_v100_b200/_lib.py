@@ -36,6 +36,8 @@ SIGNATURES = {
     "launch_nvfp4_gemv2": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "launch_nvfp4_gemv2i": ([_vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "nvfp4_b200_gemv_config": ([_i, _i, _i], _i),
+    "nvfp4_gemv_status": ([_i], _i),
+    "nvfp4_b200_gemv_stream_config": ([_i, _i, _i, _i, _i, _i, _i], _i),
     "launch_nvfp4_gemmtc_v5": ([_vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "get_kernel_shared_mem_bytes": ([], _i),
     "nvfp4_gemm_status": ([_i], _i),

@@ -22,6 +22,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "gemv_stream.cuh"
 
 namespace nvfp4 {
 
@@ -613,17 +614,30 @@ struct GemvConfig {
     int force_split = 0;   // 0 = planner decides; 1, 2 or 4 = use exactly this K split
 };
 static GemvConfig g_cfg;
-static int g_num_sms = 0;
+constexpr int MAX_DEVICES = 64;
 
+static int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) dev = 0;
+    return dev;
+}
+
+// SM count of the current device (a process may drive several GPUs: cached per device)
 static int num_sms() {
-    if (g_num_sms == 0) {
-        int dev = 0, n = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+    static int cache[MAX_DEVICES] = {0};
+    const int dev = current_device();
+    if (cache[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
             n = 148;
-        g_num_sms = n;
+        cache[dev] = n;
     }
-    return g_num_sms;
+    return cache[dev];
+}
+
+// A caller that sets one of the register-streaming kernel's tuning values wants that kernel.
+static bool old_kernel_tuned() {
+    return g_cfg.warps || g_cfg.ctas_per_sm || g_cfg.max_split || g_cfg.force_split;
 }
 
 // Work partition of one GEMV: CTAs of `warps` warps, clusters of `split` CTAs that share a row
@@ -634,15 +648,19 @@ static int num_sms() {
 // provides enough CTAs.
 struct GemvPlan { int warps, split, grid; };
 
-static GemvPlan plan_gemv(int M, int K) {
+// force_warps (0, 4 or 8) and max_split (0 = the configured cap) override the process-wide tuning
+// values for one call.
+static GemvPlan plan_gemv(int M, int K, int force_warps = 0, int max_split = 0) {
     const int ntiles = (M + 15) / 16, nsteps = (K + 255) / 256;
     GemvPlan best = {4, 1, ntiles};
     double best_score = -1.0;
+    const int want_warps = force_warps ? force_warps : g_cfg.warps;
+    const int split_cap = max_split ? max_split : (g_cfg.max_split ? g_cfg.max_split : 1);
     for (int w = 4; w <= 8; w += 4) {
-        if (g_cfg.warps && g_cfg.warps != w && (g_cfg.warps == 4 || g_cfg.warps == 8)) continue;
+        if (want_warps && want_warps != w && (want_warps == 4 || want_warps == 8)) continue;
         const int slots = num_sms() * (24 / w);
         for (int sp = 1; sp <= 4; sp *= 2) {
-            if (sp > (g_cfg.max_split ? g_cfg.max_split : 1) && !g_cfg.force_split) continue;
+            if (sp > split_cap && !g_cfg.force_split) continue;
             if (g_cfg.force_split && sp != g_cfg.force_split) continue;
             if (sp * w > nsteps && sp > 1 && !g_cfg.force_split) continue;  // nothing left to split
             const long long units = (long long)ntiles * sp;
@@ -678,12 +696,14 @@ static cudaError_t launch_mma(const void* packed, const void* scales, const void
                               void* out, int M, int K, cudaStream_t st, const GemvExtra& ex,
                               const GemvPlan& plan) {
     const int smem = (PRO == PRO_RMSNORM) ? K * 2 : (PRO == PRO_INTERLEAVED) ? K * 4 : 0;
-    static int max_smem_set = 0;
-    if (smem > 48 * 1024 && smem > max_smem_set) {
+    // the opt-in to more than 48 KB of dynamic shared memory applies to the current device only
+    static int max_smem_set[MAX_DEVICES] = {0};
+    const int dev = current_device();
+    if (smem > 48 * 1024 && smem > max_smem_set[dev]) {
         if (cudaFuncSetAttribute(gemv_mma_kernel<WARPS, NACT, PRO, EPI>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return cudaErrorInvalidValue;
-        max_smem_set = smem;
+        max_smem_set[dev] = smem;
     }
     const int ntiles = (M + 15) / 16;
     int grid = plan.grid;
@@ -739,7 +759,12 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
     cudaError_t e;
     const bool fast = !g_cfg.force_generic && (K % 128 == 0) && aligned(packed, 32) &&
                       aligned(scales, 8);
-    if (fast) {
+    StreamPlan sp;
+    if (fast && nact == 1 && !old_kernel_tuned() && aligned(scales, 16) &&
+        plan_stream(M, K, GS_PRO_NONE, GS_EPI_STORE, &sp)) {
+        e = launch_stream(packed, scales, a0, out, M, K, GS_PRO_NONE, nullptr, 0.0f, GS_EPI_STORE,
+                          nullptr, sp, st, !g_cfg.no_pdl);
+    } else if (fast) {
         GemvPlan plan = plan_gemv(M, K);
         if (g_cfg.warps == 2) plan = {2, 1, (M + 15) / 16 < num_sms() * 12 ? (M + 15) / 16 : num_sms() * 12};
         const int warps = plan.warps;
@@ -821,16 +846,21 @@ int gemv_ex_dispatch(const void* packed, const void* scales, const void* act, vo
     ex.eps = eps;
     ex.residual = (const __half*)residual;
     cudaStream_t st = (cudaStream_t)stream;
+    StreamPlan sp;
+    if (!old_kernel_tuned() && aligned(scales, 16) && plan_stream(M, K, prologue, epilogue, &sp)) {
+        const cudaError_t es = launch_stream(packed, scales, act, out, M, K, prologue, norm_w1, eps,
+                                             epilogue, residual, sp, st, !g_cfg.no_pdl);
+        if (es != cudaSuccess) {
+            fprintf(stderr, "launch_nvfp4_gemv_fused (ring): %s\n", cudaGetErrorString(es));
+            return NVFP4_ERR_LAUNCH;
+        }
+        return NVFP4_OK;
+    }
     GemvPlan plan = plan_gemv(M, K);
     if (prologue == PRO_RMSNORM) {
         // the prologue keeps PRO_NV vectors of 8 activations per thread
         if (K > PRO_NV * 8 * 256) return NVFP4_ERR_SHAPE;
-        if (K > PRO_NV * 8 * 128 && plan.warps != 8) {
-            const int save = g_cfg.warps;
-            g_cfg.warps = 8;
-            plan = plan_gemv(M, K);
-            g_cfg.warps = save;
-        }
+        if (K > PRO_NV * 8 * 128 && plan.warps != 8) plan = plan_gemv(M, K, 8);
     }
     const int warps = plan.warps;
     cudaError_t e;
@@ -874,10 +904,7 @@ int gemv_allreduce_dispatch(const void* packed, const void* scales, const void* 
     ex.world = world;
     ex.parity = parity & 1;
     ex.comm_n = n;
-    const int save = g_cfg.max_split;
-    g_cfg.max_split = 1;                         // the finished-CTA count assumes one CTA per tile
-    GemvPlan plan = plan_gemv(M, K);
-    g_cfg.max_split = save;
+    GemvPlan plan = plan_gemv(M, K, 0, 1);       // the finished-CTA count assumes one CTA per tile
     plan.split = 1;
     cudaStream_t st = (cudaStream_t)stream;
     const cudaError_t e =
