@@ -769,7 +769,16 @@ def main():
                     help="with --decode: start at this cache length (zero-filled cache)")
     ap.add_argument("--eager", action="store_true",
                     help="with --per-shape: launch from the host instead of replaying a CUDA graph")
+    ap.add_argument("--stream-config", default="",
+                    help="seven integers for nvfp4_b200_gemv_stream_config (consumer warps, shared "
+                         "memory KB, stage KB, stages per warp, CTAs per SM, row unit, flags: bit 0 = use the "
+                         "ring kernel, bits 4/5 = attribution probes); "
+                         "profiling and attribution aid")
     args = ap.parse_args()
+    if args.stream_config:
+        from nvfp4_v100_b200 import _lib
+        vals = [int(v) for v in args.stream_config.split(",")]
+        assert len(vals) == 7 and _lib.load().nvfp4_b200_gemv_stream_config(*vals) == 0
     if args.warmup < 3:
         args.warmup = 3
     if args.gemm:

@@ -86,17 +86,23 @@ int nvfp4_gemm_status(int reset);
  * Process-wide, not thread-safe.  Returns 0 or -2. */
 int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int flags);
 
-/* The batch-1 GEMV streams its weights through a shared-memory ring filled by bulk asynchronous
- * copies (K % 256 == 0, weight_scales 16-byte aligned; other shapes use the register-streaming
- * kernel).  Both are no counterpart of anything in the reference.
+/* Two kernels serve the batch-1 GEMV.  The default streams the weights through registers
+ * (gemv_mma_kernel).  The second streams them through per-warp shared-memory rings filled by TMA
+ * tensor copies (gemv_stream_kernel; K % 256 == 0, weight_scales 16-byte aligned); it is off by
+ * default because it measured slower on B200 at every 27B layer shape, and is kept for its
+ * attribution probes and as the base of a persistent variant.  Neither function below has a
+ * counterpart in the reference.
  * nvfp4_gemv_status: 0 if no bounded wait inside the ring kernel ever ran out; 1 + wait id
- * otherwise (0 producer waiting for a free stage, 1 consumer waiting for a stage's bytes, 3 final
- * drain).  reset != 0 clears it.  Synchronous.
- * nvfp4_b200_gemv_stream_config: tuning hook.  consumer warps per CTA (0 = 16; 8, 12, 16),
- * shared-memory budget per CTA in KB (0 = 100, at most 108), target stage size in KB (0 = 24),
- * minimum ring stages (0 = 3), CTAs per SM that size the grid (0 = 1; 1, 2), late (0 automatic,
- * 1 / -1 force / forbid the register-saving second-half load), disable != 0 routes every GEMV to
- * the register-streaming kernel.  Process-wide, not thread-safe.  Returns 0 or -2.
+ * otherwise (1 a warp waiting for a stage's bytes, 3 final drain, 4 a tile's partial-sum slot still
+ * in use).  reset != 0 clears it.  Synchronous.
+ * nvfp4_b200_gemv_stream_config: flags bit 0 turns the ring kernel on for the shapes it takes;
+ * bits 4 and 5 are attribution probes that give WRONG results on purpose (bit 4: no arithmetic, a
+ * launch costs what its weight stream costs; bit 5: no weight copies, a launch costs what its
+ * arithmetic costs), the counterpart of the compile-time probes in kernels/nvfp4_gemv.cu:25-33.
+ * warps per CTA (0 = 8; 4, 8, 12), shared-memory budget per CTA in KB (0 = 208 with one CTA per SM,
+ * 98 with two), stage size in KB (0 = 9), most stages per warp (0 = 4; 2..4), CTAs per SM that size
+ * the grid (0 = 1; 1, 2), unit in which rows are dealt to the CTAs (0 = 4; 4, 16).  Process-wide,
+ * not thread-safe.  Returns 0 or -2.
  *
  * Contract of every GEMV launcher under programmatic dependent launch (on by default): weights,
  * scales and norm weights may be read BEFORE the previous kernel in the stream has finished, so
@@ -106,7 +112,7 @@ int nvfp4_b200_gemv_config(int warps, int ctas_per_sm, int flags);
  * the previous kernel has completed. */
 int nvfp4_gemv_status(int reset);
 int nvfp4_b200_gemv_stream_config(int warps, int smem_kb, int stage_kb, int min_stages,
-                                  int ctas_per_sm, int late, int disable);
+                                  int ctas_per_sm, int rows_per_box, int flags);
 
 /* ---------------------------------------------------------------------------------------------
  * Zero-centred RMSNorm: out[r, :] = f16( f32(x[r, :]) * rsqrt(mean(x^2) + eps) * w1 ).

@@ -9,6 +9,10 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+// The public C ABI: every definition of an exported function is compiled against its
+// declaration, so an argument list cannot drift from the header unnoticed.
+#include "nvfp4_b200.h"
+
 #define NVFP4_BLOCK 16
 
 // Return codes shared by every launcher (reference: kernels/nvfp4_gemv.cu:842-850).
@@ -75,6 +79,15 @@ __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
     return v;
+}
+
+// Attributes set with cudaFuncSetAttribute and device properties hold for ONE device; a process
+// may drive several, so the launchers cache such facts per device index.
+constexpr int NVFP4_MAX_DEVICES = 64;
+static inline int current_device_index() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NVFP4_MAX_DEVICES) dev = 0;
+    return dev;
 }
 
 // Programmatic dependent launch.  A kernel that starts with pdl_prologue() may be launched with

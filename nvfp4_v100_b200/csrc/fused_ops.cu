@@ -718,23 +718,24 @@ int launch_silu_mul(const void* g, const void* u, void* out, int n, void* stream
 
 // Heads are the 27B model's: 24 query heads, 4 KV heads, head dim 256.  max_len is the cache's
 // allocated length and may be any value whose fp32 score buffer fits in shared memory
-// (max_len <= 57344); larger values return -2, as the reference does for an unsupported length.
+// (max_len <= 47104); larger values return -2, as the reference does for an unsupported length.
 static int attn_decode_launch(const void* q, const void* keys, const void* values,
                               const void* cum_len, const void* gate, void* out, int max_len,
                               int hq, int hkv, float scale, void* stream) {
-    static bool smem_opt_in = false;
+    static bool smem_opt_in[nvfp4::NVFP4_MAX_DEVICES] = {false};
+    const int dev = nvfp4::current_device_index();
     if (max_len <= 0 || max_len > 47104) return -2;
     if (!q || !keys || !values || !cum_len || !gate || !out) return -2;
     if (hq <= 0 || hkv <= 0 || hq % hkv != 0) return -2;
     const size_t smem = (size_t)max_len * sizeof(float);
-    if (!smem_opt_in) {
-        // one-time opt-in to the large dynamic shared memory carve-out (a host-side attribute,
+    if (!smem_opt_in[dev]) {
+        // one-time (per device) opt-in to the large dynamic shared memory carve-out (a host-side attribute,
         // not a stream operation)
         if (cudaFuncSetAttribute(nvfp4::attn_decode_kernel,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)(47104 * sizeof(float))) != cudaSuccess)
             return -2;
-        smem_opt_in = true;
+        smem_opt_in[dev] = true;
     }
     const cudaError_t e = nvfp4::launch_pdl(
         nvfp4::attn_decode_kernel, dim3(hq), dim3(ATT_THREADS), smem, (cudaStream_t)stream,
@@ -749,7 +750,8 @@ static int attn_decode_launch(const void* q, const void* keys, const void* value
 int launch_attn_prefill(const void* q, const void* keys, const void* values, int len0,
                         int n_tokens, const void* gate, void* out, int max_len, int hq, int hkv,
                         float scale, void* stream) {
-    static int smem_set = 0;
+    static int smem_set[nvfp4::NVFP4_MAX_DEVICES] = {0};
+    const int dev = nvfp4::current_device_index();
     if (max_len <= 0 || max_len > 47104 || n_tokens <= 0 || n_tokens > 65535) return -2;
     if (len0 < 1 || len0 + n_tokens - 1 > max_len) return -2;
     if (!q || !keys || !values || !gate || !out) return -2;
@@ -757,11 +759,11 @@ int launch_attn_prefill(const void* q, const void* keys, const void* values, int
     const int lcap = len0 + n_tokens - 1;
     const int smem = ATT_G * lcap * (int)sizeof(float);
     if (smem > 150 * 1024) return -2;
-    if (smem > 8 * 1024 && smem > smem_set) {
+    if (smem > 8 * 1024 && smem > smem_set[dev]) {
         if (cudaFuncSetAttribute(nvfp4::attn_prefill_group_kernel,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
             return -2;
-        smem_set = smem;
+        smem_set[dev] = smem;
     }
     const cudaError_t e = nvfp4::launch_pdl(
         nvfp4::attn_prefill_group_kernel, dim3(hq, (n_tokens + ATT_G - 1) / ATT_G),
@@ -883,10 +885,10 @@ int launch_dn_fused_heads(const void* mixed, const void* z_in, const void* b_in,
 // The function calls no cudaMalloc, cudaFree or any other allocating routine.
 // ---------------------------------------------------------------------------------------------
 #define NVFP4_DN_NOALLOC_MAX_CHANNELS 10240
-#define NVFP4_MAX_DEVICES 64
+#define NVFP4_DN_NOALLOC_MAX_DEVICES 64
 
 static __device__ __align__(256) float g_dn_noalloc_scratch[NVFP4_DN_NOALLOC_MAX_CHANNELS];
-static float* g_dn_noalloc_addr[NVFP4_MAX_DEVICES] = {};
+static float* g_dn_noalloc_addr[NVFP4_DN_NOALLOC_MAX_DEVICES] = {};
 
 int launch_dn_fused_noalloc(const void* mixed, const void* z_in, const void* b_in,
                             const void* a_in, const void* conv_w, void* conv_state,
@@ -903,7 +905,7 @@ int launch_dn_fused_noalloc(const void* mixed, const void* z_in, const void* b_i
         return -2;
     }
     int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NVFP4_MAX_DEVICES) {
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NVFP4_DN_NOALLOC_MAX_DEVICES) {
         fprintf(stderr, "launch_dn_fused_noalloc: no usable current device\n");
         return -1;
     }

@@ -33,6 +33,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tmap.cuh"
 
 namespace nvfp4 {
 
@@ -280,35 +281,17 @@ gemm_w4a16_fallback_kernel(const uint8_t* __restrict__ packed, const uint8_t* __
     out[(size_t)m * N + n] = __float2half(acc);
 }
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
-                cudaSuccess && qres == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    }
-    return fn;
-}
-
 template <int BN>
 static cudaError_t launch_tc(const CUtensorMap& map, const uint8_t* packed, const uint8_t* scales,
                              __half* out, int M, int N, int K, cudaStream_t st) {
     constexpr int SMEM = GEMM_STAGES * (GEMM_BM * 128 + (BN / 64) * GEMM_BK * 128) + 1024;
-    static bool attr = false;
-    if (!attr) {
+    static bool attr[NVFP4_MAX_DEVICES] = {false};   // the attribute is per device
+    const int dev = current_device_index();
+    if (!attr[dev]) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<BN>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
-        attr = true;
+        attr[dev] = true;
     }
     dim3 grid((unsigned)((M + GEMM_BM - 1) / GEMM_BM), (unsigned)((N + BN - 1) / BN));
     gemm_w4a16_tcgen05_kernel<BN><<<grid, GEMM_THREADS, SMEM, st>>>(map, packed, scales, out, M, N, K);
@@ -319,16 +302,16 @@ static cudaError_t launch_tc(const CUtensorMap& map, const uint8_t* packed, cons
 
 extern "C" {
 
-int launch_nvfp4_quant_dequant_T(const void* src, long long ld_src, void* dst, long long ld_dst,
-                                 int n, int K, void* stream);
-
 // out[M, N] (fp16) = dequant(W)[M, K] . act[K, N] (fp16, token-minor).  Returns 0 or the
 // cudaError_t of the launch, as the reference does; -2 for a shape no kernel takes (K % 16 != 0,
 // non-positive sizes, NULL pointers).
 int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
-                           const __half* d_activation, __half* d_output, int M, int N, int K,
+                           const void* d_activation_v, void* d_output_v, int M, int N, int K,
                            void* stream) {
     using namespace nvfp4;
+    // the header is plain C: fp16 pointers travel as void* (the reference declares __half*)
+    const __half* d_activation = static_cast<const __half*>(d_activation_v);
+    __half* d_output = static_cast<__half*>(d_output_v);
     if (M <= 0 || N <= 0 || K <= 0 || K % 16 != 0) return NVFP4_ERR_SHAPE;
     if (!d_weight_packed || !d_weight_scales || !d_activation || !d_output) return NVFP4_ERR_SHAPE;
     cudaStream_t st = (cudaStream_t)stream;
@@ -376,8 +359,8 @@ int launch_nvfp4_gemm_w4a4(const uint8_t* d_weight_packed, const uint8_t* d_weig
     const int N = (n_tokens + 7) / 8 * 8;
     const int rc = launch_nvfp4_quant_dequant_T(d_activation, K, work, N, n_tokens, K, stream);
     if (rc != 0) return rc;
-    return launch_nvfp4_gemmtc_v5(d_weight_packed, d_weight_scales, (const __half*)work,
-                                  (__half*)d_output, M, N, K, stream);
+    return launch_nvfp4_gemmtc_v5(d_weight_packed, d_weight_scales, work, d_output, M, N, K,
+                                  stream);
 }
 
 // 0 if no bounded wait inside the tensor-core GEMM has run out since the library was loaded (or

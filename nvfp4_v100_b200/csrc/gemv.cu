@@ -614,13 +614,8 @@ struct GemvConfig {
     int force_split = 0;   // 0 = planner decides; 1, 2 or 4 = use exactly this K split
 };
 static GemvConfig g_cfg;
-constexpr int MAX_DEVICES = 64;
-
-static int current_device() {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) dev = 0;
-    return dev;
-}
+constexpr int MAX_DEVICES = NVFP4_MAX_DEVICES;
+static int current_device() { return current_device_index(); }
 
 // SM count of the current device (a process may drive several GPUs: cached per device)
 static int num_sms() {

@@ -12,8 +12,6 @@ enum { GS_PRO_NONE = 0, GS_PRO_RMSNORM = 1 };
 enum { GS_EPI_STORE = 0, GS_EPI_RESIDUAL = 1, GS_EPI_SILU_MUL = 2 };
 
 struct StreamArgs {
-    const uint8_t* packed;
-    const uint8_t* scales;
     const __half* act;
     __half* out;
     const float* norm_w1;     // GS_PRO_RMSNORM: fp32 (1 + weight) [K]
@@ -23,21 +21,24 @@ struct StreamArgs {
     int KC;            // weights per ring stage and row (multiple of 256)
     int nst;           // ring stages
     int stage_bytes;   // 9 * KC
-    int gran;          // rows are dealt to the CTAs in units of this many
+    int rb;            // unit in which rows are dealt to the CTAs (4 or 16)
+    int ring_off;      // byte offset of the ring in dynamic shared memory
+    int probe;         // attribution probes (bit 0: no arithmetic, bit 1: no weight copies)
 };
 
 struct StreamPlan {
-    int warps, KC, nst, stage_bytes, gran, grid, smem, late;
+    int warps, KC, nst, stage_bytes, rb, grid, ring_off, smem;
 };
 
 struct StreamConfig {
-    int warps = 0, smem_kb = 0, stage_kb = 0, min_stages = 0, ctas_per_sm = 0, late = 0, disable = 0;
+    int warps = 0, smem_kb = 0, stage_kb = 0, min_stages = 0, ctas_per_sm = 0, rows_per_box = 0,
+        enable = 0, probe = 0;
 };
 
 StreamConfig& stream_config();
 
 // false when the ring kernel does not take the shape (K % 256 != 0, a prologue it cannot hold,
-// too little shared memory for two stages) or is switched off.
+// too little shared memory for two stages per warp) or is not switched on.
 bool plan_stream(int M, int K, int prologue, int epilogue, StreamPlan* out);
 
 // Requirements beyond plan_stream: packed and scales 16-byte aligned, act 16-byte aligned.

@@ -26,6 +26,35 @@ def test_binding_table_matches_header():
     assert sorted(_lib.SIGNATURES) == declared_functions()
 
 
+def declared_argument_counts():
+    """name -> number of parameters, parsed from the header's declarations."""
+    src = open(os.path.join(ROOT, "include", "nvfp4_b200.h")).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    out = {}
+    for name, args in re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\(([^;{]*)\)\s*;", src):
+        args = " ".join(args.split())
+        out[name] = 0 if args in ("", "void") else args.count(",") + 1
+    return out
+
+
+def test_binding_argument_counts_match_header():
+    # every .cu file is compiled against the header, so header == definitions; this closes the
+    # remaining gap between the header and the ctypes table
+    from nvfp4_v100_b200 import _lib
+
+    counts = declared_argument_counts()
+    for name, (argtypes, _res) in _lib.SIGNATURES.items():
+        assert counts[name] == len(argtypes), (name, counts[name], len(argtypes))
+
+
+def test_every_kernel_source_is_compiled_against_the_header():
+    csrc = os.path.join(ROOT, "nvfp4_v100_b200", "csrc")
+    assert '#include "nvfp4_b200.h"' in open(os.path.join(csrc, "common.cuh")).read()
+    for f in os.listdir(csrc):
+        if f.endswith(".cu"):
+            assert '#include "common.cuh"' in open(os.path.join(csrc, f)).read(), f
+
+
 def test_dll_aliases_resolve(lib):
     from nvfp4_v100_b200 import _lib, build
 

@@ -1,4 +1,4 @@
-"""The ring-streaming GEMV kernel (bulk asynchronous copies into a shared-memory ring) against the
+"""The ring-streaming GEMV kernel (TMA tensor copies into a shared-memory ring) against the
 CPU oracle and against the register-streaming kernel, through the C ABI.
 
 Tolerance as in test_gemv_gpu.py: max |y - ref| / max(|ref|, 1e-3 max|ref|) <= 1e-3 against the
@@ -20,16 +20,17 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-3
 
 
-def stream_cfg(lib, warps=0, smem_kb=0, stage_kb=0, min_stages=0, ctas=0, late=0, disable=0):
-    assert lib.nvfp4_b200_gemv_stream_config(warps, smem_kb, stage_kb, min_stages, ctas, late,
-                                             disable) == 0
+def stream_cfg(lib, warps=0, smem_kb=0, stage_kb=0, min_stages=0, ctas=0, rb=0, on=1):
+    """Switch the ring kernel on (it is off by default) with the given tuning values."""
+    assert lib.nvfp4_b200_gemv_stream_config(warps, smem_kb, stage_kb, min_stages, ctas, rb, on) == 0
 
 
 @pytest.fixture(autouse=True)
 def _reset(lib):
     lib.nvfp4_gemv_status(1)
-    yield
     stream_cfg(lib)
+    yield
+    stream_cfg(lib, on=0)
     assert lib.nvfp4_gemv_status(0) == 0, "a bounded wait inside the ring GEMV ran out"
 
 
@@ -55,20 +56,20 @@ def test_ring_kernel_against_oracle(lib, M, K):
     rc, y = gemv(lib, p, s, a)
     assert rc == 0
     check(y, p, s, a)
-    stream_cfg(lib, disable=1)                       # the register-streaming kernel
+    stream_cfg(lib, on=0)                            # the register-streaming kernel
     rc, y_old = gemv(lib, p, s, a)
     assert rc == 0
     assert oc.rel_error_floored(y, y_old.astype(np.float64)).max() <= TOL
 
 
 @pytest.mark.parametrize("cfg", [
-    dict(warps=8), dict(warps=12), dict(warps=16, late=-1), dict(warps=16, late=1),
-    dict(warps=8, late=1), dict(smem_kb=48), dict(smem_kb=108, stage_kb=48, min_stages=2),
-    dict(stage_kb=4), dict(stage_kb=9, min_stages=8), dict(ctas=2), dict(warps=12, smem_kb=64, stage_kb=12),
+    dict(warps=4), dict(warps=8), dict(warps=12), dict(rb=16), dict(warps=12, rb=16, stage_kb=5),
+    dict(smem_kb=100, warps=4), dict(stage_kb=18, warps=4), dict(stage_kb=5), dict(stage_kb=5, min_stages=2),
+    dict(stage_kb=14, warps=4, min_stages=3), dict(ctas=2, warps=4), dict(min_stages=2),
 ])
 def test_ring_kernel_configurations(lib, cfg):
-    # whole-row stages (one copy per array), row-segment stages (one copy per row), ragged last
-    # chunks, two to eight stages, every consumer-warp count
+    # one to 24 K chunks per row tile, ragged last chunks (zero-filled by the tensor map), ragged
+    # last row tiles (boxes of four rows), two to four stages per warp, every warp count
     for M, K in ((200, 1024), (531, 5120), (70, 17408), (3000, 6144)):
         w = oc.synthetic_weight(M, K, seed=M + K)
         p, s = oc.encode(w)
@@ -124,9 +125,9 @@ def fused(lib, p, s, x, M, K, pro_w1=None, epi=0, residual=None, out_rows=None):
     return rc, o[:n]
 
 
-@pytest.mark.parametrize("warps", [8, 12, 16])
+@pytest.mark.parametrize("warps,stage_kb", [(4, 0), (8, 0), (12, 5)])
 @pytest.mark.parametrize("M,K", [(772, 256), (5120, 5120), (1000, 512), (40, 6144)])
-def test_ring_fused_rmsnorm_and_residual(lib, M, K, warps):
+def test_ring_fused_rmsnorm_and_residual(lib, M, K, warps, stage_kb):
     w = oc.synthetic_weight(M, K, seed=M + K)
     p, s = oc.encode(w)
     x = oc.synthetic_act(K, seed=3)
@@ -135,14 +136,14 @@ def test_ring_fused_rmsnorm_and_residual(lib, M, K, warps):
     xn = fo.rmsnorm(x[None], w1, 1e-6)[0]
     y = oc.gemv_f64(p, s, xn).astype(np.float16)
     want = (res.astype(np.float64) + y.astype(np.float64)).astype(np.float16)
-    stream_cfg(lib, warps=warps)
+    stream_cfg(lib, warps=warps, stage_kb=stage_kb)
     rc, got = fused(lib, p, s, x, M, K, pro_w1=w1, epi=1, residual=res)
     assert rc == 0
     err = np.abs(got.astype(np.float64) - want.astype(np.float64))
     assert err.max() <= 2e-3 * max(1.0, np.abs(want.astype(np.float64)).max())
     assert (ulp_diff_f16(got, want) <= 1).mean() > 0.98
     # same call on the register-streaming kernel
-    stream_cfg(lib, disable=1)
+    stream_cfg(lib, on=0)
     rc, old = fused(lib, p, s, x, M, K, pro_w1=w1, epi=1, residual=res)
     assert rc == 0
     assert (ulp_diff_f16(got, old) <= 1).mean() > 0.98
