@@ -15,7 +15,9 @@ experiments/_bench_gemv_real_shapes.py:67) divided by device time.
            device, replays the captured GEMV launches and copies the 497 result vectors (one
            arena, one copy) back; copies are inside the timed region.
   roofline the GEMV kernel against the measured HBM copy bandwidth (MEASURED_PEAKS.json).
-  cpu_baseline  the CPU oracle (vectorised codec decode + fp32 torch matvec) timed on this host.
+  cpu_baseline  the reference's CPU path (codec decode + fp32 torch matvec) timed on this host.
+  decode   the other half of the metric, in the same line: the 27B-shape decoder (64 layers, 512
+           prompt tokens through the chunked prefill, 63 greedy tokens from the step graph).
 
 Every step streams 14.4 GB, far more than the 126 MB L2, so each weight byte is a cold HBM read.
 Synthetic data: random E2M1 bytes, scale bytes uniform in [118, 122] (the range N(0, 0.02^2)
@@ -153,91 +155,277 @@ def measured_peak():
 
 
 # ------------------------------------------------------------------------------------------------
-def cpu_gemv_gbps(shapes, threads, repeats=1):
-    """The CPU oracle (vectorised codec decode + fp32 torch matvec) on a list of shapes.
-    Returns (GB/s of algorithmic bytes, seconds spent, description)."""
+def common_config(world):
+    """The workload description both arms print (identical dictionaries)."""
+    return {"workload": "gemv_497_mix_27b", "gemvs_per_step": 497,
+            "algorithmic_bytes_per_step": sum(gemv_bytes(M, K) for _, M, K, _ in step_gemvs()),
+            "l2": "each step streams 14.4 GB of weights (>> 126 MB L2): reads are cold",
+            "parallelism": f"tp{world}"}
+
+
+def load_reference_codec():
+    """The reference's own CPU codec, byte-compiled into oracle/_ref/ by oracle/Makefile (the
+    reference checkout itself is not present where the benchmark runs).  None if absent."""
+    import importlib.machinery
+    import importlib.util
+
+    path = os.path.join(ROOT, "oracle", "_ref", "nvfp4_codec.bytecode")
+    if not os.path.exists(path):
+        return None
+    try:
+        loader = importlib.machinery.SourcelessFileLoader("nvfp4_codec_reference", path)
+        spec = importlib.util.spec_from_loader("nvfp4_codec_reference", loader)
+        mod = importlib.util.module_from_spec(spec)
+        loader.exec_module(mod)
+        return mod
+    except Exception:
+        return None
+
+
+def synthetic_layer(M, K, seed=0):
+    rng = np.random.default_rng(seed + M + K)
+    packed = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
+    scales = rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8)
+    act = rng.standard_normal(K).astype(np.float16)
+    return packed, scales, act
+
+
+def cpu_gemv(decode_fn, packed, scales, act):
+    """One GEMV on the CPU as the reference does it: decode to fp16, fp32 matvec, fp16 result.
+    Returns (seconds for the decode, seconds for the matvec)."""
+    import torch
+
+    t0 = time.perf_counter()
+    w = decode_fn(packed, scales)
+    t1 = time.perf_counter()
+    y = torch.from_numpy(w.astype(np.float32)) @ torch.from_numpy(act.astype(np.float32))
+    _ = y.to(torch.float16)
+    t2 = time.perf_counter()
+    return t1 - t0, t2 - t1
+
+
+# (M, K, launches per decode step): the reference's shape table
+CPU_SHAPES = [(5120, 5120, 0), (1024, 5120, 32), (5120, 6144, 64), (6144, 5120, 48),
+              (10240, 5120, 48), (12288, 5120, 16), (17408, 5120, 128), (5120, 17408, 64),
+              (48, 5120, 96), (VOCAB, 5120, 1)]
+
+
+def cpu_protocol(threads, full):
+    """The CPU baseline, laid out as the reference's own measurements are: the loop decoder
+    (codec/nvfp4_codec.py decode_nvfp4_to_fp16, the reference's own code when its byte-compiled
+    copy is present) once at 5120x5120; the vectorised decoder (the table look-up + exp2 recipe of
+    pipeline/_qwen38_infer.py:117-128, restated by the oracle) and the fp32 matvec separately for
+    every layer shape; their sum over the 497-GEMV mix as a lower bound on a CPU decode step
+    (norms, attention and the recurrence excluded).  full: best of 5 and the lm_head at full
+    size, in row chunks (about a minute); otherwise best of 2 and a 16384-row sample of the
+    lm_head, scaled (about 20 s)."""
     import torch
 
     from oracle import nvfp4_codec_oracle as oc
 
     torch.set_num_threads(threads)
-    rng = np.random.default_rng(0)
-    total_bytes, total_t = 0, 0.0
-    for M, K in shapes:
-        packed = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
-        scales = rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8)
-        act = rng.standard_normal(K).astype(np.float16)
-        for _ in range(repeats):
-            t0 = time.perf_counter()
-            w = oc.decode(packed, scales)                      # codec dequant -> fp16
-            y = torch.from_numpy(w.astype(np.float32)) @ torch.from_numpy(act.astype(np.float32))
-            _ = y.to(torch.float16)
-            total_t += time.perf_counter() - t0
-            total_bytes += gemv_bytes(M, K)
-    return total_bytes / total_t / 1e9, total_t
+    ref = load_reference_codec()
+    out = {"cores": threads, "os_cpu_count": os.cpu_count(), "rows": []}
+    p, s, a = synthetic_layer(5120, 5120)
+    if ref is not None:
+        d, m = cpu_gemv(ref.decode_nvfp4_to_fp16, p, s, a)
+        out["loop_decode_5120x5120"] = {"decode_s": d, "matvec_s": m, "kind": "reference",
+                                        "gbps": gemv_bytes(5120, 5120) / (d + m) / 1e9}
+    reps = 5 if full else 2
+    mix_s = 0.0
+    for M, K, cnt in CPU_SHAPES:
+        rows = M
+        if M == VOCAB and not full:
+            rows = 16384
+        # at most 16384 rows at a time: the decoder's float64 intermediate stays below 1 GB
+        chunk = 16384
+        best_d = best_m = 0.0
+        for r0 in range(0, rows, chunk):
+            p, s, a = synthetic_layer(min(chunk, rows - r0), K, seed=r0)
+            bd = bm = None
+            for _ in range(1 if rows > chunk else reps):
+                d, m = cpu_gemv(oc.decode, p, s, a)
+                bd = d if bd is None else min(bd, d)
+                bm = m if bm is None else min(bm, m)
+            best_d += bd
+            best_m += bm
+        scale = M / rows
+        row = {"shape": f"{M}x{K}", "decode_s": best_d * scale, "matvec_s": best_m * scale,
+               "sampled_rows": rows, "count_per_step": cnt,
+               "gbps": gemv_bytes(M, K) / ((best_d + best_m) * scale) / 1e9}
+        out["rows"].append(row)
+        mix_s += cnt * (best_d + best_m) * scale
+        del p, s, a
+    out["mix_497_lower_bound_s"] = mix_s
+    out["mix_497_gbps"] = common_config(1)["algorithmic_bytes_per_step"] / mix_s / 1e9
+    return out
 
 
-CPU_SAMPLE = [(5120, 5120), (1024, 5120), (5120, 6144), (6144, 5120), (17408, 5120), (5120, 17408)]
-CPU_SAMPLE_DESC = ("one GEMV each of 5120x5120, 1024x5120, 5120x6144, 6144x5120, 17408x5120, "
-                   "5120x17408 (codec decode to fp16 + fp32 torch matvec)")
-
-
-# one step of the reference arm: a bounded sample (~4 s of CPU work)
-REF_STEP_SAMPLE = CPU_SAMPLE[:3]
-REF_STEP_DESC = ("one GEMV each of 5120x5120, 1024x5120, 5120x6144 "
-                 "(codec decode to fp16 + fp32 torch matvec)")
+# one timed step of the reference arm: a bounded sample of the mix
+REF_STEP_SHAPE = (1024, 5120)
+REF_STEP_DESC_REFERENCE = ("one k/v_proj GEMV (1024x5120): the reference's decode_nvfp4_to_fp16 "
+                           "(its own byte-compiled codec) + fp32 torch matvec")
+REF_STEP_DESC_PORT = ("one GEMV each of 5120x5120, 1024x5120, 5120x6144 (vectorised codec decode "
+                      "restated by the oracle + fp32 torch matvec)")
 
 
 def run_reference(args):
-    """--impl reference: the reference's CPU path for this metric (codec dequant + torch CPU
-    matmul), restated by the oracle, on all host threads.  Rank 0 only."""
+    """--impl reference: the reference's CPU path for this metric (codec decode + torch CPU
+    matvec) on the host cores, all threads torch will use.  Rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     import torch
 
+    from oracle import nvfp4_codec_oracle as oc
+
     cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    ref = load_reference_codec()
+    if ref is not None:
+        shapes, decode_fn, kind, desc = [REF_STEP_SHAPE], ref.decode_nvfp4_to_fp16, "reference", \
+            REF_STEP_DESC_REFERENCE
+    else:
+        shapes, decode_fn, kind, desc = [(5120, 5120), (1024, 5120), (5120, 6144)], oc.decode, \
+            "port", REF_STEP_DESC_PORT
+    data = [synthetic_layer(M, K) for M, K in shapes]
+    step_bytes = sum(gemv_bytes(M, K) for M, K in shapes)
+
+    def step():
+        for p, s, a in data:
+            cpu_gemv(decode_fn, p, s, a)
+
     for _ in range(args.warmup):
-        cpu_gemv_gbps(CPU_SAMPLE[:2], cores)
+        step()
     t0 = time.perf_counter()
-    vals = []
     for _ in range(args.steps):
-        g, _t = cpu_gemv_gbps(REF_STEP_SAMPLE, cores)
-        vals.append(g)
+        step()
     dt = time.perf_counter() - t0
-    v = sum(vals) / len(vals)
+    v = step_bytes * args.steps / dt / 1e9
+    protocol = None
+    if args.cpu_protocol != "none":
+        protocol = cpu_protocol(torch.get_num_threads(), full=(args.cpu_protocol == "full"))
     line = {
         "impl": "reference", "metric": "nvfp4_gemv_hbm_gbps", "value": v, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "gemv_497_mix_27b", "sample": REF_STEP_DESC},
+        "config": common_config(args.gpus),
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": REF_STEP_DESC},
+                         "kind": kind, "sample": desc},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "cpu_protocol": protocol,
     }
     print(json.dumps(line), flush=True)
 
 
+def shutdown(world):
+    """Leave a multi-rank run: every object that referenced a captured graph or a peer mapping
+    has been released by the caller; synchronise, then tear the process group down.  The
+    teardown runs with a time limit: if it does not come back (seen once while a captured graph
+    still held library collectives), the process leaves without it rather than hang the job."""
+    import gc
+
+    import torch
+    import torch.distributed as dist
+
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if world <= 1:
+        return
+    gc.collect()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    done = threading.Event()
+
+    def destroy():
+        try:
+            dist.destroy_process_group()
+        finally:
+            done.set()
+
+    th = threading.Thread(target=destroy, daemon=True)
+    th.start()
+    if not done.wait(timeout=30):
+        os._exit(0)
+
+
 # ------------------------------------------------------------------------------------------------
+def init_ranks():
+    """(world, rank, local rank); under torchrun also the NCCL process group, which carries the
+    rendezvous only (peer-buffer handles, the prefill's bandwidth-sized all-reduces)."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        # the data path is this library's kernels over peer memory: keep NCCL's in-switch
+        # multicast groups out of the picture
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return world, rank, local
+
+
+def tp_parity_check(lib, comm, rank, world):
+    """A correctness bit for the multi-GPU record: a K-split layer (5120 x 17408) computed on the
+    shards and summed inside the consuming GEMV's prologue, against the same layer unsharded on
+    this GPU.  Every rank draws the same seeded matrix.  Returns the max relative error (floored
+    at 1e-3 of the largest output) of the all-reduced vector."""
+    import torch
+
+    vp = ctypes.c_void_p
+    M, K = HIDDEN, INTER
+    g = torch.Generator(device="cuda")
+    g.manual_seed(4242)
+    packed = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+    scales = torch.randint(118, 123, (M, K // 16), dtype=torch.uint8, device="cuda", generator=g)
+    act = torch.randn(K, device="cuda", generator=g).to(torch.float16)
+    st = vp(torch.cuda.current_stream().cuda_stream)
+    full = torch.zeros(M, dtype=torch.float16, device="cuda")
+    assert lib.launch_nvfp4_gemv_v8(vp(packed.data_ptr()), vp(scales.data_ptr()), vp(act.data_ptr()),
+                                    vp(full.data_ptr()), M, K, st) == 0
+    k0, k1 = rank * (K // world), (rank + 1) * (K // world)
+    p_l = packed[:, k0 // 2:k1 // 2].contiguous()
+    s_l = scales[:, k0 // 16:k1 // 16].contiguous()
+    a_l = act[k0:k1].contiguous()
+    slot, parity = comm.next_slot()
+    assert lib.launch_nvfp4_gemv_v8(vp(p_l.data_ptr()), vp(s_l.data_ptr()), vp(a_l.data_ptr()),
+                                    vp(slot), M, k1 - k0, st) == 0
+    # consumer: any GEMV over the hidden vector; its prologue completes the all-reduce into h
+    cw = torch.randint(0, 256, (64 * HIDDEN // 2,), dtype=torch.uint8, device="cuda", generator=g)
+    cs = torch.full((64 * HIDDEN // 16,), 120, dtype=torch.uint8, device="cuda")
+    ones = torch.ones(HIDDEN, dtype=torch.float32, device="cuda")
+    h = torch.zeros(HIDDEN, dtype=torch.float16, device="cuda")
+    out = torch.zeros(64, dtype=torch.float16, device="cuda")
+    epoch = torch.full((1,), 1 << 20, dtype=torch.int32, device="cuda")   # ahead of every flag so far
+    rc = lib.launch_nvfp4_gemv_fused_ar(vp(cw.data_ptr()), vp(cs.data_ptr()), vp(h.data_ptr()),
+                                        vp(out.data_ptr()), 64, HIDDEN, vp(ones.data_ptr()), 1e-6, 0,
+                                        comm.ptrs, rank, world, HIDDEN, parity, vp(epoch.data_ptr()),
+                                        0, 1, st)
+    assert rc == 0, rc
+    slot2, parity2 = comm.next_slot()      # keep the number of calls even (slot parity per site)
+    torch.cuda.synchronize()
+    ref = full.float()
+    err = (h.float() - ref).abs() / torch.clamp(ref.abs(), min=1e-3 * float(ref.abs().max()))
+    return float(err.max())
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
     from nvfp4_v100_b200 import _lib
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        if world == 1 and args.gpus > 1:
-            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run "
-                             "(one process per GPU)")
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    world, rank, local = init_ranks()
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run "
+                         "(one process per GPU)")
     lib = _lib.load()
     vp = ctypes.c_void_p
 
@@ -268,33 +456,55 @@ def run_ours(args):
     n_launch = len(layers)
     n_allreduce = sum(1 for l in layers if l[3] == "row") if world > 1 else 0
     comm = None
+    inline = args.allreduce == "inline"
     if world > 1:
-        # K-split layers write their partial vector into this rank's peer-visible buffer; the
-        # library's one-shot all-reduce kernel sums the ranks' vectors into `resid`
+        # K-split layers write their partial vector into this rank's peer-visible buffer.  As in
+        # the decode step, the GEMV that follows such a layer (gate_proj after o_proj / out_proj,
+        # the next layer's first projection or the lm_head after down_proj) takes the hidden
+        # vector as its activation: with --allreduce inline its prologue does the exchange, the
+        # sum, the residual add and the RMSNorm; with --allreduce peer a one-CTA kernel does the
+        # all-reduce into `resid` first.
         from nvfp4_v100_b200.comm import PeerComm
 
         comm = PeerComm(HIDDEN, rank, world)
         resid = torch.zeros(HIDDEN, dtype=torch.float16, device="cuda")
+        ones = torch.ones(HIDDEN, dtype=torch.float32, device="cuda")
+        epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
         assert n_allreduce % 2 == 0
-
-    def gemv(name, m, k, split, packed, scales, act, out, st):
-        dst = out.data_ptr()
-        parity = 0
-        if comm is not None and split == "row":
-            dst, parity = comm.next_slot()
-        rc = lib.launch_nvfp4_gemv_v8(vp(packed.data_ptr()), vp(scales.data_ptr()),
-                                      vp(act.data_ptr()), vp(dst), m, k, st)
-        if rc != 0:
-            raise RuntimeError(f"{name}: launch_nvfp4_gemv_v8 rc={rc}")
-        if comm is not None and split == "row":
-            comm.allreduce_residual(resid, parity, st)
 
     def enqueue_step():
         st = vp(torch.cuda.current_stream().cuda_stream)
+        pending = None
+        site = 0
         for name, m, k, split, packed, scales, act, out in layers:
-            gemv(name, m, k, split, packed, scales, act, out, st)
+            dst = out.data_ptr()
+            if pending is not None:
+                assert k == HIDDEN
+                rc = lib.launch_nvfp4_gemv_fused_ar(
+                    vp(packed.data_ptr()), vp(scales.data_ptr()), vp(act.data_ptr()), vp(dst), m, k,
+                    vp(ones.data_ptr()), 1e-6, 0, comm.ptrs, rank, world, HIDDEN, pending,
+                    vp(epoch.data_ptr()), site, n_allreduce, st)
+                site += 1
+                pending = None
+            else:
+                parity = 0
+                if comm is not None and split == "row":
+                    dst, parity = comm.next_slot()
+                rc = lib.launch_nvfp4_gemv_v8(vp(packed.data_ptr()), vp(scales.data_ptr()),
+                                              vp(act.data_ptr()), vp(dst), m, k, st)
+                if comm is not None and split == "row":
+                    if inline:
+                        pending = parity
+                    else:
+                        comm.allreduce_residual(resid, parity, st)
+            if rc != 0:
+                raise RuntimeError(f"{name}: GEMV launch rc={rc}")
+        if comm is not None and inline:
+            if pending is not None:      # the step's last K-split layer has no consumer in the mix
+                raise RuntimeError("the mix must end with a consumer of the last K-split layer")
+            epoch.add_(1)
 
-    # warm-up outside the graph (module load, NCCL channels), then capture one step
+    # warm-up outside the graph (module load, peer mappings), then capture one step
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -330,6 +540,17 @@ def run_ours(args):
     barrier()
     ms = ev0.elapsed_time(ev1)
 
+    # ---- sustained: the same step replayed for at least two seconds ----
+    sus_steps = max(args.steps, int(2.2e3 / max(ms / args.steps, 1e-3)))
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    s0.record()
+    for _ in range(sus_steps):
+        graph.replay()
+    s1.record()
+    barrier()
+    sus_ms = s0.elapsed_time(s1)
+
     # ---- end to end: host activations in, host results out, every step ----
     # One copy of the activation arena from pinned host memory, the captured step (the same C-ABI
     # launches), one copy of the result arena back (plus the residual vector when K-split layers
@@ -364,29 +585,34 @@ def run_ours(args):
         stop.set()
         sampler.join(timeout=5)
 
-    # max over ranks
-    t = torch.tensor([ms, e2e_ms, float(total_alg)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        tmax = t.clone()
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        tsum = t.clone()
-        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
-        ms, e2e_ms, job_bytes = float(tmax[0]), float(tmax[1]), float(tsum[2])
-    else:
-        job_bytes = float(total_alg)
+    comm_status = comm.status() if comm is not None else 0
+    parity_err = None
+    if comm is not None and inline:
+        parity_err = tp_parity_check(lib, comm, rank, world)
 
-    def finish():
-        """Leave without tearing the communicator down: destroying an NCCL process group while a
-        captured graph still references its kernels has been seen to block forever at exit."""
-        sys.stdout.flush()
-        sys.stderr.flush()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-            os._exit(0)
+    # max over ranks
+    t = torch.tensor([ms, e2e_ms, sus_ms, float(parity_err or 0.0), float(comm_status)],
+                     dtype=torch.float64, device="cuda")
+    tb = torch.tensor([float(total_alg)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(tb, op=dist.ReduceOp.SUM)
+    ms, e2e_ms, sus_ms, parity_max, comm_status = (float(x) for x in t)
+    job_bytes = float(tb[0])
+
+    # ---- release the mix before the decoder is built ----
+    del graph, layers, act_arena, out_arena, h_act, h_out
+    if comm is not None:
+        comm.close()
+        comm = None
+    torch.cuda.empty_cache()
+
+    decode = None
+    if not args.no_decode:
+        decode = run_decode(args, quiet=True)
 
     if rank != 0:
-        finish()
+        shutdown(world)
         return
 
     value = job_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -397,35 +623,50 @@ def run_ours(args):
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
         threads = min(os.cpu_count() or 1, torch.get_num_threads())
-        v, secs = cpu_gemv_gbps(CPU_SAMPLE, threads, repeats=3)   # about 10 s of host work
-        cpu = {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
-               "sample": "three passes over " + CPU_SAMPLE_DESC, "seconds": round(secs, 2)}
+        t0 = time.perf_counter()
+        proto = cpu_protocol(threads, full=False)
+        kind = "reference" if "loop_decode_5120x5120" in proto else "port"
+        cpu = {"value": proto["mix_497_gbps"], "unit": "GB/s", "cores": threads, "kind": "port",
+               "sample": "every layer shape of the mix once or twice (lm_head: 16384 of its rows, "
+                         "scaled): vectorised codec decode + fp32 torch matvec, summed over the "
+                         "497-GEMV mix; the reference's own loop decoder once at 5120x5120 beside it",
+               "seconds": round(time.perf_counter() - t0, 2), "loop_decoder_kind": kind,
+               "protocol": proto}
 
+    run = {"allreduce_per_step": n_allreduce,
+           "allreduce": ("none" if world == 1 else
+                         "inside the consuming GEMV's prologue" if inline else
+                         "one-shot peer-memory kernel"),
+           "comm_status": int(comm_status), "launch": "cuda_graph",
+           "kernel_launches_per_step": n_launch + (0 if inline else n_allreduce)}
     line = {
         "metric": "nvfp4_gemv_hbm_gbps", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "gemv_497_mix_27b", "gemvs_per_step": n_launch,
-                   "algorithmic_bytes_per_step": int(job_bytes),
-                   "l2": "each step streams 14.4 GB of weights (>> 126 MB L2): reads are cold",
-                   "parallelism": f"tp{world}", "allreduce_per_step": n_allreduce,
-                   "allreduce": "one-shot peer-memory kernel" if comm is not None else "none",
-                   "comm_status": comm.status() if comm is not None else 0,
-                   "launch": "cuda_graph"},
+        "config": common_config(world),
+        "run": run,
+        "sustained": {"value": job_bytes * sus_steps / (sus_ms * 1e-3) / 1e9, "unit": "GB/s",
+                      "steps": sus_steps, "seconds": sus_ms * 1e-3},
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "steps": e2e_steps,
                 "ms_per_step": e2e_ms / e2e_steps},
-        "gpu_launches": (n_launch + n_allreduce) * args.steps,
+        "gpu_launches": run["kernel_launches_per_step"] * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu / peak, "traffic": TRAFFIC_PER_LAUNCH, "peak_kind": peak_kind,
                      "kernel": "gemv_mma_kernel",
                      "frac_of_nominal_8000": per_gpu / 8000.0},
         "cpu_baseline": cpu,
         "clocks": summarise_clocks(clock_lines),
+        "decode": decode,
     }
+    if world > 1:
+        line["tp_parity"] = ({"max_rel_err": parity_max, "ok": bool(parity_max <= 4e-3),
+                              "layer": "5120x17408 split along K, all-reduced in the consuming "
+                                       "GEMV's prologue, against the unsharded GEMV"}
+                             if inline else None)
     print(json.dumps(line), flush=True)
-    finish()
+    shutdown(world)
 
 
 SHAPES_27B = [("lm_head", VOCAB, HIDDEN, 1), ("down_proj", HIDDEN, INTER, 64),
@@ -433,7 +674,7 @@ SHAPES_27B = [("lm_head", VOCAB, HIDDEN, 1), ("down_proj", HIDDEN, INTER, 64),
               ("in_proj_qkv", 10240, HIDDEN, 48), ("in_proj_z", 6144, HIDDEN, 48),
               ("o/out_proj", HIDDEN, 6144, 64), ("k/v_proj", 1024, HIDDEN, 32),
               ("in_proj_b/a", 48, HIDDEN, 96),
-              # shapes BASELINE.json lists beside the reference's own table
+              # further shapes of the same decoder: q without its gate, the square o_proj, a 151936-row head
               ("q_proj 6144", 6144, HIDDEN, 0), ("o_proj 5120", HIDDEN, HIDDEN, 0),
               ("lm_head 151936", 151936, HIDDEN, 0)]
 
@@ -523,7 +764,7 @@ def run_per_shape(args):
 
 
 def run_gemm(args):
-    """Dense GEMM through launch_nvfp4_gemmtc_v5 at the 27B layer shapes (BASELINE config 5):
+    """Dense GEMM through launch_nvfp4_gemmtc_v5 at the 27B layer shapes:
     tokens = 32 (batched decode, weight-bandwidth bound) and 8192 (prefill, tensor bound)."""
     import torch
 
@@ -611,20 +852,17 @@ def decode_step_bytes(cfg, context):
 
 
 def run_decode(args, quiet=False):
-    """27B-shape decode: 512-token prompt fed through the step graph, then 63 greedy tokens
-    (BASELINE configs 3 and 4).  Random-init NVFP4 weights, random token ids.  Under torchrun the
-    model is tensor-parallel over the ranks (one process per GPU, NCCL all-reduce in the graph)."""
+    """27B-shape decode: 64 layers, hidden 5120, a 512-token prompt through the chunked prefill,
+    then 63 greedy tokens from the captured step graph.  Random-init NVFP4 weights, random token
+    ids.  Under torchrun the model is tensor-parallel over the ranks (one process per GPU; the
+    all-reduces run inside the consuming GEMVs over NVLink peer memory).  quiet: return the result
+    dictionary (rank 0; None elsewhere) instead of printing it, and leave the process group up."""
     import torch
     import torch.distributed as dist
 
     from nvfp4_v100_b200.engine import DecodeEngine, ModelConfig
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    world, rank, local = init_ranks()
     cfg = ModelConfig(max_len=1024, vocab=args.vocab)
     if args.layers:
         cfg.n_layers = args.layers          # profiling aid: full width, reduced depth
@@ -721,13 +959,11 @@ def run_decode(args, quiet=False):
         }
         if not quiet:
             print(json.dumps(res), flush=True)
-    if world > 1:
-        sys.stdout.flush()
-        dist.barrier()
-        torch.cuda.synchronize()
-        os._exit(0)
+    eng.close()
     del eng
     torch.cuda.empty_cache()
+    if not quiet:
+        shutdown(world)
     return res
 
 
@@ -762,9 +998,15 @@ def main():
                     help="with --gemm: a single token count instead of 32 and 8192")
     ap.add_argument("--gen", type=int, default=63)
     ap.add_argument("--vocab", type=int, default=VOCAB)
-    ap.add_argument("--allreduce", default="peer", choices=["fused", "peer", "nccl"],
-                    help="with --decode under torchrun: GEMV+all-reduce in one kernel, a separate "
-                         "one-shot peer-memory all-reduce kernel, or NCCL")
+    ap.add_argument("--allreduce", default="inline", choices=["inline", "fused", "peer", "nccl"],
+                    help="under torchrun: the all-reduce inside the consuming GEMV's prologue, "
+                         "GEMV+all-reduce in one kernel (decode only), a separate one-shot "
+                         "peer-memory all-reduce kernel, or NCCL (decode only)")
+    ap.add_argument("--cpu-protocol", default="full", choices=["full", "quick", "none"],
+                    help="with --impl reference: how much of the per-shape CPU protocol to run "
+                         "beside the timed steps")
+    ap.add_argument("--no-decode", action="store_true",
+                    help="default mode: skip the 27B-shape decode section of the line")
     ap.add_argument("--fake-context", type=int, default=0,
                     help="with --decode: start at this cache length (zero-filled cache)")
     ap.add_argument("--eager", action="store_true",

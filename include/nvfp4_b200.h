@@ -247,6 +247,25 @@ int launch_nvfp4_gemv_allreduce(const void* weight_packed, const void* weight_sc
                                 const void* activation, void* h, int M, int K,
                                 const void* const* bufs, int rank, int world, int n, int parity,
                                 void* stream);
+/* The all-reduce inside the CONSUMING GEMV: h (fp16 [K], in/out) first receives the sum over the
+ * ranks of the partial vectors in data slot `parity` (CTA 0 exchanges flags with the peers and
+ * pulls their vectors over NVLink while every CTA's first weight loads are in flight; the other
+ * CTAs wait, bounded, for CTA 0's sequence number), then is RMS-normalised with norm_w1 and
+ * multiplied: one launch per K-split layer less than launch_allreduce_residual + fused GEMV.
+ * epilogue 0 or 2 as in launch_nvfp4_gemv_fused.  epoch: device u32 counting decode steps; site,
+ * n_sites: this call's place among a step's all-reduces (same on every rank).  K <= n, K <= 10240.
+ * launch_argmax_exchange: greedy pick over the ranks' vocabulary slices in one launch (local
+ * argmax, pairs pushed to every peer, bounded wait, global pick, history and counters advanced,
+ * *epoch += 1); logits fp16 [vocab] is this rank's slice starting at global index offset.
+ * Status codes in nvfp4_comm_status: 201 + r / 301 + r peer r missing, 299 CTA 0 never published. */
+int launch_nvfp4_gemv_fused_ar(const void* weight_packed, const void* weight_scales, void* h,
+                               void* output, int M, int K, const void* norm_w1, float eps,
+                               int epilogue, const void* const* bufs, int rank, int world, int n,
+                               int parity, const void* epoch, int site, int n_sites, void* stream);
+int launch_argmax_exchange(const void* logits, int vocab, long long offset,
+                           const void* const* bufs, int rank, int world, int n, void* epoch,
+                           void* tok, void* pos, void* len, void* history, void* hist_count,
+                           int hist_cap, void* stream);
 long long nvfp4_comm_buffer_bytes(int n);
 long long nvfp4_comm_data_offset(int n, int parity);
 int nvfp4_comm_init(void* buf, int n);

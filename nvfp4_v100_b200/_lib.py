@@ -65,6 +65,10 @@ SIGNATURES = {
     "launch_nvfp4_gemv_allreduce": ([_vp, _vp, _vp, _vp, _i, _i, ctypes.POINTER(_vp), _i, _i, _i, _i,
                                      _vp], _i),
     "launch_allreduce_residual": ([_vp, ctypes.POINTER(_vp), _i, _i, _i, _i, _vp], _i),
+    "launch_nvfp4_gemv_fused_ar": ([_vp, _vp, _vp, _vp, _i, _i, _vp, _f, _i, ctypes.POINTER(_vp), _i, _i,
+                                    _i, _i, _vp, _i, _i, _vp], _i),
+    "launch_argmax_exchange": ([_vp, _i, _ll, ctypes.POINTER(_vp), _i, _i, _i, _vp, _vp, _vp, _vp, _vp,
+                                _vp, _i, _vp], _i),
     "launch_dn_fused": ([_vp] * 12 + [_f, _vp], _i),
     "launch_dn_fused_heads": ([_vp] * 12 + [_i, _i, _f, _vp], _i),
     "launch_transpose_f16": ([_vp, _ll, _vp, _ll, _i, _i, _vp], _i),

@@ -62,3 +62,16 @@ class PeerComm:
     def status(self) -> int:
         torch.cuda.synchronize()
         return self.lib.nvfp4_comm_status(vp(self.own))
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's.  Every rank must have finished using
+        the buffers (the barrier), and no kernel may still be running on this GPU."""
+        if self.own is None:
+            return
+        torch.cuda.synchronize()
+        dist.barrier()
+        for r in range(self.world):
+            if r != self.rank and self.ptrs[r]:
+                self.lib.nvfp4_ipc_close_handle(vp(self.ptrs[r]))
+        self.lib.gpu_free(vp(self.own))
+        self.own = None

@@ -27,10 +27,7 @@
 
 #include "common.cuh"
 
-#define NVFP4_COMM_MAX_RANKS 8
-#define NVFP4_COMM_FLAGS_OFF 64
-#define NVFP4_COMM_DATA_OFF 256
-#define NVFP4_COMM_SPIN_LIMIT (1u << 22)
+#include "comm_layout.cuh"
 
 namespace nvfp4 {
 
@@ -89,17 +86,29 @@ allreduce_residual_kernel(CommPeers peers, int rank, int world, int n, int parit
         }
     }
     __syncthreads();
+    // A peer that never announced its vector leaves stale bytes in its slot: adding them would
+    // corrupt the residual stream silently, so the sum is skipped and h keeps its value (the
+    // error word says which peer was missing; the caller checks it).
+    if (*reinterpret_cast<volatile uint32_t*>(err) != 0u) return;
     const size_t slot = NVFP4_COMM_DATA_OFF + (size_t)parity * (size_t)n * sizeof(__half);
     for (int i = tid * 8; i < n; i += blockDim.x * 8) {
-        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-        for (int r = 0; r < world; r++) {
-            const uint4 v = ld_relaxed_sys_u4(peers.buf[r] + slot + (size_t)i * sizeof(__half));
-            const __half2* p = reinterpret_cast<const __half2*>(&v);
+        // all peers' loads are issued before the first is used: one NVLink round trip, not one
+        // per peer
+        uint4 v[NVFP4_COMM_MAX_RANKS];
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float2 f = __half22float2(p[j]);
-                acc[2 * j] += f.x;
-                acc[2 * j + 1] += f.y;
+        for (int r = 0; r < NVFP4_COMM_MAX_RANKS; r++)
+            if (r < world) v[r] = ld_relaxed_sys_u4(peers.buf[r] + slot + (size_t)i * sizeof(__half));
+        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int r = 0; r < NVFP4_COMM_MAX_RANKS; r++) {
+            if (r < world) {
+                const __half2* p = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float2 f = __half22float2(p[j]);
+                    acc[2 * j] += f.x;
+                    acc[2 * j + 1] += f.y;
+                }
             }
         }
         uint4 hv = *reinterpret_cast<const uint4*>(h + i);
@@ -113,6 +122,93 @@ allreduce_residual_kernel(CommPeers peers, int rank, int world, int n, int parit
     }
 }
 
+// Tensor-parallel greedy pick without a library collective: every rank finds the maximum of its
+// vocabulary slice, stores (value, global index) into slot `rank` of EVERY rank's tail area (peer
+// stores over NVLink), announces it with a release store of the step's sequence number, waits
+// (bounded) for the others, picks the global maximum (lowest index among equals), appends it to
+// the history and advances the step counters, the epoch included.  One CTA.
+__global__ void __launch_bounds__(1024)
+argmax_exchange_kernel(CommPeers peers, int rank, int world, int n, const __half* __restrict__ logits,
+                       int vocab, long long offset, unsigned int* __restrict__ epoch,
+                       long long* __restrict__ tok, long long* __restrict__ pos,
+                       long long* __restrict__ len, long long* __restrict__ history,
+                       long long* __restrict__ hist_count, int hist_cap) {
+    pdl_prologue();
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = t; i < vocab; i += 1024) {
+        const float v = __half2float(logits[i]);
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { s_v[warp] = best; s_i[warp] = bi; }
+    __syncthreads();
+    if (warp != 0) return;
+    best = s_v[lane];
+    bi = s_i[lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (bi == 0x7fffffff) bi = 0;
+    const long long tail = nvfp4_comm_tail_offset(n);
+    unsigned char* mine = peers.buf[rank];
+    uint32_t* err = reinterpret_cast<uint32_t*>(mine) + 1;
+    const uint32_t seq = *epoch + 1u;
+    // lane r hands this rank's pair to rank r (its own copy included) and then waits for rank r's
+    if (lane < world) {
+        unsigned char* dst = peers.buf[lane] + tail;
+        float2* pair = reinterpret_cast<float2*>(dst + NVFP4_TAIL_CAND_OFF) + (seq & 1u) * 8u + rank;
+        const float2 mine_pair = make_float2(best, __int_as_float((int)(offset + bi)));
+        asm volatile("st.relaxed.sys.global.v2.f32 [%0], {%1, %2};\n" ::"l"(pair), "f"(mine_pair.x),
+                     "f"(mine_pair.y) : "memory");
+        __threadfence_system();
+        st_release_sys_u32(reinterpret_cast<uint32_t*>(dst + NVFP4_TAIL_CAND_FLAGS_OFF) + rank, seq);
+        const uint32_t* flag =
+            reinterpret_cast<const uint32_t*>(mine + tail + NVFP4_TAIL_CAND_FLAGS_OFF) + lane;
+        uint32_t spins = 0;
+        while ((int32_t)(ld_acquire_sys_u32(flag) - seq) < 0) {
+            if (++spins > NVFP4_COMM_SPIN_LIMIT) {
+                atomicExch(err, 301u + (uint32_t)lane);
+                break;
+            }
+        }
+    }
+    __syncwarp();
+    if (lane == 0) {
+        float gb = -INFINITY;
+        long long gi = 0;
+        for (int r = 0; r < world; r++) {
+            float2 pr;
+            const float2* src =
+                reinterpret_cast<const float2*>(mine + tail + NVFP4_TAIL_CAND_OFF) + (seq & 1u) * 8u + r;
+            asm volatile("ld.relaxed.sys.global.v2.f32 {%0, %1}, [%2];\n"
+                         : "=f"(pr.x), "=f"(pr.y) : "l"(src) : "memory");
+            const long long i = (long long)__float_as_int(pr.y);
+            if (pr.x > gb || (pr.x == gb && i < gi) || r == 0) { gb = pr.x; gi = i; }
+        }
+        *tok = gi;
+        if (history && hist_count) {
+            const long long c = *hist_count;
+            if (c < hist_cap) history[c] = gi;
+            *hist_count = c + 1;
+        }
+        if (pos) *pos += 1;
+        if (len) *len += 1;
+        *epoch = seq;
+    }
+}
+
 }  // namespace nvfp4
 
 extern "C" {
@@ -120,8 +216,8 @@ extern "C" {
 // Bytes a communication buffer for vectors of n fp16 elements needs.
 long long nvfp4_comm_buffer_bytes(int n) {
     if (n <= 0 || n % 8 != 0) return -1;
-    // header + pull area data[2][n] + push area data[2][8][n] (launch_nvfp4_gemv_allreduce)
-    return NVFP4_COMM_DATA_OFF + 2LL * n * 2 + 2LL * 8 * n * 2;
+    // header + pull area data[2][n] + push area data[2][8][n] (launch_nvfp4_gemv_allreduce) + tail
+    return nvfp4_comm_tail_offset(n) + NVFP4_TAIL_BYTES;
 }
 
 // Byte offset of data slot `parity` (0 or 1): where the producing GEMV writes its partial vector.
@@ -199,6 +295,31 @@ int launch_allreduce_residual(void* h, const void* const* bufs, int rank, int wo
     return nvfp4::launch_pdl(nvfp4::allreduce_residual_kernel, dim3(1), dim3(threads), 0,
                              (cudaStream_t)stream, peers, rank, world, n, parity & 1, (__half*)h) ==
                    cudaSuccess ? 0 : -1;
+}
+
+
+// Tensor-parallel greedy pick in one launch (see argmax_exchange_kernel): logits fp16 [vocab] is
+// this rank's vocabulary slice starting at global index `offset`; epoch is a device u32 that
+// counts decode steps on this rank (every rank advances it in step; it also numbers the
+// all-reduces that run inside launch_nvfp4_gemv_fused_ar).  No counterpart in the reference.
+// 0; -1 bad arguments or launch error.
+int launch_argmax_exchange(const void* logits, int vocab, long long offset,
+                           const void* const* bufs, int rank, int world, int n, void* epoch,
+                           void* tok, void* pos, void* len, void* history, void* hist_count,
+                           int hist_cap, void* stream) {
+    if (!logits || !bufs || !epoch || !tok || vocab <= 0 || offset < 0 || world < 1 ||
+        world > NVFP4_COMM_MAX_RANKS || rank < 0 || rank >= world || n <= 0 || n % 8 != 0)
+        return -1;
+    nvfp4::CommPeers peers;
+    for (int r = 0; r < NVFP4_COMM_MAX_RANKS; r++)
+        peers.buf[r] = (r < world) ? (unsigned char*)bufs[r] : nullptr;
+    for (int r = 0; r < world; r++)
+        if (!peers.buf[r]) return -1;
+    return nvfp4::launch_pdl(nvfp4::argmax_exchange_kernel, dim3(1), dim3(1024), 0,
+                             (cudaStream_t)stream, peers, rank, world, n, (const __half*)logits,
+                             vocab, offset, (unsigned int*)epoch, (long long*)tok, (long long*)pos,
+                             (long long*)len, (long long*)history, (long long*)hist_count,
+                             hist_cap) == cudaSuccess ? 0 : -1;
 }
 
 }  // extern "C"

@@ -22,6 +22,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "comm_layout.cuh"
 #include "gemv_stream.cuh"
 
 namespace nvfp4 {
@@ -112,7 +113,7 @@ struct WeightRegs {
 
 // Optional work fused around the dot products (used by the decode engine; the reference-named
 // entry points run with PRO_NONE / EPI_STORE).
-enum { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_INTERLEAVED = 2 };
+enum { PRO_NONE = 0, PRO_RMSNORM = 1, PRO_INTERLEAVED = 2, PRO_AR_RMSNORM = 3 };
 #define PRO_NV 5  // 16-byte activation vectors a thread holds in the RMSNorm prologue
 enum { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SILU_MUL = 2, EPI_ALLREDUCE = 3 };
 struct GemvExtra {
@@ -123,6 +124,10 @@ struct GemvExtra {
     // the number of ranks, the data slot, and the buffers' vector capacity
     unsigned char* comm[8];
     int rank, world, parity, comm_n;
+    // PRO_AR_RMSNORM: device step counter and this call's place among the n_sites all-reduces of
+    // a step; sequence number of the exchange = *epoch * n_sites + site + 1
+    const unsigned int* epoch;
+    int site, n_sites;
 };
 
 // Layout of the push area of a communication buffer (shared with comm.cu, which owns the
@@ -257,7 +262,97 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
     // that is ordered after the wait pins them behind it.
     asm volatile("" : "+l"(xsrc));
 
-    if (PRO == PRO_RMSNORM) {
+    if (PRO == PRO_AR_RMSNORM) {
+        // Tensor-parallel: act0 is the residual stream h, still missing the sum over the ranks of
+        // the previous K-split layer's partial vectors (each rank's sits in data slot `parity`
+        // of its communication buffer, written by the previous kernel).  CTA 0 exchanges
+        // "ready" flags with the peers, pulls their vectors, adds the sum to h and publishes a
+        // sequence number; every CTA waits for that number (bounded) before it reads h.  The
+        // weight loads above are already in flight, so the exchange hides behind them.
+        unsigned char* mine = ex.comm[ex.rank];
+        const long long tail = nvfp4_comm_tail_offset(ex.comm_n);
+        uint32_t* errw = reinterpret_cast<uint32_t*>(mine) + 1;
+        uint32_t* ready = reinterpret_cast<uint32_t*>(mine + tail + NVFP4_TAIL_AR_READY_OFF);
+        const uint32_t seq = *reinterpret_cast<const volatile unsigned int*>(ex.epoch) *
+                                 (uint32_t)ex.n_sites + (uint32_t)ex.site + 1u;
+        const int tid = threadIdx.x;
+        constexpr int T = WARPS * 32;
+        if (blockIdx.x == 0) {
+            __shared__ int s_bad;
+            if (tid == 0) s_bad = 0;
+            __syncthreads();
+            if (tid < ex.world && tid != ex.rank) {
+                __threadfence_system();   // this rank's partial vector (previous kernel) first
+                uint32_t* pf = reinterpret_cast<uint32_t*>(ex.comm[tid] + tail +
+                                                           NVFP4_TAIL_AR_FLAGS_OFF) + ex.rank;
+                asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(pf), "r"(seq) : "memory");
+                const uint32_t* mf = reinterpret_cast<const uint32_t*>(mine + tail +
+                                                                       NVFP4_TAIL_AR_FLAGS_OFF) + tid;
+                uint32_t spins = 0, v;
+                do {
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(mf) : "memory");
+                    if ((int32_t)(v - seq) >= 0) break;
+                } while (++spins <= NVFP4_PUSH_SPIN_LIMIT);
+                if ((int32_t)(v - seq) < 0) {
+                    atomicExch(errw, 201u + (uint32_t)tid);
+                    s_bad = 1;
+                }
+            }
+            __syncthreads();
+            if (!s_bad) {    // a missing peer's slot holds stale bytes: leave h as it is
+                __half* h = const_cast<__half*>(act0);
+                const size_t slot = NVFP4_COMM_DATA_OFF + (size_t)ex.parity * (size_t)ex.comm_n * 2;
+                for (int i = tid * 8; i < K; i += T * 8) {
+                    uint4 v[8];
+#pragma unroll
+                    for (int r = 0; r < 8; r++) {
+                        if (r < ex.world) {
+                            const void* src = ex.comm[r] + slot + (size_t)i * 2;
+                            asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                                         : "=r"(v[r].x), "=r"(v[r].y), "=r"(v[r].z), "=r"(v[r].w)
+                                         : "l"(src) : "memory");
+                        }
+                    }
+                    float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int r = 0; r < 8; r++) {
+                        if (r < ex.world) {
+                            const __half2* hp = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const float2 f = __half22float2(hp[e]);
+                                acc[2 * e] += f.x;
+                                acc[2 * e + 1] += f.y;
+                            }
+                        }
+                    }
+                    uint4 hv = *reinterpret_cast<const uint4*>(h + i);
+                    __half2* hp = reinterpret_cast<__half2*>(&hv);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const float2 f = __half22float2(hp[e]);
+                        hp[e] = __floats2half2_rn(f.x + round_f16(acc[2 * e]),
+                                                  f.y + round_f16(acc[2 * e + 1]));
+                    }
+                    *reinterpret_cast<uint4*>(h + i) = hv;
+                }
+            }
+            __threadfence();
+            __syncthreads();
+            if (tid == 0)
+                asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(ready), "r"(seq) : "memory");
+        }
+        if (tid == 0) {
+            uint32_t spins = 0, v;
+            do {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(ready) : "memory");
+                if ((int32_t)(v - seq) >= 0) break;
+            } while (++spins <= NVFP4_PUSH_SPIN_LIMIT);
+            if ((int32_t)(v - seq) < 0) atomicExch(errw, 299u);
+        }
+        __syncthreads();
+    }
+    if (PRO == PRO_RMSNORM || PRO == PRO_AR_RMSNORM) {
         // Every thread keeps its share of x in registers between the two phases and issues all
         // of its loads up front: the prologue sits on the kernel's critical path, so it must
         // cost one memory round trip, not one per loop iteration.  K <= PRO_NV * 8 * threads.
@@ -268,7 +363,17 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
 #pragma unroll
         for (int j = 0; j < PRO_NV; j++) {
             const int i = (threadIdx.x + j * T) * 8;
-            xv[j] = (i < K) ? *reinterpret_cast<const uint4*>(act0 + i) : make_uint4(0u, 0u, 0u, 0u);
+            if (i >= K) {
+                xv[j] = make_uint4(0u, 0u, 0u, 0u);
+            } else if (PRO == PRO_AR_RMSNORM) {
+                // h was just rewritten by CTA 0 of this very kernel: a coherent load, never the
+                // read-only path
+                asm volatile("ld.relaxed.gpu.global.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(xv[j].x), "=r"(xv[j].y), "=r"(xv[j].z), "=r"(xv[j].w)
+                             : "l"(act0 + i) : "memory");
+            } else {
+                xv[j] = *reinterpret_cast<const uint4*>(act0 + i);
+            }
         }
         float4 wv[PRO_NV][2];
 #pragma unroll
@@ -690,7 +795,8 @@ template <int WARPS, int NACT, int PRO, int EPI>
 static cudaError_t launch_mma(const void* packed, const void* scales, const void* a0, const void* a1,
                               void* out, int M, int K, cudaStream_t st, const GemvExtra& ex,
                               const GemvPlan& plan) {
-    const int smem = (PRO == PRO_RMSNORM) ? K * 2 : (PRO == PRO_INTERLEAVED) ? K * 4 : 0;
+    const int smem = (PRO == PRO_RMSNORM || PRO == PRO_AR_RMSNORM) ? K * 2
+                     : (PRO == PRO_INTERLEAVED)                     ? K * 4 : 0;
     // the opt-in to more than 48 KB of dynamic shared memory applies to the current device only
     static int max_smem_set[MAX_DEVICES] = {0};
     const int dev = current_device();
@@ -880,6 +986,58 @@ int gemv_ex_dispatch(const void* packed, const void* scales, const void* act, vo
     return NVFP4_OK;
 }
 
+// GEMV whose prologue first completes the all-reduce of the PREVIOUS K-split layer into the
+// residual stream h, then RMS-normalises h (see PRO_AR_RMSNORM in the kernel).
+int gemv_ar_in_dispatch(const void* packed, const void* scales, void* h, void* out, int M, int K,
+                        const void* norm_w1, float eps, int epilogue, const void* const* bufs,
+                        int rank, int world, int n, int parity, const void* epoch, int site,
+                        int n_sites, void* stream) {
+    if (K <= 0 || K % 128 != 0 || M <= 0 || K > n) return NVFP4_ERR_SHAPE;
+    if (!packed || !scales || !h || !out || !norm_w1 || !bufs || !epoch) return NVFP4_ERR_SHAPE;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || n % 8 != 0 || site < 0 ||
+        site >= n_sites)
+        return NVFP4_ERR_SHAPE;
+    if (!aligned(packed, 32) || !aligned(scales, 8) || !aligned(h, 16) || !aligned(out, 2) ||
+        !aligned(norm_w1, 16) || K * 2 > 200 * 1024)
+        return NVFP4_ERR_SHAPE;
+    if (epilogue != EPI_STORE && epilogue != EPI_SILU_MUL) return NVFP4_ERR_SHAPE;
+    if (epilogue == EPI_SILU_MUL && M % 16 != 0) return NVFP4_ERR_SHAPE;
+    if (K > PRO_NV * 8 * 256) return NVFP4_ERR_SHAPE;
+    GemvExtra ex = {};
+    ex.norm_w1 = (const float*)norm_w1;
+    ex.eps = eps;
+    for (int r = 0; r < world; r++) {
+        if (!bufs[r]) return NVFP4_ERR_SHAPE;
+        ex.comm[r] = (unsigned char*)bufs[r];
+    }
+    ex.rank = rank;
+    ex.world = world;
+    ex.parity = parity & 1;
+    ex.comm_n = n;
+    ex.epoch = (const unsigned int*)epoch;
+    ex.site = site;
+    ex.n_sites = n_sites;
+    // every CTA waits for CTA 0 inside the kernel, so all of them must be resident at once: the
+    // planner's grids never exceed the resident slots, and the K split (clusters) is not used
+    GemvPlan plan = plan_gemv(M, K, (K > PRO_NV * 8 * 128) ? 8 : 0, 1);
+    plan.split = 1;
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+    if (epilogue == EPI_STORE)
+        e = (plan.warps == 8)
+                ? launch_mma<8, 1, PRO_AR_RMSNORM, EPI_STORE>(packed, scales, h, nullptr, out, M, K, st, ex, plan)
+                : launch_mma<4, 1, PRO_AR_RMSNORM, EPI_STORE>(packed, scales, h, nullptr, out, M, K, st, ex, plan);
+    else
+        e = (plan.warps == 8)
+                ? launch_mma<8, 1, PRO_AR_RMSNORM, EPI_SILU_MUL>(packed, scales, h, nullptr, out, M, K, st, ex, plan)
+                : launch_mma<4, 1, PRO_AR_RMSNORM, EPI_SILU_MUL>(packed, scales, h, nullptr, out, M, K, st, ex, plan);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "launch_nvfp4_gemv_fused_ar: %s\n", cudaGetErrorString(e));
+        return NVFP4_ERR_LAUNCH;
+    }
+    return NVFP4_OK;
+}
+
 // Tensor-parallel K-split layer: GEMV + all-reduce + residual add in one kernel.
 int gemv_allreduce_dispatch(const void* packed, const void* scales, const void* act, void* h, int M,
                             int K, const void* const* bufs, int rank, int world, int n, int parity,
@@ -929,6 +1087,25 @@ int launch_nvfp4_gemv_allreduce(const void* weight_packed, const void* weight_sc
                                 void* stream) {
     return nvfp4::gemv_allreduce_dispatch(weight_packed, weight_scales, activation, h, M, K, bufs,
                                           rank, world, n, parity, stream);
+}
+
+// Tensor-parallel consumer of a K-split layer (no counterpart in the reference): the all-reduce
+// of that layer's partial vectors and the residual add run INSIDE this GEMV's prologue instead of
+// in a kernel of their own.  h fp16 [K] (in/out): the residual stream, to which the sum over the
+// ranks of the partial vectors in data slot `parity` of the communication buffers is added (by
+// CTA 0, over NVLink peer loads, after a bounded flag exchange); every CTA then RMS-normalises the
+// new h with norm_w1 and multiplies.  epilogue 0 or 2 as in launch_nvfp4_gemv_fused.  epoch: a
+// device u32 counting decode steps (advanced by launch_argmax_exchange or by the caller), site /
+// n_sites: this call's place among the all-reduces of one step, the same on every rank.
+// 0; -2 bad arguments; -1 launch error.  A wait that ran out shows in nvfp4_comm_status (201 + r:
+// peer r missing; 299: CTA 0 never published) and leaves h without the sum.
+int launch_nvfp4_gemv_fused_ar(const void* weight_packed, const void* weight_scales, void* h,
+                               void* output, int M, int K, const void* norm_w1, float eps,
+                               int epilogue, const void* const* bufs, int rank, int world, int n,
+                               int parity, const void* epoch, int site, int n_sites, void* stream) {
+    return nvfp4::gemv_ar_in_dispatch(weight_packed, weight_scales, h, output, M, K, norm_w1, eps,
+                                      epilogue, bufs, rank, world, n, parity, epoch, site, n_sites,
+                                      stream);
 }
 
 // GEMV with optional fused RMSNorm of the activation (prologue = 1) and fused residual add

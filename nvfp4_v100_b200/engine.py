@@ -112,13 +112,16 @@ class DecodeEngine:
     """Holds the prepared weights and all state of one sequence and replays the step graph."""
 
     def __init__(self, cfg: ModelConfig, device: str = "cuda", tp_rank: int = 0, tp_world: int = 1,
-                 allreduce: str = "peer"):
+                 allreduce: str = "inline"):
         """tp_world > 1: this process holds shard tp_rank of a tensor-parallel group (one process
         per GPU, torch.distributed initialised with the NCCL backend by the caller).
-        allreduce: "fused" = the K-split GEMV, its all-reduce and the residual add are ONE kernel
-        (peer stores per tile, last CTA reduces); "peer" = GEMV, then this library's one-shot
-        all-reduce + residual kernel over NVLink peer memory; "nccl" = GEMV, NCCL all-reduce, then
-        a residual-add kernel."""
+        allreduce: "inline" = the K-split GEMV writes its partial vector into the peer-visible
+        buffer and the NEXT GEMV's prologue does the exchange, the sum, the residual add and the
+        RMSNorm (no kernel of its own per all-reduce; the greedy pick is exchanged the same way,
+        so a step contains no library collective); "fused" = the K-split GEMV, its all-reduce and
+        the residual add are ONE kernel (peer stores per tile, last CTA reduces); "peer" = GEMV,
+        then this library's one-shot all-reduce + residual kernel over NVLink peer memory; "nccl"
+        = GEMV, NCCL all-reduce, then a residual-add kernel."""
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; there is no CPU fallback")
         self.cfg = cfg
@@ -173,7 +176,10 @@ class DecodeEngine:
         self.lm_head = None
         self.allreduce = allreduce if W > 1 else "none"
         self.ar_calls = 0
-        if self.allreduce in ("peer", "fused"):
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)   # decode steps so far
+        self._pending = None        # ("inline"): (parity, site) of the all-reduce not yet applied
+        self._site = 0
+        if self.allreduce in ("peer", "fused", "inline"):
             self._setup_peer_comm()
 
     def _setup_peer_comm(self):
@@ -183,9 +189,17 @@ class DecodeEngine:
 
     def comm_status(self) -> int:
         """0 if every peer wait of the one-shot all-reduce was answered in time."""
-        if self.allreduce not in ("peer", "fused"):
+        if self.allreduce not in ("peer", "fused", "inline"):
             return 0
         return self.comm.status()
+
+    def close(self):
+        """Release the graph and the peer mappings (call on every rank, before tearing the
+        process group down)."""
+        self.graph = None
+        if getattr(self, "comm", None) is not None:
+            self.comm.close()
+            self.comm = None
 
     # ------------------------------------------------------------------ weights
     def _mat(self, packed: torch.Tensor, scales: torch.Tensor, M: int, K: int) -> _Mat:
@@ -347,6 +361,21 @@ class DecodeEngine:
     # ------------------------------------------------------------------ one step
     def _gemv(self, st, m: _Mat, x, out, pro_w1=None, epi=0, residual=None):
         out_ptr = out if isinstance(out, int) else out.data_ptr()
+        if self._pending is not None:
+            # the all-reduce of the previous K-split layer runs in this GEMV's prologue
+            assert x is self.h and pro_w1 is not None and residual is None
+            parity, site = self._pending
+            self._pending = None
+            rc = self.lib.launch_nvfp4_gemv_fused_ar(
+                vp(m.packed.data_ptr()), vp(m.scales.data_ptr()), vp(self.h.data_ptr()), vp(out_ptr),
+                m.M, m.K, vp(pro_w1.data_ptr()), float(self.cfg.rms_eps), epi, self.comm.ptrs,
+                self.rank, self.world, self.cfg.hidden, parity, vp(self.epoch.data_ptr()), site,
+                2 * self.cfg.n_layers, st)
+            if rc != 0:
+                raise RuntimeError(f"launch_nvfp4_gemv_fused_ar rc={rc} (M={m.M}, K={m.K})")
+            self.n_launch += 1
+            self.n_collective += 1
+            return
         rc = self.lib.launch_nvfp4_gemv_fused(
             vp(m.packed.data_ptr()), vp(m.scales.data_ptr()), vp(x.data_ptr()), vp(out_ptr),
             m.M, m.K, 0 if pro_w1 is None else 1,
@@ -375,6 +404,13 @@ class DecodeEngine:
             self.n_launch += 1
             self.n_collective += 1
             return
+        if self.allreduce == "inline":
+            slot, parity = self.comm.next_slot()
+            self.ar_calls += 1
+            self._gemv(st, m, x, slot)
+            self._pending = (parity, self._site)
+            self._site += 1
+            return
         if self.allreduce == "peer":
             slot, parity = self.comm.next_slot()
             self.ar_calls += 1
@@ -399,6 +435,8 @@ class DecodeEngine:
         st = vp(torch.cuda.current_stream().cuda_stream)
         self.n_launch = 0
         self.n_collective = 0
+        self._site = 0
+        self._pending = None
         # an even number of K-split layers per step keeps the slot parity of every call site the
         # same in every step, which a captured graph needs
         assert self.ar_calls % 2 == 0
@@ -452,6 +490,15 @@ class DecodeEngine:
                 self.hist_cap, st)
             assert rc == 0, rc
             self.n_launch += 1
+        elif self.allreduce == "inline":
+            rc = lib.launch_argmax_exchange(
+                vp(self.logits.data_ptr()), self.v_hi - self.v_lo, self.v_lo, self.comm.ptrs,
+                self.rank, self.world, c.hidden, vp(self.epoch.data_ptr()), vp(self.tok.data_ptr()),
+                vp(self.pos.data_ptr()), vp(self.len.data_ptr()), vp(self.history.data_ptr()),
+                vp(self.hist_count.data_ptr()), self.hist_cap, st)
+            assert rc == 0, rc
+            self.n_launch += 1
+            self.n_collective += 1
         else:
             import torch.distributed as dist
 
@@ -662,4 +709,8 @@ class DecodeEngine:
         for _ in range(n_gen):
             self.step()
         torch.cuda.synchronize()
+        st = self.comm_status()
+        if st != 0:
+            raise RuntimeError(f"a bounded wait on a tensor-parallel peer ran out (status {st}): "
+                               "the generated tokens are not valid")
         return self.history[base:base + n_gen].cpu().tolist()

@@ -13,7 +13,8 @@ relational: RMSNorm max-diff 0 against the model's module, experiments/_qwen38_p
 a one-step DeltaNet A/B, pipeline/_qwen38_r2.py:163-185).  The oracle is pinned instead against
 the reference kernels themselves, recompiled unchanged and run next to ours on the GPU
 (``oracle/Makefile`` -> ``oracle/_ref``, ``tests/test_ref_kernels_gpu.py``), and against the
-model's own PyTorch modules where they are importable (``tests/test_oracle_fused.py``).
+model's own PyTorch modules (the installed transformers Qwen3_5 code on the same dequantised
+weights, ``tests/test_oracle_vs_hf.py``).
 
 Only tests, the smoke check and the CPU-baseline leg of the benchmark import this module.
 """

@@ -230,7 +230,7 @@ def test_allreduce_residual_single_rank(lib):
     # world = 1: no peers to wait for; h += f16(own partial vector), alternating data slots
     n = 5120
     nbytes = lib.nvfp4_comm_buffer_bytes(n)
-    assert nbytes == 256 + 4 * n + 32 * n      # header, pull area [2][n], push area [2][8][n]
+    assert nbytes == 256 + 4 * n + 32 * n + 256   # header, pull area [2][n], push area [2][8][n], tail
     buf = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
     assert lib.nvfp4_comm_init(ptr(buf), n) == 0
     rng = np.random.default_rng(0)
@@ -304,3 +304,51 @@ def test_gemv_allreduce_single_rank_equals_residual_epilogue(lib):
     assert lib.nvfp4_comm_status(ptr(buf)) == 0
     assert lib.launch_nvfp4_gemv_allreduce(ptr(d_p), ptr(d_s), ptr(x), ptr(h_b), M + 8, K, bufs, 0,
                                            1, n, 0, stream()) == -2
+
+
+def test_gemv_with_allreduce_in_its_prologue_single_rank(lib):
+    # world = 1: the all-reduce inside the consuming GEMV adds this rank's own partial vector to h
+    # (CTA 0), every CTA waits for CTA 0's sequence number, then the RMSNorm prologue runs on the
+    # new h.  Must equal: h += f16(partial) done by hand, then the fused GEMV.  Three steps, two
+    # sites per step, both epilogues; the epoch word is advanced by hand as a decode step would.
+    M, K, n = 1024, 5120, 5120
+    w = oc.synthetic_weight(M, K, seed=31)
+    p, s = oc.encode(w)
+    d_p, d_s = dev(p), dev(s)
+    w1 = dev((1 + 0.1 * np.random.default_rng(1).standard_normal(K)).astype(np.float32))
+    buf = torch.zeros(lib.nvfp4_comm_buffer_bytes(n), dtype=torch.uint8, device="cuda")
+    assert lib.nvfp4_comm_init(ptr(buf), n) == 0
+    bufs = (ctypes.c_void_p * 1)(buf.data_ptr())
+    epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rng = np.random.default_rng(6)
+    h = dev(rng.standard_normal(K).astype(np.float16))
+    h_ref = h.clone()
+    z = ctypes.c_void_p(0)
+    for step in range(3):
+        for site in range(2):
+            parity = site & 1
+            part = torch.from_numpy(rng.standard_normal(K).astype(np.float16)).cuda()
+            off = lib.nvfp4_comm_data_offset(n, parity)
+            buf[off:off + 2 * K].copy_(part.view(torch.uint8))
+            epi = 2 if site else 0
+            rows = M // 2 if epi == 2 else M
+            out = torch.full((rows + 8,), float("nan"), dtype=torch.float16, device="cuda")
+            want = torch.full((rows + 8,), float("nan"), dtype=torch.float16, device="cuda")
+            rc = lib.launch_nvfp4_gemv_fused_ar(ptr(d_p), ptr(d_s), ptr(h), ptr(out), M, K, ptr(w1),
+                                                1e-6, epi, bufs, 0, 1, n, parity, ptr(epoch), site, 2,
+                                                stream())
+            assert rc == 0
+            h_ref = (h_ref.float() + part.float()).half()
+            rc = lib.launch_nvfp4_gemv_fused(ptr(d_p), ptr(d_s), ptr(h_ref), ptr(want), M, K, 1,
+                                             ptr(w1), 1e-6, epi, z, stream())
+            assert rc == 0
+            torch.cuda.synchronize()
+            assert torch.equal(h, h_ref), (step, site)
+            assert torch.equal(out[:rows], want[:rows]) and bool(torch.isnan(out[rows:]).all())
+        epoch += 1
+    assert lib.nvfp4_comm_status(ptr(buf)) == 0
+    one = ctypes.c_void_p(0x1000)
+    f = lib.launch_nvfp4_gemv_fused_ar
+    assert f(one, one, one, one, 16, 96, one, 1e-6, 0, bufs, 0, 1, n, 0, one, 0, 2, None) == -2
+    assert f(one, one, one, one, 16, 128, one, 1e-6, 1, bufs, 0, 1, n, 0, one, 0, 2, None) == -2
+    assert f(one, one, one, one, 16, 128, one, 1e-6, 0, bufs, 0, 1, n, 0, one, 2, 2, None) == -2

@@ -94,7 +94,7 @@ def test_argument_validation(lib):
 
 
 def test_w4a4_activation_quantisation_and_product(lib):
-    # BASELINE configuration 5 semantics: activations quantised per 16-element block along K with
+    # W4A4 semantics (both operands in the block-16 E8M0 format): activations quantised per 16-element block along K with
     # the codec, both operands dequantised, fp32-accumulated product.  Oracle: the codec on the
     # CPU for both operands, float64 matmul.
     import ctypes

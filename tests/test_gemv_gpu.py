@@ -192,7 +192,7 @@ def test_gemv2i_interleaved_activations(lib):
 
 
 def test_config1_full_size(lib):
-    # BASELINE config 1: W [5120, 5120] ~ N(0, 0.02^2), x ~ N(0, 1)
+    # the single-GEMV workload: W [5120, 5120] ~ N(0, 0.02^2), x ~ N(0, 1)
     w = oc.synthetic_weight(5120, 5120, seed=0)
     p, s = oc.encode(w)
     a = oc.synthetic_act(5120, seed=0)
