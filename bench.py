@@ -375,8 +375,8 @@ def init_ranks():
 def tp_parity_check(lib, comm, rank, world):
     """A correctness bit for the multi-GPU record: a K-split layer (5120 x 17408) computed on the
     shards and summed inside the consuming GEMV's prologue, against the same layer unsharded on
-    this GPU.  Every rank draws the same seeded matrix.  Returns the max relative error (floored
-    at 1e-3 of the largest output) of the all-reduced vector."""
+    this GPU.  Every rank draws the same seeded matrix.  Returns max |difference| / max |output|
+    of the all-reduced vector."""
     import torch
 
     vp = ctypes.c_void_p
@@ -411,9 +411,11 @@ def tp_parity_check(lib, comm, rank, world):
     assert rc == 0, rc
     slot2, parity2 = comm.next_slot()      # keep the number of calls even (slot parity per site)
     torch.cuda.synchronize()
+    # each rank's partial vector is rounded to fp16 before the sum (2^-11 of a partial's size, and
+    # the partials are as large as the result), so the error is measured against the largest
+    # output, not element by element
     ref = full.float()
-    err = (h.float() - ref).abs() / torch.clamp(ref.abs(), min=1e-3 * float(ref.abs().max()))
-    return float(err.max())
+    return float((h.float() - ref).abs().max() / ref.abs().max())
 
 
 def run_ours(args):
@@ -661,7 +663,7 @@ def run_ours(args):
         "decode": decode,
     }
     if world > 1:
-        line["tp_parity"] = ({"max_rel_err": parity_max, "ok": bool(parity_max <= 4e-3),
+        line["tp_parity"] = ({"max_err_over_max_output": parity_max, "ok": bool(parity_max <= 2e-3),
                               "layer": "5120x17408 split along K, all-reduced in the consuming "
                                        "GEMV's prologue, against the unsharded GEMV"}
                              if inline else None)

@@ -57,6 +57,7 @@ __global__ void __launch_bounds__(1024)
 allreduce_residual_kernel(CommPeers peers, int rank, int world, int n, int parity,
                           __half* __restrict__ h) {
     pdl_prologue();
+    PDL_FRESH(h);
     __shared__ uint32_t s_seq;
     unsigned char* mine = peers.buf[rank];
     uint32_t* counter = reinterpret_cast<uint32_t*>(mine);
@@ -134,6 +135,8 @@ argmax_exchange_kernel(CommPeers peers, int rank, int world, int n, const __half
                        long long* __restrict__ len, long long* __restrict__ history,
                        long long* __restrict__ hist_count, int hist_cap) {
     pdl_prologue();
+    PDL_FRESH(logits); PDL_FRESH(epoch); PDL_FRESH(tok); PDL_FRESH(pos); PDL_FRESH(len); PDL_FRESH(history);
+    PDL_FRESH(hist_count);
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;

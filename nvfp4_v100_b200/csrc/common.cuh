@@ -94,6 +94,14 @@ static inline int current_device_index() {
 // the programmatic-stream-serialization attribute: it becomes resident while the previous kernel
 // in the stream is still draining, lets ITS successor do the same, and then waits for the
 // previous kernel to complete before touching memory.  Without the attribute both are no-ops.
+// After the wait, every pointer to memory that an earlier kernel may have written goes through
+// PDL_FRESH.  A kernel parameter declared `const T* __restrict__` tells the compiler that the data
+// never changes while the kernel runs, so it may issue such a load anywhere - also ABOVE the wait,
+// while the previous kernel is still writing (seen: a token id read before the kernel that
+// produces it had finished).  An empty asm that "modifies" the pointer makes the value opaque:
+// loads through it cannot move above the asm, and are ordinary coherent loads.
+#define PDL_FRESH(p) asm volatile("" : "+l"(p))
+
 __device__ __forceinline__ void pdl_prologue() {
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
     asm volatile("griddepcontrol.wait;\n" ::: "memory");

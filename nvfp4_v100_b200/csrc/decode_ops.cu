@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(256)
 embed_gather_kernel(const __half* __restrict__ table, const long long* __restrict__ tok,
                     __half* __restrict__ out, int hidden, long long vocab) {
     pdl_prologue();
+    PDL_FRESH(table); PDL_FRESH(tok); PDL_FRESH(out);
     long long id = *tok;
     if (id < 0) id = 0;
     if (id >= vocab) id = vocab - 1;
@@ -89,6 +90,8 @@ attn_prep_kernel(const __half* __restrict__ qkv, const float* __restrict__ q_w1,
                  __half* __restrict__ keys, __half* __restrict__ values, int hq, int hkv,
                  int max_len, float eps) {
     pdl_prologue();
+    PDL_FRESH(qkv); PDL_FRESH(q_w1); PDL_FRESH(k_w1); PDL_FRESH(cos_tab); PDL_FRESH(sin_tab); PDL_FRESH(pos_ptr);
+    PDL_FRESH(q_out); PDL_FRESH(gate_out); PDL_FRESH(keys); PDL_FRESH(values);
     attn_prep_one_token(qkv, q_w1, k_w1, cos_tab, sin_tab, *pos_ptr, q_out, gate_out, keys, values,
                         hq, hkv, max_len, eps);
 }
@@ -103,6 +106,8 @@ attn_prep_tokens_kernel(const __half* __restrict__ qkv, long long ld,
                         __half* __restrict__ keys, __half* __restrict__ values, int hq, int hkv,
                         int max_len, float eps) {
     pdl_prologue();
+    PDL_FRESH(qkv); PDL_FRESH(q_w1); PDL_FRESH(k_w1); PDL_FRESH(cos_tab); PDL_FRESH(sin_tab); PDL_FRESH(q_out);
+    PDL_FRESH(gate_out); PDL_FRESH(keys); PDL_FRESH(values);
     const size_t t = blockIdx.y;
     attn_prep_one_token(qkv + t * (size_t)ld, q_w1, k_w1, cos_tab, sin_tab,
                         (long long)pos0 + (long long)t, q_out + t * (size_t)hq * 256,
@@ -117,6 +122,7 @@ argmax_advance_kernel(const __half* __restrict__ logits, int vocab, long long* _
                       long long* __restrict__ history, long long* __restrict__ hist_count,
                       int hist_cap) {
     pdl_prologue();
+    PDL_FRESH(logits); PDL_FRESH(tok); PDL_FRESH(pos); PDL_FRESH(len); PDL_FRESH(history); PDL_FRESH(hist_count);
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -189,6 +195,7 @@ argmax_advance_kernel(const __half* __restrict__ logits, int vocab, long long* _
 __global__ void __launch_bounds__(256)
 residual_add_kernel(__half* __restrict__ h, const __half* __restrict__ y, int n) {
     pdl_prologue();
+    PDL_FRESH(h); PDL_FRESH(y);
     const int i = (blockIdx.x * 256 + threadIdx.x) * 2;
     if (i + 1 < n) {
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(h + i));
@@ -229,6 +236,7 @@ __global__ void __launch_bounds__(1024)
 argmax_slice_kernel(const __half* __restrict__ logits, int vocab, long long offset,
                     float* __restrict__ cand) {
     pdl_prologue();
+    PDL_FRESH(logits); PDL_FRESH(cand);
     __shared__ float s_v[32];
     __shared__ int s_i[32];
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;

@@ -31,9 +31,10 @@ encode_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed,
     // Waits for its predecessor but does NOT let its successor start early: what it writes are
     // weights, and the GEMV requests weights before waiting for the kernel in front of it.
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    PDL_FRESH(src);
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x; b < nblocks; b += stride) {
-        const uint4 v0 = __ldg(src + 2 * b), v1 = __ldg(src + 2 * b + 1);
+        const uint4 v0 = src[2 * b], v1 = src[2 * b + 1];
         const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
         // magnitudes of fp16 values order like their bit patterns (NaN above inf above finite)
         uint32_t mx = 0;
@@ -80,6 +81,7 @@ decode_rows_kernel(const uint2* __restrict__ packed, const uint8_t* __restrict__
                    const long long* __restrict__ ids, uint4* __restrict__ out, int K,
                    long long table_rows) {
     pdl_prologue();
+    PDL_FRESH(packed); PDL_FRESH(scales); PDL_FRESH(ids); PDL_FRESH(out);
     const int nb = K >> 4;
     const int b = blockIdx.x * 256 + threadIdx.x;
     if (b >= nb) return;
@@ -114,6 +116,7 @@ __global__ void __launch_bounds__(256)
 quant_dequant_T_kernel(const __half* __restrict__ src, long long ld_src, __half* __restrict__ dst,
                        long long ld_dst, int n) {
     pdl_prologue();
+    PDL_FRESH(src); PDL_FRESH(dst);
     const int t = blockIdx.x * 256 + threadIdx.x;
     const int b = blockIdx.y;
     if (t >= ld_dst) return;

@@ -24,6 +24,7 @@ __global__ void __launch_bounds__(THREADS)
 rmsnorm_kernel(const __half* __restrict__ x, long long row_stride, const float* __restrict__ w1,
                __half* __restrict__ out, int n, float eps) {
     pdl_prologue();
+    PDL_FRESH(x); PDL_FRESH(w1); PDL_FRESH(out);
     __shared__ float s_red[THREADS / 32];
     __shared__ float s_inv;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
@@ -92,6 +93,7 @@ rope_qk_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
                const __half* __restrict__ cs, const __half* __restrict__ sn,
                __half* __restrict__ q_out, __half* __restrict__ k_out, int hq) {
     pdl_prologue();
+    PDL_FRESH(q); PDL_FRESH(k); PDL_FRESH(cs); PDL_FRESH(sn); PDL_FRESH(q_out); PDL_FRESH(k_out);
     const int h = blockIdx.x, d = threadIdx.x;  // d in [0,128): handles d and d+128
     const bool is_q = h < hq;
     const size_t off = (size_t)(is_q ? h : h - hq) * 256;
@@ -115,6 +117,7 @@ __global__ void __launch_bounds__(256)
 silu_mul_kernel(const __half* __restrict__ g, const __half* __restrict__ u,
                 __half* __restrict__ out, int n) {
     pdl_prologue();
+    PDL_FRESH(g); PDL_FRESH(u); PDL_FRESH(out);
     const int i = blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     const float gf = __half2float(g[i]), uf = __half2float(u[i]);
@@ -258,6 +261,7 @@ attn_decode_kernel(const __half* __restrict__ q, const __half* __restrict__ keys
                    const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
                    int gqa, float scale) {
     pdl_prologue();
+    PDL_FRESH(q); PDL_FRESH(keys); PDL_FRESH(values); PDL_FRESH(cum_len); PDL_FRESH(gate); PDL_FRESH(out);
     long long L64 = *cum_len;
     if (L64 > max_len) L64 = max_len;  // never index past the cache
     if (L64 < 0) L64 = 0;
@@ -287,6 +291,7 @@ dn_conv_kernel(const __half* __restrict__ mixed, const __half* __restrict__ conv
     // dn_rec_kernel on the same state, when two tokens are processed back to back — has finished.
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    PDL_FRESH(mixed); PDL_FRESH(conv_state); PDL_FRESH(scratch);
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= conv_dim) return;
     // state and weights of a channel are 4 consecutive halves: one 8-byte load each
@@ -331,6 +336,7 @@ dn_rec_kernel(const __half* __restrict__ z_in, const __half* __restrict__ b_in,
 #pragma unroll
     for (int r = 0; r < 8; r++) S[r] = *reinterpret_cast<const float4*>(Sbase + (size_t)r * DN_DK);
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    PDL_FRESH(z_in); PDL_FRESH(b_in); PDL_FRESH(a_in); PDL_FRESH(scratch); PDL_FRESH(out);
 
     const float beta = round_f16(1.0f / (1.0f + expf(-__half2float(b_in[h]))));
     const float gdec = -expf(__half2float(A_log[h])) *
@@ -413,6 +419,8 @@ attn_decode_split_kernel(const __half* __restrict__ q, const __half* __restrict_
                          float* __restrict__ part, unsigned int* __restrict__ counters,
                          int max_len, int gqa, float scale) {
     pdl_prologue();
+    PDL_FRESH(q); PDL_FRESH(keys); PDL_FRESH(values); PDL_FRESH(cum_len); PDL_FRESH(gate); PDL_FRESH(out);
+    PDL_FRESH(part); PDL_FRESH(counters);
     __shared__ float s_part[ATS_WARPS][ATS_PART];
     __shared__ unsigned int s_last;
     const int h = blockIdx.x, sp = blockIdx.y, kv = h / gqa;
@@ -534,6 +542,7 @@ attn_prefill_group_kernel(const __half* __restrict__ q, const __half* __restrict
                           const __half* __restrict__ gate, __half* __restrict__ out, int max_len,
                           int gqa, float scale, int lcap) {
     pdl_prologue();
+    PDL_FRESH(q); PDL_FRESH(keys); PDL_FRESH(values); PDL_FRESH(gate); PDL_FRESH(out);
     extern __shared__ float s_sc[];                 // [ATT_G][lcap]
     __shared__ float s_q[ATT_G][ATT_D];
     __shared__ float s_red[ATT_G][ATT_WARPS];

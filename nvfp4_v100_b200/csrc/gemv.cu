@@ -261,6 +261,12 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
     // compiler is free to move above the wait; taking their base pointer through an asm statement
     // that is ordered after the wait pins them behind it.
     asm volatile("" : "+l"(xsrc));
+    PDL_FRESH(act0); PDL_FRESH(out);
+    {
+        const __half* res = ex.residual;    // the residual stream is the previous kernels' output
+        PDL_FRESH(res);
+        ex.residual = res;
+    }
 
     if (PRO == PRO_AR_RMSNORM) {
         // Tensor-parallel: act0 is the residual stream h, still missing the sum over the ranks of

@@ -33,6 +33,7 @@ __global__ void __launch_bounds__(256)
 transpose_f16_kernel(const __half* __restrict__ src, long long ld_src, __half* __restrict__ dst,
                      long long ld_dst, int R, int C) {
     pdl_prologue();
+    PDL_FRESH(src); PDL_FRESH(dst);
     __shared__ __half tile[64][66];
     const int r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(256)
 add_transposed_kernel(__half* __restrict__ h, const __half* __restrict__ dT, long long ldT, int n,
                       int C) {
     pdl_prologue();
+    PDL_FRESH(h); PDL_FRESH(dT);
     __shared__ __half tile[64][66];
     const int t0 = blockIdx.x * 64, c0 = blockIdx.y * 64;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -106,6 +108,7 @@ __global__ void __launch_bounds__(256)
 embed_rows_kernel(const __half* __restrict__ table, const long long* __restrict__ ids,
                   __half* __restrict__ out, int hidden, long long vocab) {
     pdl_prologue();
+    PDL_FRESH(table); PDL_FRESH(ids); PDL_FRESH(out);
     long long id = ids[blockIdx.y];
     if (id < 0) id = 0;
     if (id >= vocab) id = vocab - 1;
@@ -124,6 +127,7 @@ embed_rows_kernel(const __half* __restrict__ table, const long long* __restrict_
 __global__ void __launch_bounds__(256)
 silu_mul_rows_kernel(const __half* __restrict__ gu, __half* __restrict__ act, int inter, int N) {
     pdl_prologue();
+    PDL_FRESH(gu); PDL_FRESH(act);
     const int row = blockIdx.y;                       // activation row 0 .. inter-1
     const int t = (blockIdx.x * 256 + threadIdx.x) * 2;
     if (t >= N) return;
@@ -156,6 +160,7 @@ dn_conv_tokens_kernel(const __half* __restrict__ x, long long ld, const __half* 
                       const __half* __restrict__ conv_state, __half* __restrict__ conv_out,
                       int conv_dim) {
     pdl_prologue();
+    PDL_FRESH(x); PDL_FRESH(conv_w); PDL_FRESH(conv_state); PDL_FRESH(conv_out);
     const int c = blockIdx.x * 256 + threadIdx.x;
     const int t = blockIdx.y;
     if (c >= conv_dim) return;
@@ -179,6 +184,7 @@ __global__ void __launch_bounds__(256)
 dn_conv_state_kernel(const __half* __restrict__ x, long long ld, __half* __restrict__ conv_state,
                      int conv_dim, int n) {
     pdl_prologue();
+    PDL_FRESH(x); PDL_FRESH(conv_state);
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= conv_dim) return;
     __half old[4], nw[4];
@@ -202,6 +208,8 @@ dn_prep_kernel(const __half* __restrict__ conv_out, int conv_dim, const __half* 
                float* __restrict__ qn, float* __restrict__ kn, float2* __restrict__ be, int nk,
                int nv) {
     pdl_prologue();
+    PDL_FRESH(conv_out); PDL_FRESH(x); PDL_FRESH(A_log); PDL_FRESH(dt_bias); PDL_FRESH(qn); PDL_FRESH(kn);
+    PDL_FRESH(be);
     const int t = blockIdx.y, lane = threadIdx.x;
     const int key_dim = nk * PF_DK;
     if ((int)blockIdx.x < nk) {
@@ -289,6 +297,7 @@ dn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
                const float2* __restrict__ be, const __half* __restrict__ conv_out, int conv_dim,
                float* __restrict__ state, __half* __restrict__ o_out, int nk, int nv, int n) {
     pdl_prologue();
+    PDL_FRESH(qn); PDL_FRESH(kn); PDL_FRESH(be); PDL_FRESH(conv_out); PDL_FRESH(state); PDL_FRESH(o_out);
     __shared__ __align__(16) ScanStage stage[2];
     const int per_head = PF_DK / SCAN_ROWS;                  // CTAs per value head
     const int h = blockIdx.x / per_head, part = blockIdx.x % per_head;
@@ -317,7 +326,7 @@ dn_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn,
         }
         if (tid >= 64 && tid < 64 + SCAN_TB) {
             const int tt = tid - 64;
-            s.be[tt] = __ldg(be + (size_t)min(t0 + tt, n - 1) * nv + h);
+            s.be[tt] = be[(size_t)min(t0 + tt, n - 1) * nv + h];
         }
         cp_async_commit();
     };
@@ -422,6 +431,7 @@ dn_post_kernel(const __half* __restrict__ o_in, const __half* __restrict__ x, lo
                int conv_dim, const __half* __restrict__ norm_w, __half* __restrict__ out, int nv,
                float rms_eps) {
     pdl_prologue();
+    PDL_FRESH(o_in); PDL_FRESH(x); PDL_FRESH(norm_w); PDL_FRESH(out);
     const int h = blockIdx.x, t = blockIdx.y, lane = threadIdx.x;
     const uint2 ov = *reinterpret_cast<const uint2*>(o_in + ((size_t)t * nv + h) * PF_DK + lane * 4);
     const __half* oh = reinterpret_cast<const __half*>(&ov);
