@@ -589,7 +589,7 @@ def run_ours(args):
 
     comm_status = comm.status() if comm is not None else 0
     parity_err = None
-    if comm is not None and inline:
+    if comm is not None:
         parity_err = tp_parity_check(lib, comm, rank, world)
 
     # max over ranks
@@ -663,10 +663,9 @@ def run_ours(args):
         "decode": decode,
     }
     if world > 1:
-        line["tp_parity"] = ({"max_err_over_max_output": parity_max, "ok": bool(parity_max <= 2e-3),
-                              "layer": "5120x17408 split along K, all-reduced in the consuming "
-                                       "GEMV's prologue, against the unsharded GEMV"}
-                             if inline else None)
+        line["tp_parity"] = {"max_err_over_max_output": parity_max, "ok": bool(parity_max <= 2e-3),
+                             "layer": "5120x17408 split along K, partial vectors summed over NVLink "
+                                      "peer memory, against the unsharded GEMV"}
     print(json.dumps(line), flush=True)
     shutdown(world)
 
@@ -1000,7 +999,7 @@ def main():
                     help="with --gemm: a single token count instead of 32 and 8192")
     ap.add_argument("--gen", type=int, default=63)
     ap.add_argument("--vocab", type=int, default=VOCAB)
-    ap.add_argument("--allreduce", default="inline", choices=["inline", "fused", "peer", "nccl"],
+    ap.add_argument("--allreduce", default="peer", choices=["inline", "fused", "peer", "nccl"],
                     help="under torchrun: the all-reduce inside the consuming GEMV's prologue, "
                          "GEMV+all-reduce in one kernel (decode only), a separate one-shot "
                          "peer-memory all-reduce kernel, or NCCL (decode only)")

@@ -10,7 +10,8 @@
 #define NVFP4_TAIL_CAND_OFF 0          // float2 pair[2][8]: (value, index bits) per step parity and rank
 #define NVFP4_TAIL_CAND_FLAGS_OFF 128  // u32 flags[8]
 #define NVFP4_TAIL_AR_FLAGS_OFF 160    // u32 flags[8] of the in-GEMV all-reduce
-#define NVFP4_TAIL_AR_READY_OFF 192    // u32: sequence number of the last vector CTA 0 finished
+#define NVFP4_TAIL_AR_READY_OFF 192    // u32: sequence number of the last all-reduce finished here
+#define NVFP4_TAIL_AR_DONE_OFF 196     // u32: CTAs of the running all-reduce that have finished
 #define NVFP4_TAIL_BYTES 256
 
 __host__ __device__ inline long long nvfp4_comm_tail_offset(int n) {

@@ -271,10 +271,14 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
     if (PRO == PRO_AR_RMSNORM) {
         // Tensor-parallel: act0 is the residual stream h, still missing the sum over the ranks of
         // the previous K-split layer's partial vectors (each rank's sits in data slot `parity`
-        // of its communication buffer, written by the previous kernel).  CTA 0 exchanges
-        // "ready" flags with the peers, pulls their vectors, adds the sum to h and publishes a
-        // sequence number; every CTA waits for that number (bounded) before it reads h.  The
-        // weight loads above are already in flight, so the exchange hides behind them.
+        // of its communication buffer, written by the previous kernel).  The first few CTAs
+        // (as many as it takes to cover h with one 16-byte vector per thread) do the exchange:
+        // CTA 0 announces this rank's vector to the peers, each of those CTAs waits (bounded)
+        // for the peers' announcements, pulls its slice of their vectors over NVLink (all peers'
+        // loads in flight together: one round trip), adds the sum to h and counts itself in; the
+        // last of them publishes the sequence number, which every CTA waits for (bounded) before
+        // it reads h.  The weight loads above
+        // are already in flight, so the exchange hides behind them.
         unsigned char* mine = ex.comm[ex.rank];
         const long long tail = nvfp4_comm_tail_offset(ex.comm_n);
         uint32_t* errw = reinterpret_cast<uint32_t*>(mine) + 1;
@@ -283,15 +287,18 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
                                  (uint32_t)ex.n_sites + (uint32_t)ex.site + 1u;
         const int tid = threadIdx.x;
         constexpr int T = WARPS * 32;
-        if (blockIdx.x == 0) {
+        const int n_ar = min((int)gridDim.x, (K / 8 + T - 1) / T);    // CTAs that do the exchange
+        if ((int)blockIdx.x < n_ar) {
             __shared__ int s_bad;
             if (tid == 0) s_bad = 0;
             __syncthreads();
             if (tid < ex.world && tid != ex.rank) {
-                __threadfence_system();   // this rank's partial vector (previous kernel) first
-                uint32_t* pf = reinterpret_cast<uint32_t*>(ex.comm[tid] + tail +
-                                                           NVFP4_TAIL_AR_FLAGS_OFF) + ex.rank;
-                asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(pf), "r"(seq) : "memory");
+                if (blockIdx.x == 0) {
+                    __threadfence_system();   // this rank's partial vector (previous kernel) first
+                    uint32_t* pf = reinterpret_cast<uint32_t*>(ex.comm[tid] + tail +
+                                                               NVFP4_TAIL_AR_FLAGS_OFF) + ex.rank;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;\n" ::"l"(pf), "r"(seq) : "memory");
+                }
                 const uint32_t* mf = reinterpret_cast<const uint32_t*>(mine + tail +
                                                                        NVFP4_TAIL_AR_FLAGS_OFF) + tid;
                 uint32_t spins = 0, v;
@@ -308,7 +315,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
             if (!s_bad) {    // a missing peer's slot holds stale bytes: leave h as it is
                 __half* h = const_cast<__half*>(act0);
                 const size_t slot = NVFP4_COMM_DATA_OFF + (size_t)ex.parity * (size_t)ex.comm_n * 2;
-                for (int i = tid * 8; i < K; i += T * 8) {
+                for (int i = ((int)blockIdx.x * T + tid) * 8; i < K; i += n_ar * T * 8) {
                     uint4 v[8];
 #pragma unroll
                     for (int r = 0; r < 8; r++) {
@@ -343,16 +350,27 @@ gemv_mma_kernel(const uint8_t* __restrict__ packed, const uint8_t* __restrict__ 
                     *reinterpret_cast<uint4*>(h + i) = hv;
                 }
             }
-            __threadfence();
+            // this CTA's writes to h, then its count: the barrier orders the other threads'
+            // stores before thread 0's release
             __syncthreads();
-            if (tid == 0)
-                asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(ready), "r"(seq) : "memory");
+            if (tid == 0) {
+                // the last of the n_ar CTAs to get here publishes the sequence number
+                uint32_t* done = reinterpret_cast<uint32_t*>(mine + tail + NVFP4_TAIL_AR_DONE_OFF);
+                uint32_t old;
+                asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;\n"
+                             : "=r"(old) : "l"(done) : "memory");
+                if (old == (uint32_t)n_ar - 1u) {
+                    *done = 0u;
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(ready), "r"(seq) : "memory");
+                }
+            }
         }
         if (tid == 0) {
             uint32_t spins = 0, v;
             do {
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(ready) : "memory");
                 if ((int32_t)(v - seq) >= 0) break;
+                __nanosleep(64);
             } while (++spins <= NVFP4_PUSH_SPIN_LIMIT);
             if ((int32_t)(v - seq) < 0) atomicExch(errw, 299u);
         }

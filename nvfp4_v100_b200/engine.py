@@ -112,16 +112,17 @@ class DecodeEngine:
     """Holds the prepared weights and all state of one sequence and replays the step graph."""
 
     def __init__(self, cfg: ModelConfig, device: str = "cuda", tp_rank: int = 0, tp_world: int = 1,
-                 allreduce: str = "inline"):
+                 allreduce: str = "peer"):
         """tp_world > 1: this process holds shard tp_rank of a tensor-parallel group (one process
         per GPU, torch.distributed initialised with the NCCL backend by the caller).
-        allreduce: "inline" = the K-split GEMV writes its partial vector into the peer-visible
-        buffer and the NEXT GEMV's prologue does the exchange, the sum, the residual add and the
-        RMSNorm (no kernel of its own per all-reduce; the greedy pick is exchanged the same way,
-        so a step contains no library collective); "fused" = the K-split GEMV, its all-reduce and
-        the residual add are ONE kernel (peer stores per tile, last CTA reduces); "peer" = GEMV,
-        then this library's one-shot all-reduce + residual kernel over NVLink peer memory; "nccl"
-        = GEMV, NCCL all-reduce, then a residual-add kernel."""
+        allreduce: "peer" (default, the fastest measured at 2 GPUs) = GEMV, then this library's
+        one-shot all-reduce + residual kernel over NVLink peer memory; "inline" = the K-split GEMV
+        writes its partial vector into the peer-visible buffer and the NEXT GEMV's prologue does
+        the exchange, the sum, the residual add and the RMSNorm (no kernel of its own per
+        all-reduce); "fused" = the K-split GEMV, its all-reduce and the residual add are ONE
+        kernel (peer stores per tile, last CTA reduces); "nccl" = GEMV, NCCL all-reduce, then a
+        residual-add kernel.  In "peer" and "inline" the greedy pick is exchanged through peer
+        memory as well, so a decode step contains no library collective."""
         if not torch.cuda.is_available():
             raise RuntimeError("DecodeEngine needs a CUDA device; there is no CPU fallback")
         self.cfg = cfg
@@ -490,7 +491,7 @@ class DecodeEngine:
                 self.hist_cap, st)
             assert rc == 0, rc
             self.n_launch += 1
-        elif self.allreduce == "inline":
+        elif self.allreduce in ("inline", "peer"):
             rc = lib.launch_argmax_exchange(
                 vp(self.logits.data_ptr()), self.v_hi - self.v_lo, self.v_lo, self.comm.ptrs,
                 self.rank, self.world, c.hidden, vp(self.epoch.data_ptr()), vp(self.tok.data_ptr()),
