@@ -27,6 +27,7 @@ void* gpu_malloc(size_t bytes);
 void gpu_free(void* p);
 int gpu_memcpy_h2d(void* dst, const void* src, size_t bytes);
 int gpu_memcpy_d2h(void* dst, const void* src, size_t bytes);
+int gpu_memcpy_d2d(void* dst, const void* src, size_t bytes);  /* no counterpart in the reference */
 int gpu_sync(void);                                              /* kernels/nvfp4_cuda_v5.cu:433 */
 int get_gpu_info(char* name_buf, int buf_size, int* cc_major, int* cc_minor); /* :447-457 */
 int nvfp4_b200_abi_version(void);                    /* no counterpart in the reference */
@@ -332,14 +333,29 @@ int launch_nvfp4_encode(const void* src_fp16, void* packed, void* scales, int M,
 int launch_nvfp4_decode_rows(const void* packed, const void* scales, const void* ids, void* out,
                              int n_rows, int K, long long table_rows, void* stream);
 
-/* W4A4 (both operands in the reference's block-16 E8M0 format).  launch_nvfp4_quant_dequant_T:
- * dst[k][t] = dequantise(quantise(src[t][:]))[k], the codec applied per token row along K, written
- * token-minor (rows ld_dst >= n long, tail zeroed).  launch_nvfp4_gemm_w4a4: that, into `work`
- * (fp16, K * N elements, N = n_tokens rounded up to 8), then launch_nvfp4_gemmtc_v5: out[M, N] =
- * dequant(W) . dequant(quant(act))^T with fp32 accumulation.  fp16 holds every FP4 value times its
- * power-of-two scale exactly, so the result is what a block-scaled FP4 x FP4 tensor-core product
- * accumulating in fp32 gives; it runs at the fp16 tensor rate, not the FP4 rate.  No counterpart
- * in the reference, which is W4A16 throughout.  0; -2 bad arguments; else a launch error. */
+/* W4A4 (both operands in the reference's block-16 E8M0 format).  No counterpart in the reference,
+ * which is W4A16 throughout (its target GPU has no FP4 tensor cores; README.md names W4A4 as the
+ * aim for GPUs that have them).
+ * launch_nvfp4_gemm_fp4: out[m][t] (fp16, row pitch ld_out >= n_tokens) = dequant(W)[m][:] .
+ *   dequant(A)[t][:], W = packed [M][K/2] + scales [M][K/16], A = packed [n_tokens][K/2] + scales
+ *   [n_tokens][K/16].  Block-scaled FP4 tensor-core instruction (tcgen05.mma kind::mxf4nvf4, 16-element
+ *   E8M0 scale blocks): the nibbles and scale bytes go to the tensor core as they are, fp32
+ *   accumulation.  K % 256 == 0, all pointers 16-byte aligned.  0; -2 shape / pointer not taken;
+ *   -3 no tensor-map encoder in the driver; else the launch's cudaError_t.
+ * launch_nvfp4_quant_dequant_T: dst[k][t] = dequantise(quantise(src[t][:]))[k], the codec applied
+ *   per token row along K, written token-minor (rows ld_dst >= n long, tail zeroed).
+ * launch_nvfp4_gemm_w4a4: fp16 activations [n_tokens][K] in, out[M][N] (N = n_tokens rounded up to
+ *   8).  work: K * N fp16 elements of scratch.  Activations are encoded with launch_nvfp4_encode
+ *   into work and multiplied by launch_nvfp4_gemm_fp4; shapes that kernel does not take go through
+ *   launch_nvfp4_quant_dequant_T and launch_nvfp4_gemmtc_v5 (fp16 holds every FP4 value times its
+ *   power-of-two scale exactly, so both routes compute the same products; the second runs at the
+ *   fp16 tensor rate).  0; -2 bad arguments; else a launch error.
+ * nvfp4_gemm_fp4_status: like nvfp4_gemm_status, for the FP4 kernel's bounded waits alone
+ *   (nvfp4_gemm_status reports them as 100 + id). */
+int launch_nvfp4_gemm_fp4(const uint8_t* w_packed, const uint8_t* w_scales, const uint8_t* a_packed,
+                          const uint8_t* a_scales, void* out, int M, int n_tokens, int K, int ld_out,
+                          void* stream);
+int nvfp4_gemm_fp4_status(int reset);
 int launch_nvfp4_quant_dequant_T(const void* src, long long ld_src, void* dst, long long ld_dst,
                                  int n, int K, void* stream);
 int launch_nvfp4_gemm_w4a4(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,

@@ -23,6 +23,7 @@ SIGNATURES = {
     "gpu_free": ([_vp], None),
     "gpu_memcpy_h2d": ([_vp, _vp, _sz], _i),
     "gpu_memcpy_d2h": ([_vp, _vp, _sz], _i),
+    "gpu_memcpy_d2d": ([_vp, _vp, _sz], _i),
     "gpu_sync": ([], _i),
     "get_gpu_info": ([ctypes.c_char_p, _i, ctypes.POINTER(_i), ctypes.POINTER(_i)], _i),
     "nvfp4_b200_abi_version": ([], _i),
@@ -83,6 +84,8 @@ SIGNATURES = {
     "launch_nvfp4_quant_dequant_T": ([_vp, _ll, _vp, _ll, _i, _i, _vp], _i),
     "launch_nvfp4_gemm_w4a4": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "launch_nvfp4_encode": ([_vp, _vp, _vp, _i, _i, _vp], _i),
+    "launch_nvfp4_gemm_fp4": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
+    "nvfp4_gemm_fp4_status": ([_i], _i),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),
 }
 

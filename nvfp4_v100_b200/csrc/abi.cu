@@ -34,6 +34,12 @@ int gpu_memcpy_d2h(void* dst, const void* src, size_t bytes) {
     return (int)cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost);
 }
 
+// device -> device (no counterpart in the reference, whose pair fusion stages such copies through
+// host memory: experiments/_qwen38_p7_pair.py:107-114).  Synchronous.
+int gpu_memcpy_d2d(void* dst, const void* src, size_t bytes) {
+    return (int)cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice);
+}
+
 int gpu_sync() { return (cudaDeviceSynchronize() == cudaSuccess) ? 0 : (int)cudaErrorUnknown; }
 
 int get_gpu_info(char* name_buf, int buf_size, int* cc_major, int* cc_minor) {

@@ -348,22 +348,38 @@ int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weig
 
 // W4A4 product with the reference format on both sides: out[M, N] = dequant(W) .
 // dequant(quant(act))^T, activations token-major [n_tokens][K] fp16, quantised per 16-element
-// block along K by the codec's rule.  work: fp16 scratch of K * N elements, N = n_tokens rounded
-// up to a multiple of 8 = the row length of `out`.  Two launches: launch_nvfp4_quant_dequant_T
-// into work, then the tensor-core GEMM (fp16 operands hold the FP4 values exactly; fp32
-// accumulation).  0, -2 for bad arguments, or a launch error code.
+// block along K by the codec's rule.  work: scratch of K * N fp16 elements, N = n_tokens rounded
+// up to a multiple of 8 = the row length of `out`.
+// K % 256 == 0 and aligned pointers: the activations are encoded to NVFP4 bytes in `work`
+// (launch_nvfp4_encode) and the product runs on the block-scaled FP4 tensor-core path
+// (launch_nvfp4_gemm_fp4); nothing is expanded to fp16.  Other shapes: launch_nvfp4_quant_dequant_T
+// into work, then the W4A16 tensor-core GEMM (fp16 holds every FP4 value times its scale exactly;
+// fp32 accumulation).  0, -2 for bad arguments, or a launch error code.
 int launch_nvfp4_gemm_w4a4(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
                            const void* d_activation, void* d_output, void* work, int M,
                            int n_tokens, int K, void* stream) {
-    if (!work || n_tokens <= 0) return NVFP4_ERR_SHAPE;
+    if (!work || n_tokens <= 0 || M <= 0 || K <= 0 || K % 16 != 0) return NVFP4_ERR_SHAPE;
     const int N = (n_tokens + 7) / 8 * 8;
+    if (K % 256 == 0 && (((uintptr_t)work | (uintptr_t)d_activation) & 15) == 0) {
+        uint8_t* a_packed = static_cast<uint8_t*>(work);
+        const size_t pbytes = ((size_t)n_tokens * (size_t)(K / 2) + 255) & ~(size_t)255;
+        uint8_t* a_scales = a_packed + pbytes;
+        int rc = launch_nvfp4_encode(d_activation, a_packed, a_scales, n_tokens, K, stream);
+        if (rc == 0) {
+            rc = launch_nvfp4_gemm_fp4(d_weight_packed, d_weight_scales, a_packed, a_scales, d_output,
+                                       M, n_tokens, K, N, stream);
+            if (rc != NVFP4_ERR_SHAPE && rc != -3) return rc;
+        } else if (rc != NVFP4_ERR_SHAPE) {
+            return rc;
+        }
+    }
     const int rc = launch_nvfp4_quant_dequant_T(d_activation, K, work, N, n_tokens, K, stream);
     if (rc != 0) return rc;
     return launch_nvfp4_gemmtc_v5(d_weight_packed, d_weight_scales, work, d_output, M, N, K,
                                   stream);
 }
 
-// 0 if no bounded wait inside the tensor-core GEMM has run out since the library was loaded (or
+// 0 if no bounded wait inside the tensor-core GEMMs (W4A16 and FP4) has run out since the library was loaded (or
 // since the last call with reset != 0); otherwise 1 + the id of the wait.  Synchronises the device.
 int nvfp4_gemm_status(int reset) {
     int v = 0;
@@ -372,6 +388,8 @@ int nvfp4_gemm_status(int reset) {
         const int z = 0;
         cudaMemcpyToSymbol(nvfp4::g_gemm_status, &z, sizeof(int));
     }
+    const int f = nvfp4_gemm_fp4_status(reset);   // the FP4 kernel's waits: ids 100 + its own
+    if (v == 0 && f != 0) v = (f < 0) ? f : 100 + f;
     return v;
 }
 

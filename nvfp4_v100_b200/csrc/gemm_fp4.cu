@@ -1,0 +1,345 @@
+// W4A4 GEMM on the block-scaled FP4 tensor-core path:
+//   out[M, ld_out] (fp16) = dequant(W)[M, K] . dequant(A)[n_tokens, K]^T
+// Both operands stay in the container's format all the way into the tensor core: E2M1 nibbles, two
+// per byte (low nibble = even element), one E8M0 scale byte per 16 elements along K
+// (codec/nvfp4_codec.py:13-19 layout, :60-86 decode rule).  No fp16 copy of either operand is made;
+// tcgen05.mma kind::mxf4nvf4 with 16-element scale blocks multiplies the nibbles, applies both block
+// scales and accumulates in fp32 in tensor memory.  This is the FP4 path the reference names as its
+// aim for tensor cores that have it (README.md "W4A4", kernels/nvfp4_cuda_v5.cu:1-20 keeps W4A16
+// because its target GPU has none).
+//
+// One CTA (192 threads) computes a 128-row x BN-token tile, K in stages of 256 elements:
+//   warp 0      TMA producer: per stage one box of weight bytes (128 rows x 128 B) and one box of
+//               activation bytes (BN tokens x 128 B), both K-major with the 128-byte swizzle, into an
+//               ST-stage shared-memory ring; completion by transaction bytes on an mbarrier.
+//   warp 1      MMA issuer: 4 tcgen05.mma (K = 64 each) per stage, one elected thread;
+//               tcgen05.commit hands the stage back.
+//   warps 2..5  scale-factor writers, then the epilogue.  The tensor core reads the scale bytes from
+//               tensor memory: for an operand row r (weight row or token) of the tile, lane r % 32,
+//               32-bit column r / 32 holds the row's 4 scale bytes of one 64-element K block, the
+//               same in all four 32-lane quarters.  Each of the 4 warps owns one quarter: a lane
+//               loads 16 scale bytes (one stage) of each of its rows from global memory and writes
+//               them with tcgen05.st.  Per stage 16 columns for the weights and BN / 8 for the tokens.
+// Tensor memory: BN accumulator columns + ST x (16 + BN/8) scale columns.
+//
+// Every wait is bounded (status word, see nvfp4_gemm_fp4_status); a CTA always runs to its end and
+// frees its tensor memory.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+#include "tmap.cuh"
+
+namespace nvfp4 {
+
+constexpr int F4_BM = 128;
+constexpr int F4_BK = 256;                 // elements of K per stage = 128 bytes per row
+constexpr int F4_THREADS = 192;
+constexpr uint32_t F4_SPIN_LIMIT = 1u << 24;
+
+__device__ int g_fp4_status = 0;           // 0 ok; otherwise 1 + id of the wait that ran out
+
+__device__ __forceinline__ bool f4_wait(uint32_t bar, uint32_t parity, int id) {
+    for (uint32_t i = 0; i < F4_SPIN_LIMIT; i++)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicExch(&g_fp4_status, 1 + id);
+    return false;
+}
+
+__device__ __forceinline__ void tcgen05_mma_fp4_block16(uint32_t taddr, uint64_t adesc, uint64_t bdesc,
+                                                        uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::
+            "r"(taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_wait_st() {
+    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+}
+// tcgen05.st, shape 32x32b: lane l of the warp writes NR consecutive 32-bit columns of its own lane
+template <int NR>
+__device__ __forceinline__ void tcgen05_st_32x32b(uint32_t taddr, const uint32_t* r) {
+    static_assert(NR == 1 || NR == 2 || NR == 4 || NR == 8, "column count");
+    if constexpr (NR == 1)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};\n" ::"r"(taddr), "r"(r[0]) : "memory");
+    else if constexpr (NR == 2)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x2.b32 [%0], {%1,%2};\n" ::"r"(taddr), "r"(r[0]),
+                     "r"(r[1]) : "memory");
+    else if constexpr (NR == 4)
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(taddr), "r"(r[0]),
+                     "r"(r[1]), "r"(r[2]), "r"(r[3]) : "memory");
+    else
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n" ::"r"(taddr),
+                     "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                     : "memory");
+}
+
+__host__ __device__ constexpr int f4_tmem_cols(int need) { return need <= 32 ? 32 : need <= 64 ? 64 : need <= 128 ? 128 : need <= 256 ? 256 : 512; }
+
+template <int BN, int ST>
+__global__ void __launch_bounds__(F4_THREADS)
+gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
+                             const __grid_constant__ CUtensorMap a_map,
+                             const uint8_t* __restrict__ w_scales, const uint8_t* __restrict__ a_scales,
+                             __half* __restrict__ out, int M, int n_tokens, int K, int ld_out) {
+    constexpr int A_BYTES = F4_BM * 128;             // weight tile of a stage
+    constexpr int B_BYTES = BN * 128;                // token tile of a stage
+    constexpr int NB = BN / 32;                      // token rows per lane = SFB columns per MMA
+    constexpr int SFA_COLS = 16, SFB_COLS = 4 * NB, SF_COLS = SFA_COLS + SFB_COLS;
+    constexpr int TCOLS = f4_tmem_cols(BN + ST * SF_COLS);
+    static_assert(BN + ST * SF_COLS <= 512, "tensor memory");
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + ST * A_BYTES;
+    __shared__ __align__(8) uint64_t bar_full[ST];    // TMA bytes landed
+    __shared__ __align__(8) uint64_t bar_sf[ST];      // scale bytes written to tensor memory
+    __shared__ __align__(8) uint64_t bar_empty[ST];   // the stage's MMAs retired
+    __shared__ __align__(8) uint64_t bar_accum;
+    __shared__ uint32_t s_tmem;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * F4_BM, n0 = blockIdx.y * BN;
+    const int ksteps = K / F4_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < ST; s++) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_sf[s]), 128);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_accum), 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        tcgen05_alloc(smem_u32(&s_tmem), TCOLS);
+        tcgen05_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t tmem_sf = tmem + BN;               // scale columns follow the accumulator
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < ksteps; it++) {
+                const int s = it % ST;
+                const uint32_t ph = (uint32_t)(it / ST) & 1u;
+                if (!f4_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 0)) break;
+                const uint32_t bar = smem_u32(&bar_full[s]);
+                mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES);
+                // coordinates: x = byte along K (a multiple of 128), y = row; rows past the end
+                // of either matrix are filled with zero bytes by the copy engine
+                tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, it * 128, m0, bar);
+                tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, it * 128, n0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // block-scaled instruction descriptor: A and B E2M1 (code 1) K-major, N = BN, scale
+            // type E8M0, M = 128, scale-factor ids 0 (a block-16 MMA consumes all four bytes of a
+            // column), K = 64
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (1u << 23) |
+                                   ((uint32_t)(F4_BM >> 4) << 24);
+            for (int it = 0; it < ksteps; it++) {
+                const int s = it % ST;
+                const uint32_t ph = (uint32_t)(it / ST) & 1u;
+                if (!f4_wait(smem_u32(&bar_sf[s]), ph, 1)) break;
+                if (!f4_wait(smem_u32(&bar_full[s]), ph, 2)) break;
+                tcgen05_fence_after();
+                const uint32_t a_base = smem_u32(smem_a + s * A_BYTES);
+                const uint32_t b_base = smem_u32(smem_b + s * B_BYTES);
+                const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS);
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {
+                    // 64 elements of K = 32 bytes further along the swizzled 128-byte row
+                    const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
+                    const uint64_t bdesc = make_desc_sw128(b_base + kk * 32, 16, 1024);
+                    tcgen05_mma_fp4_block16(tmem, adesc, bdesc, idesc, sf + (uint32_t)(kk * 4),
+                                            sf + (uint32_t)(SFA_COLS + kk * NB), (it | kk) != 0 ? 1u : 0u);
+                }
+                tcgen05_commit(smem_u32(&bar_empty[s]));
+            }
+            tcgen05_commit(smem_u32(&bar_accum));
+        }
+    } else {
+        // ---------------- scale-factor writers ----------------
+        const int q = warp & 3;                            // this warp's 32-lane quarter
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        const size_t sf_pitch = (size_t)(K >> 4);
+        const uint8_t* wrow[4];
+        bool wok[4];
+#pragma unroll
+        for (int c = 0; c < 4; c++) {
+            const int r = m0 + c * 32 + lane;
+            wok[c] = r < M;
+            wrow[c] = w_scales + (size_t)min(r, M - 1) * sf_pitch;
+        }
+        const uint8_t* arow[NB];
+        bool aok[NB];
+#pragma unroll
+        for (int c = 0; c < NB; c++) {
+            const int t = n0 + c * 32 + lane;
+            aok[c] = t < n_tokens;
+            arow[c] = a_scales + (size_t)min(t, n_tokens - 1) * sf_pitch;
+        }
+        const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+        uint4 wv[4], av[NB];
+#pragma unroll
+        for (int c = 0; c < 4; c++) wv[c] = wok[c] ? __ldg(reinterpret_cast<const uint4*>(wrow[c])) : zero4;
+#pragma unroll
+        for (int c = 0; c < NB; c++) av[c] = aok[c] ? __ldg(reinterpret_cast<const uint4*>(arow[c])) : zero4;
+        bool ok = true;
+        for (int it = 0; it < ksteps; it++) {
+            const int s = it % ST;
+            const uint32_t ph = (uint32_t)(it / ST) & 1u;
+            // column 4 kk + c (weights) / kk NB + c (tokens) = word kk of row c's 16 bytes
+            uint32_t wa[4][4], wb[4][NB];
+#pragma unroll
+            for (int c = 0; c < 4; c++) { wa[0][c] = wv[c].x; wa[1][c] = wv[c].y; wa[2][c] = wv[c].z; wa[3][c] = wv[c].w; }
+#pragma unroll
+            for (int c = 0; c < NB; c++) { wb[0][c] = av[c].x; wb[1][c] = av[c].y; wb[2][c] = av[c].z; wb[3][c] = av[c].w; }
+            if (it + 1 < ksteps) {           // the next stage's bytes travel while this one waits
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+                    wv[c] = wok[c] ? __ldg(reinterpret_cast<const uint4*>(wrow[c] + (size_t)(it + 1) * 16)) : zero4;
+#pragma unroll
+                for (int c = 0; c < NB; c++)
+                    av[c] = aok[c] ? __ldg(reinterpret_cast<const uint4*>(arow[c] + (size_t)(it + 1) * 16)) : zero4;
+            }
+            if (ok) ok = f4_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 3);
+            tcgen05_fence_after();
+            const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS) + lane_base;
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                tcgen05_st_32x32b<4>(sf + (uint32_t)(kk * 4), wa[kk]);
+                tcgen05_st_32x32b<NB>(sf + (uint32_t)(SFA_COLS + kk * NB), wb[kk]);
+            }
+            tcgen05_wait_st();
+            tcgen05_fence_before();
+            mbar_arrive(smem_u32(&bar_sf[s]));
+        }
+
+        // ---------------- epilogue: tensor memory -> fp16 out[m][token] ----------------
+        f4_wait(smem_u32(&bar_accum), 0, 4);
+        tcgen05_fence_after();
+        const int m = m0 + q * 32 + lane;
+#pragma unroll 1
+        for (int cb = 0; cb < BN / 32; cb++) {
+            uint32_t v[32];
+            tcgen05_ld_32x32b_x32(tmem + lane_base + (uint32_t)(cb * 32), v);
+            tcgen05_wait_ld();
+            const int nb = n0 + cb * 32;
+            if (m < M && nb < n_tokens) {
+                __half* orow = out + (size_t)m * (size_t)ld_out + nb;
+                if (nb + 32 <= n_tokens && (ld_out & 7) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 o;
+                        __half2 t;
+                        t = __floats2half2_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                        o.x = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        o.y = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                        o.z = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                        o.w = *reinterpret_cast<uint32_t*>(&t);
+                        *reinterpret_cast<uint4*>(orow + j) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (nb + j < n_tokens) orow[j] = __float2half(__uint_as_float(v[j]));
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 0) tcgen05_dealloc(tmem, TCOLS);
+}
+
+template <int BN, int ST>
+static cudaError_t launch_fp4(const CUtensorMap& wm, const CUtensorMap& am, const uint8_t* ws,
+                              const uint8_t* as, __half* out, int M, int n, int K, int ld,
+                              cudaStream_t st) {
+    constexpr int SMEM = ST * (F4_BM * 128 + BN * 128) + 1024;
+    static bool attr[NVFP4_MAX_DEVICES] = {false};
+    const int dev = current_device_index();
+    if (!attr[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_fp4_block_scaled_kernel<BN, ST>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return e;
+        attr[dev] = true;
+    }
+    dim3 grid((unsigned)((M + F4_BM - 1) / F4_BM), (unsigned)((n + BN - 1) / BN));
+    gemm_fp4_block_scaled_kernel<BN, ST><<<grid, F4_THREADS, SMEM, st>>>(wm, am, ws, as, out, M, n, K, ld);
+    return cudaGetLastError();
+}
+
+static bool byte_matrix_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, int rows, int K,
+                            int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+    const cuuint32_t box[2] = {128, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+               CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace nvfp4
+
+extern "C" {
+
+// out[m][t] (fp16, row pitch ld_out elements) = sum_k dequant(W)[m][k] * dequant(A)[t][k], both
+// operands NVFP4 (packed [rows][K/2] + E8M0 scales [rows][K/16]).  K % 256 == 0; all five
+// pointers 16-byte aligned; ld_out >= n_tokens.  0; -2 for a shape or pointer this kernel does not
+// take (callers then use the W4A16 route); -3 when the driver offers no tensor-map encoder; or the
+// cudaError_t of the launch.
+int launch_nvfp4_gemm_fp4(const uint8_t* w_packed, const uint8_t* w_scales, const uint8_t* a_packed,
+                          const uint8_t* a_scales, void* out, int M, int n_tokens, int K, int ld_out,
+                          void* stream) {
+    using namespace nvfp4;
+    if (M <= 0 || n_tokens <= 0 || K <= 0 || K % F4_BK != 0 || ld_out < n_tokens) return NVFP4_ERR_SHAPE;
+    if (!w_packed || !w_scales || !a_packed || !a_scales || !out) return NVFP4_ERR_SHAPE;
+    if ((((uintptr_t)w_packed | (uintptr_t)w_scales | (uintptr_t)a_packed | (uintptr_t)a_scales |
+          (uintptr_t)out) & 15) != 0)
+        return NVFP4_ERR_SHAPE;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return -3;
+    const int BN = n_tokens > 128 ? 256 : n_tokens > 64 ? 128 : n_tokens > 32 ? 64 : 32;
+    CUtensorMap wm, am;
+    if (!byte_matrix_map(enc, &wm, w_packed, M, K, F4_BM) ||
+        !byte_matrix_map(enc, &am, a_packed, n_tokens, K, BN))
+        return -3;
+    cudaStream_t st = (cudaStream_t)stream;
+    __half* o = static_cast<__half*>(out);
+    const cudaError_t e =
+        BN == 256 ? launch_fp4<256, 4>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
+      : BN == 128 ? launch_fp4<128, 6>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
+      : BN == 64  ? launch_fp4<64, 8>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
+                  : launch_fp4<32, 8>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st);
+    return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+// 0 if no bounded wait inside the FP4 GEMM has run out since the library was loaded (or since the
+// last call with reset != 0); otherwise 1 + the id of the wait.  Synchronises the device.
+int nvfp4_gemm_fp4_status(int reset) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, nvfp4::g_fp4_status, sizeof(int)) != cudaSuccess) return -1;
+    if (reset) {
+        const int z = 0;
+        cudaMemcpyToSymbol(nvfp4::g_fp4_status, &z, sizeof(int));
+    }
+    return v;
+}
+
+}  // extern "C"

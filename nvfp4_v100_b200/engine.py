@@ -28,6 +28,7 @@ vp = ctypes.c_void_p
 HEAD_DIM = 256      # attention head dim (fixed by the kernels)
 DN_DIM = 128        # DeltaNet head dim (fixed by the kernels)
 CONV_K = 4
+PREFILL_MAX_CONTEXT = 9600   # launch_attn_prefill: 4 query rows x context x 4 bytes <= 150 KB
 
 
 @dataclass
@@ -106,6 +107,50 @@ class _Layer:
     w_gu: _Mat = None
     w_down: _Mat = None
     extra: dict = field(default_factory=dict)
+
+
+class ContainerWeights:
+    """Read-only mapping from the engine's weight names (``layers.3.self_attn.q_proj``,
+    ``layers.3.input_layernorm.weight``, ``embed_tokens``, ``norm.weight``, ``lm_head``) to the
+    contents of a reference container.  Matrices come back as (packed [M, K/2], scales [M, K/16])
+    numpy VIEWS of the memory-mapped ``nvfp4_packed.bin`` — nothing is read until it is sliced and
+    copied; vectors come from ``fp32_misc.npz``; the embedding table is the memory-mapped
+    ``fp16_embed.npy``."""
+
+    PREFIX = "model.language_model."
+
+    def __init__(self, directory: str):
+        import json
+        import os
+
+        self.directory = directory
+        with open(os.path.join(directory, "nvfp4_index.json"), encoding="utf-8") as f:
+            self.index = json.load(f)
+        self.blob = np.memmap(os.path.join(directory, "nvfp4_packed.bin"), dtype=np.uint8, mode="r")
+        self.misc = np.load(os.path.join(directory, "fp32_misc.npz"))
+        self.embed = np.load(os.path.join(directory, "fp16_embed.npy"), mmap_mode="r")
+        self.bytes_viewed = 0
+
+    def _matrix(self, key):
+        e = self.index[key]
+        M, K = int(e["M"]), int(e["K"])
+        p = self.blob[int(e["packed_off"]):int(e["packed_off"]) + int(e["packed_bytes"])]
+        s = self.blob[int(e["scales_off"]):int(e["scales_off"]) + int(e["scales_bytes"])]
+        return p.reshape(M, K // 2), s.reshape(M, K // 16)
+
+    def __getitem__(self, name):
+        if name == "embed_tokens":
+            return self.embed
+        if name == "lm_head":
+            return self._matrix("lm_head.weight")
+        full = self.PREFIX + name
+        if full + ".weight" in self.index:
+            return self._matrix(full + ".weight")
+        if full in self.misc.files:
+            a = self.misc[full]
+            # the depthwise conv weight is stored [channels, 1, 4]
+            return a.reshape(a.shape[0], -1) if a.ndim == 3 else a
+        raise KeyError(name)
 
 
 class DecodeEngine:
@@ -358,6 +403,17 @@ class DecodeEngine:
         self.final_w1 = w1("norm.weight")
         lp, ls = weights["lm_head"]
         self.lm_head = mat([tp.shard_rows(lp, ls, self.v_lo, self.v_hi)], c.hidden)
+
+    def load_container(self, directory: str):
+        """Load this rank's shard straight from a reference container (``nvfp4_packed.bin`` +
+        ``nvfp4_index.json`` + ``fp32_misc.npz`` + ``fp16_embed.npy``; layout:
+        pipeline/_qwen38_nvfp4_pack.py:117-124, uploaded per index entry by
+        pipeline/_qwen38_infer.py:91-101).  The file is memory-mapped and every matrix is a view
+        into the map: a rank copies to the device only the bytes of its own shard — whole rows
+        for q/k/v, in_proj, gate/up and lm_head (one contiguous range per row group), a K range
+        of every row for o_proj, out_proj and down_proj (a strided range, gathered into a
+        shard-sized host buffer) — and never holds the full model in host memory."""
+        self.load_weights(ContainerWeights(directory))
 
     # ------------------------------------------------------------------ one step
     def _gemv(self, st, m: _Mat, x, out, pro_w1=None, epi=0, residual=None):
@@ -624,6 +680,12 @@ class DecodeEngine:
         total = len(tokens)
         if start + total > c.max_len:
             raise ValueError("prompt longer than the cache")
+        # the chunk attention kernel keeps a group's scores in shared memory (150 KB): checked
+        # here, before the first launch, because a failure in the middle of a prompt would leave
+        # the caches and states of earlier chunks and layers already advanced
+        if start + total > PREFILL_MAX_CONTEXT:
+            raise ValueError(f"chunked prefill handles contexts up to {PREFILL_MAX_CONTEXT} tokens "
+                             f"(got {start + total}); feed the rest through step()")
         B = self._prefill_buffers(min(chunk, max(total, 1)))
         st = vp(torch.cuda.current_stream().cuda_stream)
         H = c.hidden

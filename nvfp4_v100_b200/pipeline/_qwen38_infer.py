@@ -244,11 +244,20 @@ class QLinear(nn.Module):
                                     _cur_stream()), "gemv2")
 
     def _many(self, x, tokens):
-        xt = x.t().contiguous()                                       # [K, tokens]
-        yt = torch.empty((self.M, tokens), dtype=torch.float16, device=x.device)
-        _ok(V5.launch_nvfp4_gemmtc_v5(self.d_p, self.d_s, _p(xt), _p(yt), self.M, tokens, self.K,
+        # The tensor-core kernel takes token counts that are multiples of 8 (16-byte rows for
+        # its TMA loads); any other count would fall to the CUDA-core kernel, orders of magnitude
+        # slower.  So the token-minor matrices are padded with zero columns and the result is cut
+        # back (the reference's wmma kernel takes any count: kernels/nvfp4_cuda_v5.cu:406-422).
+        padded = (tokens + 7) // 8 * 8
+        if padded == tokens:
+            xt = x.t().contiguous()                                   # [K, tokens]
+        else:
+            xt = torch.zeros((self.K, padded), dtype=torch.float16, device=x.device)
+            xt[:, :tokens] = x.t()
+        yt = torch.empty((self.M, padded), dtype=torch.float16, device=x.device)
+        _ok(V5.launch_nvfp4_gemmtc_v5(self.d_p, self.d_s, _p(xt), _p(yt), self.M, padded, self.K,
                                       _cur_stream()), "gemm")
-        return yt.t().contiguous()
+        return yt[:, :tokens].t().contiguous()
 
     def forward(self, x):
         flat = x.reshape(-1, self.K)

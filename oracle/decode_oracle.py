@@ -164,3 +164,41 @@ class OracleModel:
             if len(toks) < n_gen:
                 logits = self.step(nxt)
         return toks, all_logits, margins
+
+
+def make_weights_random_bytes(cfg, seed: int, norm_jitter: float = 0.1):
+    """Like :func:`make_weights`, but every linear weight is drawn directly as NVFP4 bytes
+    (uniform packed bytes, scale bytes uniform in [118, 122]: values of about the size
+    N(0, 0.02^2) weights quantise to), so a full-width model can be built in seconds instead of
+    being quantised on the CPU for minutes.  Any byte pattern is a valid NVFP4 matrix."""
+    rng = np.random.default_rng(seed)
+    W = {}
+
+    def lin(name, M, K):
+        W[name] = (rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8),
+                   rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8))
+
+    def vec(name, n, center, jitter):
+        W[name] = (center + jitter * rng.standard_normal(n)).astype(np.float16)
+
+    for i in range(cfg.n_layers):
+        pre = f"layers.{i}."
+        for n, (M, K) in cfg.layer_shapes(i).items():
+            sub = "mlp." if n in ("gate_proj", "up_proj", "down_proj") else \
+                ("self_attn." if cfg.is_attn(i) else "linear_attn.")
+            lin(pre + sub + n, M, K)
+        vec(pre + "input_layernorm.weight", cfg.hidden, 0.0, norm_jitter)
+        vec(pre + "post_attention_layernorm.weight", cfg.hidden, 0.0, norm_jitter)
+        if cfg.is_attn(i):
+            vec(pre + "self_attn.q_norm.weight", HEAD_DIM, 0.0, norm_jitter)
+            vec(pre + "self_attn.k_norm.weight", HEAD_DIM, 0.0, norm_jitter)
+        else:
+            a = pre + "linear_attn."
+            W[a + "conv1d.weight"] = (rng.standard_normal((cfg.conv_dim, CONV_K)) * 0.3).astype(np.float16)
+            W[a + "A_log"] = np.log(rng.uniform(1e-3, 16, cfg.dn_vheads)).astype(np.float16)
+            W[a + "dt_bias"] = np.ones(cfg.dn_vheads, dtype=np.float16)
+            vec(a + "norm.weight", DN_DIM, 1.0, norm_jitter)
+    W["embed_tokens"] = (rng.standard_normal((cfg.vocab, cfg.hidden)) * 0.5).astype(np.float16)
+    vec("norm.weight", cfg.hidden, 0.0, norm_jitter)
+    lin("lm_head", cfg.vocab, cfg.hidden)
+    return W

@@ -167,16 +167,19 @@ def test_engine_matches_oracle_tokens(lib, seed):
     eng.capture(n_warmup=2)
     got_graph = eng.run(prompt, n_gen)
     assert got_eager == got_graph
-    matched = 0
+    matched, near_tie = 0, None
     for i in range(n_gen):
         if got_graph[i] == want[i]:
             matched += 1
             continue
         assert margins[i] < MARGIN, (i, got_graph[i], want[i], margins[i])
+        near_tie = (i, margins[i])
         break
-    assert matched >= 1
-    print(f"\nseed {seed}: {matched}/{n_gen} tokens matched; min oracle margin {min(margins):.4f}")
-    assert matched == n_gen or min(margins[:matched + 1]) < MARGIN
+    print(f"\nseed {seed}: {matched}/{n_gen} tokens matched; min oracle margin {min(margins):.4f}"
+          + (f"; near-tie at step {near_tie[0]} (margin {near_tie[1]:.5f})" if near_tie else ""))
+    # the whole length, unless the oracle's own top-1 / top-2 margin at the first differing step
+    # is a near-tie (asserted above, printed here)
+    assert matched == n_gen or near_tie is not None
 
 
 def test_engine_logits_first_step(lib):
@@ -352,3 +355,63 @@ def test_gemv_with_allreduce_in_its_prologue_single_rank(lib):
     assert f(one, one, one, one, 16, 96, one, 1e-6, 0, bufs, 0, 1, n, 0, one, 0, 2, None) == -2
     assert f(one, one, one, one, 16, 128, one, 1e-6, 1, bufs, 0, 1, n, 0, one, 0, 2, None) == -2
     assert f(one, one, one, one, 16, 128, one, 1e-6, 0, bufs, 0, 1, n, 0, one, 2, 2, None) == -2
+
+
+def test_full_width_63_tokens_after_512_prompt_match_the_oracle(lib):
+    """The acceptance run at the 27B model's WIDTHS: hidden 5120, MLP 17408, 24 query / 4 KV heads,
+    DeltaNet 16 / 48 heads, one DeltaNet layer and one attention layer, 16384-entry vocabulary;
+    512 seeded prompt tokens through the chunked prefill, then 63 greedy steps from the captured
+    step graph, against the CPU oracle's run on the same bytes (committed fixture, generated by
+    tests/golden/make_decode_golden.py: the oracle needs minutes in float64).
+
+    Rule, per step: the engine's token must equal the oracle's.  A random-weight model has
+    near-ties among its fp16 logits in any 63-step run (the fixture records the oracle's top-1 /
+    top-2 margin per step), so where that margin is below NEAR_TIE fp16 steps of the top logit the
+    engine may pick any candidate within that distance of the top; the step is counted and
+    printed, and generation continues from the ORACLE's token (teacher forcing) so that every
+    one of the 63 steps is compared.  The engine's logits on the oracle's 16 largest entries
+    must agree within LOGIT_TOL fp16 steps at every step."""
+    import os
+
+    NEAR_TIE, LOGIT_TOL = 6.0, 3.0
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden",
+                        "decode_full_width_golden.npz")
+    g = np.load(path)
+    cfg = ModelConfig(**{k: int(v) for k, v in zip(g["cfg_keys"], g["cfg_vals"])})
+    W = do.make_weights_random_bytes(cfg, int(g["seed"]))
+    prompt = g["prompt"]
+    want, margins = g["tokens"].tolist(), g["margins"]
+    eng = DecodeEngine(cfg)
+    eng.load_weights(W)
+    del W
+    eng.reset(int(prompt[0]))
+    eng.capture(n_warmup=1)
+    eng.reset(int(prompt[0]))
+    eng.prefill([int(t) for t in prompt[:-1]])
+    eng.tok.fill_(int(prompt[-1]))
+    top_idx = torch.from_numpy(g["top_idx"].astype(np.int64)).cuda()
+    clear = clear_ok = 0
+    near, diffs_ulp = [], []
+    for i in range(len(want)):
+        eng.step()
+        torch.cuda.synchronize()
+        pick = int(eng.tok)
+        top = g["top_val"][i]
+        ulp = float(np.spacing(np.float16(abs(top[0]))))           # one fp16 step at the top logit
+        lg = eng.logits[top_idx[i]].float().cpu().numpy()
+        diffs_ulp.append(float(np.abs(lg - top).max()) / ulp)
+        if margins[i] >= NEAR_TIE * ulp:
+            clear += 1
+            clear_ok += int(pick == want[i])
+            assert pick == want[i], (i, pick, want[i], float(margins[i]), ulp)
+        else:
+            tied = [int(t) for t, v in zip(g["top_idx"][i], top) if top[0] - v < NEAR_TIE * ulp]
+            assert pick in tied, (i, pick, tied, float(margins[i]))
+            near.append((i, round(float(margins[i]) / ulp, 1), pick == want[i]))
+        eng.tok.fill_(want[i])            # continue from the oracle's token
+    print(f"\nfull width, 512-token prompt: {clear_ok}/{clear} clear-margin steps equal the oracle's "
+          f"token; {len(near)} near-tie steps (step, margin in fp16 steps, same token): {near}; "
+          f"largest logit difference on the oracle's top 16: {max(diffs_ulp):.2f} fp16 steps")
+    assert clear_ok == clear and clear + len(near) == 63 and clear >= 40
+    assert max(diffs_ulp) <= LOGIT_TOL, diffs_ulp
+    assert lib.nvfp4_gemm_status(0) == 0
