@@ -19,8 +19,8 @@
 //               32-bit column r / 32 holds the row's 4 scale bytes of one 64-element K block, the
 //               same in all four 32-lane quarters.  Each of the 4 warps owns one quarter: a lane
 //               loads 16 scale bytes (one stage) of each of its rows from global memory and writes
-//               them with tcgen05.st.  Per stage 16 columns for the weights and BN / 8 for the tokens.
-// Tensor memory: BN accumulator columns + ST x (16 + BN/8) scale columns.
+//               them with tcgen05.st.  Per stage 16 columns for the weights and max(BN / 8, 16) for the tokens.
+// Tensor memory: BN accumulator columns + ST x (16 + max(BN/8, 16)) scale columns.
 //
 // Every wait is bounded (status word, see nvfp4_gemm_fp4_status); a CTA always runs to its end and
 // frees its tensor memory.
@@ -87,8 +87,11 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
                              __half* __restrict__ out, int M, int n_tokens, int K, int ld_out) {
     constexpr int A_BYTES = F4_BM * 128;             // weight tile of a stage
     constexpr int B_BYTES = BN * 128;                // token tile of a stage
-    constexpr int NB = BN / 32;                      // token rows per lane = SFB columns per MMA
-    constexpr int SFA_COLS = 16, SFB_COLS = 4 * NB, SF_COLS = SFA_COLS + SFB_COLS;
+    constexpr int NB = BN / 32;                      // token rows per lane
+    // one MMA's scale bytes start on a 4-column boundary of tensor memory (an address between
+    // boundaries raised "misaligned address"), so narrow token tiles leave columns unused
+    constexpr int NBC = NB < 4 ? 4 : NB;             // token-scale columns reserved per MMA
+    constexpr int SFA_COLS = 16, SFB_COLS = 4 * NBC, SF_COLS = SFA_COLS + SFB_COLS;
     constexpr int TCOLS = f4_tmem_cols(BN + ST * SF_COLS);
     static_assert(BN + ST * SF_COLS <= 512, "tensor memory");
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -161,7 +164,7 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
                     const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
                     const uint64_t bdesc = make_desc_sw128(b_base + kk * 32, 16, 1024);
                     tcgen05_mma_fp4_block16(tmem, adesc, bdesc, idesc, sf + (uint32_t)(kk * 4),
-                                            sf + (uint32_t)(SFA_COLS + kk * NB), (it | kk) != 0 ? 1u : 0u);
+                                            sf + (uint32_t)(SFA_COLS + kk * NBC), (it | kk) != 0 ? 1u : 0u);
                 }
                 tcgen05_commit(smem_u32(&bar_empty[s]));
             }
@@ -218,7 +221,7 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
 #pragma unroll
             for (int kk = 0; kk < 4; kk++) {
                 tcgen05_st_32x32b<4>(sf + (uint32_t)(kk * 4), wa[kk]);
-                tcgen05_st_32x32b<NB>(sf + (uint32_t)(SFA_COLS + kk * NB), wb[kk]);
+                tcgen05_st_32x32b<NB>(sf + (uint32_t)(SFA_COLS + kk * NBC), wb[kk]);
             }
             tcgen05_wait_st();
             tcgen05_fence_before();
@@ -325,8 +328,8 @@ int launch_nvfp4_gemm_fp4(const uint8_t* w_packed, const uint8_t* w_scales, cons
     const cudaError_t e =
         BN == 256 ? launch_fp4<256, 4>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
       : BN == 128 ? launch_fp4<128, 6>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
-      : BN == 64  ? launch_fp4<64, 8>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
-                  : launch_fp4<32, 8>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st);
+      : BN == 64  ? launch_fp4<64, 6>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
+                  : launch_fp4<32, 6>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st);
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 
