@@ -695,6 +695,8 @@ def run_per_shape(args):
         m, k = args.only.lower().split("x")
         only = (int(m), int(k))
     peak, peak_kind = measured_peak()
+    if args.tc_stages:
+        lib.nvfp4_b200_gemv_tc_config(args.tc_stages)
     rows = []
     for name, M, K, count in SHAPES_27B:
         if only and (M, K) != only:
@@ -709,8 +711,9 @@ def run_per_shape(args):
 
         def launch(i):
             c = i % ncopy
-            rc = lib.launch_nvfp4_gemv_v8(vp(packed[c].data_ptr()), vp(scales[c].data_ptr()),
-                                          vp(act[c].data_ptr()), vp(out[c].data_ptr()), M, K, st)
+            fn = lib.launch_nvfp4_gemv_tc if args.tc else lib.launch_nvfp4_gemv_v8
+            rc = fn(vp(packed[c].data_ptr()), vp(scales[c].data_ptr()),
+                    vp(act[c].data_ptr()), vp(out[c].data_ptr()), M, K, st)
             assert rc == 0, rc
 
         reps = args.reps
@@ -792,12 +795,21 @@ def run_gemm(args):
             a = torch.randn(K, tokens, device="cuda").to(torch.float16)
             o = torch.zeros(M, tokens, dtype=torch.float16, device="cuda")
             st = vp(torch.cuda.current_stream().cuda_stream)
-            if args.w4a4:       # activations token-major, quantised per block along K on the fly
+            if args.w4a4 or args.fp4_only:   # activations token-major, NVFP4 per block along K
                 a_tm = torch.randn(tokens, K, device="cuda").to(torch.float16)
                 work = torch.empty(K * tokens, dtype=torch.float16, device="cuda")
+                if args.fp4_only:   # activations encoded once, outside the timed launches
+                    a_p = torch.empty(tokens * K // 2, dtype=torch.uint8, device="cuda")
+                    a_s = torch.empty(tokens * K // 16, dtype=torch.uint8, device="cuda")
+                    assert lib.launch_nvfp4_encode(vp(a_tm.data_ptr()), vp(a_p.data_ptr()),
+                                                   vp(a_s.data_ptr()), tokens, K, st) == 0
 
             def launch():
-                if args.w4a4:
+                if args.fp4_only:
+                    rc = lib.launch_nvfp4_gemm_fp4(vp(p.data_ptr()), vp(s.data_ptr()),
+                                                   vp(a_p.data_ptr()), vp(a_s.data_ptr()),
+                                                   vp(o.data_ptr()), M, tokens, K, tokens, st)
+                elif args.w4a4:
                     rc = lib.launch_nvfp4_gemm_w4a4(vp(p.data_ptr()), vp(s.data_ptr()),
                                                     vp(a_tm.data_ptr()), vp(o.data_ptr()),
                                                     vp(work.data_ptr()), M, tokens, K, st)
@@ -823,6 +835,8 @@ def run_gemm(args):
                 best = us if best is None else min(best, us)
             flops = 2.0 * M * tokens * K
             nbytes = M * K * 0.5625 + 2.0 * K * tokens + 2.0 * M * tokens
+            if args.fp4_only:
+                nbytes = (M + tokens) * K * 0.5625 + 2.0 * M * tokens
             rows.append({"tokens": tokens, "M": M, "K": K, "us": best,
                          "tflops": flops / best / 1e6, "frac_tensor_" + tf_kind.split()[0]:
                          flops / best / 1e6 / tf_peak, "gbps": nbytes / best / 1e3,
@@ -831,8 +845,10 @@ def run_gemm(args):
                   f"({100 * flops / best / 1e6 / tf_peak:4.1f}% of {tf_kind} {tf_peak:.0f}) "
                   f"{nbytes / best / 1e3:7.0f} GB/s", file=sys.stderr, flush=True)
     print(json.dumps({"metric": "nvfp4_gemm_tflops", "unit": "TFLOP/s", "n_gpus": 1, "dtype": "f16",
-                      "kernel": ("quant_dequant_T_kernel + gemm_w4a16_tcgen05_kernel (W4A4 values, fp16 "
-                                 "tensor path, fp32 accumulation in TMEM)" if args.w4a4 else
+                      "kernel": ("gemm_fp4_block_scaled_kernel (tcgen05.mma kind::mxf4nvf4, block-16 "
+                                 "E8M0 scales in TMEM; activations pre-encoded)" if args.fp4_only else
+                                 "encode_kernel + gemm_fp4_block_scaled_kernel (fp16 activations "
+                                 "encoded to NVFP4 inside the timed launches)" if args.w4a4 else
                                  "gemm_w4a16_tcgen05_kernel (W4A16: fp16 activations, fp32 "
                                  "accumulation in TMEM)"),
                       "status": lib.nvfp4_gemm_status(0), "shapes": rows}), flush=True)
@@ -995,6 +1011,12 @@ def main():
                     help="with --decode: use this many layers (profiling aid; 0 = the full 64)")
     ap.add_argument("--w4a4", action="store_true",
                     help="with --gemm: quantise the activations to NVFP4 on the fly (W4A4 values)")
+    ap.add_argument("--tc-stages", type=int, default=0,
+                    help="with --tc: ring depth (8 or 4) passed to nvfp4_b200_gemv_tc_config")
+    ap.add_argument("--tc", action="store_true",
+                    help="with --per-shape: the FP4 tensor-core GEMV (launch_nvfp4_gemv_tc)")
+    ap.add_argument("--fp4-only", action="store_true",
+                    help="with --gemm: time launch_nvfp4_gemm_fp4 alone on pre-encoded activations")
     ap.add_argument("--tokens", type=int, default=0,
                     help="with --gemm: a single token count instead of 32 and 8192")
     ap.add_argument("--gen", type=int, default=63)

@@ -333,6 +333,26 @@ int launch_nvfp4_encode(const void* src_fp16, void* packed, void* scales, int M,
 int launch_nvfp4_decode_rows(const void* packed, const void* scales, const void* ids, void* out,
                              int n_rows, int K, long long table_rows, void* stream);
 
+/* GEMV on the FP4 tensor-core path: output[M] (fp16) = dequant(W)[M, K] . activation[K] (fp16), the
+ * semantics of launch_nvfp4_gemv_v8 (kernels/nvfp4_gemv.cu:88-100).  Weight and scale bytes go
+ * HBM -> shared memory (TMA) -> tcgen05.mma kind::mxf4nvf4 without passing through registers; the
+ * fp16 activation enters as 16 exact base-4 digit columns, so the products are those of the W4A16
+ * rule with fp32 accumulation.  K % 256 == 0; weight pointers and activation 16-byte aligned.  The
+ * first call on a device allocates a workspace (do it outside stream capture).  0; -2 shape or
+ * pointer not taken; -3 no tensor-map encoder / no memory; else the launch's cudaError_t.
+ * nvfp4_gemv_tc_status: 0, or 1 + id of the first bounded wait in that kernel that ran out. */
+int launch_nvfp4_gemv_tc(const uint8_t* weight_packed, const uint8_t* weight_scales,
+                         const void* activation, void* output, int M, int K, void* stream);
+int nvfp4_gemv_tc_status(int reset);
+/* Tuning hook: shared-memory ring of launch_nvfp4_gemv_tc: 3 stages and two CTAs per SM (default)
+ * or 8 stages and one CTA per SM. */
+void nvfp4_b200_gemv_tc_config(int stages);
+/* Timing probe of launch_nvfp4_gemv_tc: while a device buffer of 264 int64 words is set, launches
+ * record CTA 0's pipeline events in SM clock cycles there (words 0..5: entry, set-up done, previous
+ * kernel finished, digit planes done, last accumulation retired, flush done; 8 + 4 i + {0,1,2,3}:
+ * stage i's copy issued, bytes landed, scale bytes written, MMAs issued).  NULL switches it off. */
+void nvfp4_gemv_tc_probe(void* device_buffer);
+
 /* W4A4 (both operands in the reference's block-16 E8M0 format).  No counterpart in the reference,
  * which is W4A16 throughout (its target GPU has no FP4 tensor cores; README.md names W4A4 as the
  * aim for GPUs that have them).

@@ -86,6 +86,10 @@ SIGNATURES = {
     "launch_nvfp4_encode": ([_vp, _vp, _vp, _i, _i, _vp], _i),
     "launch_nvfp4_gemm_fp4": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "nvfp4_gemm_fp4_status": ([_i], _i),
+    "launch_nvfp4_gemv_tc": ([_vp, _vp, _vp, _vp, _i, _i, _vp], _i),
+    "nvfp4_gemv_tc_status": ([_i], _i),
+    "nvfp4_b200_gemv_tc_config": ([_i], None),
+    "nvfp4_gemv_tc_probe": ([_vp], None),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),
 }
 

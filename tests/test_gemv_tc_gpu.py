@@ -1,0 +1,94 @@
+"""GEMV on the FP4 tensor-core path (launch_nvfp4_gemv_tc) against the CPU oracle.
+
+Oracle and tolerance as for the register-streaming GEMV: codec decode of the weight bytes, float64
+dot product with the fp16 activation (kernels/nvfp4_gemv.cu:38-69 semantics); max |y - ref| /
+max(|ref|, 1e-3 max|ref|) <= 1e-3.  The activation enters the tensor core as exact base-4 digits,
+so inputs that stress the digit expansion are covered: zero blocks, a 2^20 spread inside one
+block, fp16 subnormals, the largest fp16 values."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_codec_oracle as oc
+from tests.gpu_util import dev, ptr, stream
+
+pytestmark = pytest.mark.gpu
+
+
+def run(lib, p, s, x):
+    M, K = p.shape[0], p.shape[1] * 2
+    d_p, d_s, d_x = dev(p), dev(s), dev(x)
+    out = torch.full((M + 16,), float("nan"), dtype=torch.float16, device="cuda")
+    lib.nvfp4_gemv_tc_status(1)
+    rc = lib.launch_nvfp4_gemv_tc(ptr(d_p), ptr(d_s), ptr(d_x), ptr(out), M, K, stream())
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert lib.nvfp4_gemv_tc_status(0) == 0, "a bounded wait inside the kernel ran out"
+    o = out.cpu().numpy()
+    assert np.isnan(o[M:]).all(), "wrote past the output"
+    return o[:M]
+
+
+def check(y, p, s, x, tol=1e-3):
+    ref = oc.decode_f64(p, s) @ x.astype(np.float64)
+    assert np.isfinite(y.astype(np.float64)).all()
+    rel = oc.rel_error_floored(y, ref)
+    assert rel.max() <= tol, (rel.max(), int(rel.argmax()))
+
+
+@pytest.mark.parametrize("M,K", [
+    (128, 256), (1, 256), (300, 512), (129, 1024), (1024, 5120), (5120, 5120), (33, 17408),
+    (6144, 5120), (17408, 5120), (5120, 17408), (40000, 1024),
+])
+def test_against_oracle(lib, M, K):
+    w = oc.synthetic_weight(M, K, seed=M + K)
+    p, s = oc.encode(w)
+    x = oc.synthetic_act(K, seed=K)
+    check(run(lib, p, s, x), p, s, x)
+
+
+def test_activation_extremes(lib):
+    M, K = 384, 1024
+    rng = np.random.default_rng(3)
+    p = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
+    s = rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8)
+    x = rng.standard_normal(K).astype(np.float16)
+    x[:32] = 0                                  # two all-zero blocks
+    x[32] = 1024.0; x[33] = 2.0 ** -10          # a 2^20 spread inside one block
+    x[48:64] = np.float16(6e-8) * rng.integers(-9, 10, 16).astype(np.float16)   # subnormals
+    x[64] = 60000.0; x[65] = -60000.0; x[66] = 30000.0   # near the fp16 maximum
+    x[80:96] = -x[80:96]
+    y = run(lib, p, s, x)
+    check(y, p, s, x)
+    # exactness of the digit expansion: scaling x by a power of two scales y exactly (no block
+    # changes its digits), as long as nothing leaves the fp16 range
+    x2 = (x.astype(np.float32) * 0.25).astype(np.float16)
+    keep = (x2.astype(np.float32) * 4 == x.astype(np.float32))
+    x, x2 = np.where(keep, x, 0).astype(np.float16), np.where(keep, x2, 0).astype(np.float16)
+    ya, yb = run(lib, p, s, x).astype(np.float32), run(lib, p, s, x2).astype(np.float32)
+    normal = np.abs(yb) >= 2.0 ** -13
+    assert np.array_equal(ya[normal], 4 * yb[normal])
+
+
+def test_repeated_launches_are_identical_and_leave_the_workspace_clean(lib):
+    M, K = 5120, 5120
+    p, s = oc.encode(oc.synthetic_weight(M, K, seed=1))
+    x = oc.synthetic_act(K, seed=2)
+    y0 = run(lib, p, s, x)
+    for _ in range(3):
+        assert np.array_equal(run(lib, p, s, x), y0)
+    # another shape in between uses the same counters and slots
+    p2, s2 = oc.encode(oc.synthetic_weight(300, 512, seed=4))
+    x2 = oc.synthetic_act(512, seed=5)
+    check(run(lib, p2, s2, x2), p2, s2, x2)
+    assert np.array_equal(run(lib, p, s, x), y0)
+
+
+def test_argument_validation(lib):
+    import ctypes
+
+    one = ctypes.c_void_p(0x1000)
+    assert lib.launch_nvfp4_gemv_tc(one, one, one, one, 16, 128, None) == -2     # K % 256
+    assert lib.launch_nvfp4_gemv_tc(one, one, one, one, 0, 256, None) == -2
+    assert lib.launch_nvfp4_gemv_tc(None, one, one, one, 16, 256, None) == -2
+    assert lib.launch_nvfp4_gemv_tc(ctypes.c_void_p(0x1008), one, one, one, 16, 256, None) == -2
