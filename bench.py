@@ -677,7 +677,7 @@ SHAPES_27B = [("lm_head", VOCAB, HIDDEN, 1), ("down_proj", HIDDEN, INTER, 64),
               ("in_proj_b/a", 48, HIDDEN, 96),
               # further shapes of the same decoder: q without its gate, the square o_proj, a 151936-row head
               ("q_proj 6144", 6144, HIDDEN, 0), ("o_proj 5120", HIDDEN, HIDDEN, 0),
-              ("lm_head 151936", 151936, HIDDEN, 0)]
+              ("lm_head 151936", 151936, HIDDEN, 0), ("gate+up fused", 2 * INTER, HIDDEN, 0)]
 
 
 def run_per_shape(args):
@@ -695,8 +695,6 @@ def run_per_shape(args):
         m, k = args.only.lower().split("x")
         only = (int(m), int(k))
     peak, peak_kind = measured_peak()
-    if args.tc_stages:
-        lib.nvfp4_b200_gemv_tc_config(args.tc_stages)
     rows = []
     for name, M, K, count in SHAPES_27B:
         if only and (M, K) != only:
@@ -1011,8 +1009,10 @@ def main():
                     help="with --decode: use this many layers (profiling aid; 0 = the full 64)")
     ap.add_argument("--w4a4", action="store_true",
                     help="with --gemm: quantise the activations to NVFP4 on the fly (W4A4 values)")
-    ap.add_argument("--tc-stages", type=int, default=0,
-                    help="with --tc: ring depth (8 or 4) passed to nvfp4_b200_gemv_tc_config")
+    ap.add_argument("--tc-ring", type=int, default=0, help="tensor-core GEMV weight-ring depth (3 or 5)")
+    ap.add_argument("--tc-min", type=int, default=-1,
+                    help="route GEMVs with M*K >= this many 2^20 elements to the tensor-core kernel "
+                         "(nvfp4_b200_gemv_tc_config; 0 = never; default: the library's)")
     ap.add_argument("--tc", action="store_true",
                     help="with --per-shape: the FP4 tensor-core GEMV (launch_nvfp4_gemv_tc)")
     ap.add_argument("--fp4-only", action="store_true",
@@ -1040,6 +1040,12 @@ def main():
                          "ring kernel, bits 4/5 = attribution probes); "
                          "profiling and attribution aid")
     args = ap.parse_args()
+    if args.tc_min >= 0 and args.impl == "ours":
+        from nvfp4_v100_b200 import _lib
+        _lib.load().nvfp4_b200_gemv_tc_config(args.tc_min)
+    if args.tc_ring and args.impl == "ours":
+        from nvfp4_v100_b200 import _lib
+        _lib.load().nvfp4_b200_gemv_tc_ring(args.tc_ring)
     if args.stream_config:
         from nvfp4_v100_b200 import _lib
         vals = [int(v) for v in args.stream_config.split(",")]

@@ -343,14 +343,29 @@ int launch_nvfp4_decode_rows(const void* packed, const void* scales, const void*
  * nvfp4_gemv_tc_status: 0, or 1 + id of the first bounded wait in that kernel that ran out. */
 int launch_nvfp4_gemv_tc(const uint8_t* weight_packed, const uint8_t* weight_scales,
                          const void* activation, void* output, int M, int K, void* stream);
+/* The same with the neighbours of launch_nvfp4_gemv_fused: prologue 1 = RMSNorm of the activation
+ * (norm_w1 fp32 [K], 16-byte aligned, K <= 11520), epilogue 1 = residual add, epilogue 2 =
+ * silu(gate) * up over interleaved gate / up rows (M % 16 == 0).  Same return values. */
+int launch_nvfp4_gemv_tc_fused(const uint8_t* weight_packed, const uint8_t* weight_scales,
+                               const void* activation, void* output, int M, int K, int prologue,
+                               const void* norm_w1, float eps, int epilogue, const void* residual,
+                               void* stream);
 int nvfp4_gemv_tc_status(int reset);
-/* Tuning hook: shared-memory ring of launch_nvfp4_gemv_tc: 3 stages and two CTAs per SM (default)
- * or 8 stages and one CTA per SM. */
-void nvfp4_b200_gemv_tc_config(int stages);
-/* Timing probe of launch_nvfp4_gemv_tc: while a device buffer of 264 int64 words is set, launches
- * record CTA 0's pipeline events in SM clock cycles there (words 0..5: entry, set-up done, previous
- * kernel finished, digit planes done, last accumulation retired, flush done; 8 + 4 i + {0,1,2,3}:
- * stage i's copy issued, bytes landed, scale bytes written, MMAs issued).  NULL switches it off. */
+/* Routing: launch_nvfp4_gemv_v8 and launch_nvfp4_gemv_fused hand calls with M * K >=
+ * min_mega_elements * 2^20 to the tensor-core kernel when shape and alignment allow (0 = never;
+ * default 60).  nvfp4_gemv_tc_wanted: the rule, 1 or 0.  nvfp4_gemv_tc_prepare: allocate the
+ * current device's workspace now, outside any stream capture (0 or -3). */
+void nvfp4_b200_gemv_tc_config(int min_mega_elements);
+/* Weight-ring depth of the tensor-core GEMV: 5 stages (default) or 3. */
+void nvfp4_b200_gemv_tc_ring(int stages);
+int nvfp4_gemv_tc_wanted(int M, int K);
+int nvfp4_gemv_tc_prepare(void);
+/* Timing probe of launch_nvfp4_gemv_tc: while a device buffer of 128 int64 words is set, launch n
+ * folds into words 16 (n % 8) .. the global nanosecond timer over all its CTAs: 0 earliest kernel
+ * entry, 1 latest entry, 2 / 3 latest / earliest "previous kernel finished", 4 latest digit planes
+ * done, 5 latest first MMA, 6 latest accumulation retired, 7 latest flush done, 8 latest CTA end.
+ * The caller sets words 0 and 3 of each group to the largest int64 and the rest to 0 beforehand.
+ * NULL switches it off. */
 void nvfp4_gemv_tc_probe(void* device_buffer);
 
 /* W4A4 (both operands in the reference's block-16 E8M0 format).  No counterpart in the reference,

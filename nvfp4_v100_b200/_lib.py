@@ -89,6 +89,10 @@ SIGNATURES = {
     "launch_nvfp4_gemv_tc": ([_vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "nvfp4_gemv_tc_status": ([_i], _i),
     "nvfp4_b200_gemv_tc_config": ([_i], None),
+    "nvfp4_b200_gemv_tc_ring": ([_i], None),
+    "launch_nvfp4_gemv_tc_fused": ([_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _f, _i, _vp, _vp], _i),
+    "nvfp4_gemv_tc_wanted": ([_i, _i], _i),
+    "nvfp4_gemv_tc_prepare": ([], _i),
     "nvfp4_gemv_tc_probe": ([_vp], None),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),
 }

@@ -885,6 +885,16 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
     const bool fast = !g_cfg.force_generic && (K % 128 == 0) && aligned(packed, 32) &&
                       aligned(scales, 8);
     StreamPlan sp;
+    if (fast && nact == 1 && !old_kernel_tuned() && aligned(scales, 16) && nvfp4_gemv_tc_wanted(M, K)) {
+        // large matrices: the FP4 tensor-core kernel
+        const int rc = launch_nvfp4_gemv_tc((const uint8_t*)packed, (const uint8_t*)scales, a0, out, M, K,
+                                            stream);
+        if (rc == 0) return NVFP4_OK;
+        if (rc != NVFP4_ERR_SHAPE && rc != -3) {
+            fprintf(stderr, "%s (tensor-core kernel): error %d\n", who, rc);
+            return NVFP4_ERR_LAUNCH;
+        }
+    }
     if (fast && nact == 1 && !old_kernel_tuned() && aligned(scales, 16) &&
         plan_stream(M, K, GS_PRO_NONE, GS_EPI_STORE, &sp)) {
         e = launch_stream(packed, scales, a0, out, M, K, GS_PRO_NONE, nullptr, 0.0f, GS_EPI_STORE,
@@ -966,6 +976,16 @@ int gemv_ex_dispatch(const void* packed, const void* scales, const void* act, vo
     if (epilogue < EPI_STORE || epilogue > EPI_SILU_MUL) return NVFP4_ERR_SHAPE;
     if (epilogue == EPI_RESIDUAL && !residual) return NVFP4_ERR_SHAPE;
     if (epilogue == EPI_SILU_MUL && M % 16 != 0) return NVFP4_ERR_SHAPE;
+    // large matrices: the FP4 tensor-core kernel (TMA ring, no weight byte through a register)
+    if (!old_kernel_tuned() && nvfp4_gemv_tc_wanted(M, K) && aligned(scales, 16)) {
+        const int rc = launch_nvfp4_gemv_tc_fused((const uint8_t*)packed, (const uint8_t*)scales, act, out,
+                                                  M, K, prologue, norm_w1, eps, epilogue, residual, stream);
+        if (rc == 0) return NVFP4_OK;
+        if (rc != NVFP4_ERR_SHAPE && rc != -3) {
+            fprintf(stderr, "launch_nvfp4_gemv_fused (tensor-core kernel): error %d\n", rc);
+            return NVFP4_ERR_LAUNCH;
+        }
+    }
     GemvExtra ex = {};
     ex.norm_w1 = (const float*)norm_w1;
     ex.eps = eps;

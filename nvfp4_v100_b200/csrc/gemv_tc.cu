@@ -14,19 +14,22 @@
 // of a 128-row MMA, so the digits cost no extra tensor-core time.  (Bits of an element more than
 // 2^21 below its block's largest are dropped: a relative 2^-31 of that block's contribution.)
 //
-// Work: row tiles of 128 x K stages of 256 elements, numbered tile-major; the stages are cut into
-// gridDim.x equal contiguous ranges (one persistent CTA per SM), so a row tile's sum may span two
+// Work: row tiles of 128 x K stages of 256 elements, numbered tile-major (a CTA reads consecutive
+// K of the same rows: DRAM pages stay open; a K-chunk-major order measured 25 % slower); the stages
+// are cut into gridDim.x equal contiguous ranges (two CTAs per SM), so a row tile's sum may span two
 // or more CTAs.  Each CTA flushes the partial sums of a (tile, range) segment to a workspace slot;
 // the warp that arrives last at a tile's counter adds the slots in CTA order (deterministic) and
 // writes the fp16 result.
 //
-// One CTA (320 threads), one per SM:
+// One CTA (320 threads; 58 KB of shared memory + 2 KB per cached stage of digit planes, 128
+// columns of tensor memory - a CTA of the NEXT kernel in the stream fits beside two of this one
+// when the cache is small, and prefetches its weights meanwhile):
 //   all warps   prologue (after the previous kernel in the stream has finished): the digit planes
 //               of every K stage this CTA will visit, into a shared-memory cache (2 KB per stage, the
 //               B operand tile as the tensor core reads it: 16 rows x 128 B, 128-byte swizzle), and
 //               the blocks' exponent bytes.
 //   warp 0      TMA producer: per stage 128 rows x 128 packed bytes (128-byte swizzle) and the
-//               128 x 16 scale bytes, into an ST-stage ring; begins BEFORE the previous kernel has
+//               128 x 16 scale bytes, into a 3-stage ring; begins BEFORE the previous kernel has
 //               finished (programmatic dependent launch: weights are constants).
 //   warp 1      MMA issuer: 4 x tcgen05.mma M128 N16 K64 per stage into one of two accumulators.
 //   warps 2..5  scale writers: weight scale bytes shared memory -> tensor memory (tcgen05.st; lane
@@ -44,25 +47,27 @@ namespace nvfp4 {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 256;
-constexpr int TC_NBC = 20;                     // K stages whose digit planes the cache holds
+constexpr int TC_NB = 8;                        // ring of digit-plane tiles (stages converted ahead)
 constexpr int TC_THREADS = 320;
 constexpr int TC_A_BYTES = TC_BM * 128;        // packed weights of a stage
 constexpr int TC_B_BYTES = 16 * 128;           // activation digit planes of a stage
 constexpr int TC_S_BYTES = TC_BM * 16;         // weight scale bytes of a stage
 constexpr int TC_SF_COLS = 32;                 // tensor-memory columns of a stage's scale bytes
 constexpr uint32_t TC_SPIN_LIMIT = 1u << 21;   // polls, each parked by the hardware for up to 1 us
+// dynamic shared memory: weight ring of st stages, digit-plane ring, digit table, exponent bytes,
+// scratch; tensor memory: 2 x 16 accumulator columns + st x 32 scale columns
 __host__ __device__ constexpr int tc_smem_bytes(int st) {
-    return st * (TC_A_BYTES + TC_S_BYTES) + TC_NBC * (TC_B_BYTES + 16) + 1024 /*LUT*/ + 1024 /*align*/;
+    return st * (TC_A_BYTES + TC_S_BYTES) + TC_NB * (TC_B_BYTES + 16) + 1024 + 128 + 1024 /*alignment*/;
 }
-__host__ __device__ constexpr int tc_tmem_cols(int st) {
-    return 32 + st * TC_SF_COLS <= 128 ? 128 : 32 + st * TC_SF_COLS <= 256 ? 256 : 512;
-}
+__host__ __device__ constexpr int tc_tmem_cols(int st) { return 32 + st * TC_SF_COLS <= 128 ? 128 : 256; }
 
 __device__ int g_tc_status = 0;
 
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, int id) {
-    for (uint32_t i = 0; i < TC_SPIN_LIMIT; i++)
-        if (mbar_try_wait_hint(bar, parity, 1000u)) return true;
+    for (uint32_t i = 0; i < (1u << 24); i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        __nanosleep(20);
+    }
     atomicExch(&g_tc_status, 1 + id);
     return false;
 }
@@ -117,10 +122,9 @@ __device__ __forceinline__ uint32_t tc_prmt(uint32_t a, uint32_t b, uint32_t sel
     return r;
 }
 
-// first stage of CTA b's range, and the CTA whose range holds stage g
-__device__ __forceinline__ long long tc_start(long long b, long long total, int G) { return b * total / G; }
-__device__ __forceinline__ int tc_cta_of(long long g, long long total, int G) {
-    return (int)(((g + 1) * G - 1) / total);
+// the CTA whose range [b total / G, (b + 1) total / G) holds stage g
+__device__ __forceinline__ int tc_cta_of(unsigned g, unsigned total, unsigned G) {
+    return (int)(((g + 1u) * G - 1u) / total);
 }
 
 // The 32-bit fraction |x| / 2^L of an fp16 bit pattern (sign stripped), L = the block's exponent.
@@ -131,9 +135,10 @@ __device__ __forceinline__ uint32_t tc_fraction(uint32_t h15, int L) {
     return sh >= 0 ? (m11 << sh) : (sh > -32 ? (m11 >> (-sh)) : 0u);
 }
 
-// Digit planes of 8 consecutive activations (one 16-byte load) -> 16 words, one per plane row of
-// the B tile, and the block's exponent.  lut[b] holds the E2M1 codes of the four base-4 digits of
-// byte b, one per byte (first digit = most significant = lowest byte).
+// Digit planes of 8 consecutive activations (one 16-byte vector; lane o of a warp holds elements
+// 8o .. 8o+7 of a 256-element stage) -> 16 words, one per plane row of the B tile, and the block's
+// exponent byte.  lut[b] holds the E2M1 codes of the four base-4 digits of byte b, one per byte
+// (first digit = most significant = lowest byte).
 __device__ __forceinline__ void tc_digit_planes(const uint4 xv, const uint32_t* lut, uint8_t* btile,
                                                 uint8_t* lbytes, int lane) {
     const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
@@ -175,30 +180,76 @@ __device__ __forceinline__ void tc_digit_planes(const uint4 xv, const uint32_t* 
     if ((lane & 1) == 0) lbytes[lane >> 1] = (uint8_t)(L + 125);
 }
 
-// DBG: CTA 0 records clock64() at its pipeline events into `dbg` (a timing probe, see
-// nvfp4_gemv_tc_probe): words 0..7 = kernel entry, set-up done, previous kernel finished, digit
-// planes done, last segment's accumulation retired, flush done; then per stage i < 64 four words at
-// 8 + 4 i: copy issued, bytes landed (seen by a scale writer), scale bytes written, MMAs issued.
-template <int ST, bool DBG>
+// What the kernel fuses around the dot products (the arithmetic of the register-streaming GEMV's
+// prologues and epilogues, which is that of rmsnorm_kernel and silu_mul_kernel):
+//   TPRO_RMSNORM: x' = f16(f32(x) * rsqrt(mean(x^2) + eps) * w1[k]) is what gets multiplied
+//   TEPI_RESIDUAL: out[m] = f16(f32(residual[m]) + f32(f16(y[m])))
+//   TEPI_SILU_MUL: rows in groups of 16 = 8 gate rows then 8 up rows; out[8 g + r] =
+//                  f16(f32(f16(silu(f16(gate)))) * f32(f16(up)))
+enum { TPRO_NONE = 0, TPRO_RMSNORM = 1 };
+enum { TEPI_STORE = 0, TEPI_RESIDUAL = 1, TEPI_SILU_MUL = 2 };
+struct TcFuse {
+    const float* norm_w1;
+    float eps;
+    const __half* residual;
+};
+
+// Final value of row `row` (this lane's; the warp's 32 rows are consecutive and start at a
+// multiple of 32) -> output.
+template <int EPI>
+__device__ __forceinline__ void tc_store(float tot, int row, int lane, int M, __half* y, const TcFuse& fz) {
+    if (EPI == TEPI_SILU_MUL) {
+        const float up = __shfl_down_sync(0xffffffffu, tot, 8);     // lanes 8..15 / 24..31: up rows
+        if ((lane & 8) == 0 && row + 8 < M) {
+            const float gf = round_f16(tot), uf = round_f16(up);
+            const float sl = round_f16(gf / (1.0f + expf(-gf)));
+            y[(row >> 4) * 8 + (lane & 7)] = __float2half(sl * uf);
+        }
+    } else if (row < M) {
+        if (EPI == TEPI_RESIDUAL) {
+            const __half* res = fz.residual;
+            PDL_FRESH(res);
+            y[row] = __float2half(__half2float(res[row]) + round_f16(tot));
+        } else {
+            y[row] = __float2half(tot);
+        }
+    }
+}
+
+// DBG: every CTA folds the global nanosecond timer at its pipeline events into `dbg` (a timing
+// probe, see nvfp4_gemv_tc_probe): word 0 = earliest kernel entry, 1 = latest entry, 2 / 3 = latest /
+// earliest "previous kernel finished", 4 = latest digit planes done, 5 = latest first MMA, 6 = latest
+// accumulation retired, 7 = latest flush done, 8 = latest CTA end.  Words 0 and 3 start at the
+// largest int64, the others at 0.
+__device__ __forceinline__ long long tc_now() {
+    long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
+template <int ST, int PRO, int EPI, bool DBG>
 __global__ void __launch_bounds__(TC_THREADS)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap s_map,
                const __half* x, __half* y, float* part, unsigned int* counters, int M, int K,
-               long long* dbg) {
+               const TcFuse fz, long long* dbg_) {
+    long long* dbg = dbg_;
     asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-    const bool rec = DBG && blockIdx.x == 0;
-    if (rec && threadIdx.x == 0) dbg[0] = clock64();
-    constexpr int TCOLS = tc_tmem_cols(ST);
+    constexpr int NB = TC_NB, TC_TMEM_COLS = tc_tmem_cols(ST);
+    const bool rec = DBG;
+    if (rec && threadIdx.x == 0) { const long long t = tc_now(); atomicMin(dbg + 0, t); atomicMax(dbg + 1, t); }
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~(uintptr_t)1023);
-    uint8_t* smem_a = smem;                                   // ST x 16 KB
-    uint8_t* smem_b = smem_a + ST * TC_A_BYTES;               // TC_NBC x 2 KB digit-plane cache
-    uint8_t* smem_s = smem_b + TC_NBC * TC_B_BYTES;           // ST x 2 KB weight scale bytes
+    uint8_t* smem_a = smem;                                   // ST x 16 KB packed weights
+    uint8_t* smem_b = smem_a + ST * TC_A_BYTES;               // NB x 2 KB digit planes
+    uint8_t* smem_s = smem_b + NB * TC_B_BYTES;               // ST x 2 KB weight scale bytes
     uint32_t* lut = reinterpret_cast<uint32_t*>(smem_s + ST * TC_S_BYTES);   // 256 words
-    uint8_t* smem_l = reinterpret_cast<uint8_t*>(lut + 256);  // TC_NBC x 16 exponent bytes
+    uint8_t* smem_l = reinterpret_cast<uint8_t*>(lut + 256);  // NB x 16 exponent bytes
+    float* s_part = reinterpret_cast<float*>(smem_l + NB * 16);              // 9 partial sums
     __shared__ __align__(8) uint64_t bar_full[ST];            // TMA bytes landed
     __shared__ __align__(8) uint64_t bar_ready[ST];           // scale bytes written to tensor memory
     __shared__ __align__(8) uint64_t bar_empty[ST];           // the stage's MMAs retired
+    __shared__ __align__(8) uint64_t bar_bfull[NB];           // digit planes of a stage written
+    __shared__ __align__(8) uint64_t bar_bempty[NB];          // the MMAs that read them retired
     __shared__ __align__(8) uint64_t bar_acc_full[2];         // a segment's accumulation retired
     __shared__ __align__(8) uint64_t bar_acc_empty[2];        // the flush warps have read it
     __shared__ uint32_t s_tmem;
@@ -206,11 +257,12 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x, b = blockIdx.x;
     const int ntiles = (M + TC_BM - 1) / TC_BM, nk = K / TC_BK;
-    const long long total = (long long)ntiles * nk;
-    const long long g0 = tc_start(b, total, G), g1 = tc_start(b + 1, total, G);
+    // (the launcher keeps total * (G + 1) below 2^32: 32-bit divisions)
+    const unsigned total = (unsigned)ntiles * (unsigned)nk;
+    const unsigned g0 = (unsigned)b * total / (unsigned)G, g1 = (unsigned)(b + 1) * total / (unsigned)G;
     // the loops below count stages with 32-bit counters kept by increment: the single-thread roles
-    // (copy issue, MMA issue) run one instruction at a time, a 64-bit division per stage would
-    // cost them more than the stage's four MMAs
+    // (copy issue, MMA issue) run one instruction at a time, a division per stage would cost them
+    // more than the stage's four MMAs
     const int nst = (int)(g1 - g0);                  // stages of this CTA
     const int tile0 = (int)(g0 / nk), ks0 = (int)(g0 % nk);
 
@@ -226,13 +278,16 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             mbar_init(smem_u32(&bar_ready[s]), 128);
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
+        for (int s = 0; s < NB; s++) {
+            mbar_init(smem_u32(&bar_bfull[s]), 1);
+            mbar_init(smem_u32(&bar_bempty[s]), 1);
+        }
         for (int a = 0; a < 2; a++) {
             mbar_init(smem_u32(&bar_acc_full[a]), 1);
             mbar_init(smem_u32(&bar_acc_empty[a]), 128);
         }
         fence_barrier_init();
         for (; p_i < nst && p_i < ST; p_i++) {
-            if (rec && p_i < 64) dbg[8 + 4 * p_i] = clock64();
             const uint32_t bar = smem_u32(&bar_full[p_s]);
             mbar_arrive_expect_tx(bar, TC_A_BYTES + TC_S_BYTES);
             tma_load_2d(smem_u32(smem_a + p_s * TC_A_BYTES), &w_map, p_ks * 128, p_tile * TC_BM, bar);
@@ -242,7 +297,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         }
     }
     if (warp == 1) {
-        tcgen05_alloc(smem_u32(&s_tmem), TCOLS);
+        tcgen05_alloc(smem_u32(&s_tmem), TC_TMEM_COLS);
         tcgen05_relinquish();
     }
     if (threadIdx.x >= 64) {                                  // digit-code table, one entry each
@@ -257,14 +312,12 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     tcgen05_fence_after();
     const uint32_t tmem = s_tmem;
     const uint32_t tmem_sf = tmem + 32;
-    if (rec && threadIdx.x == 0) dbg[1] = clock64();
 
     if (warp == 0) {
-        // ---------------- TMA producer (weights are constants: no wait on the previous kernel) ----
+        // ---------------- TMA producer, the stages after the first ST ----------------
         if (lane == 0) {
             for (; p_i < nst; p_i++) {
                 if (!tc_wait_poll(smem_u32(&bar_empty[p_s]), p_ph ^ 1u, 0)) break;
-                if (rec && p_i < 64) dbg[8 + 4 * p_i] = clock64();
                 const uint32_t bar = smem_u32(&bar_full[p_s]);
                 mbar_arrive_expect_tx(bar, TC_A_BYTES + TC_S_BYTES);
                 tma_load_2d(smem_u32(smem_a + p_s * TC_A_BYTES), &w_map, p_ks * 128, p_tile * TC_BM, bar);
@@ -273,44 +326,42 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 if (++p_ks == nk) { p_ks = 0; p_tile++; }
             }
         }
-        // (this warp skips the digit prologue and its barrier)
     } else {
-        // ---------------- digit planes of the K stages of this CTA's range ----------------
         asm volatile("griddepcontrol.wait;\n" ::: "memory");
         PDL_FRESH(x);
         PDL_FRESH(y);
         PDL_FRESH(part);
         PDL_FRESH(counters);
-        if (rec && threadIdx.x == 32) dbg[2] = clock64();
-        // cache slot of a stage: its K index when the cache holds all of K, else its place in this
-        // CTA's range (the launcher checked that the range then fits)
-        const bool by_k = nk <= TC_NBC;
-        {
-            const int nplanes = nst < nk ? nst : nk;
-            // at most 20 stages x 32 octets over 288 threads: three per thread, all three loads
-            // in flight before the first is used
-            constexpr int PER = (TC_NBC * 32 + TC_THREADS - 33) / (TC_THREADS - 32);
-            uint4 xv[PER];
+        if (rec && threadIdx.x == 32) { const long long t = tc_now(); atomicMax(dbg + 2, t); atomicMin(dbg + 3, t); }
+        float inv = 1.0f;
+        if (PRO == TPRO_RMSNORM) {
+            // mean of squares over the WHOLE activation (K <= 5 * 8 * 288), all loads in flight at once
+            const int t0 = (int)threadIdx.x - 32;
+            constexpr int T = TC_THREADS - 32;
+            uint4 v[5];
 #pragma unroll
-            for (int j = 0; j < PER; j++) {
-                const int t = (int)threadIdx.x - 32 + j * (TC_THREADS - 32);
-                int ks = ks0 + (t >> 5);
-                if (ks >= nk) ks -= nk;
-                if (t < nplanes * 32)
-                    xv[j] = *reinterpret_cast<const uint4*>(x + (size_t)ks * TC_BK + (t & 31) * 8);
+            for (int j = 0; j < 5; j++) {
+                const int i = (t0 + j * T) * 8;
+                v[j] = (i < K) ? *reinterpret_cast<const uint4*>(x + i) : make_uint4(0u, 0u, 0u, 0u);
             }
+            float ss = 0.0f;
 #pragma unroll
-            for (int j = 0; j < PER; j++) {
-                const int t = (int)threadIdx.x - 32 + j * (TC_THREADS - 32);
-                int ks = ks0 + (t >> 5);
-                if (ks >= nk) ks -= nk;
-                const int slot = by_k ? ks : (t >> 5);
-                if (t < nplanes * 32)     // uniform over a warp: t & 31 is the lane
-                    tc_digit_planes(xv[j], lut, smem_b + slot * TC_B_BYTES, smem_l + slot * 16, t & 31);
+            for (int j = 0; j < 5; j++) {
+                const __half2* h = reinterpret_cast<const __half2*>(&v[j]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(h[e]);
+                    ss = fmaf(f.x, f.x, ss);
+                    ss = fmaf(f.y, f.y, ss);
+                }
             }
-            fence_proxy_async_smem();          // the tensor core reads the planes (async proxy)
+            ss = warp_sum(ss);
+            if (lane == 0) s_part[warp - 1] = ss;
             asm volatile("bar.sync 1, 288;\n" ::: "memory");
-            if (rec && threadIdx.x == 32) dbg[3] = clock64();
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 9; w++) tot += s_part[w];
+            inv = rsqrtf(tot / (float)K + fz.eps);
         }
         if (warp == 1) {
             // ---------------- MMA issuer ----------------
@@ -321,7 +372,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 // descriptors: +1 in the low word = 16 bytes further in shared memory
                 const uint64_t a_desc0 = make_desc_sw128(smem_u32(smem_a), 16, 1024);
                 const uint64_t b_desc0 = make_desc_sw128(smem_u32(smem_b), 16, 1024);
-                int s = 0, ks = ks0, seg = 0;
+                int s = 0, ks = ks0, seg = 0, bs = 0;
                 uint32_t ph = 0;
                 bool first = true;
                 for (int i = 0; i < nst; i++) {
@@ -329,12 +380,13 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                     if (first &&  // the flush warps must have drained this accumulator's previous use
                         !tc_wait_poll(smem_u32(&bar_acc_empty[buf]), (((uint32_t)seg >> 1) & 1u) ^ 1u, 1))
                         break;
-                    // the scale writers arrive here only after they saw the stage's copies land
+                    // the scale writers arrive here only after they saw the stage's copies land and
+                    // its digit planes written
                     if (!tc_wait_poll(smem_u32(&bar_ready[s]), ph, 3)) break;
                     tcgen05_fence_after();
-                    if (rec && i < 64) dbg[8 + 4 * i + 3] = clock64();
+                    if (rec && i == 0) atomicMax(dbg + 5, tc_now());
                     const uint64_t adesc = a_desc0 + (uint64_t)(s * (TC_A_BYTES >> 4));
-                    const uint64_t bdesc = b_desc0 + (uint64_t)((by_k ? ks : i) * (TC_B_BYTES >> 4));
+                    const uint64_t bdesc = b_desc0 + (uint64_t)(bs * (TC_B_BYTES >> 4));
                     const uint32_t sf = tmem_sf + (uint32_t)(s * TC_SF_COLS);
                     const uint32_t d = tmem + (uint32_t)(buf * 16);
                     tc_mma(d, adesc, bdesc, idesc, sf, sf + 16, first ? 0u : 1u);
@@ -342,13 +394,15 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                     tc_mma(d, adesc + 4, bdesc + 4, idesc, sf + 8, sf + 24, 1u);
                     tc_mma(d, adesc + 6, bdesc + 6, idesc, sf + 12, sf + 28, 1u);
                     tcgen05_commit(smem_u32(&bar_empty[s]));
+                    tcgen05_commit(smem_u32(&bar_bempty[bs]));
                     first = false;
                     if (++s == ST) { s = 0; ph ^= 1u; }
+                    bs = (bs + 1) & (NB - 1);
                     if (++ks == nk || i == nst - 1) {       // the segment ends with this stage
                         tcgen05_commit(smem_u32(&bar_acc_full[buf]));
                         seg++;
                         first = true;
-                        if (ks == nk) ks = 0;
+                        ks = 0;
                     }
                 }
             }
@@ -358,14 +412,14 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             const uint32_t lane_base = (uint32_t)(q * 32) << 16;
             const uint32_t sub = 0x01010101u * (uint32_t)(2 * (lane & 15));
             bool ok = true;
-            int s = 0, ks = ks0;
-            uint32_t ph = 0;
+            int s = 0, bs = 0;
+            uint32_t ph = 0, bph = 0;
             for (int i = 0; i < nst; i++) {
+                if (ok) ok = tc_wait(smem_u32(&bar_bfull[bs]), bph, 6);
                 // digit column n, block blk: exponent byte L_blk + 125 - 2n (word kk = blocks 4kk..)
-                const uint4 lw = *reinterpret_cast<const uint4*>(smem_l + (by_k ? ks : i) * 16);
+                const uint4 lw = *reinterpret_cast<const uint4*>(smem_l + bs * 16);
                 if (ok) ok = tc_wait(smem_u32(&bar_full[s]), ph, 4);
                 tcgen05_fence_after();
-                if (rec && i < 64 && threadIdx.x == 64) dbg[8 + 4 * i + 1] = clock64();
                 const uint32_t sf = tmem_sf + (uint32_t)(s * TC_SF_COLS) + lane_base;
                 // weight scales: row c*32 + lane holds 16 bytes = 4 MMAs x 4 blocks
                 const uint8_t* ss = smem_s + s * TC_S_BYTES;
@@ -382,23 +436,59 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 tc_st_x32(sf, cols);
                 tc_wait_st();
                 tcgen05_fence_before();
-                if (rec && i < 64 && threadIdx.x == 64) dbg[8 + 4 * i + 2] = clock64();
                 mbar_arrive(smem_u32(&bar_ready[s]));
                 if (++s == ST) { s = 0; ph ^= 1u; }
-                if (++ks == nk) ks = 0;
+                if (++bs == NB) { bs = 0; bph ^= 1u; }
             }
         } else {
-            // ---------------- flush ----------------
-            const int q = warp & 3;
+            // ---------------- digit conversion (ahead of the MMAs) and flush ----------------
+            // Warp f of the four converts the stages i = f, f + 4, ... of this CTA's range, one
+            // 256-element stage (32 octets) a time, into plane-ring slot i % 8 - as far ahead as
+            // the ring allows (slot free = the MMAs of stage i - 8 retired).  Before it waits for
+            // a segment's accumulation it has converted its stages up to 7 beyond the segment's
+            // end: those waits depend only on MMAs inside or before the segment, and the MMAs of
+            // the next segment find their planes ready.
+            const int f = warp - 6, q = warp & 3;
             const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-            int seg = 0;
-            int tile = tile0, left = nst, seg_len = nk - ks0;   // stages of this tile in the range
+            int cv = f;                                          // next stage this warp converts
+            int cv_ks = ks0 + f;
+            while (cv_ks >= nk) cv_ks -= nk;
+            auto convert_upto = [&](int last) {
+                for (; cv <= last && cv < nst; cv += 4) {
+                    const int slot = cv & (NB - 1);
+                    const int k = cv_ks * TC_BK + lane * 8;
+                    uint4 xv = *reinterpret_cast<const uint4*>(x + k);
+                    if (PRO == TPRO_RMSNORM) {
+                        const float4 w0 = __ldg(reinterpret_cast<const float4*>(fz.norm_w1 + k));
+                        const float4 w1 = __ldg(reinterpret_cast<const float4*>(fz.norm_w1 + k + 4));
+                        const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                        __half2* h = reinterpret_cast<__half2*>(&xv);
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            const float2 fv = __half22float2(h[e]);
+                            h[e] = __halves2half2(__float2half(fv.x * inv * w[2 * e]),
+                                                  __float2half(fv.y * inv * w[2 * e + 1]));
+                        }
+                    }
+                    // the slot's previous planes (stage cv - 8) must have been consumed
+                    tc_wait(smem_u32(&bar_bempty[slot]), (((uint32_t)cv >> 3) & 1u) ^ 1u, 7);
+                    tc_digit_planes(xv, lut, smem_b + slot * TC_B_BYTES, smem_l + slot * 16, lane);
+                    fence_proxy_async_smem();        // the tensor core reads the planes (async proxy)
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(smem_u32(&bar_bfull[slot]));
+                    cv_ks += 4;
+                    while (cv_ks >= nk) cv_ks -= nk;
+                }
+            };
+            int seg = 0, tile = tile0, left = nst, seg_len = nk - ks0, done = 0;
             while (left > 0) {
                 if (seg_len > left) seg_len = left;
+                convert_upto(done + seg_len - 1 + (NB - 1));
+                if (rec && seg == 0 && lane == 0) atomicMax(dbg + 4, tc_now());
                 const int buf = seg & 1;
                 const bool got = tc_wait(smem_u32(&bar_acc_full[buf]), ((uint32_t)seg >> 1) & 1u, 5);
                 tcgen05_fence_after();
-                if (rec && threadIdx.x == 192) dbg[4] = clock64();
+                if (rec && lane == 0) atomicMax(dbg + 6, tc_now());
                 uint32_t v[16];
                 tc_ld_x16(tmem + lane_base + (uint32_t)(buf * 16), v);
                 tcgen05_wait_ld();
@@ -409,10 +499,10 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 for (int j = 15; j >= 0; j--) sum += __uint_as_float(v[j]);   // small digits first
                 if (!got) sum = 0.0f;
                 const int row = tile * TC_BM + q * 32 + lane;
-                const int c_first = tc_cta_of((long long)tile * nk, total, G);
-                const int c_last = tc_cta_of((long long)(tile + 1) * nk - 1, total, G);
+                const int c_first = tc_cta_of((unsigned)tile * nk, total, G);
+                const int c_last = tc_cta_of((unsigned)(tile + 1) * nk - 1u, total, G);
                 if (c_first == c_last) {
-                    if (row < M) y[row] = __float2half(sum);
+                    tc_store<EPI>(sum, row, lane, M, y, fz);
                 } else {
                     // slot (tile + CTA) is unique: a CTA boundary inside a tile adds one slot
                     part[(size_t)(tile + b) * TC_BM + q * 32 + lane] = sum;
@@ -432,29 +522,31 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
 #pragma unroll
                             for (int u = 0; u < 4; u++) tot += pv[u];
                         }
-                        if (row < M) y[row] = __float2half(tot);
+                        tc_store<EPI>(tot, row, lane, M, y, fz);
                         if (lane == 0) counters[tile * 4 + q] = 0u;   // ready for the next launch
                     }
                 }
                 left -= seg_len;
+                done += seg_len;
                 seg_len = nk;
                 tile++;
                 seg++;
             }
-            if (rec && threadIdx.x == 192) dbg[5] = clock64();
+            if (rec && lane == 0) atomicMax(dbg + 7, tc_now());
         }
     }
 
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 1) tcgen05_dealloc(tmem, TCOLS);
+    if (warp == 1) tcgen05_dealloc(tmem, TC_TMEM_COLS);
+    if (rec && threadIdx.x == 32) atomicMax(dbg + 8, tc_now());
 }
 
 // Per-device workspace (partial sums + counters), grown on demand outside stream capture.
 struct TcWorkspace { float* part = nullptr; unsigned int* counters = nullptr; size_t slots = 0, tiles = 0; };
 static TcWorkspace g_tc_ws[NVFP4_MAX_DEVICES];
-static int g_tc_stages = 3;     // ring depth: 3 (two CTAs per SM, the default) or 8 (one)
-static long long* g_tc_probe = nullptr;   // device buffer of 264 words while the timing probe is on
+static long long* g_tc_probe = nullptr;   // device buffer of 8 x 16 words while the timing probe is on
+static unsigned g_tc_probe_seq = 0;       // launches since the probe was switched on
 
 static bool tc_workspace(int dev, size_t slots, size_t tiles, TcWorkspace** out) {
     TcWorkspace& w = g_tc_ws[dev];
@@ -475,42 +567,57 @@ static bool tc_workspace(int dev, size_t slots, size_t tiles, TcWorkspace** out)
 
 }  // namespace nvfp4
 
-extern "C" {
+namespace nvfp4 {
 
-// y[M] (fp16) = dequant(W)[M, K] . x[K] (fp16) on the FP4 tensor-core path.  K % 256 == 0, packed
-// and scales 16-byte aligned, x 16-byte aligned.  The first call on a device (and a call with more
-// row tiles than any before) allocates a workspace and must not run inside a stream capture.
-// 0; -2 shape / pointer not taken; -3 no tensor-map encoder or no memory; else the launch error.
-int launch_nvfp4_gemv_tc(const uint8_t* weight_packed, const uint8_t* weight_scales,
-                         const void* activation, void* output, int M, int K, void* stream) {
-    using namespace nvfp4;
+template <int ST, int PRO, int EPI, bool DBG>
+static cudaError_t tc_launch_st(int dev, int G, cudaStream_t st, const CUtensorMap& wm,
+                                 const CUtensorMap& sm, const __half* x, __half* y, TcWorkspace* ws,
+                                 int M, int K, const TcFuse& fz, long long* dbg) {
+    static bool attr[NVFP4_MAX_DEVICES] = {false};      // per instantiation and device
+    if (!attr[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(gemv_tc_kernel<ST, PRO, EPI, DBG>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   tc_smem_bytes(ST));
+        if (e != cudaSuccess) return e;
+        attr[dev] = true;
+    }
+    return launch_pdl(gemv_tc_kernel<ST, PRO, EPI, DBG>, dim3((unsigned)G), dim3(TC_THREADS),
+                      (size_t)tc_smem_bytes(ST), st, wm, sm, x, y, ws->part, ws->counters, M, K, fz, dbg);
+}
+static int g_tc_ring = 5;      // weight-ring depth: 5 (110 KB per CTA) or 3 (74 KB)
+template <int PRO, int EPI, bool DBG>
+static cudaError_t tc_launch_one(int dev, int G, size_t, cudaStream_t st, const CUtensorMap& wm,
+                                 const CUtensorMap& sm, const __half* x, __half* y, TcWorkspace* ws,
+                                 int M, int K, const TcFuse& fz, long long* dbg) {
+    return g_tc_ring == 3 ? tc_launch_st<3, PRO, EPI, DBG>(dev, G, st, wm, sm, x, y, ws, M, K, fz, dbg)
+                          : tc_launch_st<5, PRO, EPI, DBG>(dev, G, st, wm, sm, x, y, ws, M, K, fz, dbg);
+}
+
+// 0; -2 shape / pointer not taken; -3 no tensor-map encoder or no memory; else the launch error
+static int tc_launch(const uint8_t* weight_packed, const uint8_t* weight_scales, const void* activation,
+                     void* output, int M, int K, int pro, const float* norm_w1, float eps, int epi,
+                     const void* residual, void* stream) {
     if (M <= 0 || K <= 0 || K % TC_BK != 0) return NVFP4_ERR_SHAPE;
     if (!weight_packed || !weight_scales || !activation || !output) return NVFP4_ERR_SHAPE;
     if ((((uintptr_t)weight_packed | (uintptr_t)weight_scales | (uintptr_t)activation) & 15) != 0)
         return NVFP4_ERR_SHAPE;
+    if (pro < TPRO_NONE || pro > TPRO_RMSNORM || epi < TEPI_STORE || epi > TEPI_SILU_MUL) return NVFP4_ERR_SHAPE;
+    if (pro == TPRO_RMSNORM && (!norm_w1 || ((uintptr_t)norm_w1 & 15) != 0 || K > 5 * 8 * (TC_THREADS - 32)))
+        return NVFP4_ERR_SHAPE;
+    if (epi == TEPI_RESIDUAL && !residual) return NVFP4_ERR_SHAPE;
+    if (epi == TEPI_SILU_MUL && M % 16 != 0) return NVFP4_ERR_SHAPE;
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return -3;
     const int dev = current_device_index();
     static int sms[NVFP4_MAX_DEVICES] = {0};
-    static bool attr[NVFP4_MAX_DEVICES] = {false};
     if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
-    if (!attr[dev]) {
-        if (cudaFuncSetAttribute(gemv_tc_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 tc_smem_bytes(8)) != cudaSuccess ||
-            cudaFuncSetAttribute(gemv_tc_kernel<3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 tc_smem_bytes(3)) != cudaSuccess ||
-            cudaFuncSetAttribute(gemv_tc_kernel<3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 tc_smem_bytes(3)) != cudaSuccess)
-            return -3;
-        attr[dev] = true;
-    }
     const int ntiles = (M + TC_BM - 1) / TC_BM, nk = K / TC_BK;
     const long long total = (long long)ntiles * nk;
-    const int slots = sms[dev] * (g_tc_stages == 8 ? 1 : 2);   // resident CTAs: one or two per SM
+    // two CTAs per SM, equal shares of the stages
+    const int slots = 2 * sms[dev];
     const int G = (int)(total < slots ? total : slots);
-    // the digit-plane cache must hold every K stage a CTA visits
-    const long long per_cta = (total + G - 1) / G;
-    if (nk > TC_NBC && per_cta > TC_NBC) return NVFP4_ERR_SHAPE;
+    if (total * (G + 1) >= (1ll << 32)) return NVFP4_ERR_SHAPE;
+    const size_t smem = 0;
     TcWorkspace* ws = nullptr;
     if (!tc_workspace(dev, (size_t)ntiles + G, (size_t)ntiles, &ws)) return -3;
 
@@ -534,31 +641,78 @@ int launch_nvfp4_gemv_tc(const uint8_t* weight_packed, const uint8_t* weight_sca
                 CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return -3;
     }
-    const cudaError_t e =
-        g_tc_probe
-            ? launch_pdl(gemv_tc_kernel<3, true>, dim3((unsigned)G), dim3(TC_THREADS),
-                         (size_t)tc_smem_bytes(3), (cudaStream_t)stream, wm, sm,
-                         static_cast<const __half*>(activation), static_cast<__half*>(output), ws->part,
-                         ws->counters, M, K, g_tc_probe)
-        : g_tc_stages == 8
-            ? launch_pdl(gemv_tc_kernel<8, false>, dim3((unsigned)G), dim3(TC_THREADS),
-                         (size_t)tc_smem_bytes(8), (cudaStream_t)stream, wm, sm,
-                         static_cast<const __half*>(activation), static_cast<__half*>(output), ws->part,
-                         ws->counters, M, K, (long long*)nullptr)
-            : launch_pdl(gemv_tc_kernel<3, false>, dim3((unsigned)G), dim3(TC_THREADS),
-                         (size_t)tc_smem_bytes(3), (cudaStream_t)stream, wm, sm,
-                         static_cast<const __half*>(activation), static_cast<__half*>(output), ws->part,
-                         ws->counters, M, K, (long long*)nullptr);
+    const TcFuse fz = {norm_w1, eps, static_cast<const __half*>(residual)};
+    const __half* x = static_cast<const __half*>(activation);
+    __half* y = static_cast<__half*>(output);
+    cudaStream_t st = (cudaStream_t)stream;
+    cudaError_t e;
+#define TC_CASE(P, E) \
+    if (pro == P && epi == E) e = tc_launch_one<P, E, false>(dev, G, smem, st, wm, sm, x, y, ws, M, K, fz, nullptr); else
+    if (g_tc_probe && pro == TPRO_NONE && epi == TEPI_STORE)
+        e = tc_launch_one<TPRO_NONE, TEPI_STORE, true>(dev, G, smem, st, wm, sm, x, y, ws, M, K, fz,
+                                                       g_tc_probe + 16 * (g_tc_probe_seq++ % 8u));
+    else
+    TC_CASE(TPRO_NONE, TEPI_STORE) TC_CASE(TPRO_NONE, TEPI_RESIDUAL) TC_CASE(TPRO_NONE, TEPI_SILU_MUL)
+    TC_CASE(TPRO_RMSNORM, TEPI_STORE) TC_CASE(TPRO_RMSNORM, TEPI_RESIDUAL) TC_CASE(TPRO_RMSNORM, TEPI_SILU_MUL)
+        e = cudaErrorInvalidValue;
+#undef TC_CASE
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 
-// Tuning hook: ring depth of the tensor-core GEMV: 3 stages of 18 KB and two CTAs per SM (default),
-// or 8 stages and one CTA per SM.
-void nvfp4_b200_gemv_tc_config(int stages) { nvfp4::g_tc_stages = (stages == 8) ? 8 : 3; }
+}  // namespace nvfp4
 
-// Timing probe: with a device buffer of 264 int64 words, the following launches run the build that
-// records CTA 0's pipeline events (SM clock cycles) there; NULL switches it off.
-void nvfp4_gemv_tc_probe(void* device_buffer) { nvfp4::g_tc_probe = static_cast<long long*>(device_buffer); }
+extern "C" {
+
+// y[M] (fp16) = dequant(W)[M, K] . x[K] (fp16) on the FP4 tensor-core path.  K % 256 == 0, packed
+// and scales 16-byte aligned, x 16-byte aligned.  The first call on a device (and a call with more
+// row tiles than any before) allocates a workspace and must not run inside a stream capture.
+// 0; -2 shape / pointer not taken; -3 no tensor-map encoder or no memory; else the launch error.
+int launch_nvfp4_gemv_tc(const uint8_t* weight_packed, const uint8_t* weight_scales,
+                         const void* activation, void* output, int M, int K, void* stream) {
+    return nvfp4::tc_launch(weight_packed, weight_scales, activation, output, M, K, 0, nullptr, 0.0f, 0,
+                            nullptr, stream);
+}
+
+// The same with the neighbours launch_nvfp4_gemv_fused fuses: prologue 1 = RMSNorm of the
+// activation with norm_w1 (fp32 [K], 1 + weight; K <= 11520), epilogue 1 = residual add, epilogue
+// 2 = silu(gate) * up over gate / up rows interleaved in groups of 8 (M = 2 x outputs).
+int launch_nvfp4_gemv_tc_fused(const uint8_t* weight_packed, const uint8_t* weight_scales,
+                               const void* activation, void* output, int M, int K, int prologue,
+                               const void* norm_w1, float eps, int epilogue, const void* residual,
+                               void* stream) {
+    return nvfp4::tc_launch(weight_packed, weight_scales, activation, output, M, K, prologue,
+                            static_cast<const float*>(norm_w1), eps, epilogue, residual, stream);
+}
+
+// Routing of the register-streaming entry points (launch_nvfp4_gemv_v8, launch_nvfp4_gemv_fused) to
+// this kernel: calls with M * K >= min_mega_elements * 2^20 take it (when shape and alignment
+// allow), smaller ones keep the register-streaming kernel, whose fixed cost per launch is lower.
+// 0 = never route.  Default 60: the MLP projections and the vocabulary head of the 27B decoder (a
+// decode step measured 224 tok/s with 60, 199 with routing off, 214 with 25).
+static long long g_tc_route_min = 60ll << 20;
+void nvfp4_b200_gemv_tc_config(int min_mega_elements) {
+    g_tc_route_min = min_mega_elements <= 0 ? 0 : ((long long)min_mega_elements << 20);
+}
+// Weight-ring depth of the kernel: 5 stages (default; 110 KB of shared memory per CTA, two CTAs per
+// SM) or 3 (74 KB, room for a third CTA - of the next kernel - on the SM).
+void nvfp4_b200_gemv_tc_ring(int stages) { nvfp4::g_tc_ring = (stages == 3) ? 3 : 5; }
+int nvfp4_gemv_tc_wanted(int M, int K) {
+    return g_tc_route_min > 0 && (long long)M * K >= g_tc_route_min && K % nvfp4::TC_BK == 0;
+}
+// Allocates this device's workspace now (the launches do it on first use, which must not happen
+// inside a stream capture).  0 or -3.
+int nvfp4_gemv_tc_prepare(void) {
+    nvfp4::TcWorkspace* ws = nullptr;
+    return nvfp4::tc_workspace(nvfp4::current_device_index(), 1, 1, &ws) ? 0 : -3;
+}
+
+// Timing probe: with a device buffer of 128 int64 words, the following launches run the build that
+// records the first and last CTA's pipeline events (global timer, ns) there, launch n into words
+// 16 (n % 8) ..; NULL switches it off.
+void nvfp4_gemv_tc_probe(void* device_buffer) {
+    nvfp4::g_tc_probe = static_cast<long long*>(device_buffer);
+    nvfp4::g_tc_probe_seq = 0;
+}
 
 // 0, or 1 + the id of the first bounded wait inside the tensor-core GEMV that ran out (reset != 0
 // clears it).  Synchronises the device.

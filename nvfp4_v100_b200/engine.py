@@ -173,6 +173,9 @@ class DecodeEngine:
         self.cfg = cfg
         self.dev = torch.device(device)
         self.lib = _lib.load()
+        # the tensor-core GEMV's workspace must exist before any stream capture
+        if self.lib.nvfp4_gemv_tc_prepare() != 0:
+            raise RuntimeError("nvfp4_gemv_tc_prepare failed (no device memory for the GEMV workspace)")
         self.rank, self.world = tp_rank, tp_world
         c = cfg
         W = tp_world

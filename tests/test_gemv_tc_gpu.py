@@ -38,7 +38,7 @@ def check(y, p, s, x, tol=1e-3):
 
 @pytest.mark.parametrize("M,K", [
     (128, 256), (1, 256), (300, 512), (129, 1024), (1024, 5120), (5120, 5120), (33, 17408),
-    (6144, 5120), (17408, 5120), (5120, 17408), (40000, 1024),
+    (6144, 5120), (17408, 5120), (5120, 17408), (40000, 1024), (5120, 6144), (48, 5120),
 ])
 def test_against_oracle(lib, M, K):
     w = oc.synthetic_weight(M, K, seed=M + K)
@@ -78,17 +78,94 @@ def test_repeated_launches_are_identical_and_leave_the_workspace_clean(lib):
     for _ in range(3):
         assert np.array_equal(run(lib, p, s, x), y0)
     # another shape in between uses the same counters and slots
-    p2, s2 = oc.encode(oc.synthetic_weight(300, 512, seed=4))
-    x2 = oc.synthetic_act(512, seed=5)
+    p2, s2 = oc.encode(oc.synthetic_weight(300, 2048, seed=4))
+    x2 = oc.synthetic_act(2048, seed=5)
     check(run(lib, p2, s2, x2), p2, s2, x2)
     assert np.array_equal(run(lib, p, s, x), y0)
+
+
+def fused(lib, p, s, x, M, K, pro_w1=None, epi=0, residual=None, out_rows=None, entry=None):
+    import ctypes
+
+    d_p, d_s, d_x = dev(p), dev(s), dev(x.astype(np.float16))
+    n = out_rows or M
+    out = torch.full((n + 8,), float("nan"), dtype=torch.float16, device="cuda")
+    d_w = dev(pro_w1) if pro_w1 is not None else None
+    d_r = dev(residual.astype(np.float16)) if residual is not None else None
+    z = ctypes.c_void_p(0)
+    lib.nvfp4_gemv_tc_status(1)
+    rc = (entry or lib.launch_nvfp4_gemv_tc_fused)(
+        ptr(d_p), ptr(d_s), ptr(d_x), ptr(out), M, K, 0 if d_w is None else 1,
+        z if d_w is None else ptr(d_w), 1e-6, epi, z if d_r is None else ptr(d_r), stream())
+    torch.cuda.synchronize()
+    assert rc == 0 and lib.nvfp4_gemv_tc_status(0) == 0
+    o = out.cpu().numpy()
+    assert np.isnan(o[n:]).all()
+    return o[:n]
+
+
+@pytest.mark.parametrize("M,K", [(772, 256), (5120, 5120), (100, 10240), (1000, 512), (5120, 17408)])
+def test_fused_rmsnorm_prologue_and_residual(lib, M, K):
+    from oracle import fused_ops_oracle as fo
+
+    p, s = oc.encode(oc.synthetic_weight(M, K, seed=M + K))
+    x = oc.synthetic_act(K, seed=3)
+    res = np.random.default_rng(2).standard_normal(M).astype(np.float16)
+    if K <= 10240:
+        w1 = (1 + 0.1 * np.random.default_rng(1).standard_normal(K)).astype(np.float32)
+        xn = fo.rmsnorm(x[None], w1, 1e-6)[0]
+    else:
+        w1, xn = None, x          # the prologue takes K <= 11520; the residual epilogue any K
+    y = oc.gemv_f64(p, s, xn).astype(np.float16)
+    want = (res.astype(np.float64) + y.astype(np.float64)).astype(np.float16)
+    got = fused(lib, p, s, x, M, K, pro_w1=w1, epi=1, residual=res)
+    # the normalised activation may differ from the oracle's in a few last bits, which moves y by
+    # at most ~1e-3 of its scale; against the residual sum that is a couple of fp16 steps
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert err.max() <= 2e-3 * max(1.0, np.abs(y.astype(np.float64)).max())
+
+
+@pytest.mark.parametrize("inter,K", [(512, 256), (17408, 5120), (40, 1024)])
+def test_fused_silu_mul_epilogue(lib, inter, K):
+    from nvfp4_v100_b200.engine import interleave_gate_up
+    from oracle import fused_ops_oracle as fo
+    from tests.gpu_util import ulp_diff_f16
+
+    gp, gs = oc.encode(oc.synthetic_weight(inter, K, seed=inter, sigma=0.05))
+    upk, us = oc.encode(oc.synthetic_weight(inter, K, seed=inter + 1, sigma=0.05))
+    x = oc.synthetic_act(K, seed=4)
+    w1 = (1 + 0.1 * np.random.default_rng(5).standard_normal(K)).astype(np.float32)
+    xn = fo.rmsnorm(x[None], w1, 1e-6)[0]
+    want = fo.silu_mul(oc.gemv_f64(gp, gs, xn).astype(np.float16), oc.gemv_f64(upk, us, xn).astype(np.float16))
+    p = interleave_gate_up(torch.from_numpy(gp), torch.from_numpy(upk)).numpy()
+    s = interleave_gate_up(torch.from_numpy(gs), torch.from_numpy(us)).numpy()
+    got = fused(lib, p, s, x, 2 * inter, K, pro_w1=w1, epi=2, out_rows=inter)
+    d = ulp_diff_f16(got, want)
+    assert (d == 0).mean() > 0.97, (d == 0).mean()
+    err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+    assert (err <= 6e-3 * np.abs(want.astype(np.float64)) + 2e-6).all(), d.max()
+    # the routed entry (launch_nvfp4_gemv_fused sends this size to the tensor-core kernel when the
+    # matrix is large enough) gives the same bits as the direct one
+    if lib.nvfp4_gemv_tc_wanted(2 * inter, K):
+        again = fused(lib, p, s, x, 2 * inter, K, pro_w1=w1, epi=2, out_rows=inter,
+                      entry=lib.launch_nvfp4_gemv_fused)
+        assert np.array_equal(again, got)
+
+
+def test_routing_rule(lib):
+    assert lib.nvfp4_gemv_tc_prepare() == 0
+    assert lib.nvfp4_gemv_tc_wanted(34816, 5120) == 1 and lib.nvfp4_gemv_tc_wanted(5120, 5120) == 0
+    lib.nvfp4_b200_gemv_tc_config(0)
+    assert lib.nvfp4_gemv_tc_wanted(34816, 5120) == 0
+    lib.nvfp4_b200_gemv_tc_config(60)
+    assert lib.nvfp4_gemv_tc_wanted(34816, 5120) == 1 and lib.nvfp4_gemv_tc_wanted(34816, 5100) == 0
 
 
 def test_argument_validation(lib):
     import ctypes
 
     one = ctypes.c_void_p(0x1000)
-    assert lib.launch_nvfp4_gemv_tc(one, one, one, one, 16, 128, None) == -2     # K % 256
-    assert lib.launch_nvfp4_gemv_tc(one, one, one, one, 0, 256, None) == -2
-    assert lib.launch_nvfp4_gemv_tc(None, one, one, one, 16, 256, None) == -2
-    assert lib.launch_nvfp4_gemv_tc(ctypes.c_void_p(0x1008), one, one, one, 16, 256, None) == -2
+    assert lib.launch_nvfp4_gemv_tc(one, one, one, one, 16, 384, None) == -2     # K % 256
+    assert lib.launch_nvfp4_gemv_tc(one, one, one, one, 0, 1024, None) == -2
+    assert lib.launch_nvfp4_gemv_tc(None, one, one, one, 16, 1024, None) == -2
+    assert lib.launch_nvfp4_gemv_tc(ctypes.c_void_p(0x1008), one, one, one, 16, 1024, None) == -2
