@@ -1043,6 +1043,7 @@ def main():
     if args.tc_min >= 0 and args.impl == "ours":
         from nvfp4_v100_b200 import _lib
         _lib.load().nvfp4_b200_gemv_tc_config(args.tc_min)
+        _lib.load().nvfp4_b200_gemv_tc_config_plain(args.tc_min)
     if args.tc_ring and args.impl == "ours":
         from nvfp4_v100_b200 import _lib
         _lib.load().nvfp4_b200_gemv_tc_ring(args.tc_ring)

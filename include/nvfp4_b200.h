@@ -351,14 +351,18 @@ int launch_nvfp4_gemv_tc_fused(const uint8_t* weight_packed, const uint8_t* weig
                                const void* norm_w1, float eps, int epilogue, const void* residual,
                                void* stream);
 int nvfp4_gemv_tc_status(int reset);
-/* Routing: launch_nvfp4_gemv_v8 and launch_nvfp4_gemv_fused hand calls with M * K >=
- * min_mega_elements * 2^20 to the tensor-core kernel when shape and alignment allow (0 = never;
- * default 60).  nvfp4_gemv_tc_wanted: the rule, 1 or 0.  nvfp4_gemv_tc_prepare: allocate the
+/* Routing: launch_nvfp4_gemv_fused hands calls with M * K >= min_mega_elements * 2^20 to the
+ * tensor-core kernel when shape and alignment allow (nvfp4_b200_gemv_tc_config; 0 = never; default
+ * 60), launch_nvfp4_gemv_v8 those above its own threshold (nvfp4_b200_gemv_tc_config_plain; default
+ * 150: timed back to back on cold activations the register-streaming kernel wins below about
+ * 100 MB).  nvfp4_gemv_tc_wanted / _plain: the rules, 1 or 0.  nvfp4_gemv_tc_prepare: allocate the
  * current device's workspace now, outside any stream capture (0 or -3). */
 void nvfp4_b200_gemv_tc_config(int min_mega_elements);
 /* Weight-ring depth of the tensor-core GEMV: 5 stages (default) or 3. */
 void nvfp4_b200_gemv_tc_ring(int stages);
 int nvfp4_gemv_tc_wanted(int M, int K);
+int nvfp4_gemv_tc_wanted_plain(int M, int K);
+void nvfp4_b200_gemv_tc_config_plain(int min_mega_elements);
 int nvfp4_gemv_tc_prepare(void);
 /* Timing probe of launch_nvfp4_gemv_tc: while a device buffer of 128 int64 words is set, launch n
  * folds into words 16 (n % 8) .. the global nanosecond timer over all its CTAs: 0 earliest kernel

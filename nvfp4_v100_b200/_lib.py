@@ -92,6 +92,8 @@ SIGNATURES = {
     "nvfp4_b200_gemv_tc_ring": ([_i], None),
     "launch_nvfp4_gemv_tc_fused": ([_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _f, _i, _vp, _vp], _i),
     "nvfp4_gemv_tc_wanted": ([_i, _i], _i),
+    "nvfp4_gemv_tc_wanted_plain": ([_i, _i], _i),
+    "nvfp4_b200_gemv_tc_config_plain": ([_i], None),
     "nvfp4_gemv_tc_prepare": ([], _i),
     "nvfp4_gemv_tc_probe": ([_vp], None),
     "launch_dn_fused_noalloc": ([_vp] * 11 + [_i, _i, _f, _vp], _i),

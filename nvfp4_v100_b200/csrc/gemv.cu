@@ -885,7 +885,7 @@ int gemv_dispatch(const void* packed, const void* scales, const void* a0, const 
     const bool fast = !g_cfg.force_generic && (K % 128 == 0) && aligned(packed, 32) &&
                       aligned(scales, 8);
     StreamPlan sp;
-    if (fast && nact == 1 && !old_kernel_tuned() && aligned(scales, 16) && nvfp4_gemv_tc_wanted(M, K)) {
+    if (fast && nact == 1 && !old_kernel_tuned() && aligned(scales, 16) && nvfp4_gemv_tc_wanted_plain(M, K)) {
         // large matrices: the FP4 tensor-core kernel
         const int rc = launch_nvfp4_gemv_tc((const uint8_t*)packed, (const uint8_t*)scales, a0, out, M, K,
                                             stream);

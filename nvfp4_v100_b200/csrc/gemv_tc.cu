@@ -684,21 +684,33 @@ int launch_nvfp4_gemv_tc_fused(const uint8_t* weight_packed, const uint8_t* weig
                             static_cast<const float*>(norm_w1), eps, epilogue, residual, stream);
 }
 
-// Routing of the register-streaming entry points (launch_nvfp4_gemv_v8, launch_nvfp4_gemv_fused) to
-// this kernel: calls with M * K >= min_mega_elements * 2^20 take it (when shape and alignment
-// allow), smaller ones keep the register-streaming kernel, whose fixed cost per launch is lower.
-// 0 = never route.  Default 60: the MLP projections and the vocabulary head of the 27B decoder (a
-// decode step measured 224 tok/s with 60, 199 with routing off, 214 with 25).
+// Routing of the register-streaming entry points to this kernel: calls with M * K >= a threshold
+// (in units of 2^20 elements) take it when shape and alignment allow; smaller ones keep the
+// register-streaming kernel, whose fixed cost per launch is lower.  0 = never route.
+//   fused entry (launch_nvfp4_gemv_fused: the decode engine's calls, activation hot in L2, other
+//   kernels in between): default 60 = the MLP projections, q_proj and the vocabulary head of the 27B
+//   decoder.  A decode step measured 224 tok/s with 60, 199 with routing off, 214 with 25.
+//   plain entry (launch_nvfp4_gemv_v8, timed back to back on cold activations): default 150; at
+//   50 MB the two kernels tie there (15.3 us against 14.7 us), at 715 MB this one wins (112 us
+//   against 131 us).
 static long long g_tc_route_min = 60ll << 20;
+static long long g_tc_route_min_plain = 150ll << 20;
 void nvfp4_b200_gemv_tc_config(int min_mega_elements) {
     g_tc_route_min = min_mega_elements <= 0 ? 0 : ((long long)min_mega_elements << 20);
 }
-// Weight-ring depth of the kernel: 5 stages (default; 110 KB of shared memory per CTA, two CTAs per
-// SM) or 3 (74 KB, room for a third CTA - of the next kernel - on the SM).
-void nvfp4_b200_gemv_tc_ring(int stages) { nvfp4::g_tc_ring = (stages == 3) ? 3 : 5; }
+void nvfp4_b200_gemv_tc_config_plain(int min_mega_elements) {
+    g_tc_route_min_plain = min_mega_elements <= 0 ? 0 : ((long long)min_mega_elements << 20);
+}
 int nvfp4_gemv_tc_wanted(int M, int K) {
     return g_tc_route_min > 0 && (long long)M * K >= g_tc_route_min && K % nvfp4::TC_BK == 0;
 }
+int nvfp4_gemv_tc_wanted_plain(int M, int K) {
+    return g_tc_route_min_plain > 0 && (long long)M * K >= g_tc_route_min_plain && K % nvfp4::TC_BK == 0;
+}
+// Weight-ring depth of the kernel: 5 stages (default; 110 KB of shared memory per CTA, two CTAs per
+// SM; a decode step measured 223 tok/s) or 3 (74 KB, room for a third CTA - of the next kernel - on
+// the SM; 209 tok/s).
+void nvfp4_b200_gemv_tc_ring(int stages) { nvfp4::g_tc_ring = (stages == 3) ? 3 : 5; }
 // Allocates this device's workspace now (the launches do it on first use, which must not happen
 // inside a stream capture).  0 or -3.
 int nvfp4_gemv_tc_prepare(void) {
