@@ -543,7 +543,11 @@ def run_ours(args):
     ms = ev0.elapsed_time(ev1)
 
     # ---- sustained: the same step replayed for at least two seconds ----
-    sus_steps = max(args.steps, int(2.2e3 / max(ms / args.steps, 1e-3)))
+    # (every rank must replay the SAME number of steps: the count comes from the slowest rank's time)
+    ms_all = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(ms_all, op=dist.ReduceOp.MAX)
+    sus_steps = max(args.steps, int(2.2e3 / max(float(ms_all) / args.steps, 1e-3)))
     s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     s0.record()
