@@ -360,6 +360,8 @@ int nvfp4_gemv_tc_status(int reset);
 void nvfp4_b200_gemv_tc_config(int min_mega_elements);
 /* Weight-ring depth of the tensor-core GEMV: 5 stages (default) or 3. */
 void nvfp4_b200_gemv_tc_ring(int stages);
+/* CTAs of one tensor-core GEMV launch per SM: 2 (default) or 1. */
+void nvfp4_b200_gemv_tc_ctas(int per_sm);
 int nvfp4_gemv_tc_wanted(int M, int K);
 int nvfp4_gemv_tc_wanted_plain(int M, int K);
 void nvfp4_b200_gemv_tc_config_plain(int min_mega_elements);

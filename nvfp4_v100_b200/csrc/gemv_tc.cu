@@ -17,9 +17,10 @@
 // Work: row tiles of 128 x K stages of 256 elements, numbered tile-major (a CTA reads consecutive
 // K of the same rows: DRAM pages stay open; a K-chunk-major order measured 25 % slower); the stages
 // are cut into gridDim.x equal contiguous ranges (two CTAs per SM), so a row tile's sum may span two
-// or more CTAs.  Each CTA flushes the partial sums of a (tile, range) segment to a workspace slot;
-// the warp that arrives last at a tile's counter adds the slots in CTA order (deterministic) and
-// writes the fp16 result.
+// or more CTAs.  Each CTA stores the partial sums of its part of a tile to a workspace slot; the
+// CTA that holds the tile's last stages polls the others' slots (an empty slot holds a NaN pattern
+// no sum produces; bounded wait), adds them in CTA order (deterministic) and writes the fp16
+// result.
 //
 // One CTA (320 threads; 58 KB of shared memory + 2 KB per cached stage of digit planes, 128
 // columns of tensor memory - a CTA of the NEXT kernel in the stream fits beside two of this one
@@ -53,7 +54,7 @@ constexpr int TC_A_BYTES = TC_BM * 128;        // packed weights of a stage
 constexpr int TC_B_BYTES = 16 * 128;           // activation digit planes of a stage
 constexpr int TC_S_BYTES = TC_BM * 16;         // weight scale bytes of a stage
 constexpr int TC_SF_COLS = 32;                 // tensor-memory columns of a stage's scale bytes
-constexpr uint32_t TC_SPIN_LIMIT = 1u << 21;   // polls, each parked by the hardware for up to 1 us
+constexpr uint32_t TC_EMPTY = 0xFFFFFFFFu;      // an empty partial-sum slot
 // dynamic shared memory: weight ring of st stages, digit-plane ring, digit table, exponent bytes,
 // scratch; tensor memory: 2 x 16 accumulator columns + st x 32 scale columns
 __host__ __device__ constexpr int tc_smem_bytes(int st) {
@@ -503,28 +504,48 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 const int c_last = tc_cta_of((unsigned)(tile + 1) * nk - 1u, total, G);
                 if (c_first == c_last) {
                     tc_store<EPI>(sum, row, lane, M, y, fz);
+                } else if (b != c_first) {
+                    // a contributor: one store into slot (tile + CTA) - unique, because a CTA
+                    // boundary inside a tile adds one slot - and done.  An empty slot holds the
+                    // all-ones pattern (a NaN no sum of products produces); the value IS the flag.
+                    uint32_t bits = __float_as_uint(sum);
+                    if (bits == TC_EMPTY) bits = 0x7FFFFFFFu;
+                    __stcg(reinterpret_cast<unsigned int*>(&part[(size_t)(tile + b) * TC_BM + q * 32 + lane]), bits);
                 } else {
-                    // slot (tile + CTA) is unique: a CTA boundary inside a tile adds one slot
-                    part[(size_t)(tile + b) * TC_BM + q * 32 + lane] = sum;
-                    __threadfence();
-                    unsigned int old = 0;
-                    if (lane == 0) old = atomicAdd(&counters[tile * 4 + q], 1u);
-                    old = __shfl_sync(0xffffffffu, old, 0);
-                    if (old == (unsigned int)(c_last - c_first)) {
-                        __threadfence();
-                        float tot = 0.0f;
-                        for (int c = c_first; c <= c_last; c += 4) {   // four loads in flight
-                            float pv[4];
+                    // the reducer: the CTA with the tile's FIRST stages, for which this is the last
+                    // segment of its range (the contributors meet the tile at the start of theirs,
+                    // or lie wholly inside it and end when this CTA ends; none of them ever waits,
+                    // so there is no chain of waits).  It polls their slots until none is empty
+                    // (bounded), adds its own part and theirs in CTA order, and leaves the slots
+                    // empty for the next launch: one memory round trip on the critical path, where
+                    // fence + counter + fence + loads took four.
+                    float tot = sum;
+                    for (int c = c_first + 1; c <= c_last; c += 8) {     // eight loads in flight
+                        uint32_t pv[8];
+                        bool all = false;
+                        for (uint32_t spin = 0; spin < (1u << 18) && !all; spin++) {
+                            all = true;
 #pragma unroll
-                            for (int u = 0; u < 4; u++)
-                                pv[u] = (c + u <= c_last)
-                                            ? __ldcg(&part[(size_t)(tile + c + u) * TC_BM + q * 32 + lane]) : 0.0f;
-#pragma unroll
-                            for (int u = 0; u < 4; u++) tot += pv[u];
+                            for (int u = 0; u < 8; u++) {
+                                pv[u] = 0u;
+                                if (c + u <= c_last) {
+                                    asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];\n" : "=r"(pv[u])
+                                                 : "l"(&part[(size_t)(tile + c + u) * TC_BM + q * 32 + lane]) : "memory");
+                                    all = all && (pv[u] != TC_EMPTY);
+                                }
+                            }
+                            if (!all) __nanosleep(100);
                         }
-                        tc_store<EPI>(tot, row, lane, M, y, fz);
-                        if (lane == 0) counters[tile * 4 + q] = 0u;   // ready for the next launch
+                        if (!all) atomicExch(&g_tc_status, 9);
+#pragma unroll
+                        for (int u = 0; u < 8; u++)
+                            if (c + u <= c_last) {
+                                tot += __uint_as_float(pv[u]);
+                                __stcg(reinterpret_cast<unsigned int*>(&part[(size_t)(tile + c + u) * TC_BM + q * 32 + lane]),
+                                       TC_EMPTY);
+                            }
                     }
+                    tc_store<EPI>(tot, row, lane, M, y, fz);
                 }
                 left -= seg_len;
                 done += seg_len;
@@ -558,6 +579,7 @@ static bool tc_workspace(int dev, size_t slots, size_t tiles, TcWorkspace** out)
         if (cudaMalloc(&w.part, ns * TC_BM * sizeof(float)) != cudaSuccess) return false;
         if (cudaMalloc(&w.counters, nt * 4 * sizeof(unsigned int)) != cudaSuccess) return false;
         if (cudaMemset(w.counters, 0, nt * 4 * sizeof(unsigned int)) != cudaSuccess) return false;
+        if (cudaMemset(w.part, 0xFF, ns * TC_BM * sizeof(float)) != cudaSuccess) return false;   // all slots empty
         w.slots = ns;
         w.tiles = nt;
     }
@@ -585,6 +607,7 @@ static cudaError_t tc_launch_st(int dev, int G, cudaStream_t st, const CUtensorM
                       (size_t)tc_smem_bytes(ST), st, wm, sm, x, y, ws->part, ws->counters, M, K, fz, dbg);
 }
 static int g_tc_ring = 5;      // weight-ring depth: 5 (110 KB per CTA) or 3 (74 KB)
+static int g_tc_ctas = 2;      // CTAs of one launch per SM: 2, or 1 (the next kernel's CTA fits beside it)
 template <int PRO, int EPI, bool DBG>
 static cudaError_t tc_launch_one(int dev, int G, size_t, cudaStream_t st, const CUtensorMap& wm,
                                  const CUtensorMap& sm, const __half* x, __half* y, TcWorkspace* ws,
@@ -614,7 +637,7 @@ static int tc_launch(const uint8_t* weight_packed, const uint8_t* weight_scales,
     const int ntiles = (M + TC_BM - 1) / TC_BM, nk = K / TC_BK;
     const long long total = (long long)ntiles * nk;
     // two CTAs per SM, equal shares of the stages
-    const int slots = 2 * sms[dev];
+    const int slots = g_tc_ctas * sms[dev];
     const int G = (int)(total < slots ? total : slots);
     if (total * (G + 1) >= (1ll << 32)) return NVFP4_ERR_SHAPE;
     const size_t smem = 0;
@@ -711,6 +734,8 @@ int nvfp4_gemv_tc_wanted_plain(int M, int K) {
 // SM; a decode step measured 223 tok/s) or 3 (74 KB, room for a third CTA - of the next kernel - on
 // the SM; 209 tok/s).
 void nvfp4_b200_gemv_tc_ring(int stages) { nvfp4::g_tc_ring = (stages == 3) ? 3 : 5; }
+// CTAs of one launch per SM: 2 (default) or 1.
+void nvfp4_b200_gemv_tc_ctas(int per_sm) { nvfp4::g_tc_ctas = (per_sm == 1) ? 1 : 2; }
 // Allocates this device's workspace now (the launches do it on first use, which must not happen
 // inside a stream capture).  0 or -3.
 int nvfp4_gemv_tc_prepare(void) {
@@ -734,6 +759,9 @@ int nvfp4_gemv_tc_status(int reset) {
     if (reset) {
         const int z = 0;
         cudaMemcpyToSymbol(nvfp4::g_tc_status, &z, sizeof(int));
+        // after a wait that ran out, slots may have been left filled: empty them all again
+        nvfp4::TcWorkspace& w = nvfp4::g_tc_ws[nvfp4::current_device_index()];
+        if (v != 0 && w.part) cudaMemset(w.part, 0xFF, w.slots * nvfp4::TC_BM * sizeof(float));
     }
     return v;
 }
