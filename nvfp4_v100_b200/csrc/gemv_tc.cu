@@ -328,11 +328,27 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             }
         }
     } else {
+        // converting warps: the loads of the next stage to convert are kept one conversion ahead;
+        // the first stage's norm weights (constants) are requested before the previous kernel has
+        // finished, its activations right after, together with the loads of the mean of squares
+        int cv = 0, cv_ks = 0;
+        uint4 pre_x = make_uint4(0u, 0u, 0u, 0u);
+        float4 pre_w0 = make_float4(0.f, 0.f, 0.f, 0.f), pre_w1 = pre_w0;
+        if (warp >= 6) {
+            cv = warp - 6;
+            cv_ks = ks0 + cv;
+            while (cv_ks >= nk) cv_ks -= nk;
+            if (PRO == TPRO_RMSNORM && cv < nst) {
+                pre_w0 = __ldg(reinterpret_cast<const float4*>(fz.norm_w1 + cv_ks * TC_BK + lane * 8));
+                pre_w1 = __ldg(reinterpret_cast<const float4*>(fz.norm_w1 + cv_ks * TC_BK + lane * 8 + 4));
+            }
+        }
         asm volatile("griddepcontrol.wait;\n" ::: "memory");
         PDL_FRESH(x);
         PDL_FRESH(y);
         PDL_FRESH(part);
         PDL_FRESH(counters);
+        if (warp >= 6 && cv < nst) pre_x = *reinterpret_cast<const uint4*>(x + cv_ks * TC_BK + lane * 8);
         if (rec && threadIdx.x == 32) { const long long t = tc_now(); atomicMax(dbg + 2, t); atomicMin(dbg + 3, t); }
         float inv = 1.0f;
         if (PRO == TPRO_RMSNORM) {
@@ -449,20 +465,15 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             // a segment's accumulation it has converted its stages up to 7 beyond the segment's
             // end: those waits depend only on MMAs inside or before the segment, and the MMAs of
             // the next segment find their planes ready.
-            const int f = warp - 6, q = warp & 3;
+            const int q = warp & 3;
             const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-            int cv = f;                                          // next stage this warp converts
-            int cv_ks = ks0 + f;
-            while (cv_ks >= nk) cv_ks -= nk;
             auto convert_upto = [&](int last) {
                 for (; cv <= last && cv < nst; cv += 4) {
                     const int slot = cv & (NB - 1);
-                    const int k = cv_ks * TC_BK + lane * 8;
-                    uint4 xv = *reinterpret_cast<const uint4*>(x + k);
+                    uint4 xv = pre_x;
                     if (PRO == TPRO_RMSNORM) {
-                        const float4 w0 = __ldg(reinterpret_cast<const float4*>(fz.norm_w1 + k));
-                        const float4 w1 = __ldg(reinterpret_cast<const float4*>(fz.norm_w1 + k + 4));
-                        const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                        const float w[8] = {pre_w0.x, pre_w0.y, pre_w0.z, pre_w0.w,
+                                            pre_w1.x, pre_w1.y, pre_w1.z, pre_w1.w};
                         __half2* h = reinterpret_cast<__half2*>(&xv);
 #pragma unroll
                         for (int e = 0; e < 4; e++) {
@@ -471,14 +482,22 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                                                   __float2half(fv.y * inv * w[2 * e + 1]));
                         }
                     }
+                    cv_ks += 4;
+                    while (cv_ks >= nk) cv_ks -= nk;
+                    if (cv + 4 < nst) {                  // the next conversion's loads travel meanwhile
+                        const int k = cv_ks * TC_BK + lane * 8;
+                        pre_x = *reinterpret_cast<const uint4*>(x + k);
+                        if (PRO == TPRO_RMSNORM) {
+                            pre_w0 = __ldg(reinterpret_cast<const float4*>(fz.norm_w1 + k));
+                            pre_w1 = __ldg(reinterpret_cast<const float4*>(fz.norm_w1 + k + 4));
+                        }
+                    }
                     // the slot's previous planes (stage cv - 8) must have been consumed
                     tc_wait(smem_u32(&bar_bempty[slot]), (((uint32_t)cv >> 3) & 1u) ^ 1u, 7);
                     tc_digit_planes(xv, lut, smem_b + slot * TC_B_BYTES, smem_l + slot * 16, lane);
                     fence_proxy_async_smem();        // the tensor core reads the planes (async proxy)
                     __syncwarp();
                     if (lane == 0) mbar_arrive(smem_u32(&bar_bfull[slot]));
-                    cv_ks += 4;
-                    while (cv_ks >= nk) cv_ks -= nk;
                 }
             };
             int seg = 0, tile = tile0, left = nst, seg_len = nk - ks0, done = 0;
@@ -713,11 +732,11 @@ int launch_nvfp4_gemv_tc_fused(const uint8_t* weight_packed, const uint8_t* weig
 //   fused entry (launch_nvfp4_gemv_fused: the decode engine's calls, activation hot in L2, other
 //   kernels in between): default 60 = the MLP projections, q_proj and the vocabulary head of the 27B
 //   decoder.  A decode step measured 224 tok/s with 60, 199 with routing off, 214 with 25.
-//   plain entry (launch_nvfp4_gemv_v8, timed back to back on cold activations): default 150; at
-//   50 MB the two kernels tie there (15.3 us against 14.7 us), at 715 MB this one wins (112 us
-//   against 131 us).
+//   plain entry (launch_nvfp4_gemv_v8, timed back to back on cold activations): default 80; at
+//   89 M elements this kernel takes 12.2 us against 14.7 us, at 63 M the two tie (10.2 / 10.0 us),
+//   at 52 M the register-streaming kernel wins (8.6 against 9.3 us).
 static long long g_tc_route_min = 60ll << 20;
-static long long g_tc_route_min_plain = 150ll << 20;
+static long long g_tc_route_min_plain = 80ll << 20;
 void nvfp4_b200_gemv_tc_config(int min_mega_elements) {
     g_tc_route_min = min_mega_elements <= 0 ? 0 : ((long long)min_mega_elements << 20);
 }
