@@ -542,7 +542,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                     for (int c = c_first + 1; c <= c_last; c += 8) {     // eight loads in flight
                         uint32_t pv[8];
                         bool all = false;
-                        for (uint32_t spin = 0; spin < (1u << 18) && !all; spin++) {
+                        for (uint32_t spin = 0; spin < (1u << 20) && !all; spin++) {
                             all = true;
 #pragma unroll
                             for (int u = 0; u < 8; u++) {
@@ -553,7 +553,6 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                                     all = all && (pv[u] != TC_EMPTY);
                                 }
                             }
-                            if (!all) __nanosleep(100);
                         }
                         if (!all) atomicExch(&g_tc_status, 9);
 #pragma unroll
