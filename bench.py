@@ -1015,6 +1015,7 @@ def main():
                     help="with --gemm: quantise the activations to NVFP4 on the fly (W4A4 values)")
     ap.add_argument("--tc-ring", type=int, default=0, help="tensor-core GEMV weight-ring depth (3 or 5)")
     ap.add_argument("--tc-ctas", type=int, default=0, help="tensor-core GEMV CTAs per SM (1 or 2)")
+    ap.add_argument("--tc-pre", type=int, default=0, help="tensor-core GEMV weight stages requested at entry")
     ap.add_argument("--tc-min", type=int, default=-1,
                     help="route GEMVs with M*K >= this many 2^20 elements to the tensor-core kernel "
                          "(nvfp4_b200_gemv_tc_config; 0 = never; default: the library's)")
@@ -1049,6 +1050,9 @@ def main():
         from nvfp4_v100_b200 import _lib
         _lib.load().nvfp4_b200_gemv_tc_config(args.tc_min)
         _lib.load().nvfp4_b200_gemv_tc_config_plain(args.tc_min)
+    if args.tc_pre and args.impl == "ours":
+        from nvfp4_v100_b200 import _lib
+        _lib.load().nvfp4_b200_gemv_tc_prefetch(args.tc_pre)
     if args.tc_ctas and args.impl == "ours":
         from nvfp4_v100_b200 import _lib
         _lib.load().nvfp4_b200_gemv_tc_ctas(args.tc_ctas)

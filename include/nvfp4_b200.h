@@ -354,12 +354,14 @@ int nvfp4_gemv_tc_status(int reset);
 /* Routing: launch_nvfp4_gemv_fused hands calls with M * K >= min_mega_elements * 2^20 to the
  * tensor-core kernel when shape and alignment allow (nvfp4_b200_gemv_tc_config; 0 = never; default
  * 60), launch_nvfp4_gemv_v8 those above its own threshold (nvfp4_b200_gemv_tc_config_plain; default
- * 80: timed back to back on cold activations the register-streaming kernel wins below about
- * 60 M elements).  nvfp4_gemv_tc_wanted / _plain: the rules, 1 or 0.  nvfp4_gemv_tc_prepare: allocate the
+ * 50: timed back to back on cold activations the register-streaming kernel wins below that).  nvfp4_gemv_tc_wanted / _plain: the rules, 1 or 0.  nvfp4_gemv_tc_prepare: allocate the
  * current device's workspace now, outside any stream capture (0 or -3). */
 void nvfp4_b200_gemv_tc_config(int min_mega_elements);
 /* Weight-ring depth of the tensor-core GEMV: 5 stages (default) or 3. */
 void nvfp4_b200_gemv_tc_ring(int stages);
+/* Weight stages a CTA of the tensor-core GEMV requests at kernel entry (1..5, default 2); the rest
+ * follow its activation loads. */
+void nvfp4_b200_gemv_tc_prefetch(int stages_at_entry);
 /* CTAs of one tensor-core GEMV launch per SM: 2 (default) or 1. */
 void nvfp4_b200_gemv_tc_ctas(int per_sm);
 int nvfp4_gemv_tc_wanted(int M, int K);

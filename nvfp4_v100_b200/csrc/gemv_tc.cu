@@ -193,6 +193,7 @@ struct TcFuse {
     const float* norm_w1;
     float eps;
     const __half* residual;
+    int pre;       // weight stages requested at kernel entry; the others follow the activation request
 };
 
 // Final value of row `row` (this lane's; the warp's 32 rows are consecutive and start at a
@@ -254,6 +255,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     __shared__ __align__(8) uint64_t bar_acc_full[2];         // a segment's accumulation retired
     __shared__ __align__(8) uint64_t bar_acc_empty[2];        // the flush warps have read it
     __shared__ uint32_t s_tmem;
+    __shared__ volatile int s_xreq;                           // the activation loads have been issued
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = gridDim.x, b = blockIdx.x;
@@ -287,8 +289,9 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
             mbar_init(smem_u32(&bar_acc_full[a]), 1);
             mbar_init(smem_u32(&bar_acc_empty[a]), 128);
         }
+        s_xreq = 0;
         fence_barrier_init();
-        for (; p_i < nst && p_i < ST; p_i++) {
+        for (; p_i < nst && p_i < ST && p_i < fz.pre; p_i++) {
             const uint32_t bar = smem_u32(&bar_full[p_s]);
             mbar_arrive_expect_tx(bar, TC_A_BYTES + TC_S_BYTES);
             tma_load_2d(smem_u32(smem_a + p_s * TC_A_BYTES), &w_map, p_ks * 128, p_tile * TC_BM, bar);
@@ -317,6 +320,9 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     if (warp == 0) {
         // ---------------- TMA producer, the stages after the first ST ----------------
         if (lane == 0) {
+            // the stages held back at entry go out once the activation loads are on their way: in
+            // the SM's request path they would otherwise queue behind 90 KB of weight requests
+            for (uint32_t w = 0; w < (1u << 24) && s_xreq == 0; w++) {}
             for (; p_i < nst; p_i++) {
                 if (!tc_wait_poll(smem_u32(&bar_empty[p_s]), p_ph ^ 1u, 0)) break;
                 const uint32_t bar = smem_u32(&bar_full[p_s]);
@@ -349,6 +355,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
         PDL_FRESH(part);
         PDL_FRESH(counters);
         if (warp >= 6 && cv < nst) pre_x = *reinterpret_cast<const uint4*>(x + cv_ks * TC_BK + lane * 8);
+        if (PRO != TPRO_RMSNORM && threadIdx.x == 192) s_xreq = 1;
         if (rec && threadIdx.x == 32) { const long long t = tc_now(); atomicMax(dbg + 2, t); atomicMin(dbg + 3, t); }
         float inv = 1.0f;
         if (PRO == TPRO_RMSNORM) {
@@ -361,6 +368,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
                 const int i = (t0 + j * T) * 8;
                 v[j] = (i < K) ? *reinterpret_cast<const uint4*>(x + i) : make_uint4(0u, 0u, 0u, 0u);
             }
+            if (threadIdx.x == 192) s_xreq = 1;
             float ss = 0.0f;
 #pragma unroll
             for (int j = 0; j < 5; j++) {
@@ -625,6 +633,7 @@ static cudaError_t tc_launch_st(int dev, int G, cudaStream_t st, const CUtensorM
                       (size_t)tc_smem_bytes(ST), st, wm, sm, x, y, ws->part, ws->counters, M, K, fz, dbg);
 }
 static int g_tc_ring = 5;      // weight-ring depth: 5 (110 KB per CTA) or 3 (74 KB)
+static int g_tc_pre = 2;       // weight stages a CTA requests at entry (the rest after its activation loads)
 static int g_tc_ctas = 2;      // CTAs of one launch per SM: 2, or 1 (the next kernel's CTA fits beside it)
 template <int PRO, int EPI, bool DBG>
 static cudaError_t tc_launch_one(int dev, int G, size_t, cudaStream_t st, const CUtensorMap& wm,
@@ -682,7 +691,7 @@ static int tc_launch(const uint8_t* weight_packed, const uint8_t* weight_scales,
                 CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return -3;
     }
-    const TcFuse fz = {norm_w1, eps, static_cast<const __half*>(residual)};
+    const TcFuse fz = {norm_w1, eps, static_cast<const __half*>(residual), g_tc_pre};
     const __half* x = static_cast<const __half*>(activation);
     __half* y = static_cast<__half*>(output);
     cudaStream_t st = (cudaStream_t)stream;
@@ -729,13 +738,14 @@ int launch_nvfp4_gemv_tc_fused(const uint8_t* weight_packed, const uint8_t* weig
 // (in units of 2^20 elements) take it when shape and alignment allow; smaller ones keep the
 // register-streaming kernel, whose fixed cost per launch is lower.  0 = never route.
 //   fused entry (launch_nvfp4_gemv_fused: the decode engine's calls, activation hot in L2, other
-//   kernels in between): default 60 = the MLP projections, q_proj and the vocabulary head of the 27B
-//   decoder.  A decode step measured 224 tok/s with 60, 199 with routing off, 214 with 25.
-//   plain entry (launch_nvfp4_gemv_v8, timed back to back on cold activations): default 80; at
-//   89 M elements this kernel takes 12.2 us against 14.7 us, at 63 M the two tie (10.2 / 10.0 us),
-//   at 52 M the register-streaming kernel wins (8.6 against 9.3 us).
+//   kernels in between): default 60 = the MLP projections, the fused input projections and the
+//   vocabulary head of the 27B decoder.  A decode step measured 258 tok/s with 40 or 60, 251 with
+//   25, 199 with routing off.
+//   plain entry (launch_nvfp4_gemv_v8, timed back to back on cold activations): default 50; at
+//   89 M elements this kernel takes 11.4 us against 14.7 us, at 52 M 8.2 against 8.6 us, at 31 M the
+//   register-streaming kernel wins (6.0 against 6.7 us).
 static long long g_tc_route_min = 60ll << 20;
-static long long g_tc_route_min_plain = 80ll << 20;
+static long long g_tc_route_min_plain = 50ll << 20;
 void nvfp4_b200_gemv_tc_config(int min_mega_elements) {
     g_tc_route_min = min_mega_elements <= 0 ? 0 : ((long long)min_mega_elements << 20);
 }
@@ -752,6 +762,11 @@ int nvfp4_gemv_tc_wanted_plain(int M, int K) {
 // SM; a decode step measured 223 tok/s) or 3 (74 KB, room for a third CTA - of the next kernel - on
 // the SM; 209 tok/s).
 void nvfp4_b200_gemv_tc_ring(int stages) { nvfp4::g_tc_ring = (stages == 3) ? 3 : 5; }
+// Weight stages a CTA requests at kernel entry, 1..5; the others are requested once the activation
+// loads have been issued.
+void nvfp4_b200_gemv_tc_prefetch(int stages_at_entry) {
+    nvfp4::g_tc_pre = stages_at_entry < 1 ? 1 : stages_at_entry > 5 ? 5 : stages_at_entry;
+}
 // CTAs of one launch per SM: 2 (default) or 1.
 void nvfp4_b200_gemv_tc_ctas(int per_sm) { nvfp4::g_tc_ctas = (per_sm == 1) ? 1 : 2; }
 // Allocates this device's workspace now (the launches do it on first use, which must not happen
