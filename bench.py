@@ -660,7 +660,8 @@ def run_ours(args):
         "gpu_launches": run["kernel_launches_per_step"] * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu / peak, "traffic": TRAFFIC_PER_LAUNCH, "peak_kind": peak_kind,
-                     "kernel": "gemv_mma_kernel",
+                     "kernel": "gemv_tc_kernel (matrices of >= 50 M elements: 85 % of the step's bytes) + "
+                               "gemv_mma_kernel (the rest)",
                      "frac_of_nominal_8000": per_gpu / 8000.0},
         "cpu_baseline": cpu,
         "clocks": summarise_clocks(clock_lines),
@@ -986,11 +987,14 @@ def run_decode(args, quiet=False):
     return res
 
 
-# DRAM bytes (read + write) per average GEMV launch of the mix.  The full-set ncu capture was taken
-# on the 151936x5120 shape (profiles/gemv_mma_kernel_lm_head_151936x5120.md): 441.69 MB of DRAM
-# traffic for 437.89 MB of algorithmic bytes, ratio 1.0087; every weight byte is read once at any
-# shape, so the traffic of the mix's average launch (14 427 447 296 B / 497) is scaled by that ratio.
-TRAFFIC_PER_LAUNCH = int(14_427_447_296 / 497 * (441.69 / 437.89))
+# DRAM bytes (read + write) per average GEMV launch of the mix, from two full-set ncu captures on the
+# 151936x5120 shape: the tensor-core kernel, which runs 85 % of the step's bytes, moved 452.1 MB for
+# 437.6 MB of algorithmic bytes (profiles/gemv_tc_kernel_lm_head_151936x5120.md: ratio 1.033, reads
+# 1.024 + partial-sum slots), the register-streaming kernel 441.69 MB for 437.89 MB
+# (profiles/gemv_mma_kernel_lm_head_151936x5120.md: 1.0087).  Every weight byte is read once at any
+# shape, so the traffic of the mix's average launch (14 427 447 296 B / 497) is scaled by the
+# byte-weighted ratio.
+TRAFFIC_PER_LAUNCH = int(14_427_447_296 / 497 * (0.85 * 1.033 + 0.15 * 1.0087))
 
 
 def main():
