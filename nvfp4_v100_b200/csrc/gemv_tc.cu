@@ -22,21 +22,23 @@
 // no sum produces; bounded wait), adds them in CTA order (deterministic) and writes the fp16
 // result.
 //
-// One CTA (320 threads; 58 KB of shared memory + 2 KB per cached stage of digit planes, 128
-// columns of tensor memory - a CTA of the NEXT kernel in the stream fits beside two of this one
-// when the cache is small, and prefetches its weights meanwhile):
-//   all warps   prologue (after the previous kernel in the stream has finished): the digit planes
-//               of every K stage this CTA will visit, into a shared-memory cache (2 KB per stage, the
-//               B operand tile as the tensor core reads it: 16 rows x 128 B, 128-byte swizzle), and
-//               the blocks' exponent bytes.
-//   warp 0      TMA producer: per stage 128 rows x 128 packed bytes (128-byte swizzle) and the
-//               128 x 16 scale bytes, into a 3-stage ring; begins BEFORE the previous kernel has
-//               finished (programmatic dependent launch: weights are constants).
-//   warp 1      MMA issuer: 4 x tcgen05.mma M128 N16 K64 per stage into one of two accumulators.
+// One CTA (320 threads; 111 KB of shared memory: a 5-stage weight ring of 18 KB stages, an 8-slot
+// ring of 2 KB digit-plane tiles, a 1 KB digit table; 256 columns of tensor memory; two CTAs per SM):
+//   thread 0    TMA producer: per stage 128 rows x 128 packed bytes (128-byte swizzle) and the
+//               128 x 16 scale bytes.  Two stages are requested at kernel entry, BEFORE the previous
+//               kernel in the stream has finished (programmatic dependent launch: weights are
+//               constants); the others once the activation loads have been issued, because those
+//               would queue behind the weight requests in the SM's request path.
+//   warp 1      MMA issuer (one thread): 4 x tcgen05.mma M128 N16 K64 per stage into one of two
+//               accumulators.  All its stage counters are kept by increment: this thread runs one
+//               instruction at a time, a division per stage would cost more than the MMAs.
 //   warps 2..5  scale writers: weight scale bytes shared memory -> tensor memory (tcgen05.st; lane
 //               r % 32, column r / 32, replicated in the four lane quarters) and the digit columns'
-//               scale bytes.
-//   warps 6..9  flush: accumulator (128 lanes x 16 columns) -> 16-term sum per row -> result.
+//               scale bytes, one 32-column store per stage.
+//   warps 6..9  digit conversion, one 256-element stage per warp task, up to 8 stages ahead of the
+//               MMAs (plane-ring slot free = the MMAs of stage i - 8 retired), with the optional
+//               RMSNorm applied on the way; and the flush: accumulator (128 lanes x 16 columns)
+//               -> 16-term sum per row -> slot or result, with the optional epilogue.
 // Every wait is bounded; nvfp4_gemv_tc_status reports the first one that ran out.
 #include <cuda.h>
 
