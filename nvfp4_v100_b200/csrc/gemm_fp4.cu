@@ -10,15 +10,16 @@
 //
 // One CTA (192 threads) computes a 128-row x BN-token tile, K in stages of 256 elements:
 //   warp 0      TMA producer: per stage one box of weight bytes (128 rows x 128 B) and one box of
-//               activation bytes (BN tokens x 128 B), both K-major with the 128-byte swizzle, into an
-//               ST-stage shared-memory ring; completion by transaction bytes on an mbarrier.
+//               activation bytes (BN tokens x 128 B), both K-major with the 128-byte swizzle, and the
+//               two boxes of their scale bytes (rows x 16 B), into an ST-stage shared-memory ring;
+//               completion by transaction bytes on an mbarrier.
 //   warp 1      MMA issuer: 4 tcgen05.mma (K = 64 each) per stage, one elected thread;
 //               tcgen05.commit hands the stage back.
 //   warps 2..5  scale-factor writers, then the epilogue.  The tensor core reads the scale bytes from
 //               tensor memory: for an operand row r (weight row or token) of the tile, lane r % 32,
 //               32-bit column r / 32 holds the row's 4 scale bytes of one 64-element K block, the
 //               same in all four 32-lane quarters.  Each of the 4 warps owns one quarter: a lane
-//               loads 16 scale bytes (one stage) of each of its rows from global memory and writes
+//               reads 16 scale bytes (one stage) of each of its rows from the ring and writes
 //               them with tcgen05.st.  Per stage 16 columns for the weights and max(BN / 8, 16) for the tokens.
 // Tensor memory: BN accumulator columns + ST x (16 + max(BN/8, 16)) scale columns.
 //
@@ -83,7 +84,8 @@ template <int BN, int ST>
 __global__ void __launch_bounds__(F4_THREADS)
 gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
                              const __grid_constant__ CUtensorMap a_map,
-                             const uint8_t* __restrict__ w_scales, const uint8_t* __restrict__ a_scales,
+                             const __grid_constant__ CUtensorMap ws_map,
+                             const __grid_constant__ CUtensorMap as_map,
                              __half* __restrict__ out, int M, int n_tokens, int K, int ld_out) {
     constexpr int A_BYTES = F4_BM * 128;             // weight tile of a stage
     constexpr int B_BYTES = BN * 128;                // token tile of a stage
@@ -97,8 +99,12 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~(uintptr_t)1023);
+    constexpr int SA_BYTES = F4_BM * 16;             // weight scale bytes of a stage
+    constexpr int SB_BYTES = BN * 16;                // token scale bytes of a stage
     uint8_t* smem_a = smem;
     uint8_t* smem_b = smem + ST * A_BYTES;
+    uint8_t* smem_sa = smem_b + ST * B_BYTES;
+    uint8_t* smem_sb = smem_sa + ST * SA_BYTES;
     __shared__ __align__(8) uint64_t bar_full[ST];    // TMA bytes landed
     __shared__ __align__(8) uint64_t bar_sf[ST];      // scale bytes written to tensor memory
     __shared__ __align__(8) uint64_t bar_empty[ST];   // the stage's MMAs retired
@@ -135,11 +141,13 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
                 const uint32_t ph = (uint32_t)(it / ST) & 1u;
                 if (!f4_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 0)) break;
                 const uint32_t bar = smem_u32(&bar_full[s]);
-                mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES);
-                // coordinates: x = byte along K (a multiple of 128), y = row; rows past the end
-                // of either matrix are filled with zero bytes by the copy engine
+                mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES + SA_BYTES + SB_BYTES);
+                // coordinates: x = byte along K (a multiple of 128 / of 16), y = row; rows past
+                // the end of either matrix are filled with zero bytes by the copy engine
                 tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, it * 128, m0, bar);
                 tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, it * 128, n0, bar);
+                tma_load_2d(smem_u32(smem_sa + s * SA_BYTES), &ws_map, it * 16, m0, bar);
+                tma_load_2d(smem_u32(smem_sb + s * SB_BYTES), &as_map, it * 16, n0, bar);
             }
         }
     } else if (warp == 1) {
@@ -152,8 +160,8 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
             for (int it = 0; it < ksteps; it++) {
                 const int s = it % ST;
                 const uint32_t ph = (uint32_t)(it / ST) & 1u;
+                // (the scale writers arrive only after they saw the stage's copies land)
                 if (!f4_wait(smem_u32(&bar_sf[s]), ph, 1)) break;
-                if (!f4_wait(smem_u32(&bar_full[s]), ph, 2)) break;
                 tcgen05_fence_after();
                 const uint32_t a_base = smem_u32(smem_a + s * A_BYTES);
                 const uint32_t b_base = smem_u32(smem_b + s * B_BYTES);
@@ -174,49 +182,30 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
         // ---------------- scale-factor writers ----------------
         const int q = warp & 3;                            // this warp's 32-lane quarter
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        const size_t sf_pitch = (size_t)(K >> 4);
-        const uint8_t* wrow[4];
-        bool wok[4];
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            const int r = m0 + c * 32 + lane;
-            wok[c] = r < M;
-            wrow[c] = w_scales + (size_t)min(r, M - 1) * sf_pitch;
-        }
-        const uint8_t* arow[NB];
-        bool aok[NB];
-#pragma unroll
-        for (int c = 0; c < NB; c++) {
-            const int t = n0 + c * 32 + lane;
-            aok[c] = t < n_tokens;
-            arow[c] = a_scales + (size_t)min(t, n_tokens - 1) * sf_pitch;
-        }
-        const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-        uint4 wv[4], av[NB];
-#pragma unroll
-        for (int c = 0; c < 4; c++) wv[c] = wok[c] ? __ldg(reinterpret_cast<const uint4*>(wrow[c])) : zero4;
-#pragma unroll
-        for (int c = 0; c < NB; c++) av[c] = aok[c] ? __ldg(reinterpret_cast<const uint4*>(arow[c])) : zero4;
         bool ok = true;
         for (int it = 0; it < ksteps; it++) {
             const int s = it % ST;
             const uint32_t ph = (uint32_t)(it / ST) & 1u;
-            // column 4 kk + c (weights) / kk NB + c (tokens) = word kk of row c's 16 bytes
+            // The scale bytes travel with the stage (two more TMA boxes: 128 x 16 B and BN x 16 B),
+            // so they are requested ST stages ahead like the operands.  (Loaded by the lanes
+            // from global memory one stage ahead, they queued behind the operand requests in the
+            // SM's request path.)  The stage's landing also means that the MMAs which read this
+            // slot's tensor-memory columns a ring round ago have retired.
+            if (ok) ok = f4_wait(smem_u32(&bar_full[s]), ph, 3);
+            tcgen05_fence_after();
+            const uint8_t* sa = smem_sa + s * SA_BYTES;
+            const uint8_t* sb = smem_sb + s * SB_BYTES;
+            uint4 wv[4], av[NB];
+#pragma unroll
+            for (int c = 0; c < 4; c++) wv[c] = *reinterpret_cast<const uint4*>(sa + (c * 32 + lane) * 16);
+#pragma unroll
+            for (int c = 0; c < NB; c++) av[c] = *reinterpret_cast<const uint4*>(sb + (c * 32 + lane) * 16);
+            // column 4 kk + c (weights) / kk NBC + c (tokens) = word kk of row c's 16 bytes
             uint32_t wa[4][4], wb[4][NB];
 #pragma unroll
             for (int c = 0; c < 4; c++) { wa[0][c] = wv[c].x; wa[1][c] = wv[c].y; wa[2][c] = wv[c].z; wa[3][c] = wv[c].w; }
 #pragma unroll
             for (int c = 0; c < NB; c++) { wb[0][c] = av[c].x; wb[1][c] = av[c].y; wb[2][c] = av[c].z; wb[3][c] = av[c].w; }
-            if (it + 1 < ksteps) {           // the next stage's bytes travel while this one waits
-#pragma unroll
-                for (int c = 0; c < 4; c++)
-                    wv[c] = wok[c] ? __ldg(reinterpret_cast<const uint4*>(wrow[c] + (size_t)(it + 1) * 16)) : zero4;
-#pragma unroll
-                for (int c = 0; c < NB; c++)
-                    av[c] = aok[c] ? __ldg(reinterpret_cast<const uint4*>(arow[c] + (size_t)(it + 1) * 16)) : zero4;
-            }
-            if (ok) ok = f4_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 3);
-            tcgen05_fence_after();
             const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS) + lane_base;
 #pragma unroll
             for (int kk = 0; kk < 4; kk++) {
@@ -270,10 +259,10 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
 }
 
 template <int BN, int ST>
-static cudaError_t launch_fp4(const CUtensorMap& wm, const CUtensorMap& am, const uint8_t* ws,
-                              const uint8_t* as, __half* out, int M, int n, int K, int ld,
+static cudaError_t launch_fp4(const CUtensorMap& wm, const CUtensorMap& am, const CUtensorMap& ws,
+                              const CUtensorMap& as, __half* out, int M, int n, int K, int ld,
                               cudaStream_t st) {
-    constexpr int SMEM = ST * (F4_BM * 128 + BN * 128) + 1024;
+    constexpr int SMEM = ST * (F4_BM * 128 + BN * 128 + F4_BM * 16 + BN * 16) + 1024;
     static bool attr[NVFP4_MAX_DEVICES] = {false};
     const int dev = current_device_index();
     if (!attr[dev]) {
@@ -298,6 +287,18 @@ static bool byte_matrix_map(EncodeTiledFn enc, CUtensorMap* map, const void* bas
                CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// scale bytes [rows][K/16]: boxes of 16 bytes (one 256-element stage) x box_rows rows, unswizzled
+static bool scale_matrix_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, int rows, int K,
+                             int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)(K / 16), (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)(K / 16)};
+    const cuuint32_t box[2] = {16, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    return enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace nvfp4
 
 extern "C" {
@@ -319,17 +320,19 @@ int launch_nvfp4_gemm_fp4(const uint8_t* w_packed, const uint8_t* w_scales, cons
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return -3;
     const int BN = n_tokens > 128 ? 256 : n_tokens > 64 ? 128 : n_tokens > 32 ? 64 : 32;
-    CUtensorMap wm, am;
+    CUtensorMap wm, am, wsm, asm_;
     if (!byte_matrix_map(enc, &wm, w_packed, M, K, F4_BM) ||
-        !byte_matrix_map(enc, &am, a_packed, n_tokens, K, BN))
+        !byte_matrix_map(enc, &am, a_packed, n_tokens, K, BN) ||
+        !scale_matrix_map(enc, &wsm, w_scales, M, K, F4_BM) ||
+        !scale_matrix_map(enc, &asm_, a_scales, n_tokens, K, BN))
         return -3;
     cudaStream_t st = (cudaStream_t)stream;
     __half* o = static_cast<__half*>(out);
     const cudaError_t e =
-        BN == 256 ? launch_fp4<256, 4>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
-      : BN == 128 ? launch_fp4<128, 6>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
-      : BN == 64  ? launch_fp4<64, 6>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st)
-                  : launch_fp4<32, 6>(wm, am, w_scales, a_scales, o, M, n_tokens, K, ld_out, st);
+        BN == 256 ? launch_fp4<256, 4>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st)
+      : BN == 128 ? launch_fp4<128, 6>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st)
+      : BN == 64  ? launch_fp4<64, 6>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st)
+                  : launch_fp4<32, 6>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st);
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 
