@@ -786,6 +786,8 @@ def run_gemm(args):
     except Exception:
         tf_peak, tf_kind = 1590.0, "fallback"
     hbm_peak, hbm_kind = measured_peak()
+    if args.gemm_rows128:
+        lib.nvfp4_b200_gemm_config(0)
     rows = []
     token_counts = (args.tokens,) if args.tokens else (32, 8192)
     shapes = ((6144, HIDDEN), (INTER, HIDDEN), (HIDDEN, HIDDEN), (HIDDEN, INTER))
@@ -1025,6 +1027,8 @@ def main():
                          "(nvfp4_b200_gemv_tc_config; 0 = never; default: the library's)")
     ap.add_argument("--tc", action="store_true",
                     help="with --per-shape: the FP4 tensor-core GEMV (launch_nvfp4_gemv_tc)")
+    ap.add_argument("--gemm-rows128", action="store_true",
+                    help="with --gemm: 128-row CTA tiles only (nvfp4_b200_gemm_config(0))")
     ap.add_argument("--fp4-only", action="store_true",
                     help="with --gemm: time launch_nvfp4_gemm_fp4 alone on pre-encoded activations")
     ap.add_argument("--tokens", type=int, default=0,

@@ -89,6 +89,7 @@ SIGNATURES = {
     "launch_nvfp4_gemv_tc": ([_vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "nvfp4_gemv_tc_status": ([_i], _i),
     "nvfp4_b200_gemv_tc_config": ([_i], None),
+    "nvfp4_b200_gemm_config": ([_i], None),
     "nvfp4_b200_gemv_tc_ring": ([_i], None),
     "nvfp4_b200_gemv_tc_ctas": ([_i], None),
     "nvfp4_b200_gemv_tc_prefetch": ([_i], None),

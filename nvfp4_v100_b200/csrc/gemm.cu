@@ -46,6 +46,7 @@ constexpr int GEMM_WPF = 4;               // K steps the weight loads run ahead 
 constexpr uint32_t GEMM_SPIN_LIMIT = 1u << 24;
 
 __device__ int g_gemm_status = 0;  // 0 ok; otherwise 1 + id of the wait that ran out
+static int g_gemm_rows256 = 1;     // 256-row CTA tiles for more than 128 tokens (0: 128-row tiles only)
 
 // Bounded wait.  Returns false (after recording `id`) if the barrier never completed.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int id) {
@@ -59,14 +60,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int id)
 // Shared memory (dynamic, 1024-byte aligned): per stage A tile 128 x 128 B = 16 KB, then per stage
 // B tile (BN/64) boxes of 64 k-rows x 128 B = 8 KB each.
 // ---------------------------------------------------------------------------------------------
-template <int BN>
+// MT = weight row tiles of 128 per CTA (1 or 2).  With MT = 2 a CTA computes 256 rows x BN tokens
+// in two accumulators (2 x BN columns of tensor memory): the activation tile, which is most of the
+// operand traffic from L2 (32 KB of the 36.5 KB a 128-row CTA pulls per K step at BN = 256), is
+// fetched once for twice the rows.  The kernel was bound by that feed, not by the tensor pipe.
+template <int BN, int MT>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                           const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
                           __half* __restrict__ out, int M, int N, int K) {
     // (two stages and two CTAs per SM for the 256-token tile measured 8 % slower than this)
-    constexpr int ST = GEMM_STAGES;
-    constexpr int A_BYTES = GEMM_BM * 128;          // 16 KB
+    constexpr int ST = (MT == 2 && BN == 256) ? 3 : GEMM_STAGES;
+    constexpr int A_TILE = GEMM_BM * 128;           // 16 KB: one 128-row tile of a stage
+    constexpr int A_BYTES = MT * A_TILE;
     constexpr int B_BOX = GEMM_BK * 128;            // 8 KB: 64 k rows of 64 tokens
     constexpr int B_BYTES = (BN / 64) * B_BOX;
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -82,7 +88,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
     __shared__ uint32_t s_tmem;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * GEMM_BM, n0 = blockIdx.y * BN;
+    const int m0 = blockIdx.x * GEMM_BM * MT, n0 = blockIdx.y * BN;
     const int ksteps = K / GEMM_BK;
 
     if (threadIdx.x == 0) {
@@ -95,7 +101,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
         fence_barrier_init();
     }
     if (warp == 0) {  // one warp allocates the accumulator's tensor-memory columns
-        tcgen05_alloc(smem_u32(&s_tmem), BN);
+        tcgen05_alloc(smem_u32(&s_tmem), MT * BN);
         tcgen05_relinquish();
     }
     tcgen05_fence_before();
@@ -141,9 +147,13 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                     // A, K-major: 16 k = 32 bytes further along the 128-byte row; 8-row groups
                     // are 1024 bytes apart.  B, MN-major: 16 k = two groups of 8 k rows (1024
                     // bytes each); 64-token atoms are one box (8 KB) apart.
-                    const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
                     const uint64_t bdesc = make_desc_sw128(b_base + kk * 2048, B_BOX, 1024);
-                    tcgen05_mma_f16(tmem, adesc, bdesc, idesc, (it | kk) != 0 ? 1u : 0u);
+#pragma unroll
+                    for (int mt = 0; mt < MT; mt++) {
+                        const uint64_t adesc = make_desc_sw128(a_base + mt * A_TILE + kk * 32, 16, 1024);
+                        tcgen05_mma_f16(tmem + (uint32_t)(mt * BN), adesc, bdesc, idesc,
+                                        (it | kk) != 0 ? 1u : 0u);
+                    }
                 }
                 tcgen05_commit(smem_u32(&bar_empty[s]));   // stage reusable when these MMAs retire
             }
@@ -152,22 +162,32 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
     } else {
         // ---------------- weight producers (two threads per weight row), then epilogue ----------------
         const int pt = threadIdx.x - 64;                 // 0..255
-        const int r = pt >> 1, half = pt & 1;            // row of the tile, which 32 of its 64 weights
-        const int row = min(m0 + r, M - 1);
-        const bool row_ok = (m0 + r) < M;
-        const uint8_t* prow = packed + (size_t)row * (size_t)(K >> 1) + half * 16;
-        const uint8_t* srow = scales + (size_t)row * (size_t)(K >> 4) + half * 2;
+        const int r = pt >> 1, half = pt & 1;            // row of a 128-row tile, which 32 of its 64 weights
+        const uint8_t* prow[MT];
+        const uint8_t* srow[MT];
+        bool row_ok[MT];
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++) {
+            const int rr = m0 + mt * GEMM_BM + r;
+            row_ok[mt] = rr < M;
+            const int row = min(rr, M - 1);
+            prow[mt] = packed + (size_t)row * (size_t)(K >> 1) + half * 16;
+            srow[mt] = scales + (size_t)row * (size_t)(K >> 4) + half * 2;
+        }
         bool ok = true;
-        // 16 packed bytes (32 weights = 2 scale blocks) per K step, requested GEMM_WPF steps ahead
-        // of their use: the weight stream comes from HBM and its latency is longer than the
+        // 16 packed bytes (32 weights = 2 scale blocks) per row and K step, requested GEMM_WPF steps
+        // ahead of their use: the weight stream comes from HBM and its latency is longer than the
         // tensor core needs for one K step
-        uint4 pw[GEMM_WPF];
-        uint32_t ps[GEMM_WPF];
+        uint4 pw[GEMM_WPF][MT];
+        uint32_t ps[GEMM_WPF][MT];
 #pragma unroll
         for (int u = 0; u < GEMM_WPF; u++) {
             if (u < ksteps) {
-                pw[u] = ld_stream_u4(prow + (size_t)u * 32);
-                ps[u] = __ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)u * 4));
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++) {
+                    pw[u][mt] = ld_stream_u4(prow[mt] + (size_t)u * 32);
+                    ps[u][mt] = __ldg(reinterpret_cast<const unsigned short*>(srow[mt] + (size_t)u * 4));
+                }
             }
         }
         for (int it0 = 0; it0 < ksteps; it0 += GEMM_WPF) {
@@ -177,31 +197,39 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
             if (it >= ksteps) break;
             const int s = it % ST;
             const uint32_t ph = (uint32_t)(it / ST) & 1u;
-            const uint4 p0 = pw[u];
-            const uint32_t sc2 = ps[u];
-            if (it + GEMM_WPF < ksteps) {
-                pw[u] = ld_stream_u4(prow + (size_t)(it + GEMM_WPF) * 32);
-                ps[u] = __ldg(reinterpret_cast<const unsigned short*>(srow + (size_t)(it + GEMM_WPF) * 4));
+            uint4 p0[MT];
+            uint32_t sc2[MT];
+#pragma unroll
+            for (int mt = 0; mt < MT; mt++) {
+                p0[mt] = pw[u][mt];
+                sc2[mt] = ps[u][mt];
+                if (it + GEMM_WPF < ksteps) {
+                    pw[u][mt] = ld_stream_u4(prow[mt] + (size_t)(it + GEMM_WPF) * 32);
+                    ps[u][mt] = __ldg(reinterpret_cast<const unsigned short*>(srow[mt] + (size_t)(it + GEMM_WPF) * 4));
+                }
             }
             if (ok) ok = mbar_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 3);
-            const uint32_t w[4] = {p0.x, p0.y, p0.z, p0.w};
-            uint8_t* arow = smem_a + s * A_BYTES + r * 128;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {               // 16-byte chunk c = weights 8c .. 8c+7
-                const int c = half * 4 + j;
-                uint32_t h0, h1, h2, h3;
-                e2m1x8_to_half2x4(w[j], h0, h1, h2, h3);
-                // block scale 2^(sb-127) as fp16, applied in fp16 as the reference does
-                const __half sc = __float2half(e8m0_to_f32((sc2 >> (8 * (j >> 1))) & 0xFFu));
-                const __half2 s2 = __half2half2(sc);
-                uint4 v;
-                __half2 t;
-                t = __hmul2(*reinterpret_cast<__half2*>(&h0), s2); v.x = *reinterpret_cast<uint32_t*>(&t);
-                t = __hmul2(*reinterpret_cast<__half2*>(&h1), s2); v.y = *reinterpret_cast<uint32_t*>(&t);
-                t = __hmul2(*reinterpret_cast<__half2*>(&h2), s2); v.z = *reinterpret_cast<uint32_t*>(&t);
-                t = __hmul2(*reinterpret_cast<__half2*>(&h3), s2); v.w = *reinterpret_cast<uint32_t*>(&t);
-                if (!row_ok) v = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = v;   // 128-byte swizzle
+            for (int mt = 0; mt < MT; mt++) {
+                const uint32_t w[4] = {p0[mt].x, p0[mt].y, p0[mt].z, p0[mt].w};
+                uint8_t* arow = smem_a + s * A_BYTES + mt * A_TILE + r * 128;
+#pragma unroll
+                for (int j = 0; j < 4; j++) {               // 16-byte chunk c = weights 8c .. 8c+7
+                    const int c = half * 4 + j;
+                    uint32_t h0, h1, h2, h3;
+                    e2m1x8_to_half2x4(w[j], h0, h1, h2, h3);
+                    // block scale 2^(sb-127) as fp16, applied in fp16 as the reference does
+                    const __half sc = __float2half(e8m0_to_f32((sc2[mt] >> (8 * (j >> 1))) & 0xFFu));
+                    const __half2 s2 = __half2half2(sc);
+                    uint4 v;
+                    __half2 t;
+                    t = __hmul2(*reinterpret_cast<__half2*>(&h0), s2); v.x = *reinterpret_cast<uint32_t*>(&t);
+                    t = __hmul2(*reinterpret_cast<__half2*>(&h1), s2); v.y = *reinterpret_cast<uint32_t*>(&t);
+                    t = __hmul2(*reinterpret_cast<__half2*>(&h2), s2); v.z = *reinterpret_cast<uint32_t*>(&t);
+                    t = __hmul2(*reinterpret_cast<__half2*>(&h3), s2); v.w = *reinterpret_cast<uint32_t*>(&t);
+                    if (!row_ok[mt]) v = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(arow + ((c ^ (r & 7)) << 4)) = v;   // 128-byte swizzle
+                }
             }
             fence_proxy_async_smem();     // make the generic-proxy writes visible to the tensor core
             mbar_arrive(smem_u32(&bar_full_a[s]));
@@ -213,14 +241,16 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
         tcgen05_fence_after();
         const int q = warp & 3;                          // this warp's 32-lane quarter of TMEM
         const int chalf = (warp - 2) >> 2;               // which half of the token columns
-        const int m = m0 + q * 32 + lane;
         constexpr int CB = BN / 32;                      // 32-column blocks in the tile
+#pragma unroll 1
+        for (int mt = 0; mt < MT; mt++) {
+        const int m = m0 + mt * GEMM_BM + q * 32 + lane;
 #pragma unroll
         for (int cbi = 0; cbi < (CB + 1) / 2; cbi++) {
             const int cb = chalf * ((CB + 1) / 2) + cbi;
             if (cb >= CB) break;
             uint32_t v[32];
-            tcgen05_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(cb * 32), v);
+            tcgen05_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * BN + cb * 32), v);
             tcgen05_wait_ld();
             const int nb = n0 + cb * 32;
             if (m < M && nb < N) {
@@ -247,11 +277,12 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                 }
             }
         }
+        }
     }
 
     tcgen05_fence_before();
     __syncthreads();
-    if (warp == 0) tcgen05_dealloc(tmem, BN);
+    if (warp == 0) tcgen05_dealloc(tmem, MT * BN);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -281,20 +312,21 @@ gemm_w4a16_fallback_kernel(const uint8_t* __restrict__ packed, const uint8_t* __
     out[(size_t)m * N + n] = __float2half(acc);
 }
 
-template <int BN>
+template <int BN, int MT>
 static cudaError_t launch_tc(const CUtensorMap& map, const uint8_t* packed, const uint8_t* scales,
                              __half* out, int M, int N, int K, cudaStream_t st) {
-    constexpr int SMEM = GEMM_STAGES * (GEMM_BM * 128 + (BN / 64) * GEMM_BK * 128) + 1024;
+    constexpr int ST = (MT == 2 && BN == 256) ? 3 : GEMM_STAGES;
+    constexpr int SMEM = ST * (MT * GEMM_BM * 128 + (BN / 64) * GEMM_BK * 128) + 1024;
     static bool attr[NVFP4_MAX_DEVICES] = {false};   // the attribute is per device
     const int dev = current_device_index();
     if (!attr[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<BN>,
+        const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<BN, MT>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
         attr[dev] = true;
     }
-    dim3 grid((unsigned)((M + GEMM_BM - 1) / GEMM_BM), (unsigned)((N + BN - 1) / BN));
-    gemm_w4a16_tcgen05_kernel<BN><<<grid, GEMM_THREADS, SMEM, st>>>(map, packed, scales, out, M, N, K);
+    dim3 grid((unsigned)((M + GEMM_BM * MT - 1) / (GEMM_BM * MT)), (unsigned)((N + BN - 1) / BN));
+    gemm_w4a16_tcgen05_kernel<BN, MT><<<grid, GEMM_THREADS, SMEM, st>>>(map, packed, scales, out, M, N, K);
     return cudaGetLastError();
 }
 
@@ -333,9 +365,14 @@ int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weig
         if (r == CUDA_SUCCESS) {
             // wider token tiles amortise the weight dequantisation over more tensor-core work
             const cudaError_t e =
-                (N > 128) ? launch_tc<256>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
-              : (N > 64)  ? launch_tc<128>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
-                          : launch_tc<64>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st);
+                // 256-row tiles when they still give every SM a CTA (17408 x 512 tokens: 136 CTAs,
+                // 1282 TFLOP/s against 967 with 128-row tiles; 6144 x 512: 48 CTAs, slower)
+                (N > 128 && g_gemm_rows256 &&
+                 (long long)((M + 255) / 256) * ((N + 255) / 256) >= 120)
+                          ? launch_tc<256, 2>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
+              : (N > 128) ? launch_tc<256, 1>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
+              : (N > 64)  ? launch_tc<128, 1>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
+                          : launch_tc<64, 1>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st);
             return (e == cudaSuccess) ? 0 : (int)e;
         }
     }
@@ -393,10 +430,13 @@ int nvfp4_gemm_status(int reset) {
     return v;
 }
 
+// Tuning hook: 256-row CTA tiles (two accumulators) for more than 128 tokens: 1 (default) or 0.
+void nvfp4_b200_gemm_config(int rows256) { nvfp4::g_gemm_rows256 = rows256 ? 1 : 0; }
+
 // Shared memory of the tensor-core GEMM's widest tile, for callers that size their launches the
 // way the reference's get_kernel_shared_mem_bytes does (kernels/nvfp4_cuda_v5.cu:460-464).
 int get_kernel_shared_mem_bytes() {
-    return nvfp4::GEMM_STAGES * (nvfp4::GEMM_BM * 128 + 4 * nvfp4::GEMM_BK * 128) + 1024;
+    return 3 * (2 * nvfp4::GEMM_BM * 128 + 4 * nvfp4::GEMM_BK * 128) + 1024;
 }
 
 }  // extern "C"
