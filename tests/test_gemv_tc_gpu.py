@@ -157,7 +157,7 @@ def test_routing_rule(lib):
     assert lib.nvfp4_gemv_tc_wanted(34816, 5120) == 1 and lib.nvfp4_gemv_tc_wanted(5120, 5120) == 0
     lib.nvfp4_b200_gemv_tc_config(0)
     assert lib.nvfp4_gemv_tc_wanted(34816, 5120) == 0
-    lib.nvfp4_b200_gemv_tc_config(60)
+    lib.nvfp4_b200_gemv_tc_config(35)
     assert lib.nvfp4_gemv_tc_wanted(34816, 5120) == 1 and lib.nvfp4_gemv_tc_wanted(34816, 5100) == 0
 
 
