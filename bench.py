@@ -620,6 +620,9 @@ def run_ours(args):
     if rank != 0:
         shutdown(world)
         return
+    gemm = None
+    if world == 1 and not args.no_decode:
+        gemm = quick_gemm(lib)
 
     value = job_bytes * args.steps / (ms * 1e-3) / 1e9
     e2e_value = job_bytes * e2e_steps / (e2e_ms * 1e-3) / 1e9
@@ -666,6 +669,7 @@ def run_ours(args):
         "cpu_baseline": cpu,
         "clocks": summarise_clocks(clock_lines),
         "decode": decode,
+        "gemm": gemm,
     }
     if world > 1:
         line["tp_parity"] = {"max_err_over_max_output": parity_max, "ok": bool(parity_max <= 2e-3),
@@ -682,7 +686,9 @@ SHAPES_27B = [("lm_head", VOCAB, HIDDEN, 1), ("down_proj", HIDDEN, INTER, 64),
               ("in_proj_b/a", 48, HIDDEN, 96),
               # further shapes of the same decoder: q without its gate, the square o_proj, a 151936-row head
               ("q_proj 6144", 6144, HIDDEN, 0), ("o_proj 5120", HIDDEN, HIDDEN, 0),
-              ("lm_head 151936", 151936, HIDDEN, 0), ("gate+up fused", 2 * INTER, HIDDEN, 0)]
+              ("lm_head 151936", 151936, HIDDEN, 0), ("gate+up fused", 2 * INTER, HIDDEN, 0),
+              # two-GPU shards of the MLP projections
+              ("gate/up shard", INTER // 2, HIDDEN, 0), ("down shard", HIDDEN, INTER // 2, 0)]
 
 
 def run_per_shape(args):
@@ -768,6 +774,62 @@ def run_per_shape(args):
             "mix_497": {"ms_per_step": mix_us / 1e3,
                         "gbps": (mix_bytes / (mix_us * 1e-6) / 1e9) if mix_us else None}}
     print(json.dumps(line), flush=True)
+
+
+def quick_gemm(lib):
+    """The dense GEMM on one prefill-sized problem (17408 x 5120 weights, 8192 tokens), for the
+    default line: W4A16 (launch_nvfp4_gemmtc_v5, the reference's semantics) and W4A4
+    (launch_nvfp4_gemm_w4a4: activations encoded to NVFP4 inside the timed launches, then the
+    block-scaled FP4 tensor-core kernel).  CUDA events, best of 3 x 3 launches."""
+    import torch
+
+    vp = ctypes.c_void_p
+    M, K, tokens = INTER, HIDDEN, 8192
+    try:
+        tf_peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+        kind = "measured"
+    except Exception:
+        tf_peak, kind = 1590.0, "fallback"
+    p = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device="cuda")
+    s = torch.randint(118, 123, (M * K // 16,), dtype=torch.uint8, device="cuda")
+    a_kn = torch.randn(K, tokens, device="cuda").to(torch.float16)
+    a_tm = torch.randn(tokens, K, device="cuda").to(torch.float16)
+    o = torch.zeros(M, tokens, dtype=torch.float16, device="cuda")
+    work = torch.empty(K * tokens, dtype=torch.float16, device="cuda")
+    st = vp(torch.cuda.current_stream().cuda_stream)
+
+    def w4a16():
+        assert lib.launch_nvfp4_gemmtc_v5(vp(p.data_ptr()), vp(s.data_ptr()), vp(a_kn.data_ptr()),
+                                          vp(o.data_ptr()), M, tokens, K, st) == 0
+
+    def w4a4():
+        assert lib.launch_nvfp4_gemm_w4a4(vp(p.data_ptr()), vp(s.data_ptr()), vp(a_tm.data_ptr()),
+                                          vp(o.data_ptr()), vp(work.data_ptr()), M, tokens, K, st) == 0
+
+    out = {"workload": f"{M}x{K} weights, {tokens} tokens", "flop": 2.0 * M * K * tokens}
+    for name, fn in (("w4a16", w4a16), ("w4a4", w4a4)):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        best = None
+        for _ in range(3):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                fn()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / 3
+            best = us if best is None else min(best, us)
+        tf = out["flop"] / best / 1e6
+        # W4A4 against 4 x the bf16 figure: the FP4 tensor rate is four times the bf16 rate
+        peak = tf_peak * (4.0 if name == "w4a4" else 1.0)
+        out[name] = {"us": best, "tflops": tf, "peak_tflops": peak, "frac": tf / peak,
+                     "peak_kind": kind + (" bf16 burst x 4" if name == "w4a4" else " bf16 burst")}
+    out["status"] = lib.nvfp4_gemm_status(0)
+    del p, s, a_kn, a_tm, o, work
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_gemm(args):

@@ -357,7 +357,7 @@ int nvfp4_gemv_tc_status(int reset);
 /* Routing: launch_nvfp4_gemv_fused hands calls with M * K >= min_mega_elements * 2^20 to the
  * tensor-core kernel when shape and alignment allow (nvfp4_b200_gemv_tc_config; 0 = never; default
  * 35), launch_nvfp4_gemv_v8 those above its own threshold (nvfp4_b200_gemv_tc_config_plain; default
- * 50: timed back to back on cold activations the register-streaming kernel wins below that).  nvfp4_gemv_tc_wanted / _plain: the rules, 1 or 0.  nvfp4_gemv_tc_prepare: allocate the
+ * 40: timed back to back on cold activations the register-streaming kernel wins below that).  nvfp4_gemv_tc_wanted / _plain: the rules, 1 or 0.  nvfp4_gemv_tc_prepare: allocate the
  * current device's workspace now, outside any stream capture (0 or -3). */
 void nvfp4_b200_gemv_tc_config(int min_mega_elements);
 /* Weight-ring depth of the tensor-core GEMV: 5 stages (default) or 3. */

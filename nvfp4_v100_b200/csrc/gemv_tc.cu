@@ -745,11 +745,12 @@ int launch_nvfp4_gemv_tc_fused(const uint8_t* weight_packed, const uint8_t* weig
 //   258 tok/s with 40 or 60, 251 with 25, 199 with routing off on one GPU (the 31 M-element output
 //   projections stay on the register-streaming kernel); on two GPUs 281 tok/s with 30, 273 with
 //   40, 244 with 60 (the 37 M-element shard of the fused q/k/v projection).
-//   plain entry (launch_nvfp4_gemv_v8, timed back to back on cold activations): default 50; at
-//   89 M elements this kernel takes 11.4 us against 14.7 us, at 52 M 8.2 against 8.6 us, at 31 M the
+//   plain entry (launch_nvfp4_gemv_v8, timed back to back on cold activations): default 40; at
+//   89 M elements this kernel takes 11.4 us against 14.7 us, at 52 M 8.2 against 8.6 us, at 44.5 M
+//   (the two-GPU shards of the MLP projections) 7.4 / 7.6 against 8.4 / 8.1 us, at 31 M the
 //   register-streaming kernel wins (6.0 against 6.7 us).
 static long long g_tc_route_min = 35ll << 20;
-static long long g_tc_route_min_plain = 50ll << 20;
+static long long g_tc_route_min_plain = 40ll << 20;
 void nvfp4_b200_gemv_tc_config(int min_mega_elements) {
     g_tc_route_min = min_mega_elements <= 0 ? 0 : ((long long)min_mega_elements << 20);
 }

@@ -415,3 +415,28 @@ def test_full_width_63_tokens_after_512_prompt_match_the_oracle(lib):
     assert clear_ok == clear and clear + len(near) == 63 and clear >= 40
     assert max(diffs_ulp) <= LOGIT_TOL, diffs_ulp
     assert lib.nvfp4_gemm_status(0) == 0
+
+
+def test_container_loader_gives_the_same_engine_as_tensors(lib, tmp_path):
+    # DecodeEngine.load_container (memory-mapped reference-format container, shard-sized copies) must
+    # put the same bytes on the device as load_weights from the in-memory arrays: identical logits
+    # after the same prompt and identical greedy tokens
+    from tests.test_container_loader import SMALL as CSMALL, write_container
+
+    cfg = ModelConfig(**CSMALL)
+    W = do.make_weights(cfg, 3)
+    write_container(str(tmp_path), W)
+    prompt = np.random.default_rng(3).integers(0, cfg.vocab, 9)
+    outs = []
+    for how in ("tensors", "container"):
+        eng = DecodeEngine(cfg)
+        if how == "tensors":
+            eng.load_weights(W)
+        else:
+            eng.load_container(str(tmp_path))
+        eng.reset(int(prompt[0]))
+        eng.capture(n_warmup=1)
+        toks = eng.run(prompt, 10, native_prefill=True)
+        outs.append((toks, eng.logits.float().cpu().numpy().copy()))
+    assert outs[0][0] == outs[1][0]
+    assert np.array_equal(outs[0][1], outs[1][1])
