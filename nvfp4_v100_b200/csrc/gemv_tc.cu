@@ -20,7 +20,12 @@
 // or more CTAs.  Each CTA stores the partial sums of its part of a tile to a workspace slot; the
 // CTA that holds the tile's last stages polls the others' slots (an empty slot holds a NaN pattern
 // no sum produces; bounded wait), adds them in CTA order (deterministic) and writes the fp16
-// result.
+// result.  That is a wait between CTAs of one launch: the grid is at most two CTAs per SM, which
+// is what fits, so all of them are resident once the previous kernel has left the SMs (a kernel
+// launched behind this one cannot start before every CTA of this one runs); a CTA only waits for
+// CTAs with higher indices that never wait themselves before they have stored.  If something
+// else holds the SMs' shared memory for longer than the bound (about a second), the wait runs
+// out, the result of that tile is wrong and nvfp4_gemv_tc_status says so; nothing hangs.
 //
 // One CTA (320 threads; 111 KB of shared memory: a 5-stage weight ring of 18 KB stages, an 8-slot
 // ring of 2 KB digit-plane tiles, a 1 KB digit table; 256 columns of tensor memory; two CTAs per SM):
