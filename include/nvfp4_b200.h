@@ -353,6 +353,16 @@ int launch_nvfp4_gemv_tc_fused(const uint8_t* weight_packed, const uint8_t* weig
                                const void* activation, void* output, int M, int K, int prologue,
                                const void* norm_w1, float eps, int epilogue, const void* residual,
                                void* stream);
+/* The MLP block of a decoder layer in ONE launch of the tensor-core GEMV kernel: act[inter] =
+ * silu(gate) * up over W_gu . rmsnorm(h) (W_gu = [2 inter][hidden], gate / up rows interleaved in
+ * groups of 8, norm_w1 fp32 [hidden] = 1 + weight), then h[hidden] += W_down . act (W_down =
+ * [hidden][inter]); the weight ring streams on from the first matrix into the second across a
+ * bounded grid-wide barrier.  Results are those of launch_nvfp4_gemv_tc_fused(prologue 1, epilogue
+ * 2) followed by (prologue 0, epilogue 1).  hidden, inter % 256 == 0, hidden <= 11520, all pointers
+ * 16-byte aligned.  Return values of launch_nvfp4_gemv_tc. */
+int launch_nvfp4_mlp_tc(const uint8_t* gu_packed, const uint8_t* gu_scales, const uint8_t* down_packed,
+                        const uint8_t* down_scales, void* h, void* act, const void* norm_w1, float eps,
+                        int inter, int hidden, void* stream);
 int nvfp4_gemv_tc_status(int reset);
 /* Routing: launch_nvfp4_gemv_fused hands calls with M * K >= min_mega_elements * 2^20 to the
  * tensor-core kernel when shape and alignment allow (nvfp4_b200_gemv_tc_config; 0 = never; default

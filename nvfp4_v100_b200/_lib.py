@@ -94,6 +94,7 @@ SIGNATURES = {
     "nvfp4_b200_gemv_tc_ctas": ([_i], None),
     "nvfp4_b200_gemv_tc_prefetch": ([_i], None),
     "launch_nvfp4_gemv_tc_fused": ([_vp, _vp, _vp, _vp, _i, _i, _i, _vp, _f, _i, _vp, _vp], _i),
+    "launch_nvfp4_mlp_tc": ([_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f, _i, _i, _vp], _i),
     "nvfp4_gemv_tc_wanted": ([_i, _i], _i),
     "nvfp4_gemv_tc_wanted_plain": ([_i, _i], _i),
     "nvfp4_b200_gemv_tc_config_plain": ([_i], None),

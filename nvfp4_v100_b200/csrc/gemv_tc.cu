@@ -596,6 +596,436 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant_
     if (rec && threadIdx.x == 32) atomicMax(dbg + 8, tc_now());
 }
 
+// ---------------------------------------------------------------------------------------------
+// The MLP block of a decoder layer in ONE launch:
+//   phase 0: act = silu(gate) * up,  [gate; up] = W_gu . rmsnorm(h)      (rows interleaved in 8s)
+//   phase 1: h  += W_down . act
+// i.e. launch_nvfp4_gemv_tc_fused(prologue 1, epilogue 2) followed by (prologue 0, epilogue 1), with
+// the same arithmetic, roles and partial-sum protocol as gemv_tc_kernel.  What the fusion buys: the
+// weight ring never drains between the two matrices - while the flush warps finish phase 0 and
+// meet at a grid-wide barrier (all of `act` must exist before any CTA converts a stage of it), the
+// producer already streams W_down into the ring slots the last gate/up stages free - and one
+// kernel boundary per layer disappears.  The barrier is a counter + generation pair in global
+// memory that resets itself (the generation is read after the previous kernel has finished and
+// cannot change before this CTA itself has arrived); the wait is bounded.  Like the reducer's wait
+// it needs every CTA of the grid resident: two per SM.
+// ---------------------------------------------------------------------------------------------
+struct TcMlpArgs {
+    __half* h;                 // residual stream [hidden], in and out
+    __half* act;               // [inter] scratch
+    const float* norm_w1;      // post-attention RMSNorm weights (1 + w), fp32 [hidden]
+    float eps;
+    int inter, hidden;
+    float* part;               // partial-sum slots: (ntiles0 + G) for phase 0, then those of phase 1
+    unsigned int* gbar;        // {arrival count, generation}
+    int pre;                   // weight stages requested at kernel entry
+};
+struct TcRange { int ntiles, nk, nst, tile0, ks0; unsigned total; };
+__device__ __forceinline__ TcRange tc_range(int M, int K, unsigned G, unsigned b) {
+    TcRange r;
+    r.ntiles = (M + TC_BM - 1) / TC_BM;
+    r.nk = K / TC_BK;
+    r.total = (unsigned)r.ntiles * (unsigned)r.nk;
+    const unsigned g0 = b * r.total / G, g1 = (b + 1) * r.total / G;
+    r.nst = (int)(g1 - g0);
+    r.tile0 = (int)(g0 / r.nk);
+    r.ks0 = (int)(g0 % r.nk);
+    return r;
+}
+
+template <int ST>
+__global__ void __launch_bounds__(TC_THREADS)
+gemv_tc_mlp_kernel(const __grid_constant__ CUtensorMap w_map0, const __grid_constant__ CUtensorMap s_map0,
+                   const __grid_constant__ CUtensorMap w_map1, const __grid_constant__ CUtensorMap s_map1,
+                   const TcMlpArgs a) {
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+    constexpr int NB = TC_NB, TC_TMEM_COLS = tc_tmem_cols(ST);
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem_a + ST * TC_A_BYTES;
+    uint8_t* smem_s = smem_b + NB * TC_B_BYTES;
+    uint32_t* lut = reinterpret_cast<uint32_t*>(smem_s + ST * TC_S_BYTES);
+    uint8_t* smem_l = reinterpret_cast<uint8_t*>(lut + 256);
+    float* s_part = reinterpret_cast<float*>(smem_l + NB * 16);
+    __shared__ __align__(8) uint64_t bar_full[ST];
+    __shared__ __align__(8) uint64_t bar_ready[ST];
+    __shared__ __align__(8) uint64_t bar_empty[ST];
+    __shared__ __align__(8) uint64_t bar_bfull[NB];
+    __shared__ __align__(8) uint64_t bar_bempty[NB];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t s_tmem;
+    __shared__ volatile int s_xreq;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned G = gridDim.x, b = blockIdx.x;
+    const int M0 = 2 * a.inter, K0 = a.hidden, M1 = a.hidden, K1 = a.inter;
+    const TcRange R0 = tc_range(M0, K0, G, b), R1 = tc_range(M1, K1, G, b);
+
+    int p_s = 0, p_i = 0;                                   // producer state (thread 0)
+    uint32_t p_ph = 0;
+    int p_tile = R0.tile0, p_ks = R0.ks0;
+    auto issue0 = [&]() {
+        const uint32_t bar = smem_u32(&bar_full[p_s]);
+        mbar_arrive_expect_tx(bar, TC_A_BYTES + TC_S_BYTES);
+        tma_load_2d(smem_u32(smem_a + p_s * TC_A_BYTES), &w_map0, p_ks * 128, p_tile * TC_BM, bar);
+        tma_load_2d(smem_u32(smem_s + p_s * TC_S_BYTES), &s_map0, p_ks * 16, p_tile * TC_BM, bar);
+        if (++p_s == ST) { p_s = 0; p_ph ^= 1u; }
+        if (++p_ks == R0.nk) { p_ks = 0; p_tile++; }
+    };
+    if (threadIdx.x == 0) {
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&w_map0) : "memory");
+        asm volatile("prefetch.tensormap [%0];\n" ::"l"(&s_map0) : "memory");
+        for (int s = 0; s < ST; s++) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_ready[s]), 128);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int s = 0; s < NB; s++) {
+            mbar_init(smem_u32(&bar_bfull[s]), 1);
+            mbar_init(smem_u32(&bar_bempty[s]), 1);
+        }
+        for (int c = 0; c < 2; c++) {
+            mbar_init(smem_u32(&bar_acc_full[c]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[c]), 128);
+        }
+        s_xreq = 0;
+        fence_barrier_init();
+        for (; p_i < R0.nst && p_i < ST && p_i < a.pre; p_i++) issue0();
+    }
+    if (warp == 1) {
+        tcgen05_alloc(smem_u32(&s_tmem), TC_TMEM_COLS);
+        tcgen05_relinquish();
+    }
+    if (threadIdx.x >= 64) {
+        const uint32_t v = threadIdx.x - 64;
+        uint32_t w = 0;
+#pragma unroll
+        for (int p = 0; p < 4; p++) w |= ((0x5420u >> (4 * ((v >> (6 - 2 * p)) & 3u))) & 0xFu) << (8 * p);
+        lut[v] = w;
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t tmem_sf = tmem + 32;
+
+    if (warp == 0) {
+        // ---------------- TMA producer: the rest of W_gu, then W_down, without a pause ----------------
+        if (lane == 0) {
+            for (uint32_t w = 0; w < (1u << 24) && s_xreq == 0; w++) {}
+            bool ok = true;
+            for (; p_i < R0.nst && ok; p_i++) {
+                ok = tc_wait_poll(smem_u32(&bar_empty[p_s]), p_ph ^ 1u, 0);
+                if (ok) issue0();
+            }
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&w_map1) : "memory");
+            asm volatile("prefetch.tensormap [%0];\n" ::"l"(&s_map1) : "memory");
+            p_tile = R1.tile0;
+            p_ks = R1.ks0;
+            for (int i = 0; i < R1.nst && ok; i++) {
+                // as at kernel entry: only a.pre stages of the second matrix are requested before
+                // the flush warps have passed the barrier and issued their loads of `act`; the
+                // tail of phase 0 (partial sums, barrier) needs the SM's request path short
+                if (i == a.pre)
+                    for (uint32_t w = 0; w < (1u << 24) && s_xreq < 2; w++) {}
+                ok = tc_wait_poll(smem_u32(&bar_empty[p_s]), p_ph ^ 1u, 0);
+                if (!ok) break;
+                const uint32_t bar = smem_u32(&bar_full[p_s]);
+                mbar_arrive_expect_tx(bar, TC_A_BYTES + TC_S_BYTES);
+                tma_load_2d(smem_u32(smem_a + p_s * TC_A_BYTES), &w_map1, p_ks * 128, p_tile * TC_BM, bar);
+                tma_load_2d(smem_u32(smem_s + p_s * TC_S_BYTES), &s_map1, p_ks * 16, p_tile * TC_BM, bar);
+                if (++p_s == ST) { p_s = 0; p_ph ^= 1u; }
+                if (++p_ks == R1.nk) { p_ks = 0; p_tile++; }
+            }
+        }
+    } else {
+        __half* h = a.h;
+        __half* act = a.act;
+        float* part = a.part;
+        unsigned int* gbar = a.gbar;
+        // first conversion of this warp (phase 0): norm weights before the wait, activations after
+        int cv = 0, cv_ks = 0;
+        uint4 pre_x = make_uint4(0u, 0u, 0u, 0u);
+        float4 pre_w0 = make_float4(0.f, 0.f, 0.f, 0.f), pre_w1 = pre_w0;
+        if (warp >= 6) {
+            cv = warp - 6;
+            cv_ks = R0.ks0 + cv;
+            while (cv_ks >= R0.nk) cv_ks -= R0.nk;
+            if (cv < R0.nst) {
+                pre_w0 = __ldg(reinterpret_cast<const float4*>(a.norm_w1 + cv_ks * TC_BK + lane * 8));
+                pre_w1 = __ldg(reinterpret_cast<const float4*>(a.norm_w1 + cv_ks * TC_BK + lane * 8 + 4));
+            }
+        }
+        asm volatile("griddepcontrol.wait;\n" ::: "memory");
+        PDL_FRESH(h);
+        PDL_FRESH(act);
+        PDL_FRESH(part);
+        PDL_FRESH(gbar);
+        if (warp >= 6 && cv < R0.nst) pre_x = *reinterpret_cast<const uint4*>(h + cv_ks * TC_BK + lane * 8);
+        // generation of the grid barrier: cannot change before this CTA has arrived
+        unsigned int gen0;
+        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];\n" : "=r"(gen0) : "l"(gbar + 1) : "memory");
+        float inv;
+        {
+            const int t0 = (int)threadIdx.x - 32;
+            constexpr int T = TC_THREADS - 32;
+            uint4 v[5];
+#pragma unroll
+            for (int j = 0; j < 5; j++) {
+                const int i = (t0 + j * T) * 8;
+                v[j] = (i < K0) ? *reinterpret_cast<const uint4*>(h + i) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (threadIdx.x == 192) s_xreq = 1;
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 5; j++) {
+                const __half2* hh = reinterpret_cast<const __half2*>(&v[j]);
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const float2 f = __half22float2(hh[e]);
+                    ss = fmaf(f.x, f.x, ss);
+                    ss = fmaf(f.y, f.y, ss);
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) s_part[warp - 1] = ss;
+            asm volatile("bar.sync 1, 288;\n" ::: "memory");
+            float tot = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 9; w++) tot += s_part[w];
+            inv = rsqrtf(tot / (float)K0 + a.eps);
+        }
+        if (warp == 1) {
+            // ---------------- MMA issuer: both phases, one stage sequence ----------------
+            if (lane == 0) {
+                const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(16 >> 3) << 17) | (1u << 23) |
+                                       ((uint32_t)(TC_BM >> 4) << 24);
+                const uint64_t a_desc0 = make_desc_sw128(smem_u32(smem_a), 16, 1024);
+                const uint64_t b_desc0 = make_desc_sw128(smem_u32(smem_b), 16, 1024);
+                int s = 0, seg = 0, bs = 0;
+                uint32_t ph = 0;
+                bool ok = true;
+                for (int p = 0; p < 2 && ok; p++) {
+                    const int nst = p ? R1.nst : R0.nst, nk = p ? R1.nk : R0.nk;
+                    int ks = p ? R1.ks0 : R0.ks0;
+                    bool first = true;
+                    for (int i = 0; i < nst; i++) {
+                        const int buf = seg & 1;
+                        if (first &&
+                            !tc_wait_poll(smem_u32(&bar_acc_empty[buf]), (((uint32_t)seg >> 1) & 1u) ^ 1u, 1)) {
+                            ok = false;
+                            break;
+                        }
+                        if (!tc_wait_poll(smem_u32(&bar_ready[s]), ph, 3)) { ok = false; break; }
+                        tcgen05_fence_after();
+                        const uint64_t adesc = a_desc0 + (uint64_t)(s * (TC_A_BYTES >> 4));
+                        const uint64_t bdesc = b_desc0 + (uint64_t)(bs * (TC_B_BYTES >> 4));
+                        const uint32_t sf = tmem_sf + (uint32_t)(s * TC_SF_COLS);
+                        const uint32_t d = tmem + (uint32_t)(buf * 16);
+                        tc_mma(d, adesc, bdesc, idesc, sf, sf + 16, first ? 0u : 1u);
+                        tc_mma(d, adesc + 2, bdesc + 2, idesc, sf + 4, sf + 20, 1u);
+                        tc_mma(d, adesc + 4, bdesc + 4, idesc, sf + 8, sf + 24, 1u);
+                        tc_mma(d, adesc + 6, bdesc + 6, idesc, sf + 12, sf + 28, 1u);
+                        tcgen05_commit(smem_u32(&bar_empty[s]));
+                        tcgen05_commit(smem_u32(&bar_bempty[bs]));
+                        first = false;
+                        if (++s == ST) { s = 0; ph ^= 1u; }
+                        bs = (bs + 1) & (NB - 1);
+                        if (++ks == nk || i == nst - 1) {
+                            tcgen05_commit(smem_u32(&bar_acc_full[buf]));
+                            seg++;
+                            first = true;
+                            ks = 0;
+                        }
+                    }
+                }
+            }
+        } else if (warp < 6) {
+            // ---------------- scale writers: one sequence of nst0 + nst1 stages ----------------
+            const int q = warp & 3;
+            const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+            const uint32_t sub = 0x01010101u * (uint32_t)(2 * (lane & 15));
+            bool ok = true;
+            int s = 0, bs = 0;
+            uint32_t ph = 0, bph = 0;
+            const int n_all = R0.nst + R1.nst;
+            for (int i = 0; i < n_all; i++) {
+                if (ok) ok = tc_wait(smem_u32(&bar_bfull[bs]), bph, 6);
+                const uint4 lw = *reinterpret_cast<const uint4*>(smem_l + bs * 16);
+                if (ok) ok = tc_wait(smem_u32(&bar_full[s]), ph, 4);
+                tcgen05_fence_after();
+                const uint32_t sf = tmem_sf + (uint32_t)(s * TC_SF_COLS) + lane_base;
+                const uint8_t* ss = smem_s + s * TC_S_BYTES;
+                const uint4 r0 = *reinterpret_cast<const uint4*>(ss + (0 * 32 + lane) * 16);
+                const uint4 r1 = *reinterpret_cast<const uint4*>(ss + (1 * 32 + lane) * 16);
+                const uint4 r2 = *reinterpret_cast<const uint4*>(ss + (2 * 32 + lane) * 16);
+                const uint4 r3 = *reinterpret_cast<const uint4*>(ss + (3 * 32 + lane) * 16);
+                const uint32_t cols[32] = {r0.x, r1.x, r2.x, r3.x, r0.y, r1.y, r2.y, r3.y,
+                                           r0.z, r1.z, r2.z, r3.z, r0.w, r1.w, r2.w, r3.w,
+                                           lw.x - sub, 0u, 0u, 0u, lw.y - sub, 0u, 0u, 0u,
+                                           lw.z - sub, 0u, 0u, 0u, lw.w - sub, 0u, 0u, 0u};
+                tc_st_x32(sf, cols);
+                tc_wait_st();
+                tcgen05_fence_before();
+                mbar_arrive(smem_u32(&bar_ready[s]));
+                if (++s == ST) { s = 0; ph ^= 1u; }
+                if (++bs == NB) { bs = 0; bph ^= 1u; }
+            }
+        } else {
+            // ---------------- digit conversion and flush, phase 0, barrier, phase 1 ----------------
+            const int q = warp & 3;
+            const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+            int seg = 0;
+            for (int p = 0; p < 2; p++) {
+                const TcRange& R = p ? R1 : R0;
+                const int base = p ? R0.nst : 0;             // index of the phase's first stage in the CTA's sequence
+                const int M = p ? M1 : M0;
+                const __half* x = p ? act : h;
+                float* pslots = part + (p ? (size_t)(R0.ntiles + (int)G) * TC_BM : 0);
+                TcFuse fz;
+                fz.norm_w1 = a.norm_w1;
+                fz.eps = a.eps;
+                fz.residual = h;
+                fz.pre = a.pre;
+                if (p == 1) {
+                    // ---- grid barrier: every CTA's part of `act` is stored ----
+                    asm volatile("bar.sync 2, 128;\n" ::: "memory");
+                    if (threadIdx.x == 192) {
+                        __threadfence();
+                        const unsigned int old = atomicAdd(gbar, 1u);
+                        if (old == G - 1u) {
+                            atomicExch(gbar, 0u);
+                            __threadfence();
+                            atomicAdd(gbar + 1, 1u);
+                        }
+                        bool passed = false;             // one poller per CTA
+                        for (uint32_t spin = 0; spin < (1u << 22) && !passed; spin++) {
+                            unsigned int g;
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(g) : "l"(gbar + 1) : "memory");
+                            passed = (g != gen0);
+                            if (!passed) __nanosleep(40);
+                        }
+                        if (!passed) atomicExch(&g_tc_status, 10);
+                    }
+                    asm volatile("bar.sync 2, 128;\n" ::: "memory");
+                    // this warp's first stage of phase 1: sequence index = f (mod 4), at or after base
+                    const int f = warp - 6;
+                    cv = base + ((f - base) & 3);
+                    cv_ks = R.ks0 + (cv - base);
+                    while (cv_ks >= R.nk) cv_ks -= R.nk;
+                    if (cv - base < R.nst)
+                        pre_x = __ldcg(reinterpret_cast<const uint4*>(x + cv_ks * TC_BK + lane * 8));
+                    if (threadIdx.x == 192) s_xreq = 2;
+                }
+                auto convert_upto = [&](int last) {            // `last`: index within the phase
+                    for (; cv - base <= last && cv - base < R.nst; cv += 4) {
+                        const int slot = cv & (NB - 1);
+                        uint4 xv = pre_x;
+                        if (p == 0) {
+                            const float w[8] = {pre_w0.x, pre_w0.y, pre_w0.z, pre_w0.w,
+                                                pre_w1.x, pre_w1.y, pre_w1.z, pre_w1.w};
+                            __half2* hh = reinterpret_cast<__half2*>(&xv);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const float2 fv = __half22float2(hh[e]);
+                                hh[e] = __halves2half2(__float2half(fv.x * inv * w[2 * e]),
+                                                       __float2half(fv.y * inv * w[2 * e + 1]));
+                            }
+                        }
+                        cv_ks += 4;
+                        while (cv_ks >= R.nk) cv_ks -= R.nk;
+                        if (cv + 4 - base < R.nst) {
+                            const int k = cv_ks * TC_BK + lane * 8;
+                            if (p == 0) {
+                                pre_x = *reinterpret_cast<const uint4*>(x + k);
+                                pre_w0 = __ldg(reinterpret_cast<const float4*>(a.norm_w1 + k));
+                                pre_w1 = __ldg(reinterpret_cast<const float4*>(a.norm_w1 + k + 4));
+                            } else {
+                                pre_x = __ldcg(reinterpret_cast<const uint4*>(x + k));
+                            }
+                        }
+                        tc_wait(smem_u32(&bar_bempty[slot]), (((uint32_t)cv >> 3) & 1u) ^ 1u, 7);
+                        tc_digit_planes(xv, lut, smem_b + slot * TC_B_BYTES, smem_l + slot * 16, lane);
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(smem_u32(&bar_bfull[slot]));
+                    }
+                };
+                int tile = R.tile0, left = R.nst, seg_len = R.nk - R.ks0, done = 0;
+                while (left > 0) {
+                    if (seg_len > left) seg_len = left;
+                    convert_upto(done + seg_len - 1 + (NB - 1));
+                    const int buf = seg & 1;
+                    const bool got = tc_wait(smem_u32(&bar_acc_full[buf]), ((uint32_t)seg >> 1) & 1u, 5);
+                    tcgen05_fence_after();
+                    uint32_t v[16];
+                    tc_ld_x16(tmem + lane_base + (uint32_t)(buf * 16), v);
+                    tcgen05_wait_ld();
+                    tcgen05_fence_before();
+                    mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+                    float sum = 0.0f;
+#pragma unroll
+                    for (int j = 15; j >= 0; j--) sum += __uint_as_float(v[j]);
+                    if (!got) sum = 0.0f;
+                    const int row = tile * TC_BM + q * 32 + lane;
+                    const int c_first = tc_cta_of((unsigned)tile * R.nk, R.total, G);
+                    const int c_last = tc_cta_of((unsigned)(tile + 1) * R.nk - 1u, R.total, G);
+                    float tot = sum;
+                    bool store = true;
+                    if (c_first != c_last && (int)b != c_first) {
+                        uint32_t bits = __float_as_uint(sum);
+                        if (bits == TC_EMPTY) bits = 0x7FFFFFFFu;
+                        __stcg(reinterpret_cast<unsigned int*>(&pslots[(size_t)(tile + b) * TC_BM + q * 32 + lane]), bits);
+                        store = false;
+                    } else if (c_first != c_last) {
+                        for (int c = c_first + 1; c <= c_last; c += 8) {
+                            uint32_t pv[8];
+                            bool all = false;
+                            for (uint32_t spin = 0; spin < (1u << 20) && !all; spin++) {
+                                all = true;
+#pragma unroll
+                                for (int u = 0; u < 8; u++) {
+                                    pv[u] = 0u;
+                                    if (c + u <= c_last) {
+                                        asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];\n" : "=r"(pv[u])
+                                                     : "l"(&pslots[(size_t)(tile + c + u) * TC_BM + q * 32 + lane]) : "memory");
+                                        all = all && (pv[u] != TC_EMPTY);
+                                    }
+                                }
+                            }
+                            if (!all) atomicExch(&g_tc_status, 9);
+#pragma unroll
+                            for (int u = 0; u < 8; u++)
+                                if (c + u <= c_last) {
+                                    tot += __uint_as_float(pv[u]);
+                                    __stcg(reinterpret_cast<unsigned int*>(&pslots[(size_t)(tile + c + u) * TC_BM + q * 32 + lane]),
+                                           TC_EMPTY);
+                                }
+                        }
+                    }
+                    // (both calls contain warp shuffles or none: `store` is uniform over the warp)
+                    if (store) {
+                        if (p == 0) tc_store<TEPI_SILU_MUL>(tot, row, lane, M, act, fz);
+                        else tc_store<TEPI_RESIDUAL>(tot, row, lane, M, h, fz);
+                    }
+                    left -= seg_len;
+                    done += seg_len;
+                    seg_len = R.nk;
+                    tile++;
+                    seg++;
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) tcgen05_dealloc(tmem, TC_TMEM_COLS);
+}
+
 // Per-device workspace (partial sums + counters), grown on demand outside stream capture.
 struct TcWorkspace { float* part = nullptr; unsigned int* counters = nullptr; size_t slots = 0, tiles = 0; };
 static TcWorkspace g_tc_ws[NVFP4_MAX_DEVICES];
@@ -728,6 +1158,75 @@ int launch_nvfp4_gemv_tc(const uint8_t* weight_packed, const uint8_t* weight_sca
                          const void* activation, void* output, int M, int K, void* stream) {
     return nvfp4::tc_launch(weight_packed, weight_scales, activation, output, M, K, 0, nullptr, 0.0f, 0,
                             nullptr, stream);
+}
+
+// The MLP block of a decoder layer in one launch (gemv_tc_mlp_kernel): act = silu(gate) * up over
+// W_gu . rmsnorm(h) with W_gu = [2 inter][hidden], gate / up rows interleaved in groups of 8, then
+// h += W_down . act with W_down = [hidden][inter].  hidden % 256 == 0, hidden <= 11520,
+// inter % 256 == 0; weights and vectors 16-byte aligned.  Same return values as
+// launch_nvfp4_gemv_tc; the results are those of the two fused launches it replaces.
+int launch_nvfp4_mlp_tc(const uint8_t* gu_packed, const uint8_t* gu_scales, const uint8_t* down_packed,
+                        const uint8_t* down_scales, void* h, void* act, const void* norm_w1, float eps,
+                        int inter, int hidden, void* stream) {
+    using namespace nvfp4;
+    if (inter <= 0 || hidden <= 0 || hidden % TC_BK != 0 || inter % TC_BK != 0 ||
+        hidden > 5 * 8 * (TC_THREADS - 32))
+        return NVFP4_ERR_SHAPE;
+    if (!gu_packed || !gu_scales || !down_packed || !down_scales || !h || !act || !norm_w1) return NVFP4_ERR_SHAPE;
+    if ((((uintptr_t)gu_packed | (uintptr_t)gu_scales | (uintptr_t)down_packed | (uintptr_t)down_scales |
+          (uintptr_t)h | (uintptr_t)act | (uintptr_t)norm_w1) & 15) != 0)
+        return NVFP4_ERR_SHAPE;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return -3;
+    const int dev = current_device_index();
+    static int sms[NVFP4_MAX_DEVICES] = {0};
+    static bool attr[NVFP4_MAX_DEVICES] = {false};
+    if (!sms[dev]) cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (!attr[dev]) {
+        if (cudaFuncSetAttribute(gemv_tc_mlp_kernel<5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 tc_smem_bytes(5)) != cudaSuccess)
+            return -3;
+        attr[dev] = true;
+    }
+    const int M0 = 2 * inter, K0 = hidden, M1 = hidden, K1 = inter;
+    const long long nt0 = (M0 + TC_BM - 1) / TC_BM, nt1 = (M1 + TC_BM - 1) / TC_BM;
+    const long long total0 = nt0 * (K0 / TC_BK), total1 = nt1 * (K1 / TC_BK);
+    long long G = 2ll * sms[dev];
+    if (G > total0) G = total0;
+    if (G > total1) G = total1;
+    if (total0 * (G + 1) >= (1ll << 32) || total1 * (G + 1) >= (1ll << 32)) return NVFP4_ERR_SHAPE;
+    TcWorkspace* ws = nullptr;
+    if (!tc_workspace(dev, (size_t)(nt0 + nt1 + 2 * G), 1, &ws)) return -3;
+    CUtensorMap m[4];
+    const cuuint32_t estr[2] = {1, 1};
+    const uint8_t* bases[4] = {gu_packed, gu_scales, down_packed, down_scales};
+    const int rows[4] = {M0, M0, M1, M1}, ks[4] = {K0, K0, K1, K1};
+    for (int i = 0; i < 4; i++) {
+        const bool sc = (i & 1) != 0;
+        const cuuint64_t inner = (cuuint64_t)(sc ? ks[i] / 16 : ks[i] / 2);
+        const cuuint64_t dims[2] = {inner, (cuuint64_t)rows[i]};
+        const cuuint64_t strides[1] = {inner};
+        const cuuint32_t box[2] = {(cuuint32_t)(sc ? 16 : 128), TC_BM};
+        if (enc(&m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(bases[i]), dims, strides, box,
+                estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                sc ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
+                sc ? CU_TENSOR_MAP_L2_PROMOTION_NONE : CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return -3;
+    }
+    TcMlpArgs a;
+    a.h = static_cast<__half*>(h);
+    a.act = static_cast<__half*>(act);
+    a.norm_w1 = static_cast<const float*>(norm_w1);
+    a.eps = eps;
+    a.inter = inter;
+    a.hidden = hidden;
+    a.part = ws->part;
+    a.gbar = ws->counters;
+    a.pre = g_tc_pre;
+    const cudaError_t e = launch_pdl(gemv_tc_mlp_kernel<5>, dim3((unsigned)G), dim3(TC_THREADS),
+                                     (size_t)tc_smem_bytes(5), (cudaStream_t)stream, m[0], m[1], m[2], m[3], a);
+    return (e == cudaSuccess) ? 0 : (int)e;
 }
 
 // The same with the neighbours launch_nvfp4_gemv_fused fuses: prologue 1 = RMSNorm of the

@@ -169,3 +169,75 @@ def test_argument_validation(lib):
     assert lib.launch_nvfp4_gemv_tc(one, one, one, one, 0, 1024, None) == -2
     assert lib.launch_nvfp4_gemv_tc(None, one, one, one, 16, 1024, None) == -2
     assert lib.launch_nvfp4_gemv_tc(ctypes.c_void_p(0x1008), one, one, one, 16, 1024, None) == -2
+
+
+@pytest.mark.parametrize("hidden,inter", [(256, 512), (1024, 2816), (5120, 17408)])
+def test_mlp_block_in_one_launch(lib, hidden, inter):
+    # launch_nvfp4_mlp_tc = [RMSNorm -> gate/up GEMV -> silu*mul] and [down GEMV -> residual add] in
+    # one kernel with a grid-wide barrier between the phases.  Checked against the two fused
+    # launches it replaces (same arithmetic; bit-identical when both use the same grid, i.e. at
+    # full size) and against the float64 oracle of the chain.
+    import ctypes
+
+    from nvfp4_v100_b200.engine import interleave_gate_up
+    from oracle import fused_ops_oracle as fo
+
+    rng = np.random.default_rng(hidden + inter)
+    gp, gs = oc.encode(oc.synthetic_weight(inter, hidden, seed=1, sigma=0.05))
+    upk, us = oc.encode(oc.synthetic_weight(inter, hidden, seed=2, sigma=0.05))
+    dp, ds = oc.encode(oc.synthetic_weight(hidden, inter, seed=3, sigma=0.02))
+    h0 = rng.standard_normal(hidden).astype(np.float16)
+    w1 = (1 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)
+    p = interleave_gate_up(torch.from_numpy(gp), torch.from_numpy(upk)).numpy()
+    s = interleave_gate_up(torch.from_numpy(gs), torch.from_numpy(us)).numpy()
+    d_p, d_s, d_dp, d_ds, d_w = dev(p), dev(s), dev(dp), dev(ds), dev(w1)
+    z = ctypes.c_void_p(0)
+
+    # the two launches
+    h_a = dev(h0.copy())
+    act_a = torch.zeros(inter, dtype=torch.float16, device="cuda")
+    assert lib.launch_nvfp4_gemv_tc_fused(ptr(d_p), ptr(d_s), ptr(h_a), ptr(act_a), 2 * inter, hidden, 1,
+                                          ptr(d_w), 1e-6, 2, z, stream()) == 0
+    assert lib.launch_nvfp4_gemv_tc_fused(ptr(d_dp), ptr(d_ds), ptr(act_a), ptr(h_a), hidden, inter, 0,
+                                          z, 1e-6, 1, ptr(h_a), stream()) == 0
+    # the one launch, three times in a row (the barrier and the slots must reset themselves)
+    lib.nvfp4_gemv_tc_status(1)
+    outs = []
+    for _ in range(3):
+        h_b = dev(h0.copy())
+        act_b = torch.full((inter + 8,), float("nan"), dtype=torch.float16, device="cuda")
+        rc = lib.launch_nvfp4_mlp_tc(ptr(d_p), ptr(d_s), ptr(d_dp), ptr(d_ds), ptr(h_b), ptr(act_b),
+                                     ptr(d_w), 1e-6, inter, hidden, stream())
+        torch.cuda.synchronize()
+        assert rc == 0 and lib.nvfp4_gemv_tc_status(0) == 0
+        assert bool(torch.isnan(act_b[inter:]).all())
+        outs.append((h_b.cpu().numpy(), act_b[:inter].cpu().numpy()))
+    torch.cuda.synchronize()
+    for hb, ab in outs[1:]:
+        assert np.array_equal(hb, outs[0][0]) and np.array_equal(ab, outs[0][1])
+    ha, aa = h_a.cpu().numpy(), act_a.cpu().numpy()
+    hb, ab = outs[0]
+    if hidden == 5120:
+        # same grid in both forms: the same bits (the two fused launches are checked against the
+        # oracle at this size in test_fused_silu_mul_epilogue / test_fused_rmsnorm_prologue_and_residual)
+        assert np.array_equal(ab, aa) and np.array_equal(hb, ha)
+        return
+    # smaller grids differ between the forms (fp32 partial sums are grouped differently): oracle
+    xn = fo.rmsnorm(h0[None], w1, 1e-6)[0]
+    act_ref = fo.silu_mul(oc.gemv_f64(gp, gs, xn).astype(np.float16), oc.gemv_f64(upk, us, xn).astype(np.float16))
+    err = np.abs(ab.astype(np.float64) - act_ref.astype(np.float64))
+    assert (err <= 2e-2 * np.abs(act_ref.astype(np.float64)) + 1e-4 * np.abs(act_ref).max()).all()
+    y = oc.gemv_f64(dp, ds, ab)                  # the down projection of the act the kernel produced
+    want = h0.astype(np.float64) + y.astype(np.float16).astype(np.float64)
+    assert np.abs(hb.astype(np.float64) - want).max() <= 2e-3 * max(1.0, np.abs(y).max())
+
+
+def test_mlp_block_rejects_bad_arguments(lib):
+    import ctypes
+
+    one = ctypes.c_void_p(0x1000)
+    f = lib.launch_nvfp4_mlp_tc
+    assert f(one, one, one, one, one, one, one, 1e-6, 512, 200, None) == -2      # hidden % 256
+    assert f(one, one, one, one, one, one, one, 1e-6, 500, 256, None) == -2      # inter % 256
+    assert f(one, one, one, one, one, one, None, 1e-6, 512, 256, None) == -2     # norm weights missing
+    assert f(one, one, one, one, one, one, one, 1e-6, 512, 12288, None) == -2    # hidden > 11520
