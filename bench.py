@@ -834,7 +834,8 @@ def quick_gemm(lib):
 
 def run_gemm(args):
     """Dense GEMM through launch_nvfp4_gemmtc_v5 at the 27B layer shapes:
-    tokens = 32 (batched decode, weight-bandwidth bound) and 8192 (prefill, tensor bound)."""
+    tokens = 32 (batched decode, weight-bandwidth bound, weights cold by rotation) and 8192
+    (prefill, tensor bound)."""
     import torch
 
     from nvfp4_v100_b200 import _lib
@@ -850,6 +851,8 @@ def run_gemm(args):
     hbm_peak, hbm_kind = measured_peak()
     if args.gemm_rows128:
         lib.nvfp4_b200_gemm_config(0)
+    if args.fp4_no_split:
+        lib.nvfp4_b200_gemm_fp4_config(0)
     rows = []
     token_counts = (args.tokens,) if args.tokens else (32, 8192)
     shapes = ((6144, HIDDEN), (INTER, HIDDEN), (HIDDEN, HIDDEN), (HIDDEN, INTER))
@@ -857,8 +860,14 @@ def run_gemm(args):
         shapes = (tuple(int(v) for v in args.only.lower().split("x")),)
     for tokens in token_counts:
         for M, K in shapes:
-            p = torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device="cuda")
-            s = torch.randint(118, 123, (M * K // 16,), dtype=torch.uint8, device="cuda")
+            # few tokens = the weight stream from HBM is the bound: rotate over enough copies of
+            # the weights that none is still in L2 when its turn comes again
+            copies = 1 if tokens > 64 else max(2, int(np.ceil(300e6 / (M * K * 0.5625))))
+            ps = [torch.randint(0, 256, (M * K // 2,), dtype=torch.uint8, device="cuda")
+                  for _ in range(copies)]
+            ss = [torch.randint(118, 123, (M * K // 16,), dtype=torch.uint8, device="cuda")
+                  for _ in range(copies)]
+            turn = [0]
             a = torch.randn(K, tokens, device="cuda").to(torch.float16)
             o = torch.zeros(M, tokens, dtype=torch.float16, device="cuda")
             st = vp(torch.cuda.current_stream().cuda_stream)
@@ -872,6 +881,8 @@ def run_gemm(args):
                                                    vp(a_s.data_ptr()), tokens, K, st) == 0
 
             def launch():
+                p, s = ps[turn[0] % copies], ss[turn[0] % copies]
+                turn[0] += 1
                 if args.fp4_only:
                     rc = lib.launch_nvfp4_gemm_fp4(vp(p.data_ptr()), vp(s.data_ptr()),
                                                    vp(a_p.data_ptr()), vp(a_s.data_ptr()),
@@ -889,13 +900,26 @@ def run_gemm(args):
             for _ in range(3):
                 launch()
             torch.cuda.synchronize()
-            reps = 20 if tokens == 32 else 5
+            reps = max(20, 2 * copies) if tokens <= 64 else 5
+            graph = None
+            if tokens <= 64:    # launches of ~10 us: replay a captured graph, or the host's issue rate is what gets timed
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    st = vp(torch.cuda.current_stream().cuda_stream)
+                    for _ in range(reps):
+                        launch()
+                st = vp(torch.cuda.current_stream().cuda_stream)
+                graph.replay()
+                torch.cuda.synchronize()
             best = None
             for _ in range(3):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
-                for _ in range(reps):
-                    launch()
+                if graph is not None:
+                    graph.replay()
+                else:
+                    for _ in range(reps):
+                        launch()
                 e1.record()
                 torch.cuda.synchronize()
                 us = e0.elapsed_time(e1) * 1e3 / reps
@@ -904,7 +928,7 @@ def run_gemm(args):
             nbytes = M * K * 0.5625 + 2.0 * K * tokens + 2.0 * M * tokens
             if args.fp4_only:
                 nbytes = (M + tokens) * K * 0.5625 + 2.0 * M * tokens
-            rows.append({"tokens": tokens, "M": M, "K": K, "us": best,
+            rows.append({"tokens": tokens, "M": M, "K": K, "us": best, "weight_copies": copies,
                          "tflops": flops / best / 1e6, "frac_tensor_" + tf_kind.split()[0]:
                          flops / best / 1e6 / tf_peak, "gbps": nbytes / best / 1e3,
                          "frac_hbm_" + hbm_kind: nbytes / best / 1e3 / hbm_peak})
@@ -1091,6 +1115,8 @@ def main():
                     help="with --per-shape: the FP4 tensor-core GEMV (launch_nvfp4_gemv_tc)")
     ap.add_argument("--gemm-rows128", action="store_true",
                     help="with --gemm: 128-row CTA tiles only (nvfp4_b200_gemm_config(0))")
+    ap.add_argument("--fp4-no-split", action="store_true",
+                    help="with --gemm: FP4 GEMM without the K split of few-tile shapes")
     ap.add_argument("--fp4-only", action="store_true",
                     help="with --gemm: time launch_nvfp4_gemm_fp4 alone on pre-encoded activations")
     ap.add_argument("--tokens", type=int, default=0,

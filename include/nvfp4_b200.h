@@ -407,7 +407,12 @@ void nvfp4_gemv_tc_probe(void* device_buffer);
  *   power-of-two scale exactly, so both routes compute the same products; the second runs at the
  *   fp16 tensor rate).  0; -2 bad arguments; else a launch error.
  * nvfp4_gemm_fp4_status: like nvfp4_gemm_status, for the FP4 kernel's bounded waits alone
- *   (nvfp4_gemm_status reports them as 100 + id). */
+ *   (nvfp4_gemm_status reports them as 100 + id).
+ * nvfp4_b200_gemm_fp4_config: shapes whose output tiles would leave more than half of the SMs idle
+ *   (32 tokens x 5120 rows: 40 tiles) split K over several CTAs per tile; the CTA that arrives last
+ *   adds the fp32 partial tiles in split order.  1 = on (default), 0 = off.  Split launches on one
+ *   device share a workspace and must follow one another in stream order. */
+void nvfp4_b200_gemm_fp4_config(int split_k);
 int launch_nvfp4_gemm_fp4(const uint8_t* w_packed, const uint8_t* w_scales, const uint8_t* a_packed,
                           const uint8_t* a_scales, void* out, int M, int n_tokens, int K, int ld_out,
                           void* stream);

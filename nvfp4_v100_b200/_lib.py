@@ -86,6 +86,7 @@ SIGNATURES = {
     "launch_nvfp4_encode": ([_vp, _vp, _vp, _i, _i, _vp], _i),
     "launch_nvfp4_gemm_fp4": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "nvfp4_gemm_fp4_status": ([_i], _i),
+    "nvfp4_b200_gemm_fp4_config": ([_i], None),
     "launch_nvfp4_gemv_tc": ([_vp, _vp, _vp, _vp, _i, _i, _vp], _i),
     "nvfp4_gemv_tc_status": ([_i], _i),
     "nvfp4_b200_gemv_tc_config": ([_i], None),

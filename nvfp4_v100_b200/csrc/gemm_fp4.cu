@@ -27,6 +27,8 @@
 // frees its tensor memory.
 #include <cuda.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tmap.cuh"
@@ -86,7 +88,8 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
                              const __grid_constant__ CUtensorMap a_map,
                              const __grid_constant__ CUtensorMap ws_map,
                              const __grid_constant__ CUtensorMap as_map,
-                             __half* __restrict__ out, int M, int n_tokens, int K, int ld_out) {
+                             __half* __restrict__ out, int M, int n_tokens, int K, int ld_out,
+                             float* __restrict__ part, unsigned int* __restrict__ counters, int kper) {
     constexpr int A_BYTES = F4_BM * 128;             // weight tile of a stage
     constexpr int B_BYTES = BN * 128;                // token tile of a stage
     constexpr int NB = BN / 32;                      // token rows per lane
@@ -113,7 +116,11 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * F4_BM, n0 = blockIdx.y * BN;
-    const int ksteps = K / F4_BK;
+    // K split (gridDim.z > 1; few CTA tiles, e.g. 32 tokens x 5120 rows): this CTA takes the stages
+    // [k_first, k_first + ksteps) and the tile's CTAs meet in the epilogue
+    const int k_first = (int)blockIdx.z * kper;
+    const int ksteps = min(kper, K / F4_BK - k_first);
+    __shared__ int s_last;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < ST; s++) {
@@ -144,10 +151,11 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
                 mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES + SA_BYTES + SB_BYTES);
                 // coordinates: x = byte along K (a multiple of 128 / of 16), y = row; rows past
                 // the end of either matrix are filled with zero bytes by the copy engine
-                tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, it * 128, m0, bar);
-                tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, it * 128, n0, bar);
-                tma_load_2d(smem_u32(smem_sa + s * SA_BYTES), &ws_map, it * 16, m0, bar);
-                tma_load_2d(smem_u32(smem_sb + s * SB_BYTES), &as_map, it * 16, n0, bar);
+                const int kt = k_first + it;
+                tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, kt * 128, m0, bar);
+                tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, kt * 128, n0, bar);
+                tma_load_2d(smem_u32(smem_sa + s * SA_BYTES), &ws_map, kt * 16, m0, bar);
+                tma_load_2d(smem_u32(smem_sb + s * SB_BYTES), &as_map, kt * 16, n0, bar);
             }
         }
     } else if (warp == 1) {
@@ -221,33 +229,84 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
         f4_wait(smem_u32(&bar_accum), 0, 4);
         tcgen05_fence_after();
         const int m = m0 + q * 32 + lane;
+        const int Z = (int)gridDim.z;
+        const unsigned tile = blockIdx.y * gridDim.x + blockIdx.x;
+        bool reduce = false;
+        if (Z > 1) {
+            // Every CTA of the tile stores its fp32 partial tile; the one that finds the others'
+            // already counted adds them in split order (the same sum whichever CTA comes last) and
+            // writes the fp16 result.  Nobody waits for anybody.
+            float* mine = part + (((size_t)tile * Z + blockIdx.z) * F4_BM + (q * 32 + lane)) * BN;
 #pragma unroll 1
-        for (int cb = 0; cb < BN / 32; cb++) {
-            uint32_t v[32];
-            tcgen05_ld_32x32b_x32(tmem + lane_base + (uint32_t)(cb * 32), v);
-            tcgen05_wait_ld();
-            const int nb = n0 + cb * 32;
-            if (m < M && nb < n_tokens) {
-                __half* orow = out + (size_t)m * (size_t)ld_out + nb;
-                if (nb + 32 <= n_tokens && (ld_out & 7) == 0) {
+            for (int cb = 0; cb < BN / 32; cb++) {
+                uint32_t v[32];
+                tcgen05_ld_32x32b_x32(tmem + lane_base + (uint32_t)(cb * 32), v);
+                tcgen05_wait_ld();
 #pragma unroll
-                    for (int j = 0; j < 32; j += 8) {
-                        uint4 o;
-                        __half2 t;
-                        t = __floats2half2_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-                        o.x = *reinterpret_cast<uint32_t*>(&t);
-                        t = __floats2half2_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
-                        o.y = *reinterpret_cast<uint32_t*>(&t);
-                        t = __floats2half2_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
-                        o.z = *reinterpret_cast<uint32_t*>(&t);
-                        t = __floats2half2_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
-                        o.w = *reinterpret_cast<uint32_t*>(&t);
-                        *reinterpret_cast<uint4*>(orow + j) = o;
-                    }
+                for (int j = 0; j < 32; j += 4)
+                    __stcg(reinterpret_cast<uint4*>(mine + cb * 32 + j), make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            if (threadIdx.x == 64) {
+                const unsigned seen = atomicAdd(counters + tile, 1u);
+                s_last = (seen == (unsigned)(Z - 1));
+                if (s_last) counters[tile] = 0u;                 // ready for the next launch
+            }
+            asm volatile("bar.sync 1, 128;\n" ::: "memory");
+            reduce = s_last != 0;
+            if (reduce) __threadfence();
+        }
+        if (Z == 1 || reduce) {
+#pragma unroll 1
+            for (int cb = 0; cb < BN / 32; cb++) {
+                uint32_t v[32];
+                if (Z == 1) {
+                    tcgen05_ld_32x32b_x32(tmem + lane_base + (uint32_t)(cb * 32), v);
+                    tcgen05_wait_ld();
                 } else {
+                    const float* p0 = part + (((size_t)tile * Z) * F4_BM + (q * 32 + lane)) * BN + cb * 32;
 #pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (nb + j < n_tokens) orow[j] = __float2half(__uint_as_float(v[j]));
+                    for (int j = 0; j < 32; j += 4) {
+                        const float4 a = __ldcg(reinterpret_cast<const float4*>(p0 + j));
+                        v[j] = __float_as_uint(a.x); v[j + 1] = __float_as_uint(a.y);
+                        v[j + 2] = __float_as_uint(a.z); v[j + 3] = __float_as_uint(a.w);
+                    }
+                    for (int z = 1; z < Z; z++) {
+                        const float* pz = p0 + (size_t)z * F4_BM * BN;
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) {
+                            const float4 a = __ldcg(reinterpret_cast<const float4*>(pz + j));
+                            v[j] = __float_as_uint(__uint_as_float(v[j]) + a.x);
+                            v[j + 1] = __float_as_uint(__uint_as_float(v[j + 1]) + a.y);
+                            v[j + 2] = __float_as_uint(__uint_as_float(v[j + 2]) + a.z);
+                            v[j + 3] = __float_as_uint(__uint_as_float(v[j + 3]) + a.w);
+                        }
+                    }
+                }
+                const int nb = n0 + cb * 32;
+                if (m < M && nb < n_tokens) {
+                    __half* orow = out + (size_t)m * (size_t)ld_out + nb;
+                    if (nb + 32 <= n_tokens && (ld_out & 7) == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 o;
+                            __half2 t;
+                            t = __floats2half2_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                            o.x = *reinterpret_cast<uint32_t*>(&t);
+                            t = __floats2half2_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                            o.y = *reinterpret_cast<uint32_t*>(&t);
+                            t = __floats2half2_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                            o.z = *reinterpret_cast<uint32_t*>(&t);
+                            t = __floats2half2_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                            o.w = *reinterpret_cast<uint32_t*>(&t);
+                            *reinterpret_cast<uint4*>(orow + j) = o;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (nb + j < n_tokens) orow[j] = __float2half(__uint_as_float(v[j]));
+                    }
                 }
             }
         }
@@ -256,6 +315,47 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
     tcgen05_fence_before();
     __syncthreads();
     if (warp == 0) tcgen05_dealloc(tmem, TCOLS);
+}
+
+// Workspace of the K split, one per device: fp32 partial tiles (at most F4_SPLIT_CTAS CTAs of 128 x
+// 256 values) and one arrival counter per output tile (zero between launches).  Launches that split
+// K share it: they must follow one another in stream order on a device.
+constexpr int F4_SPLIT_CTAS = 160;
+struct F4Workspace { float* part; unsigned int* counters; };
+static F4Workspace g_f4_ws[NVFP4_MAX_DEVICES] = {};
+static int g_f4_split = 1;          // 0: never split K
+static int f4_sm_count(int dev) {
+    static int sms[NVFP4_MAX_DEVICES] = {0};
+    if (!sms[dev] && (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+                      sms[dev] <= 0))
+        sms[dev] = 148;
+    return sms[dev];
+}
+
+static bool f4_workspace(int dev, cudaStream_t st, F4Workspace* out) {
+    F4Workspace& w = g_f4_ws[dev];
+    if (!w.part) {
+        // (an allocation is not allowed while the stream is being captured: such a launch runs unsplit)
+        cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) return false;
+        float* p = nullptr;
+        unsigned int* c = nullptr;
+        if (cudaMalloc(&p, (size_t)F4_SPLIT_CTAS * F4_BM * 256 * sizeof(float)) != cudaSuccess) {
+            cudaGetLastError();
+            return false;
+        }
+        if (cudaMalloc(&c, F4_SPLIT_CTAS * sizeof(unsigned int)) != cudaSuccess ||
+            cudaMemset(c, 0, F4_SPLIT_CTAS * sizeof(unsigned int)) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFree(p);
+            if (c) cudaFree(c);
+            return false;
+        }
+        w.part = p;
+        w.counters = c;
+    }
+    *out = w;
+    return true;
 }
 
 template <int BN, int ST>
@@ -271,8 +371,24 @@ static cudaError_t launch_fp4(const CUtensorMap& wm, const CUtensorMap& am, cons
         if (e != cudaSuccess) return e;
         attr[dev] = true;
     }
-    dim3 grid((unsigned)((M + F4_BM - 1) / F4_BM), (unsigned)((n + BN - 1) / BN));
-    gemm_fp4_block_scaled_kernel<BN, ST><<<grid, F4_THREADS, SMEM, st>>>(wm, am, ws, as, out, M, n, K, ld);
+    dim3 grid((unsigned)((M + F4_BM - 1) / F4_BM), (unsigned)((n + BN - 1) / BN), 1);
+    // K split: when the output tiles leave more than half of the SMs idle AND K is deep (32 tokens
+    // x 5120 rows x K 17408 is 40 tiles of 68 stages: 25.2 us unsplit, 16.3 us in three splits).
+    // Meeting in the epilogue costs about 4 us, more than a 20-stage tile saves (K = 5120: 10.0 us
+    // unsplit, 11.0 us split), hence the floor of 40 stages; splits keep >= 8 stages each.
+    const int tiles = (int)(grid.x * grid.y), total = K / F4_BK;
+    int Z = 1, kper = total;
+    F4Workspace w = {nullptr, nullptr};
+    const int sms = f4_sm_count(dev);
+    if (g_f4_split && tiles * 2 <= sms && total >= 40 && f4_workspace(dev, st, &w)) {
+        Z = std::min(std::min(sms / tiles, total / 8), F4_SPLIT_CTAS / tiles);
+        if (Z < 1) Z = 1;
+        kper = (total + Z - 1) / Z;
+        Z = (total + kper - 1) / kper;                   // no split without stages
+    }
+    grid.z = (unsigned)Z;
+    gemm_fp4_block_scaled_kernel<BN, ST><<<grid, F4_THREADS, SMEM, st>>>(wm, am, ws, as, out, M, n, K, ld,
+                                                                        w.part, w.counters, kper);
     return cudaGetLastError();
 }
 
@@ -344,8 +460,14 @@ int nvfp4_gemm_fp4_status(int reset) {
     if (reset) {
         const int z = 0;
         cudaMemcpyToSymbol(nvfp4::g_fp4_status, &z, sizeof(int));
+        // a launch that gave up may have left arrival counters of the K split behind
+        const nvfp4::F4Workspace& w = nvfp4::g_f4_ws[nvfp4::current_device_index()];
+        if (v != 0 && w.counters) cudaMemset(w.counters, 0, nvfp4::F4_SPLIT_CTAS * sizeof(unsigned int));
     }
     return v;
 }
+
+// K split of the FP4 GEMM for shapes with few output tiles: 1 = on (default), 0 = off.
+void nvfp4_b200_gemm_fp4_config(int split_k) { nvfp4::g_f4_split = split_k ? 1 : 0; }
 
 }  // extern "C"

@@ -216,6 +216,48 @@ def test_fp4_prefill_size_8192_tokens(lib):
     assert_doubled(out2.view(M, tokens), y)
 
 
+@pytest.mark.parametrize("M,n,K", [(5120, 32, 17408), (640, 64, 10240), (300, 100, 10240), (1000, 7, 12288),
+                                   (200, 136, 16384)])
+def test_fp4_batched_decode_splits_k(lib, M, n, K):
+    # batched decode (32 tokens) of a down projection: 40 output tiles of 68 K stages would leave
+    # two thirds of the SMs idle, so K (>= 40 stages of 256) is split over several CTAs per tile
+    # and the last to arrive adds the fp32 partial tiles in split order.  Oracle as above over the whole output; the split result is reproducible bit
+    # for bit (the order of the sum does not depend on which CTA comes last), and differs from
+    # the unsplit kernel's only by the fp32 association of the K sum.
+    rng = np.random.default_rng(M + n)
+    p = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
+    s = rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8)
+    ap = rng.integers(0, 256, size=(n, K // 2), dtype=np.uint8)
+    asc = rng.integers(122, 127, size=(n, K // 16), dtype=np.uint8)
+    d_p, d_s, d_ap, d_as = dev(p), dev(s), dev(ap), dev(asc)
+    ld = (n + 7) // 8 * 8
+    ref = oc.decode_f64(p, s) @ oc.decode_f64(ap, asc).T
+    tol = 2e-3 * max(1.0, (K / 4096) ** 0.5)
+
+    def run():
+        out = torch.full((M * ld + 16,), float("nan"), dtype=torch.float16, device="cuda")
+        rc = lib.launch_nvfp4_gemm_fp4(ptr(d_p), ptr(d_s), ptr(d_ap), ptr(d_as), ptr(out), M, n, K,
+                                       ld, stream())
+        torch.cuda.synchronize()
+        assert rc == 0 and lib.nvfp4_gemm_fp4_status(0) == 0
+        o = out.cpu().numpy()
+        assert np.isnan(o[M * ld:]).all(), "wrote past the output"
+        return o[:M * ld].reshape(M, ld)[:, :n]
+
+    lib.nvfp4_gemm_fp4_status(1)
+    try:
+        ys = [run() for _ in range(3)]
+        lib.nvfp4_b200_gemm_fp4_config(0)
+        y1 = run()
+    finally:
+        lib.nvfp4_b200_gemm_fp4_config(1)
+    for y in ys + [y1]:
+        assert np.isfinite(y.astype(np.float64)).all()
+        assert oc.rel_error_floored(y, ref).max() <= tol
+    assert np.array_equal(ys[0], ys[1]) and np.array_equal(ys[0], ys[2])
+    assert oc.rel_error_floored(ys[0], y1.astype(np.float64)).max() <= tol
+
+
 @pytest.mark.parametrize("M,K", [(17408, 5120), (5120, 17408)])
 def test_prefill_size_8192_tokens(lib, M, K):
     # the prefill workload (4 sequences x 2048 tokens): 32 token tiles of 256 per row tile.  The
