@@ -870,6 +870,7 @@ def run_gemm(args):
             turn = [0]
             a = torch.randn(K, tokens, device="cuda").to(torch.float16)
             o = torch.zeros(M, tokens, dtype=torch.float16, device="cuda")
+            a_tok = a.t().contiguous() if args.gemm_flags >= 0 else None
             st = vp(torch.cuda.current_stream().cuda_stream)
             if args.w4a4 or args.fp4_only:   # activations token-major, NVFP4 per block along K
                 a_tm = torch.randn(tokens, K, device="cuda").to(torch.float16)
@@ -891,6 +892,12 @@ def run_gemm(args):
                     rc = lib.launch_nvfp4_gemm_w4a4(vp(p.data_ptr()), vp(s.data_ptr()),
                                                     vp(a_tm.data_ptr()), vp(o.data_ptr()),
                                                     vp(work.data_ptr()), M, tokens, K, st)
+                elif args.gemm_flags >= 0:   # token-major sides: bit 0 input, bit 1 output, bit 2 += output
+                    f = args.gemm_flags
+                    rc = lib.launch_nvfp4_gemm_w4a16_ex(
+                        vp(p.data_ptr()), vp(s.data_ptr()), vp((a_tok if f & 1 else a).data_ptr()),
+                        K if f & 1 else tokens, vp(o.data_ptr()), M if f & 2 else tokens, M, tokens, K,
+                        f, st)
                 else:
                     rc = lib.launch_nvfp4_gemmtc_v5(vp(p.data_ptr()), vp(s.data_ptr()),
                                                     vp(a.data_ptr()), vp(o.data_ptr()), M, tokens,
@@ -1115,6 +1122,9 @@ def main():
                     help="with --per-shape: the FP4 tensor-core GEMV (launch_nvfp4_gemv_tc)")
     ap.add_argument("--gemm-rows128", action="store_true",
                     help="with --gemm: 128-row CTA tiles only (nvfp4_b200_gemm_config(0))")
+    ap.add_argument("--gemm-flags", type=int, default=-1,
+                    help="with --gemm: time launch_nvfp4_gemm_w4a16_ex with these layout flags "
+                         "(bit 0 token-major activations, bit 1 token-major output, bit 2 add into it)")
     ap.add_argument("--fp4-no-split", action="store_true",
                     help="with --gemm: FP4 GEMM without the K split of few-tile shapes")
     ap.add_argument("--fp4-only", action="store_true",

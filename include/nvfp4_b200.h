@@ -75,6 +75,20 @@ int launch_nvfp4_gemv2i(const void* weight_packed, const void* weight_scales, co
 int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
                            const void* d_activation, void* d_output, int M, int N, int K,
                            void* stream);
+/* The same product for a caller that keeps tokens as rows (the chunked prefill; the reference's
+ * caller transposes through torch around launch_nvfp4_gemmtc_v5, pipeline/_qwen38_infer.py:175-181).
+ * flags bit 0: act is token-major act[n_tokens][ld_act] (else act[K][ld_act], tokens minor);
+ * bit 1: out is token-major out[n_tokens][ld_out] (else out[M][ld_out]); bit 2 (needs bit 1):
+ * out[t][m] += result, the decoder layer's residual add (the fp16-rounded result added in fp32 and
+ * rounded once more: exactly what a separate add of the fp16 GEMM output gives).  Same arithmetic
+ * and accumulation order as launch_nvfp4_gemmtc_v5: the outputs are bit-identical to transposing
+ * around it.  Tensor-core kernel only: K % 64 == 0, ld_act % 8 == 0, 16-byte aligned act and
+ * weights, a feature-major side has ld == n_tokens rounded up to 8 (its columns past n_tokens are
+ * read as / written with zeros).  0; -2 for anything else; -3 no tensor-map encoder; or the
+ * launch's cudaError_t. */
+int launch_nvfp4_gemm_w4a16_ex(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
+                               const void* act, long long ld_act, void* out, long long ld_out, int M,
+                               int n_tokens, int K, int flags, void* stream);
 int get_kernel_shared_mem_bytes(void);                          /* kernels/nvfp4_cuda_v5.cu:460-464 */
 /* 0 if no bounded wait inside the tensor-core GEMM ever ran out; 1 + wait id otherwise.  reset != 0
  * clears it.  Synchronous.  No counterpart in the reference. */

@@ -40,6 +40,7 @@ SIGNATURES = {
     "nvfp4_gemv_status": ([_i], _i),
     "nvfp4_b200_gemv_stream_config": ([_i, _i, _i, _i, _i, _i, _i], _i),
     "launch_nvfp4_gemmtc_v5": ([_vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
+    "launch_nvfp4_gemm_w4a16_ex": ([_vp, _vp, _vp, _ll, _vp, _ll, _i, _i, _i, _i, _vp], _i),
     "get_kernel_shared_mem_bytes": ([], _i),
     "nvfp4_gemm_status": ([_i], _i),
     "launch_rmsnorm": ([_vp, _ll, _vp, _vp, _i, _i, _f, _vp], _i),

@@ -67,11 +67,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int id)
 // in two accumulators (2 x BN columns of tensor memory): the activation tile, which is most of the
 // operand traffic from L2 (32 KB of the 36.5 KB a 128-row CTA pulls per K step at BN = 256), is
 // fetched once for twice the rows.  The kernel was bound by that feed, not by the tensor pipe.
-template <int BN, int MT>
+// IN_TM: the activations are token-major [tokens][K] (the layout the prefill keeps them in): one
+// TMA box of BN tokens x 64 k per stage, a K-major B operand like the weights'.  Otherwise
+// [K][tokens] as the reference's entry point takes them (an MN-major B operand).
+// out_mode (run time): GEMM_OUT_FM out[m][token], row pitch N; GEMM_OUT_TM out[token][m], row pitch
+// ld_out, tokens below n_out only (N may be padded to 8); GEMM_OUT_TM_ADD out[token][m] += result (the fp16-rounded result added in fp32, one more
+// rounding: what a separate residual add of the fp16 output computes).
+enum { GEMM_OUT_FM = 0, GEMM_OUT_TM = 1, GEMM_OUT_TM_ADD = 2 };
+template <int BN, int MT, bool IN_TM>
 __global__ void __launch_bounds__(GEMM_THREADS)
 gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                           const uint8_t* __restrict__ packed, const uint8_t* __restrict__ scales,
-                          __half* __restrict__ out, int M, int N, int K) {
+                          __half* out, int M, int N, int K, int ld_out, int out_mode, int n_out) {
     // (two stages and two CTAs per SM for the 256-token tile measured 8 % slower than this)
     constexpr int ST = (MT == 2 && BN == 256) ? 3 : GEMM_STAGES;
     constexpr int A_TILE = GEMM_BM * 128;           // 16 KB: one 128-row tile of a stage
@@ -124,17 +131,22 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                 if (!ok) break;
                 const uint32_t bar = smem_u32(&bar_full[s]);
                 mbar_arrive_expect_tx(bar, B_BYTES);
+                if constexpr (IN_TM) {
+                    // x = element along K (64 fp16 = 128 bytes per step), y = token
+                    tma_load_2d(smem_u32(smem_b + s * B_BYTES), &act_map, it * GEMM_BK, n0, bar);
+                } else {
 #pragma unroll
-                for (int b = 0; b < BN / 64; b++)
-                    tma_load_2d(smem_u32(smem_b + s * B_BYTES + b * B_BOX), &act_map, n0 + b * 64,
-                                it * GEMM_BK, bar);
+                    for (int b = 0; b < BN / 64; b++)
+                        tma_load_2d(smem_u32(smem_b + s * B_BYTES + b * B_BOX), &act_map, n0 + b * 64,
+                                    it * GEMM_BK, bar);
+                }
             }
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             // instruction descriptor: D fp32, A fp16 K-major, B fp16 MN-major, N = BN, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) |
+            const uint32_t idesc = (1u << 4) | (IN_TM ? 0u : (1u << 16)) | ((uint32_t)(BN >> 3) << 17) |
                                    ((uint32_t)(GEMM_BM >> 4) << 24);
             // stage index, phase and operand addresses are kept by increment (no division, no
             // address arithmetic from scratch in this one-thread loop)
@@ -150,7 +162,9 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
                     // A, K-major: 16 k = 32 bytes further along the 128-byte row; 8-row groups
                     // are 1024 bytes apart.  B, MN-major: 16 k = two groups of 8 k rows (1024
                     // bytes each); 64-token atoms are one box (8 KB) apart.
-                    const uint64_t bdesc = make_desc_sw128(b_base + kk * 2048, B_BOX, 1024);
+                    // (token-major activations: a K-major tile of BN token rows, like A)
+                    const uint64_t bdesc = IN_TM ? make_desc_sw128(b_base + kk * 32, 16, 1024)
+                                                 : make_desc_sw128(b_base + kk * 2048, B_BOX, 1024);
 #pragma unroll
                     for (int mt = 0; mt < MT; mt++) {
                         const uint64_t adesc = make_desc_sw128(a_base + mt * A_TILE + kk * 32, 16, 1024);
@@ -251,6 +265,7 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
         const int q = warp & 3;                          // this warp's 32-lane quarter of TMEM
         const int chalf = (warp - 2) >> 2;               // which half of the token columns
         constexpr int CB = BN / 32;                      // 32-column blocks in the tile
+        int piece = 0;
 #pragma unroll 1
         for (int mt = 0; mt < MT; mt++) {
         const int m = m0 + mt * GEMM_BM + q * 32 + lane;
@@ -262,7 +277,52 @@ gemm_w4a16_tcgen05_kernel(const __grid_constant__ CUtensorMap act_map,
             tcgen05_ld_32x32b_x32(tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(mt * BN + cb * 32), v);
             tcgen05_wait_ld();
             const int nb = n0 + cb * 32;
-            if (m < M && nb < N) {
+            if (out_mode != GEMM_OUT_FM) {
+                // Token-major: a thread holds one row's 32 tokens, memory wants one token's rows
+                // together.  The four warps of this column half (128 rows) turn the 32 x 128 piece
+                // over in shared memory - the operand ring is free once the accumulation has
+                // retired - and then store 16 bytes (8 rows of one token) per thread.  Two staging
+                // pieces alternate, so the one barrier per piece also orders a piece's writes
+                // after the reads of the piece before last.  (Storing 2 bytes per lane straight
+                // from the registers cost 4 us per 512-token GEMM, 23 us with the residual add.)
+                __half* stg = reinterpret_cast<__half*>(smem + (chalf * 2 + (piece & 1)) * 8192);
+                const int rr = q * 32 + lane;
+#pragma unroll
+                for (int j = 0; j < 32; j++) stg[j * 128 + rr] = __float2half(__uint_as_float(v[j]));
+                asm volatile("bar.sync %0, 128;\n" ::"r"(1 + chalf) : "memory");
+                const bool vec = ((ld_out & 7) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const int pid = i * 128 + rr, tok = pid >> 4, part = pid & 15;
+                    const int tg = nb + tok, mg = m0 + mt * GEMM_BM + part * 8;
+                    if (tg >= n_out || mg >= M) continue;
+                    const uint4 val = *reinterpret_cast<const uint4*>(stg + tok * 128 + part * 8);
+                    __half* p = out + (size_t)tg * (size_t)ld_out + mg;
+                    const __half2* h2 = reinterpret_cast<const __half2*>(&val);
+                    if (vec && mg + 8 <= M) {
+                        uint4 o = val;
+                        if (out_mode == GEMM_OUT_TM_ADD) {
+                            const uint4 old = *reinterpret_cast<const uint4*>(p);
+                            const __half2* r2 = reinterpret_cast<const __half2*>(&old);
+                            __half2* o2 = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const float2 a = __half22float2(h2[e]), b = __half22float2(r2[e]);
+                                o2[e] = __floats2half2_rn(a.x + b.x, a.y + b.y);
+                            }
+                        }
+                        *reinterpret_cast<uint4*>(p) = o;
+                    } else {
+                        const __half* h1 = reinterpret_cast<const __half*>(&val);
+                        for (int e = 0; e < 8 && mg + e < M; e++) {
+                            __half r = h1[e];
+                            if (out_mode == GEMM_OUT_TM_ADD) r = __float2half(__half2float(r) + __half2float(p[e]));
+                            p[e] = r;
+                        }
+                    }
+                }
+                piece++;
+            } else if (m < M && nb < N) {
                 __half* orow = out + (size_t)m * (size_t)N + nb;
                 if (nb + 32 <= N) {
 #pragma unroll
@@ -321,22 +381,41 @@ gemm_w4a16_fallback_kernel(const uint8_t* __restrict__ packed, const uint8_t* __
     out[(size_t)m * N + n] = __float2half(acc);
 }
 
-template <int BN, int MT>
+template <int BN, int MT, bool IN_TM>
 static cudaError_t launch_tc(const CUtensorMap& map, const uint8_t* packed, const uint8_t* scales,
-                             __half* out, int M, int N, int K, cudaStream_t st) {
+                             __half* out, int M, int N, int K, int ld_out, int out_mode, int n_out,
+                             cudaStream_t st) {
     constexpr int ST = (MT == 2 && BN == 256) ? 3 : GEMM_STAGES;
     constexpr int SMEM = ST * (MT * GEMM_BM * 128 + (BN / 64) * GEMM_BK * 128) + 1024;
     static bool attr[NVFP4_MAX_DEVICES] = {false};   // the attribute is per device
     const int dev = current_device_index();
     if (!attr[dev]) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<BN, MT>,
+        const cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tcgen05_kernel<BN, MT, IN_TM>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return e;
         attr[dev] = true;
     }
     dim3 grid((unsigned)((M + GEMM_BM * MT - 1) / (GEMM_BM * MT)), (unsigned)((N + BN - 1) / BN));
-    gemm_w4a16_tcgen05_kernel<BN, MT><<<grid, GEMM_THREADS, SMEM, st>>>(map, packed, scales, out, M, N, K);
+    gemm_w4a16_tcgen05_kernel<BN, MT, IN_TM><<<grid, GEMM_THREADS, SMEM, st>>>(map, packed, scales, out, M, N,
+                                                                             K, ld_out, out_mode, n_out);
     return cudaGetLastError();
+}
+
+// Tile choice, shared by both entry points.  Wider token tiles amortise the weight dequantisation
+// over more tensor-core work; 256-row tiles when they still give every SM a CTA (17408 x 512
+// tokens: 136 CTAs, 1282 TFLOP/s against 967 with 128-row tiles; 6144 x 512: 48 CTAs, slower).
+static int gemm_tile_bn(int N) { return N > 128 ? 256 : N > 64 ? 128 : 64; }
+static bool gemm_tile_rows256(int M, int N) {
+    return N > 128 && g_gemm_rows256 && (long long)((M + 255) / 256) * ((N + 255) / 256) >= 120;
+}
+template <bool IN_TM>
+static cudaError_t launch_tc_any(const CUtensorMap& map, const uint8_t* packed, const uint8_t* scales,
+                                 __half* out, int M, int N, int K, int ld_out, int out_mode, int n_out,
+                                 cudaStream_t st) {
+    return gemm_tile_rows256(M, N) ? launch_tc<256, 2, IN_TM>(map, packed, scales, out, M, N, K, ld_out, out_mode, n_out, st)
+         : (N > 128)               ? launch_tc<256, 1, IN_TM>(map, packed, scales, out, M, N, K, ld_out, out_mode, n_out, st)
+         : (N > 64)                ? launch_tc<128, 1, IN_TM>(map, packed, scales, out, M, N, K, ld_out, out_mode, n_out, st)
+                                   : launch_tc<64, 1, IN_TM>(map, packed, scales, out, M, N, K, ld_out, out_mode, n_out, st);
 }
 
 }  // namespace nvfp4
@@ -372,16 +451,8 @@ int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weig
                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r == CUDA_SUCCESS) {
-            // wider token tiles amortise the weight dequantisation over more tensor-core work
-            const cudaError_t e =
-                // 256-row tiles when they still give every SM a CTA (17408 x 512 tokens: 136 CTAs,
-                // 1282 TFLOP/s against 967 with 128-row tiles; 6144 x 512: 48 CTAs, slower)
-                (N > 128 && g_gemm_rows256 &&
-                 (long long)((M + 255) / 256) * ((N + 255) / 256) >= 120)
-                          ? launch_tc<256, 2>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
-              : (N > 128) ? launch_tc<256, 1>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
-              : (N > 64)  ? launch_tc<128, 1>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st)
-                          : launch_tc<64, 1>(map, d_weight_packed, d_weight_scales, d_output, M, N, K, st);
+            const cudaError_t e = launch_tc_any<false>(map, d_weight_packed, d_weight_scales, d_output, M,
+                                                       N, K, N, GEMM_OUT_FM, N, st);
             return (e == cudaSuccess) ? 0 : (int)e;
         }
     }
@@ -389,6 +460,63 @@ int launch_nvfp4_gemmtc_v5(const uint8_t* d_weight_packed, const uint8_t* d_weig
     gemm_w4a16_fallback_kernel<<<grid, 256, 0, st>>>(d_weight_packed, d_weight_scales, d_activation,
                                                      d_output, M, N, K);
     const cudaError_t e = cudaGetLastError();
+    return (e == cudaSuccess) ? 0 : (int)e;
+}
+
+// The same product with the layouts a token-major caller (the chunked prefill) has and wants:
+//   flags bit 0: activations token-major act[n_tokens][ld_act] (else act[K][ld_act], tokens minor)
+//   flags bit 1: output token-major out[n_tokens][ld_out] (else out[M][ld_out])
+//   flags bit 2 (with bit 1): out[t][m] += result - the residual add of the reference's decoder
+//                layer, computed as a separate fp16 add of the rounded GEMM output would
+// Tensor-core kernel only: K % 64 == 0, ld_act % 8 == 0, 16-byte aligned pointers, feature-major
+// sides need ld == n_tokens rounded up to 8.  0; -2 for anything else (callers then transpose and use
+// launch_nvfp4_gemmtc_v5); -3 without a tensor-map encoder; or the launch's cudaError_t.
+int launch_nvfp4_gemm_w4a16_ex(const uint8_t* d_weight_packed, const uint8_t* d_weight_scales,
+                               const void* act, long long ld_act, void* out, long long ld_out, int M,
+                               int n_tokens, int K, int flags, void* stream) {
+    using namespace nvfp4;
+    if (M <= 0 || n_tokens <= 0 || K <= 0 || K % 64 != 0 || (flags & ~7) != 0) return NVFP4_ERR_SHAPE;
+    if (!d_weight_packed || !d_weight_scales || !act || !out) return NVFP4_ERR_SHAPE;
+    const bool in_tm = flags & 1, out_tm = flags & 2, add = flags & 4;
+    if (add && !out_tm) return NVFP4_ERR_SHAPE;
+    const int N8 = (n_tokens + 7) / 8 * 8;
+    if (ld_act % 8 != 0 || ld_act < (in_tm ? K : n_tokens) || ld_act > 0x7fffffffLL) return NVFP4_ERR_SHAPE;
+    if (!in_tm && ld_act != N8) return NVFP4_ERR_SHAPE;
+    if (out_tm ? (ld_out < M) : (ld_out != N8)) return NVFP4_ERR_SHAPE;
+    if (ld_out > 0x7fffffffLL) return NVFP4_ERR_SHAPE;
+    if ((((uintptr_t)d_weight_packed | (uintptr_t)act) & 15) != 0 || ((uintptr_t)d_weight_scales & 3) != 0 ||
+        ((uintptr_t)out & (out_tm ? 1 : 15)) != 0)
+        return NVFP4_ERR_SHAPE;
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (!enc) return -3;
+    // token count the kernel's bounds use: feature-major sides are padded to 8
+    const int N = (in_tm && out_tm) ? n_tokens : N8;
+    CUtensorMap map;
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r;
+    if (in_tm) {
+        const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)n_tokens};       // inner = K
+        const cuuint64_t strides[1] = {(cuuint64_t)ld_act * sizeof(__half)};
+        const cuuint32_t box[2] = {(cuuint32_t)GEMM_BK, (cuuint32_t)gemm_tile_bn(N)};
+        r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(act), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        const cuuint64_t dims[2] = {(cuuint64_t)N8, (cuuint64_t)K};
+        const cuuint64_t strides[1] = {(cuuint64_t)N8 * sizeof(__half)};
+        const cuuint32_t box[2] = {64, (cuuint32_t)GEMM_BK};
+        r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(act), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r != CUDA_SUCCESS) return -3;
+    const int mode = !out_tm ? GEMM_OUT_FM : add ? GEMM_OUT_TM_ADD : GEMM_OUT_TM;
+    __half* o = static_cast<__half*>(out);
+    cudaStream_t st = (cudaStream_t)stream;
+    const cudaError_t e = in_tm ? launch_tc_any<true>(map, d_weight_packed, d_weight_scales, o, M, N, K,
+                                                      (int)ld_out, mode, n_tokens, st)
+                                : launch_tc_any<false>(map, d_weight_packed, d_weight_scales, o, M, N, K,
+                                                       (int)ld_out, mode, n_tokens, st);
     return (e == cudaSuccess) ? 0 : (int)e;
 }
 

@@ -225,6 +225,9 @@ class DecodeEngine:
         self.final_w1 = None
         self.lm_head = None
         self.allreduce = allreduce if W > 1 else "none"
+        # chunked prefill through the token-major GEMM entry (no transposes around the GEMMs);
+        # NVFP4_PREFILL_TRANSPOSE=1 keeps the reference-shaped call with explicit layout changes
+        self.prefill_token_major = os.environ.get("NVFP4_PREFILL_TRANSPOSE", "0") != "1"
         self.mlp_one_launch = os.environ.get("NVFP4_MLP_ONE_LAUNCH", "0") == "1"
         self.ar_calls = 0
         self.epoch = torch.zeros(1, dtype=torch.int32, device=self.dev)   # decode steps so far
@@ -736,6 +739,22 @@ class DecodeEngine:
             ok(lib.launch_nvfp4_gemmtc_v5(ptr(m.packed), ptr(m.scales), ptr(act), ptr(out), m.M, Np,
                                           m.K, st), "launch_nvfp4_gemmtc_v5")
 
+        def gemm_ex(m: _Mat, act, ld_act, out, ld_out, n, flags):
+            # flags: 1 = act token-major, 2 = out token-major, 4 = out += (residual)
+            ok(lib.launch_nvfp4_gemm_w4a16_ex(ptr(m.packed), ptr(m.scales), ptr(act), ld_act, ptr(out),
+                                              ld_out, m.M, n, m.K, flags, st),
+               "launch_nvfp4_gemm_w4a16_ex")
+
+        def residual_gemm(m: _Mat, act, ld_act, in_flag, n):
+            """h[t] += W . act[t]: the residual add inside the GEMM's epilogue on one GPU; over
+            ranks the token-major partial products are summed first."""
+            if self.world == 1:
+                gemm_ex(m, act, ld_act, B["h"], H, n, in_flag | 2 | 4)
+            else:
+                gemm_ex(m, act, ld_act, B["dT"], H, n, in_flag | 2)
+                dist.all_reduce(B["dT"][:n * H])
+                B["h"][:n * H] += B["dT"][:n * H]
+
         for lo in range(0, total, B["chunk"]):
             n = min(B["chunk"], total - lo)
             Np = (n + 7) // 8 * 8
@@ -745,12 +764,17 @@ class DecodeEngine:
                "launch_embed_rows")
             for L in self.layers:
                 e = L.extra
-                rmsnorm(L.in_w1, n)
-                to_gemm(B["xn"], n, H, Np)
-                gemm(L.w_in, B["xT"], B["yT"], Np)
                 m_in = L.w_in.M
-                ok(lib.launch_transpose_f16(ptr(B["yT"]), Np, ptr(B["y"]), m_in, m_in, n, st),
-                   "transpose")
+                rmsnorm(L.in_w1, n)
+                if self.prefill_token_major:
+                    # the GEMM reads the token-major rows as its K-major B operand and writes
+                    # token-major: no layout change around it
+                    gemm_ex(L.w_in, B["xn"], H, B["y"], m_in, n, 1 | 2)
+                else:
+                    to_gemm(B["xn"], n, H, Np)
+                    gemm(L.w_in, B["xT"], B["yT"], Np)
+                    ok(lib.launch_transpose_f16(ptr(B["yT"]), Np, ptr(B["y"]), m_in, m_in, n, st),
+                       "transpose")
                 if L.attn:
                     ok(lib.launch_attn_prep_tokens(
                         ptr(B["y"]), m_in, ptr(e["q_w1"]), ptr(e["k_w1"]), ptr(self.cos),
@@ -767,20 +791,31 @@ class DecodeEngine:
                         ptr(e["dt_bias"]), ptr(e["norm_w"]), ptr(e["state"]), ptr(B["work"]),
                         B["work_bytes"], ptr(B["mix"]), n, self.nk_l, self.nv_l, float(c.rms_eps),
                         st), "launch_dn_prefill")
-                to_gemm(B["mix"], n, L.w_out.K, Np)
-                gemm(L.w_out, B["xT"], B["dT"], Np)
-                if self.world > 1:
-                    dist.all_reduce(B["dT"][:H * Np])
-                ok(lib.launch_add_transposed(ptr(B["h"]), ptr(B["dT"]), Np, n, H, st), "add")
+                if self.prefill_token_major:
+                    residual_gemm(L.w_out, B["mix"], L.w_out.K, 1, n)
+                else:
+                    to_gemm(B["mix"], n, L.w_out.K, Np)
+                    gemm(L.w_out, B["xT"], B["dT"], Np)
+                    if self.world > 1:
+                        dist.all_reduce(B["dT"][:H * Np])
+                    ok(lib.launch_add_transposed(ptr(B["h"]), ptr(B["dT"]), Np, n, H, st), "add")
                 rmsnorm(L.post_w1, n)
-                to_gemm(B["xn"], n, H, Np)
-                gemm(L.w_gu, B["xT"], B["yT"], Np)
+                if self.prefill_token_major:
+                    # gate/up leaves [2 inter][tokens] for the row-wise silu-mul; the down
+                    # projection reads that layout and adds into the token-major residual
+                    gemm_ex(L.w_gu, B["xn"], H, B["yT"], Np, n, 1)
+                else:
+                    to_gemm(B["xn"], n, H, Np)
+                    gemm(L.w_gu, B["xT"], B["yT"], Np)
                 ok(lib.launch_silu_mul_rows(ptr(B["yT"]), ptr(B["actT"]), self.inter_l, Np, st),
                    "launch_silu_mul_rows")
-                gemm(L.w_down, B["actT"], B["dT"], Np)
-                if self.world > 1:
-                    dist.all_reduce(B["dT"][:H * Np])
-                ok(lib.launch_add_transposed(ptr(B["h"]), ptr(B["dT"]), Np, n, H, st), "add")
+                if self.prefill_token_major:
+                    residual_gemm(L.w_down, B["actT"], Np, 0, n)
+                else:
+                    gemm(L.w_down, B["actT"], B["dT"], Np)
+                    if self.world > 1:
+                        dist.all_reduce(B["dT"][:H * Np])
+                    ok(lib.launch_add_transposed(ptr(B["h"]), ptr(B["dT"]), Np, n, H, st), "add")
         self.pos.fill_(start + total)
         self.len.fill_(start + total + 1)
         if lib.nvfp4_gemm_status(0) != 0:

@@ -327,3 +327,75 @@ def test_against_the_reference_gemm_kernel(lib):
         for y in outs:
             assert oc.reference_gemm_check(y, truth)[0]
         assert oc.rel_error_floored(outs[0], outs[1].astype(np.float64)).max() <= 4e-3
+
+
+@pytest.mark.parametrize("M,n,K", [
+    (256, 64, 512), (1000, 13, 1024), (640, 100, 2048), (640, 200, 6144), (5120, 512, 5120),
+    (17408, 512, 5120), (5120, 509, 8704),
+])
+def test_token_major_entry_equals_transposing_around_the_gemm(lib, M, n, K):
+    # launch_nvfp4_gemm_w4a16_ex reads token-major activations as a K-major B operand and / or
+    # writes token-major (optionally adding into the output, the decoder's residual add): the same
+    # MMAs in the same order as launch_nvfp4_gemmtc_v5, so every combination is bit-identical to
+    # transposing around that call.  The plain call itself is checked against the oracle above;
+    # here also directly for the all-token-major combination.
+    rng = np.random.default_rng(M + n + K)
+    p = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
+    s = rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8)
+    act = rng.standard_normal((n, K)).astype(np.float16)          # token-major
+    N8 = (n + 7) // 8 * 8
+    d_p, d_s = dev(p), dev(s)
+    a_tm = torch.from_numpy(act).cuda()
+    a_fm = torch.zeros((K, N8), dtype=torch.float16, device="cuda")
+    a_fm[:, :n] = a_tm.t()
+    base = torch.zeros((M, N8), dtype=torch.float16, device="cuda")
+    lib.nvfp4_gemm_status(1)
+    assert lib.launch_nvfp4_gemmtc_v5(ptr(d_p), ptr(d_s), ptr(a_fm), ptr(base), M, N8, K, stream()) == 0
+    torch.cuda.synchronize()
+    want_fm = base[:, :n].clone()
+    want_tm = want_fm.t().contiguous()
+    resid = torch.from_numpy(rng.standard_normal((n, M)).astype(np.float16)).cuda()
+    want_add = (resid.float() + want_tm.float()).half()
+    pitch = M + 24                                               # an output pitch wider than M
+    for in_tm in (0, 1):
+        a, ld_a = (a_tm, K) if in_tm else (a_fm, N8)
+        out = torch.full((M * N8 + 16,), float("nan"), dtype=torch.float16, device="cuda")
+        assert lib.launch_nvfp4_gemm_w4a16_ex(ptr(d_p), ptr(d_s), ptr(a), ld_a, ptr(out), N8, M, n, K,
+                                              in_tm, stream()) == 0
+        torch.cuda.synchronize()
+        assert bool(torch.isnan(out[M * N8:]).all()), "wrote past the output"
+        got = out[:M * N8].view(M, N8)
+        assert torch.equal(got[:, :n], want_fm)
+        assert bool((got[:, n:] == 0).all())
+        out = torch.full((n * pitch + 16,), float("nan"), dtype=torch.float16, device="cuda")
+        assert lib.launch_nvfp4_gemm_w4a16_ex(ptr(d_p), ptr(d_s), ptr(a), ld_a, ptr(out), pitch, M, n,
+                                              K, in_tm | 2, stream()) == 0
+        torch.cuda.synchronize()
+        got = out[:n * pitch].view(n, pitch)
+        assert torch.equal(got[:, :M], want_tm)
+        assert bool(torch.isnan(got[:, M:]).all()) and bool(torch.isnan(out[n * pitch:]).all())
+        acc = resid.clone()
+        assert lib.launch_nvfp4_gemm_w4a16_ex(ptr(d_p), ptr(d_s), ptr(a), ld_a, ptr(acc), M, M, n, K,
+                                              in_tm | 2 | 4, stream()) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(acc, want_add)
+    assert lib.nvfp4_gemm_status(0) == 0
+    if M * n <= 1 << 20:
+        check(want_tm.t().cpu().numpy(), p, s, act.T)
+
+
+def test_token_major_entry_argument_validation(lib):
+    z = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
+    b = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    st = stream()
+    ok = lambda *a: lib.launch_nvfp4_gemm_w4a16_ex(*a, st)
+    assert ok(ptr(b), ptr(b), ptr(z), 64, ptr(z), 128, 128, 16, 64, 3) == 0
+    assert ok(ptr(b), ptr(b), ptr(z), 64, ptr(z), 128, 128, 16, 48, 3) == -2      # K % 64
+    assert ok(ptr(b), ptr(b), ptr(z), 60, ptr(z), 128, 128, 16, 64, 3) == -2      # ld_act % 8 / < K
+    assert ok(ptr(b), ptr(b), ptr(z), 64, ptr(z), 100, 128, 16, 64, 3) == -2      # ld_out < M
+    assert ok(ptr(b), ptr(b), ptr(z), 64, ptr(z), 128, 128, 16, 64, 4) == -2      # add without token-major out
+    assert ok(ptr(b), ptr(b), ptr(z), 24, ptr(z), 16, 128, 13, 64, 0) == -2       # feature-major pitch != 16
+    assert ok(ptr(b), ptr(b), ptr(z), 16, ptr(z), 16, 128, 13, 64, 0) == 0
+    assert ok(ptr(b), ptr(b), None, 64, ptr(z), 128, 128, 16, 64, 3) == -2
+    assert ok(ptr(b), ptr(b), ptr(z), 64, ptr(z), 128, 128, 16, 64, 8) == -2
+    torch.cuda.synchronize()
