@@ -703,7 +703,7 @@ class DecodeEngine:
         tensor-core GEMM as every projection, filling the KV caches, conv windows and recurrent
         states for positions start .. start + len(tokens) - 1.  Leaves the engine ready to process
         the token at the next position (``tok`` is the caller's to set).  Tensor parallel: every
-        rank runs its shard of each projection; the K-split projections' [hidden, tokens] outputs
+        rank runs its shard of each projection; the K-split projections' token-major partial outputs
         are summed over the ranks with an NCCL all-reduce (bandwidth-sized messages, 5 MB per
         call for 512 tokens) before the residual add.  The reference's flow is
         pipeline/_qwen38_infer.py:796-809 (512-token chunks through the third-party model code)."""
