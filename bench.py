@@ -851,6 +851,10 @@ def run_gemm(args):
     hbm_peak, hbm_kind = measured_peak()
     if args.gemm_rows128:
         lib.nvfp4_b200_gemm_config(0)
+    if args.gemm_pair:
+        lib.nvfp4_b200_gemm_config(7)
+    if args.gemm_config >= 0:
+        lib.nvfp4_b200_gemm_config(args.gemm_config)
     if args.fp4_no_split:
         lib.nvfp4_b200_gemm_fp4_config(0)
     rows = []
@@ -1122,6 +1126,10 @@ def main():
                     help="with --per-shape: the FP4 tensor-core GEMV (launch_nvfp4_gemv_tc)")
     ap.add_argument("--gemm-rows128", action="store_true",
                     help="with --gemm: 128-row CTA tiles only (nvfp4_b200_gemm_config(0))")
+    ap.add_argument("--gemm-pair", action="store_true",
+                    help="with --gemm: the CTA-pair kernel (cta_group::2) for every shape of more than 128 tokens")
+    ap.add_argument("--gemm-config", type=int, default=-1,
+                    help="with --gemm: nvfp4_b200_gemm_config flags (1 = single-CTA kernels only, 3 = default)")
     ap.add_argument("--gemm-flags", type=int, default=-1,
                     help="with --gemm: time launch_nvfp4_gemm_w4a16_ex with these layout flags "
                          "(bit 0 token-major activations, bit 1 token-major output, bit 2 add into it)")

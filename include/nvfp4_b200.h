@@ -93,9 +93,13 @@ int get_kernel_shared_mem_bytes(void);                          /* kernels/nvfp4
 /* 0 if no bounded wait inside the tensor-core GEMM ever ran out; 1 + wait id otherwise.  reset != 0
  * clears it.  Synchronous.  No counterpart in the reference. */
 int nvfp4_gemm_status(int reset);
-/* Tuning hook of launch_nvfp4_gemmtc_v5: 256-row CTA tiles (two accumulators in tensor memory, the
- * activation tile fetched once for twice the rows) for more than 128 tokens: 1 (default) or 0. */
-void nvfp4_b200_gemm_config(int rows256);
+/* Tuning hook of the W4A16 GEMM entry points.  Bit 0: 256-row CTA tiles (two accumulators in tensor
+ * memory, the activation tile fetched once for twice the rows) for more than 128 tokens when they
+ * still give every SM a CTA.  Bit 1: the CTA-pair kernel (clusters of two CTAs, tcgen05
+ * cta_group::2: each CTA dequantises 128 rows and loads half of a 256-token tile) for shapes of more
+ * than 128 tokens that do not get 256-row tiles.  Bit 2: the CTA-pair kernel wherever it can run
+ * (more than 128 tokens, K % 128 == 0).  Default 3.  All kernels give bit-identical results. */
+void nvfp4_b200_gemm_config(int flags);
 
 /* Tuning hook; no counterpart in the reference.  warps per CTA (0 = auto, 2, 4 or 8), resident
  * CTAs per SM used to size the grid (0 = planner; above 64 = an exact grid size), flags: bit 0 routes every GEMV to

@@ -177,6 +177,8 @@ class DecodeEngine:
         # the tensor-core GEMV's workspace must exist before any stream capture
         if self.lib.nvfp4_gemv_tc_prepare() != 0:
             raise RuntimeError("nvfp4_gemv_tc_prepare failed (no device memory for the GEMV workspace)")
+        if "NVFP4_GEMM_CONFIG" in os.environ:      # W4A16 GEMM tile policy (see nvfp4_b200_gemm_config)
+            self.lib.nvfp4_b200_gemm_config(int(os.environ["NVFP4_GEMM_CONFIG"]))
         self.rank, self.world = tp_rank, tp_world
         c = cfg
         W = tp_world

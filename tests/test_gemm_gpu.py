@@ -399,3 +399,55 @@ def test_token_major_entry_argument_validation(lib):
     assert ok(ptr(b), ptr(b), None, 64, ptr(z), 128, 128, 16, 64, 3) == -2
     assert ok(ptr(b), ptr(b), ptr(z), 64, ptr(z), 128, 128, 16, 64, 8) == -2
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("M,n,K", [
+    (300, 136, 512), (640, 200, 2048), (5120, 512, 5120), (17408, 512, 5120), (5120, 509, 8704),
+    (1000, 1000, 1024),
+])
+def test_cta_pair_kernel_equals_the_single_cta_kernel(lib, M, n, K):
+    # the CTA-pair kernel (clusters of two, one M = 256 MMA on both SMs' tensor cores, each CTA
+    # holding half of the token tile) adds the same products in the same K order: every layout
+    # combination is bit-identical to the single-CTA kernel, which the tests above pin to the oracle
+    rng = np.random.default_rng(M * 3 + n + K)
+    p = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
+    s = rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8)
+    act = rng.standard_normal((n, K)).astype(np.float16)
+    N8 = (n + 7) // 8 * 8
+    d_p, d_s = dev(p), dev(s)
+    a_tm = torch.from_numpy(act).cuda()
+    a_fm = torch.zeros((K, N8), dtype=torch.float16, device="cuda")
+    a_fm[:, :n] = a_tm.t()
+    resid = torch.from_numpy(rng.standard_normal((n, M)).astype(np.float16)).cuda()
+
+    def run_all():
+        outs = []
+        o = torch.full((M * N8 + 16,), float("nan"), dtype=torch.float16, device="cuda")
+        assert lib.launch_nvfp4_gemmtc_v5(ptr(d_p), ptr(d_s), ptr(a_fm), ptr(o), M, N8, K, stream()) == 0
+        outs.append(o)
+        for flags in (1, 2, 3, 6, 7):
+            a, ld_a = (a_tm, K) if flags & 1 else (a_fm, N8)
+            if flags & 2:
+                o = resid.clone() if flags & 4 else torch.full((n * M + 16,), float("nan"),
+                                                               dtype=torch.float16, device="cuda")
+                ld_o = M
+            else:
+                o = torch.full((M * N8 + 16,), float("nan"), dtype=torch.float16, device="cuda")
+                ld_o = N8
+            assert lib.launch_nvfp4_gemm_w4a16_ex(ptr(d_p), ptr(d_s), ptr(a), ld_a, ptr(o), ld_o, M, n, K,
+                                                  flags, stream()) == 0
+            outs.append(o)
+        torch.cuda.synchronize()
+        assert lib.nvfp4_gemm_status(0) == 0, "a bounded wait inside the kernel ran out"
+        return outs
+
+    lib.nvfp4_gemm_status(1)
+    try:
+        lib.nvfp4_b200_gemm_config(1)          # single-CTA kernels only
+        want = run_all()
+        lib.nvfp4_b200_gemm_config(7)          # the pair kernel for every shape
+        got = run_all()
+    finally:
+        lib.nvfp4_b200_gemm_config(3)
+    for w, g in zip(want, got):
+        assert torch.equal(torch.nan_to_num(w, nan=12345.0), torch.nan_to_num(g, nan=12345.0))
