@@ -856,7 +856,9 @@ def run_gemm(args):
     if args.gemm_config >= 0:
         lib.nvfp4_b200_gemm_config(args.gemm_config)
     if args.fp4_no_split:
-        lib.nvfp4_b200_gemm_fp4_config(0)
+        lib.nvfp4_b200_gemm_fp4_config(2)
+    if args.fp4_config >= 0:
+        lib.nvfp4_b200_gemm_fp4_config(args.fp4_config)
     rows = []
     token_counts = (args.tokens,) if args.tokens else (32, 8192)
     shapes = ((6144, HIDDEN), (INTER, HIDDEN), (HIDDEN, HIDDEN), (HIDDEN, INTER))
@@ -1133,6 +1135,8 @@ def main():
     ap.add_argument("--gemm-flags", type=int, default=-1,
                     help="with --gemm: time launch_nvfp4_gemm_w4a16_ex with these layout flags "
                          "(bit 0 token-major activations, bit 1 token-major output, bit 2 add into it)")
+    ap.add_argument("--fp4-config", type=int, default=-1,
+                    help="with --gemm: nvfp4_b200_gemm_fp4_config flags (bit 0 K split, bit 1 CTA-pair kernel)")
     ap.add_argument("--fp4-no-split", action="store_true",
                     help="with --gemm: FP4 GEMM without the K split of few-tile shapes")
     ap.add_argument("--fp4-only", action="store_true",

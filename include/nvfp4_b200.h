@@ -426,11 +426,13 @@ void nvfp4_gemv_tc_probe(void* device_buffer);
  *   fp16 tensor rate).  0; -2 bad arguments; else a launch error.
  * nvfp4_gemm_fp4_status: like nvfp4_gemm_status, for the FP4 kernel's bounded waits alone
  *   (nvfp4_gemm_status reports them as 100 + id).
- * nvfp4_b200_gemm_fp4_config: shapes whose output tiles would leave more than half of the SMs idle
- *   (32 tokens x 5120 rows: 40 tiles) split K over several CTAs per tile; the CTA that arrives last
- *   adds the fp32 partial tiles in split order.  1 = on (default), 0 = off.  Split launches on one
- *   device share a workspace and must follow one another in stream order. */
-void nvfp4_b200_gemm_fp4_config(int split_k);
+ * nvfp4_b200_gemm_fp4_config: bit 0: shapes whose output tiles would leave more than half of the SMs
+ *   idle and whose K is deep (32 tokens x 5120 rows x K 17408: 40 tiles) split K over several CTAs per
+ *   tile; the CTA that arrives last adds the fp32 partial tiles in split order (split launches on one
+ *   device share a workspace and must follow one another in stream order).  Bit 1: more than 128
+ *   tokens and K >= 10240 run on the CTA-pair kernel (clusters of two, tcgen05 cta_group::2, each
+ *   CTA loading half of the token tile); bit 2: every K.  Default 3.  Bit-identical results. */
+void nvfp4_b200_gemm_fp4_config(int flags);
 int launch_nvfp4_gemm_fp4(const uint8_t* w_packed, const uint8_t* w_scales, const uint8_t* a_packed,
                           const uint8_t* a_scales, void* out, int M, int n_tokens, int K, int ld_out,
                           void* stream);

@@ -38,6 +38,7 @@ namespace nvfp4 {
 constexpr int F4_BM = 128;
 constexpr int F4_BK = 256;                 // elements of K per stage = 128 bytes per row
 constexpr int F4_THREADS = 192;
+constexpr int F4_PAIR_THREADS = 320;       // the CTA-pair kernel: two sets of scale-writing warps
 constexpr uint32_t F4_SPIN_LIMIT = 1u << 24;
 
 __device__ int g_fp4_status = 0;           // 0 ok; otherwise 1 + id of the wait that ran out
@@ -56,6 +57,23 @@ __device__ __forceinline__ void tcgen05_mma_fp4_block16(uint32_t taddr, uint64_t
         "{\n.reg .pred p;\n"
         "setp.ne.u32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::
+            "r"(taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+// Non-suspending poll: for barriers that the peer CTA of a pair, or a commit issued there, arrives on.
+__device__ __forceinline__ bool f4_wait_poll(uint32_t bar, uint32_t parity, int id) {
+    for (uint32_t i = 0; i < F4_SPIN_LIMIT; i++)
+        if (mbar_test_wait_cluster(bar, parity)) return true;
+    atomicExch(&g_fp4_status, 1 + id);
+    return false;
+}
+__device__ __forceinline__ void tcgen05_mma_fp4_block16_pair(uint32_t taddr, uint64_t adesc, uint64_t bdesc,
+                                                             uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.u32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n}\n" ::
             "r"(taddr), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
         : "memory");
 }
@@ -317,6 +335,193 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
     if (warp == 0) tcgen05_dealloc(tmem, TCOLS);
 }
 
+// ---------------------------------------------------------------------------------------------
+// CTA-pair kernel (cluster of two, tcgen05 cta_group::2) for more than 128 tokens: a pair computes
+// 256 weight rows x 256 tokens.  Each CTA loads its own 128 weight rows and HALF of the token tile
+// (plus its rows' scale bytes and the scale bytes of all 256 tokens, which every tensor core needs);
+// one thread of the pair's first CTA issues M = 256 MMAs for both SMs.  Per SM and stage that is 38
+// KB from L2 instead of 54 KB - the single-CTA kernel stops at the SM's ingest rate (about 41 bytes
+// per clock), not at the tensor pipe.
+// Barriers (same offsets in both CTAs): full[s] local (this CTA's copies landed; its scale
+// writers wait on it), sf[s] in the first CTA only (one arrival per scale-writing warp of either
+// CTA once its columns are in tensor memory - which also says that CTA's operands have landed),
+// empty[s] / accum committed to in each CTA.
+// ---------------------------------------------------------------------------------------------
+template <int ST>
+__global__ void __launch_bounds__(F4_PAIR_THREADS)
+gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap a_map,
+                     const __grid_constant__ CUtensorMap ws_map, const __grid_constant__ CUtensorMap as_map,
+                     __half* __restrict__ out, int M, int n_tokens, int K, int ld_out) {
+    constexpr int BN = 256, HALF = 128;
+    constexpr int A_BYTES = F4_BM * 128;             // this CTA's weight rows of a stage
+    constexpr int B_BYTES = HALF * 128;              // this CTA's half of the token tile
+    constexpr int SA_BYTES = F4_BM * 16, SB_BYTES = BN * 16;
+    constexpr int NB = BN / 32;                      // token rows per lane = scale columns per MMA
+    constexpr int SFA_COLS = 16, SFB_COLS = 4 * NB, SF_COLS = SFA_COLS + SFB_COLS;
+    constexpr int TCOLS = f4_tmem_cols(BN + ST * SF_COLS);
+    static_assert(BN + ST * SF_COLS <= 512, "tensor memory");
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~(uintptr_t)1023);
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + ST * A_BYTES;
+    uint8_t* smem_sa = smem_b + ST * B_BYTES;
+    uint8_t* smem_sb = smem_sa + ST * SA_BYTES;
+    __shared__ __align__(8) uint64_t bar_full[ST];
+    __shared__ __align__(8) uint64_t bar_sf[ST];
+    __shared__ __align__(8) uint64_t bar_empty[ST];
+    __shared__ __align__(8) uint64_t bar_accum;
+    __shared__ uint32_t s_tmem;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const int m0 = blockIdx.x * F4_BM, n0 = blockIdx.y * BN;
+    const int nh = n0 + (int)rank * HALF;
+    const int ksteps = K / F4_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < ST; s++) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_sf[s]), 8);       // 4 scale-writing warps of each CTA
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bar_accum), 1);
+        fence_barrier_init();
+    }
+    if (warp == 0) {
+        tcgen05_alloc_pair(smem_u32(&s_tmem), TCOLS);
+        tcgen05_relinquish_pair();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    tcgen05_fence_after();
+    const uint32_t tmem = s_tmem;
+    const uint32_t tmem_sf = tmem + BN;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int it = 0; it < ksteps; it++) {
+                if (!f4_wait_poll(smem_u32(&bar_empty[s]), ph ^ 1u, 0)) break;
+                const uint32_t bar = smem_u32(&bar_full[s]);
+                mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES + SA_BYTES + SB_BYTES);
+                tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, it * 128, m0, bar);
+                tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, it * 128, nh, bar);
+                tma_load_2d(smem_u32(smem_sa + s * SA_BYTES), &ws_map, it * 16, m0, bar);
+                tma_load_2d(smem_u32(smem_sb + s * SB_BYTES), &as_map, it * 16, n0, bar);
+                if (++s == ST) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (1u << 23) |
+                                   ((uint32_t)((2 * F4_BM) >> 4) << 24);
+            int s = 0;
+            uint32_t ph = 0;
+            for (int it = 0; it < ksteps; it++) {
+                if (!f4_wait_poll(smem_u32(&bar_sf[s]), ph, 1)) break;
+                tcgen05_fence_after();
+                const uint32_t a_base = smem_u32(smem_a + s * A_BYTES);
+                const uint32_t b_base = smem_u32(smem_b + s * B_BYTES);
+                const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS);
+#pragma unroll
+                for (int kk = 0; kk < 4; kk++) {
+                    const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
+                    const uint64_t bdesc = make_desc_sw128(b_base + kk * 32, 16, 1024);
+                    tcgen05_mma_fp4_block16_pair(tmem, adesc, bdesc, idesc, sf + (uint32_t)(kk * 4),
+                                                 sf + (uint32_t)(SFA_COLS + kk * NB), (it | kk) != 0 ? 1u : 0u);
+                }
+                const uint32_t be = smem_u32(&bar_empty[s]);
+                tcgen05_commit_pair(cluster_map_shared(be, 0));
+                tcgen05_commit_pair(cluster_map_shared(be, 1));
+                if (++s == ST) { s = 0; ph ^= 1u; }
+            }
+            const uint32_t ba = smem_u32(&bar_accum);
+            tcgen05_commit_pair(cluster_map_shared(ba, 0));
+            tcgen05_commit_pair(cluster_map_shared(ba, 1));
+        }
+    } else {
+        // ---------------- scale-factor writers (this CTA's tensor memory) ----------------
+        // Two sets of four warps (a warp reaches the 32 lanes of tensor memory given by its index
+        // modulo 4) take alternate stages: from the landing of a stage's bytes to the arrival on
+        // sf[s] a set needs longer than the tensor core needs for the stage's MMAs.
+        const int q = warp & 3;
+        const int set = (warp - 2) >> 2;
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        bool ok = true;
+        for (int it = set; it < ksteps; it += 2) {
+            const int s = it % ST;
+            const uint32_t ph = (uint32_t)(it / ST) & 1u;
+            if (ok) ok = f4_wait(smem_u32(&bar_full[s]), ph, 3);
+            tcgen05_fence_after();
+            const uint8_t* sa = smem_sa + s * SA_BYTES;
+            const uint8_t* sb = smem_sb + s * SB_BYTES;
+            uint4 wv[4], av[NB];
+#pragma unroll
+            for (int c = 0; c < 4; c++) wv[c] = *reinterpret_cast<const uint4*>(sa + (c * 32 + lane) * 16);
+#pragma unroll
+            for (int c = 0; c < NB; c++) av[c] = *reinterpret_cast<const uint4*>(sb + (c * 32 + lane) * 16);
+            uint32_t wa[4][4], wb[4][NB];
+#pragma unroll
+            for (int c = 0; c < 4; c++) { wa[0][c] = wv[c].x; wa[1][c] = wv[c].y; wa[2][c] = wv[c].z; wa[3][c] = wv[c].w; }
+#pragma unroll
+            for (int c = 0; c < NB; c++) { wb[0][c] = av[c].x; wb[1][c] = av[c].y; wb[2][c] = av[c].z; wb[3][c] = av[c].w; }
+            const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS) + lane_base;
+#pragma unroll
+            for (int kk = 0; kk < 4; kk++) {
+                tcgen05_st_32x32b<4>(sf + (uint32_t)(kk * 4), wa[kk]);
+                tcgen05_st_32x32b<NB>(sf + (uint32_t)(SFA_COLS + kk * NB), wb[kk]);
+            }
+            tcgen05_wait_st();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(cluster_map_shared(smem_u32(&bar_sf[s]), 0));
+        }
+
+        // ---------------- epilogue: this CTA's 128 rows x 256 tokens ----------------
+        f4_wait_poll(smem_u32(&bar_accum), 0, 4);
+        tcgen05_fence_after();
+        const int m = m0 + q * 32 + lane;
+#pragma unroll 1
+        for (int cb = set * (BN / 64); cb < (set + 1) * (BN / 64); cb++) {    // each set half of the tokens
+            uint32_t v[32];
+            tcgen05_ld_32x32b_x32(tmem + lane_base + (uint32_t)(cb * 32), v);
+            tcgen05_wait_ld();
+            const int nb = n0 + cb * 32;
+            if (m < M && nb < n_tokens) {
+                __half* orow = out + (size_t)m * (size_t)ld_out + nb;
+                if (nb + 32 <= n_tokens && (ld_out & 7) == 0) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 o;
+                        __half2 t;
+                        t = __floats2half2_rn(__uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+                        o.x = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+                        o.y = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+                        o.z = *reinterpret_cast<uint32_t*>(&t);
+                        t = __floats2half2_rn(__uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
+                        o.w = *reinterpret_cast<uint32_t*>(&t);
+                        *reinterpret_cast<uint4*>(orow + j) = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (nb + j < n_tokens) orow[j] = __float2half(__uint_as_float(v[j]));
+                }
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 0) tcgen05_dealloc_pair(tmem, TCOLS);
+}
+
 // Workspace of the K split, one per device: fp32 partial tiles (at most F4_SPLIT_CTAS CTAs of 128 x
 // 256 values) and one arrival counter per output tile (zero between launches).  Launches that split
 // K share it: they must follow one another in stream order on a device.
@@ -392,6 +597,35 @@ static cudaError_t launch_fp4(const CUtensorMap& wm, const CUtensorMap& am, cons
     return cudaGetLastError();
 }
 
+static int g_f4_pair = 1;           // the CTA-pair kernel: 1 = more than 128 tokens and K >= 10240, 2 = more than 128 tokens, 0 = never
+static cudaError_t launch_fp4_pair(const CUtensorMap& wm, const CUtensorMap& am, const CUtensorMap& ws,
+                                   const CUtensorMap& as, __half* out, int M, int n, int K, int ld,
+                                   cudaStream_t st) {
+    constexpr int ST = 5;
+    constexpr int SMEM = ST * (F4_BM * 128 + 128 * 128 + F4_BM * 16 + 256 * 16) + 1024;
+    static bool attr[NVFP4_MAX_DEVICES] = {false};
+    const int dev = current_device_index();
+    if (!attr[dev]) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_fp4_pair_kernel<ST>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return e;
+        attr[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * ((M + 255) / 256)), (unsigned)((n + 255) / 256), 1);
+    cfg.blockDim = dim3(F4_PAIR_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2;
+    at[0].val.clusterDim.y = 1;
+    at[0].val.clusterDim.z = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, gemm_fp4_pair_kernel<ST>, wm, am, ws, as, out, M, n, K, ld);
+}
+
 static bool byte_matrix_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, int rows, int K,
                             int box_rows) {
     const cuuint64_t dims[2] = {(cuuint64_t)(K / 2), (cuuint64_t)rows};
@@ -436,16 +670,25 @@ int launch_nvfp4_gemm_fp4(const uint8_t* w_packed, const uint8_t* w_scales, cons
     EncodeTiledFn enc = encode_tiled_fn();
     if (!enc) return -3;
     const int BN = n_tokens > 128 ? 256 : n_tokens > 64 ? 128 : n_tokens > 32 ? 64 : 32;
+    // The pair kernel takes more than 128 tokens.  Measured at 8192 tokens: a stage costs it 790
+    // cycles against 950, a tile's fixed part (prologue, cluster barriers, epilogue) 7.9 us against
+    // 5.5: it wins from about 40 stages on (5120 x 17408: 310 us against 342; 6144 x 5120, 20
+    // stages: 168 against 161).  Few deep-K tiles are better served by the K split.
+    const int tiles1 = ((M + F4_BM - 1) / F4_BM) * ((n_tokens + 255) / 256);
+    const bool few_deep = g_f4_split && tiles1 * 2 <= f4_sm_count(current_device_index()) && K / F4_BK >= 40;
+    const bool pair = n_tokens > 128 && M > F4_BM && !few_deep &&
+                      (g_f4_pair == 2 || (g_f4_pair == 1 && K / F4_BK >= 40));
     CUtensorMap wm, am, wsm, asm_;
     if (!byte_matrix_map(enc, &wm, w_packed, M, K, F4_BM) ||
-        !byte_matrix_map(enc, &am, a_packed, n_tokens, K, BN) ||
+        !byte_matrix_map(enc, &am, a_packed, n_tokens, K, pair ? 128 : BN) ||
         !scale_matrix_map(enc, &wsm, w_scales, M, K, F4_BM) ||
         !scale_matrix_map(enc, &asm_, a_scales, n_tokens, K, BN))
         return -3;
     cudaStream_t st = (cudaStream_t)stream;
     __half* o = static_cast<__half*>(out);
     const cudaError_t e =
-        BN == 256 ? launch_fp4<256, 4>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st)
+        pair      ? launch_fp4_pair(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st)
+      : BN == 256 ? launch_fp4<256, 4>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st)
       : BN == 128 ? launch_fp4<128, 6>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st)
       : BN == 64  ? launch_fp4<64, 6>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st)
                   : launch_fp4<32, 6>(wm, am, wsm, asm_, o, M, n_tokens, K, ld_out, st);
@@ -467,7 +710,11 @@ int nvfp4_gemm_fp4_status(int reset) {
     return v;
 }
 
-// K split of the FP4 GEMM for shapes with few output tiles: 1 = on (default), 0 = off.
-void nvfp4_b200_gemm_fp4_config(int split_k) { nvfp4::g_f4_split = split_k ? 1 : 0; }
+// Bit 0: K split of the FP4 GEMM for shapes with few output tiles.  Bit 1: the CTA-pair kernel for
+// more than 128 tokens and K >= 10240.  Bit 2: the CTA-pair kernel for every K.  Default 3.
+void nvfp4_b200_gemm_fp4_config(int flags) {
+    nvfp4::g_f4_split = (flags & 1) ? 1 : 0;
+    nvfp4::g_f4_pair = (flags & 4) ? 2 : (flags & 2) ? 1 : 0;
+}
 
 }  // extern "C"

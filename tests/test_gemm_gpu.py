@@ -250,7 +250,7 @@ def test_fp4_batched_decode_splits_k(lib, M, n, K):
         lib.nvfp4_b200_gemm_fp4_config(0)
         y1 = run()
     finally:
-        lib.nvfp4_b200_gemm_fp4_config(1)
+        lib.nvfp4_b200_gemm_fp4_config(3)
     for y in ys + [y1]:
         assert np.isfinite(y.astype(np.float64)).all()
         assert oc.rel_error_floored(y, ref).max() <= tol
@@ -451,3 +451,37 @@ def test_cta_pair_kernel_equals_the_single_cta_kernel(lib, M, n, K):
         lib.nvfp4_b200_gemm_config(3)
     for w, g in zip(want, got):
         assert torch.equal(torch.nan_to_num(w, nan=12345.0), torch.nan_to_num(g, nan=12345.0))
+
+
+@pytest.mark.parametrize("M,n,K", [(300, 136, 512), (1024, 512, 5120), (640, 1000, 1024), (5120, 509, 8704),
+                                   (384, 200, 12288)])
+def test_fp4_cta_pair_kernel_equals_the_single_cta_kernel(lib, M, n, K):
+    # more than 128 tokens run on clusters of two CTAs (one M = 256 block-scaled MMA on both SMs'
+    # tensor cores, each CTA holding half of the token tile): same products, same K order, so the
+    # output is bit-identical to the single-CTA kernel's, which the tests above pin to the oracle
+    rng = np.random.default_rng(M + 7 * n + K)
+    p = rng.integers(0, 256, size=(M, K // 2), dtype=np.uint8)
+    s = rng.integers(118, 123, size=(M, K // 16), dtype=np.uint8)
+    ap = rng.integers(0, 256, size=(n, K // 2), dtype=np.uint8)
+    asc = rng.integers(122, 127, size=(n, K // 16), dtype=np.uint8)
+    d_p, d_s, d_ap, d_as = dev(p), dev(s), dev(ap), dev(asc)
+    ld = (n + 7) // 8 * 8
+    outs = []
+    lib.nvfp4_gemm_fp4_status(1)
+    try:
+        for cfg in (1, 7):                       # single-CTA kernel, then the pair kernel for every K
+            lib.nvfp4_b200_gemm_fp4_config(cfg)
+            out = torch.full((M * ld + 16,), float("nan"), dtype=torch.float16, device="cuda")
+            assert lib.launch_nvfp4_gemm_fp4(ptr(d_p), ptr(d_s), ptr(d_ap), ptr(d_as), ptr(out), M, n, K,
+                                             ld, stream()) == 0
+            torch.cuda.synchronize()
+            assert lib.nvfp4_gemm_fp4_status(0) == 0, "a bounded wait inside the kernel ran out"
+            assert bool(torch.isnan(out[M * ld:]).all()), "wrote past the output"
+            outs.append(out[:M * ld].view(M, ld)[:, :n].clone())
+    finally:
+        lib.nvfp4_b200_gemm_fp4_config(3)
+    assert bool(torch.isfinite(outs[0]).all())
+    assert torch.equal(outs[0], outs[1])
+    if M * n <= 1 << 19:
+        ref = oc.decode_f64(p, s) @ oc.decode_f64(ap, asc).T
+        assert oc.rel_error_floored(outs[1].cpu().numpy(), ref).max() <= 2e-3 * max(1.0, (K / 4096) ** 0.5)
