@@ -129,11 +129,17 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
     __shared__ __align__(8) uint64_t bar_full[ST];    // TMA bytes landed
     __shared__ __align__(8) uint64_t bar_sf[ST];      // scale bytes written to tensor memory
     __shared__ __align__(8) uint64_t bar_empty[ST];   // the stage's MMAs retired
-    __shared__ __align__(8) uint64_t bar_accum;
+    __shared__ __align__(8) uint64_t bar_accum;       // a tile's accumulation retired
+    __shared__ __align__(8) uint64_t bar_acc_free;    // the epilogue has read the accumulator
     __shared__ uint32_t s_tmem;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * F4_BM, n0 = blockIdx.y * BN;
+    // A CTA walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ... (row tile fastest): barriers,
+    // tensor memory and the tensor maps are set up once, and the copies of the next tile's first
+    // stages run under this tile's epilogue.  With a K split (gridDim.z > 1) the grid has one
+    // CTA per tile and split.
+    const int tiles_m = (M + F4_BM - 1) / F4_BM;
+    const int ntiles = tiles_m * ((n_tokens + BN - 1) / BN);
     // K split (gridDim.z > 1; few CTA tiles, e.g. 32 tokens x 5120 rows): this CTA takes the stages
     // [k_first, k_first + ksteps) and the tile's CTAs meet in the epilogue
     const int k_first = (int)blockIdx.z * kper;
@@ -147,6 +153,7 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
         mbar_init(smem_u32(&bar_accum), 1);
+        mbar_init(smem_u32(&bar_acc_free), 128);
         fence_barrier_init();
     }
     if (warp == 0) {
@@ -161,19 +168,24 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int it = 0; it < ksteps; it++) {
-                const int s = it % ST;
-                const uint32_t ph = (uint32_t)(it / ST) & 1u;
-                if (!f4_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 0)) break;
-                const uint32_t bar = smem_u32(&bar_full[s]);
-                mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES + SA_BYTES + SB_BYTES);
-                // coordinates: x = byte along K (a multiple of 128 / of 16), y = row; rows past
-                // the end of either matrix are filled with zero bytes by the copy engine
-                const int kt = k_first + it;
-                tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, kt * 128, m0, bar);
-                tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, kt * 128, n0, bar);
-                tma_load_2d(smem_u32(smem_sa + s * SA_BYTES), &ws_map, kt * 16, m0, bar);
-                tma_load_2d(smem_u32(smem_sb + s * SB_BYTES), &as_map, kt * 16, n0, bar);
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x) {
+                const int m0 = (tile % tiles_m) * F4_BM, n0 = (tile / tiles_m) * BN;
+                for (int it = 0; it < ksteps; it++) {
+                    if (!f4_wait(smem_u32(&bar_empty[s]), ph ^ 1u, 0)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&bar_full[s]);
+                    mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES + SA_BYTES + SB_BYTES);
+                    // coordinates: x = byte along K (a multiple of 128 / of 16), y = row; rows past
+                    // the end of either matrix are filled with zero bytes by the copy engine
+                    const int kt = k_first + it;
+                    tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, kt * 128, m0, bar);
+                    tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, kt * 128, n0, bar);
+                    tma_load_2d(smem_u32(smem_sa + s * SA_BYTES), &ws_map, kt * 16, m0, bar);
+                    tma_load_2d(smem_u32(smem_sb + s * SB_BYTES), &as_map, kt * 16, n0, bar);
+                    if (++s == ST) { s = 0; ph ^= 1u; }
+                }
             }
         }
     } else if (warp == 1) {
@@ -183,35 +195,44 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
             // column), K = 64
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (1u << 23) |
                                    ((uint32_t)(F4_BM >> 4) << 24);
-            for (int it = 0; it < ksteps; it++) {
-                const int s = it % ST;
-                const uint32_t ph = (uint32_t)(it / ST) & 1u;
-                // (the scale writers arrive only after they saw the stage's copies land)
-                if (!f4_wait(smem_u32(&bar_sf[s]), ph, 1)) break;
+            int s = 0, ti = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ti++) {
+                // the epilogue of the tile before must have read the accumulator
+                if (ti > 0 && !f4_wait(smem_u32(&bar_acc_free), (uint32_t)(ti - 1) & 1u, 5)) break;
                 tcgen05_fence_after();
-                const uint32_t a_base = smem_u32(smem_a + s * A_BYTES);
-                const uint32_t b_base = smem_u32(smem_b + s * B_BYTES);
-                const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS);
+                for (int it = 0; it < ksteps; it++) {
+                    // (the scale writers arrive only after they saw the stage's copies land)
+                    if (!f4_wait(smem_u32(&bar_sf[s]), ph, 1)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_base = smem_u32(smem_a + s * A_BYTES);
+                    const uint32_t b_base = smem_u32(smem_b + s * B_BYTES);
+                    const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS);
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
-                    // 64 elements of K = 32 bytes further along the swizzled 128-byte row
-                    const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
-                    const uint64_t bdesc = make_desc_sw128(b_base + kk * 32, 16, 1024);
-                    tcgen05_mma_fp4_block16(tmem, adesc, bdesc, idesc, sf + (uint32_t)(kk * 4),
-                                            sf + (uint32_t)(SFA_COLS + kk * NBC), (it | kk) != 0 ? 1u : 0u);
+                    for (int kk = 0; kk < 4; kk++) {
+                        // 64 elements of K = 32 bytes further along the swizzled 128-byte row
+                        const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
+                        const uint64_t bdesc = make_desc_sw128(b_base + kk * 32, 16, 1024);
+                        tcgen05_mma_fp4_block16(tmem, adesc, bdesc, idesc, sf + (uint32_t)(kk * 4),
+                                                sf + (uint32_t)(SFA_COLS + kk * NBC), (it | kk) != 0 ? 1u : 0u);
+                    }
+                    tcgen05_commit(smem_u32(&bar_empty[s]));
+                    if (++s == ST) { s = 0; ph ^= 1u; }
                 }
-                tcgen05_commit(smem_u32(&bar_empty[s]));
+                tcgen05_commit(smem_u32(&bar_accum));
             }
-            tcgen05_commit(smem_u32(&bar_accum));
         }
     } else {
         // ---------------- scale-factor writers ----------------
         const int q = warp & 3;                            // this warp's 32-lane quarter
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         bool ok = true;
+        int s = 0, ti = 0;
+        uint32_t ph = 0;
+        for (int tile = blockIdx.x; tile < ntiles; tile += gridDim.x, ti++) {
+        const int m0 = (tile % tiles_m) * F4_BM, n0 = (tile / tiles_m) * BN;
         for (int it = 0; it < ksteps; it++) {
-            const int s = it % ST;
-            const uint32_t ph = (uint32_t)(it / ST) & 1u;
             // The scale bytes travel with the stage (two more TMA boxes: 128 x 16 B and BN x 16 B),
             // so they are requested ST stages ahead like the operands.  (Loaded by the lanes
             // from global memory one stage ahead, they queued behind the operand requests in the
@@ -241,14 +262,14 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
             tcgen05_wait_st();
             tcgen05_fence_before();
             mbar_arrive(smem_u32(&bar_sf[s]));
+            if (++s == ST) { s = 0; ph ^= 1u; }
         }
 
         // ---------------- epilogue: tensor memory -> fp16 out[m][token] ----------------
-        f4_wait(smem_u32(&bar_accum), 0, 4);
+        if (ok) ok = f4_wait(smem_u32(&bar_accum), (uint32_t)ti & 1u, 4);
         tcgen05_fence_after();
         const int m = m0 + q * 32 + lane;
         const int Z = (int)gridDim.z;
-        const unsigned tile = blockIdx.y * gridDim.x + blockIdx.x;
         bool reduce = false;
         if (Z > 1) {
             // Every CTA of the tile stores its fp32 partial tile; the one that finds the others'
@@ -264,6 +285,8 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
                 for (int j = 0; j < 32; j += 4)
                     __stcg(reinterpret_cast<uint4*>(mine + cb * 32 + j), make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]));
             }
+            tcgen05_fence_before();
+            mbar_arrive(smem_u32(&bar_acc_free));
             __threadfence();
             asm volatile("bar.sync 1, 128;\n" ::: "memory");
             if (threadIdx.x == 64) {
@@ -328,6 +351,11 @@ gemm_fp4_block_scaled_kernel(const __grid_constant__ CUtensorMap w_map,
                 }
             }
         }
+        if (Z == 1) {     // this thread's part of the accumulator is read: the next tile may overwrite it
+            tcgen05_fence_before();
+            mbar_arrive(smem_u32(&bar_acc_free));
+        }
+        }   // tiles
     }
 
     tcgen05_fence_before();
@@ -529,6 +557,7 @@ constexpr int F4_SPLIT_CTAS = 160;
 struct F4Workspace { float* part; unsigned int* counters; };
 static F4Workspace g_f4_ws[NVFP4_MAX_DEVICES] = {};
 static int g_f4_split = 1;          // 0: never split K
+static int g_f4_persistent = 1;     // 0: one CTA per output tile
 static int f4_sm_count(int dev) {
     static int sms[NVFP4_MAX_DEVICES] = {0};
     if (!sms[dev] && (cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
@@ -576,12 +605,13 @@ static cudaError_t launch_fp4(const CUtensorMap& wm, const CUtensorMap& am, cons
         if (e != cudaSuccess) return e;
         attr[dev] = true;
     }
-    dim3 grid((unsigned)((M + F4_BM - 1) / F4_BM), (unsigned)((n + BN - 1) / BN), 1);
+    const int ntiles = ((M + F4_BM - 1) / F4_BM) * ((n + BN - 1) / BN);
+    dim3 grid((unsigned)ntiles, 1, 1);
     // K split: when the output tiles leave more than half of the SMs idle AND K is deep (32 tokens
     // x 5120 rows x K 17408 is 40 tiles of 68 stages: 25.2 us unsplit, 16.3 us in three splits).
     // Meeting in the epilogue costs about 4 us, more than a 20-stage tile saves (K = 5120: 10.0 us
     // unsplit, 11.0 us split), hence the floor of 40 stages; splits keep >= 8 stages each.
-    const int tiles = (int)(grid.x * grid.y), total = K / F4_BK;
+    const int tiles = ntiles, total = K / F4_BK;
     int Z = 1, kper = total;
     F4Workspace w = {nullptr, nullptr};
     const int sms = f4_sm_count(dev);
@@ -592,6 +622,8 @@ static cudaError_t launch_fp4(const CUtensorMap& wm, const CUtensorMap& am, cons
         Z = (total + kper - 1) / kper;                   // no split without stages
     }
     grid.z = (unsigned)Z;
+    // without a K split a CTA per SM walks the tiles (see the kernel); with one, a CTA per tile and split
+    if (Z == 1 && g_f4_persistent) grid.x = (unsigned)std::min(ntiles, sms);
     gemm_fp4_block_scaled_kernel<BN, ST><<<grid, F4_THREADS, SMEM, st>>>(wm, am, ws, as, out, M, n, K, ld,
                                                                         w.part, w.counters, kper);
     return cudaGetLastError();
@@ -711,10 +743,12 @@ int nvfp4_gemm_fp4_status(int reset) {
 }
 
 // Bit 0: K split of the FP4 GEMM for shapes with few output tiles.  Bit 1: the CTA-pair kernel for
-// more than 128 tokens and K >= 10240.  Bit 2: the CTA-pair kernel for every K.  Default 3.
+// more than 128 tokens and K >= 10240.  Bit 2: the CTA-pair kernel for every K.  Bit 3: one CTA per
+// output tile instead of a CTA per SM walking the tiles.  Default 3.
 void nvfp4_b200_gemm_fp4_config(int flags) {
     nvfp4::g_f4_split = (flags & 1) ? 1 : 0;
     nvfp4::g_f4_pair = (flags & 4) ? 2 : (flags & 2) ? 1 : 0;
+    nvfp4::g_f4_persistent = (flags & 8) ? 0 : 1;
 }
 
 }  // extern "C"
