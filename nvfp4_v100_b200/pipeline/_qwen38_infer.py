@@ -244,6 +244,17 @@ class QLinear(nn.Module):
                                     _cur_stream()), "gemv2")
 
     def _many(self, x, tokens):
+        # x is [tokens, K] and the caller wants [tokens, M]: the token-major entry reads and writes
+        # exactly that (bit-identical to transposing around launch_nvfp4_gemmtc_v5, which is what
+        # the reference does: pipeline/_qwen38_infer.py:175-181).  -2 = a shape or pointer the
+        # tensor-core kernel does not take: then the reference-shaped call below.
+        y = torch.empty((tokens, self.M), dtype=torch.float16, device=x.device)
+        rc = V5.launch_nvfp4_gemm_w4a16_ex(self.d_p, self.d_s, _p(x), self.K, _p(y), self.M, self.M,
+                                           tokens, self.K, 3, _cur_stream())
+        if rc == 0:
+            return y
+        if rc != -2:
+            _ok(rc, "gemm")
         # The tensor-core kernel takes token counts that are multiples of 8 (16-byte rows for
         # its TMA loads); any other count would fall to the CUDA-core kernel, orders of magnitude
         # slower.  So the token-minor matrices are padded with zero columns and the result is cut

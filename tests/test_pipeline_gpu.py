@@ -225,10 +225,11 @@ def test_qlinear_dispatch_by_token_count(lib):
         assert oc.rel_error_floored(y[0].cpu().numpy(), ref).max() <= 2e-3, T
 
 
-def test_qlinear_pads_ragged_token_counts_onto_the_tensor_cores(lib):
-    # 13 tokens (a ragged last prefill chunk): the bridge pads the token-minor matrices to a
-    # multiple of 8 so that the call stays on the tensor-core kernel; the result equals the
-    # oracle's, and equals the same rows of a 16-token call bit for bit
+def test_qlinear_keeps_ragged_token_counts_on_the_tensor_cores(lib):
+    # 13 tokens (a ragged last prefill chunk): the bridge hands its [tokens, K] rows to the
+    # token-major GEMM entry, which takes any token count on the tensor-core kernel; the result
+    # equals the oracle's, and equals the same rows of a 16-token call bit for bit.  A K that the
+    # tensor-core kernel does not take (112) goes through the reference-shaped padded call.
     from nvfp4_v100_b200.pipeline import _qwen38_infer as Q
     from oracle import nvfp4_codec_oracle as oc
 
@@ -250,6 +251,13 @@ def test_qlinear_pads_ragged_token_counts_onto_the_tensor_cores(lib):
         if T <= 16:
             assert torch.equal(y, y16[:, :T]), T      # same kernel, same tile, same arithmetic
     assert lib.nvfp4_gemm_status(0) == 0
+    M2, K2 = 100, 112
+    p2, s2 = oc.encode(oc.synthetic_weight(M2, K2, seed=5))
+    d_p2, d_s2 = torch.from_numpy(p2).cuda(), torch.from_numpy(s2).cuda()
+    lin2 = Q.QLinear(d_p2.data_ptr(), d_s2.data_ptr(), M2, K2)
+    x = torch.randn(1, 13, K2, device="cuda").half()
+    ref = x[0].double().cpu().numpy() @ oc.decode_f64(p2, s2).T
+    assert oc.rel_error_floored(lin2(x)[0].cpu().numpy(), ref).max() <= 2e-3
 
 
 def test_pair_fusion_of_small_projections(lib):
