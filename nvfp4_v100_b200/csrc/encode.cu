@@ -19,6 +19,17 @@
 
 namespace nvfp4 {
 
+// One byte: low nibble = code of lo, high nibble = code of hi (hardware conversion, see its use).
+__device__ __forceinline__ uint32_t e2m1x2_of(float lo, float hi) {
+    uint32_t r;
+    asm("{\n.reg .b8 b;\n"
+        "cvt.rn.satfinite.e2m1x2.f32 b, %1, %2;\n"
+        "cvt.u32.u8 %0, b;\n}\n"
+        : "=r"(r)
+        : "f"(hi), "f"(lo));
+    return r;
+}
+
 __device__ __forceinline__ uint32_t e2m1_code_of(float a) {
     uint32_t c = (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) +
                  (a > 5.0f);
@@ -55,14 +66,20 @@ encode_kernel(const uint4* __restrict__ src, uint2* __restrict__ packed,
         // 2^-e; e = 127 needs the subnormal 2^-127
         const float inv = (e == 127) ? __uint_as_float(0x00400000u)
                                      : __uint_as_float((uint32_t)(127 - e) << 23);
+        // The code of |x| 2^-e is the hardware conversion's (cvt.rn.satfinite.e2m1x2: round to
+        // nearest, ties to the even code, NaN to +6) once ties are out of the way: the rule here is
+        // "a value on a midpoint takes the smaller code", the hardware's would take the larger one
+        // at 0.75, 1.75 and 3.5.  Scaling by 2^-e (1 - 2^-20) instead of 2^-e moves a midpoint just
+        // below itself and no other input across one (|x| 2^-e has 11 significant bits: it is on a
+        // midpoint or at least 2^-11 of its size away).  The fused add of +0 turns a -0 product
+        // into +0: the sign bit is for values below zero only.
+        const float invn = inv * 0.99999904632568359375f;
         uint32_t out[2] = {0u, 0u};
 #pragma unroll
         for (int i = 0; i < 8; i++) {
             const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
-            const float lo = f.x * inv, hi = f.y * inv;
-            const uint32_t nlo = e2m1_code_of(fabsf(lo)) | (lo < 0.0f ? 8u : 0u);
-            const uint32_t nhi = e2m1_code_of(fabsf(hi)) | (hi < 0.0f ? 8u : 0u);
-            out[i >> 2] |= (nlo | (nhi << 4)) << (8 * (i & 3));
+            const float lo = fmaf(f.x, invn, 0.0f), hi = fmaf(f.y, invn, 0.0f);
+            out[i >> 2] |= e2m1x2_of(lo, hi) << (8 * (i & 3));
         }
         packed[b] = make_uint2(out[0], out[1]);
         scales[b] = (uint8_t)(e + 127);
