@@ -431,8 +431,9 @@ void nvfp4_gemv_tc_probe(void* device_buffer);
  *   tile; the CTA that arrives last adds the fp32 partial tiles in split order (split launches on one
  *   device share a workspace and must follow one another in stream order).  Bit 1: more than 128
  *   tokens and K >= 10240 run on the CTA-pair kernel (clusters of two, tcgen05 cta_group::2, each
- *   CTA loading half of the token tile); bit 2: every K.  Bit 3: the single-CTA kernel launches one CTA
- *   per output tile instead of one per SM that walks the tiles.  Default 3.  Bit-identical results. */
+ *   CTA loading half of the token tile); bit 2: every K.  Bit 3: one CTA (pair) per output
+ *   tile instead of one per SM (two SMs) that walks the tiles; bits 8..15: pairs of the walking pair
+ *   kernel (0 = half the SM count).  Default 3.  Bit-identical results. */
 void nvfp4_b200_gemm_fp4_config(int flags);
 int launch_nvfp4_gemm_fp4(const uint8_t* w_packed, const uint8_t* w_scales, const uint8_t* a_packed,
                           const uint8_t* a_scales, void* out, int M, int n_tokens, int K, int ld_out,

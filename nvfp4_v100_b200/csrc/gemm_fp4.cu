@@ -399,12 +399,15 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_con
     __shared__ __align__(8) uint64_t bar_sf[ST];
     __shared__ __align__(8) uint64_t bar_empty[ST];
     __shared__ __align__(8) uint64_t bar_accum;
+    __shared__ __align__(8) uint64_t bar_acc_free;    // first CTA's: both epilogues have read the accumulators
     __shared__ uint32_t s_tmem;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_cta_rank();
-    const int m0 = blockIdx.x * F4_BM, n0 = blockIdx.y * BN;
-    const int nh = n0 + (int)rank * HALF;
+    // a pair walks the pair tiles pair, pair + pairs, ... (256 rows x 256 tokens each, row pair fastest)
+    const int pairs = (int)(gridDim.x >> 1), pair0 = (int)(blockIdx.x >> 1);
+    const int tiles_m = (M + 2 * F4_BM - 1) / (2 * F4_BM);
+    const int ntiles = tiles_m * ((n_tokens + BN - 1) / BN);
     const int ksteps = K / F4_BK;
 
     if (threadIdx.x == 0) {
@@ -414,6 +417,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_con
             mbar_init(smem_u32(&bar_empty[s]), 1);
         }
         mbar_init(smem_u32(&bar_accum), 1);
+        mbar_init(smem_u32(&bar_acc_free), 16);   // 8 epilogue warps of each CTA
         fence_barrier_init();
     }
     if (warp == 0) {
@@ -431,44 +435,55 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_con
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            for (int it = 0; it < ksteps; it++) {
-                if (!f4_wait_poll(smem_u32(&bar_empty[s]), ph ^ 1u, 0)) break;
-                const uint32_t bar = smem_u32(&bar_full[s]);
-                mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES + SA_BYTES + SB_BYTES);
-                tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, it * 128, m0, bar);
-                tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, it * 128, nh, bar);
-                tma_load_2d(smem_u32(smem_sa + s * SA_BYTES), &ws_map, it * 16, m0, bar);
-                tma_load_2d(smem_u32(smem_sb + s * SB_BYTES), &as_map, it * 16, n0, bar);
-                if (++s == ST) { s = 0; ph ^= 1u; }
+            bool ok = true;
+            for (int tile = pair0; tile < ntiles && ok; tile += pairs) {
+                const int m0 = ((tile % tiles_m) * 2 + (int)rank) * F4_BM, n0 = (tile / tiles_m) * BN;
+                const int nh = n0 + (int)rank * HALF;
+                for (int it = 0; it < ksteps; it++) {
+                    if (!f4_wait_poll(smem_u32(&bar_empty[s]), ph ^ 1u, 0)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&bar_full[s]);
+                    mbar_arrive_expect_tx(bar, A_BYTES + B_BYTES + SA_BYTES + SB_BYTES);
+                    tma_load_2d(smem_u32(smem_a + s * A_BYTES), &w_map, it * 128, m0, bar);
+                    tma_load_2d(smem_u32(smem_b + s * B_BYTES), &a_map, it * 128, nh, bar);
+                    tma_load_2d(smem_u32(smem_sa + s * SA_BYTES), &ws_map, it * 16, m0, bar);
+                    tma_load_2d(smem_u32(smem_sb + s * SB_BYTES), &as_map, it * 16, n0, bar);
+                    if (++s == ST) { s = 0; ph ^= 1u; }
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             const uint32_t idesc = (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | (1u << 23) |
                                    ((uint32_t)((2 * F4_BM) >> 4) << 24);
-            int s = 0;
+            int s = 0, ti = 0;
             uint32_t ph = 0;
-            for (int it = 0; it < ksteps; it++) {
-                if (!f4_wait_poll(smem_u32(&bar_sf[s]), ph, 1)) break;
+            bool ok = true;
+            for (int tile = pair0; tile < ntiles && ok; tile += pairs, ti++) {
+                // both CTAs' epilogues of the tile before must have read their accumulators
+                if (ti > 0 && !f4_wait_poll(smem_u32(&bar_acc_free), (uint32_t)(ti - 1) & 1u, 5)) break;
                 tcgen05_fence_after();
-                const uint32_t a_base = smem_u32(smem_a + s * A_BYTES);
-                const uint32_t b_base = smem_u32(smem_b + s * B_BYTES);
-                const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS);
+                for (int it = 0; it < ksteps; it++) {
+                    if (!f4_wait_poll(smem_u32(&bar_sf[s]), ph, 1)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_base = smem_u32(smem_a + s * A_BYTES);
+                    const uint32_t b_base = smem_u32(smem_b + s * B_BYTES);
+                    const uint32_t sf = tmem_sf + (uint32_t)(s * SF_COLS);
 #pragma unroll
-                for (int kk = 0; kk < 4; kk++) {
-                    const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
-                    const uint64_t bdesc = make_desc_sw128(b_base + kk * 32, 16, 1024);
-                    tcgen05_mma_fp4_block16_pair(tmem, adesc, bdesc, idesc, sf + (uint32_t)(kk * 4),
-                                                 sf + (uint32_t)(SFA_COLS + kk * NB), (it | kk) != 0 ? 1u : 0u);
+                    for (int kk = 0; kk < 4; kk++) {
+                        const uint64_t adesc = make_desc_sw128(a_base + kk * 32, 16, 1024);
+                        const uint64_t bdesc = make_desc_sw128(b_base + kk * 32, 16, 1024);
+                        tcgen05_mma_fp4_block16_pair(tmem, adesc, bdesc, idesc, sf + (uint32_t)(kk * 4),
+                                                     sf + (uint32_t)(SFA_COLS + kk * NB), (it | kk) != 0 ? 1u : 0u);
+                    }
+                    const uint32_t be = smem_u32(&bar_empty[s]);
+                    tcgen05_commit_pair(cluster_map_shared(be, 0));
+                    tcgen05_commit_pair(cluster_map_shared(be, 1));
+                    if (++s == ST) { s = 0; ph ^= 1u; }
                 }
-                const uint32_t be = smem_u32(&bar_empty[s]);
-                tcgen05_commit_pair(cluster_map_shared(be, 0));
-                tcgen05_commit_pair(cluster_map_shared(be, 1));
-                if (++s == ST) { s = 0; ph ^= 1u; }
+                const uint32_t ba = smem_u32(&bar_accum);
+                tcgen05_commit_pair(cluster_map_shared(ba, 0));
+                tcgen05_commit_pair(cluster_map_shared(ba, 1));
             }
-            const uint32_t ba = smem_u32(&bar_accum);
-            tcgen05_commit_pair(cluster_map_shared(ba, 0));
-            tcgen05_commit_pair(cluster_map_shared(ba, 1));
         }
     } else {
         // ---------------- scale-factor writers (this CTA's tensor memory) ----------------
@@ -479,9 +494,13 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_con
         const int set = (warp - 2) >> 2;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         bool ok = true;
+        int ti = 0;
+        for (int tile = pair0; tile < ntiles; tile += pairs, ti++) {
+        const int m0 = ((tile % tiles_m) * 2 + (int)rank) * F4_BM, n0 = (tile / tiles_m) * BN;
         for (int it = set; it < ksteps; it += 2) {
-            const int s = it % ST;
-            const uint32_t ph = (uint32_t)(it / ST) & 1u;
+            const int g = ti * ksteps + it;              // stages since the kernel began
+            const int s = g % ST;
+            const uint32_t ph = (uint32_t)(g / ST) & 1u;
             if (ok) ok = f4_wait(smem_u32(&bar_full[s]), ph, 3);
             tcgen05_fence_after();
             const uint8_t* sa = smem_sa + s * SA_BYTES;
@@ -509,7 +528,7 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_con
         }
 
         // ---------------- epilogue: this CTA's 128 rows x 256 tokens ----------------
-        f4_wait_poll(smem_u32(&bar_accum), 0, 4);
+        if (ok) ok = f4_wait_poll(smem_u32(&bar_accum), (uint32_t)ti & 1u, 4);
         tcgen05_fence_after();
         const int m = m0 + q * 32 + lane;
 #pragma unroll 1
@@ -542,6 +561,11 @@ gemm_fp4_pair_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_con
                 }
             }
         }
+        // this warp's part of the accumulator is read: tell the thread that issues the next tile's MMAs
+        tcgen05_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(cluster_map_shared(smem_u32(&bar_acc_free), 0));
+        }   // tiles
     }
 
     tcgen05_fence_before();
@@ -629,6 +653,7 @@ static cudaError_t launch_fp4(const CUtensorMap& wm, const CUtensorMap& am, cons
     return cudaGetLastError();
 }
 
+static int g_f4_pairs_override = 0;  // pairs of the tile-walking pair kernel (0: one per two SMs)
 static int g_f4_pair = 1;           // the CTA-pair kernel: 1 = more than 128 tokens and K >= 10240, 2 = more than 128 tokens, 0 = never
 static cudaError_t launch_fp4_pair(const CUtensorMap& wm, const CUtensorMap& am, const CUtensorMap& ws,
                                    const CUtensorMap& as, __half* out, int M, int n, int K, int ld,
@@ -644,7 +669,12 @@ static cudaError_t launch_fp4_pair(const CUtensorMap& wm, const CUtensorMap& am,
         attr[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(2 * ((M + 255) / 256)), (unsigned)((n + 255) / 256), 1);
+    // a pair of CTAs per pair of SMs walks the 256 x 256 tiles (one pair per tile with bit 3 of the config)
+    const int ptiles = ((M + 255) / 256) * ((n + 255) / 256);
+    const int pairs = g_f4_persistent ? std::min(ptiles, g_f4_pairs_override > 0 ? g_f4_pairs_override
+                                                                               : f4_sm_count(dev) / 2)
+                                      : ptiles;
+    cfg.gridDim = dim3((unsigned)(2 * pairs), 1, 1);
     cfg.blockDim = dim3(F4_PAIR_THREADS, 1, 1);
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = st;
@@ -743,12 +773,14 @@ int nvfp4_gemm_fp4_status(int reset) {
 }
 
 // Bit 0: K split of the FP4 GEMM for shapes with few output tiles.  Bit 1: the CTA-pair kernel for
-// more than 128 tokens and K >= 10240.  Bit 2: the CTA-pair kernel for every K.  Bit 3: one CTA per
-// output tile instead of a CTA per SM walking the tiles.  Default 3.
+// more than 128 tokens and K >= 10240.  Bit 2: the CTA-pair kernel for every K.  Bit 3: one CTA (pair)
+// per output tile instead of one per SM (two SMs) walking the tiles.  Bits 8..15: number of pairs of
+// the walking pair kernel (0 = half the SM count).  Default 3.
 void nvfp4_b200_gemm_fp4_config(int flags) {
     nvfp4::g_f4_split = (flags & 1) ? 1 : 0;
     nvfp4::g_f4_pair = (flags & 4) ? 2 : (flags & 2) ? 1 : 0;
     nvfp4::g_f4_persistent = (flags & 8) ? 0 : 1;
+    nvfp4::g_f4_pairs_override = (flags >> 8) & 0xFF;     // bits 8..15: CTA pairs of the tile-walking pair kernel
 }
 
 }  // extern "C"
